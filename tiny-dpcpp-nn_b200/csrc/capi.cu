@@ -1,0 +1,586 @@
+// Host side of libtnn_b200: the Network / Encoding classes behind the C ABI declared in
+// include/tnn_b200.h.  Argument checks mirror the reference's host classes
+// (include/network/Network.h:129-167, include/network/SwiftNetMLP.h:277-346,
+// include/encodings/grid.h:588-659, include/encodings/encoding_factory.h:109-176).
+#include "../../include/tnn_b200.h"
+
+#include "elementwise.h"
+#include "grid.h"
+#include "json_min.h"
+#include "mlp_common.cuh"
+#include "mlp_launch.h"
+
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <random>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(const std::string &msg, int code = 1) {
+    g_last_error = msg;
+    return code;
+}
+#define TNN_CUDA(expr)                                                                                                 \
+    do {                                                                                                               \
+        cudaError_t e_ = (expr);                                                                                       \
+        if (e_ != cudaSuccess) return fail(std::string(#expr) + ": " + cudaGetErrorString(e_), 2);                     \
+    } while (0)
+#define TNN_GUARD_BEGIN try {
+#define TNN_GUARD_END                                                                                                  \
+    }                                                                                                                  \
+    catch (const std::exception &ex) { return fail(ex.what()); }                                                      \
+    catch (...) { return fail("unknown C++ exception"); }
+
+// cuTensorMapEncodeTiled is fetched through the runtime so the library does not link libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess || !p)
+            throw std::runtime_error("cuTensorMapEncodeTiled is not available from this driver");
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+CUtensorMapSwizzle swizzle_for(int width) {
+    return width >= 64 ? CU_TENSOR_MAP_SWIZZLE_128B : width == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+}
+
+// [n_mat][rows][width] bf16 (n_mat == 1: plain 2-D), box = 128 rows x min(width, 64) columns.
+void make_act_tmap(CUtensorMap *m, const void *base, size_t rows, int width, int n_mat) {
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0) throw std::invalid_argument("device buffer must be 16-byte aligned");
+    const cuuint32_t box_cols = width < 64 ? width : 64;
+    cuuint64_t dims[3] = {(cuuint64_t)width, (cuuint64_t)rows, (cuuint64_t)n_mat};
+    cuuint64_t strides[2] = {(cuuint64_t)width * 2, (cuuint64_t)width * 2 * rows};
+    cuuint32_t box[3] = {box_cols, 128, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const cuuint32_t rank = n_mat > 1 ? 3 : 2;
+    CUresult r = get_encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void *>(base), dims, strides, box,
+                                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(width),
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+}
+
+int device_checks() {
+    int dev = 0;
+    TNN_CUDA(cudaGetDevice(&dev));
+    int major = 0;
+    TNN_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10)
+        return fail("libtnn_b200 needs a compute-capability 10.x device (B200); found major " + std::to_string(major));
+    return 0;
+}
+
+bool act_supported(int a) { return a == tnn::ACT_RELU || a == tnn::ACT_SIGMOID || a == tnn::ACT_NONE; }
+
+} // namespace
+
+// ======================================================================== network
+struct tnn_network {
+    int input_width = 0, output_width = 0; // as requested (unpadded)
+    int width = 0, n_hidden = 0, n_mat = 0;
+    int act = 0, out_act = 0, use_bias = 1;
+    int variant = 0;
+    int n_sm = 0;
+    size_t n_params = 0;
+    __nv_bfloat16 *packed = nullptr; // packed-layout bf16 weights (what get_params returns)
+    __nv_bfloat16 *wimg = nullptr;   // swizzled operand images, rows = input feature
+    __nv_bfloat16 *wimg_t = nullptr; // swizzled operand images, rows = output feature
+    float *dw_slabs = nullptr;       // per-CTA weight-gradient partial sums
+    int *status = nullptr;
+
+    int one_padded_input() const {
+        // rows of the first matrix that can carry signal: the real inputs, plus (with bias) the
+        // ones-padding up to the next multiple of 16 (Network.h:188-200)
+        if (!use_bias) return input_width;
+        if (input_width % 16 == 0) return width;
+        return (input_width / 16 + 1) * 16;
+    }
+};
+
+extern "C" {
+
+const char *tnn_last_error(void) { return g_last_error.c_str(); }
+const char *tnn_version(void) { return "tnn_b200 0.1 (sm_100a)"; }
+
+int tnn_network_create(int input_width, int output_width, int n_hidden_layers, int activation, int output_activation,
+                       int width, int dtype, int use_bias, tnn_network **out) {
+    TNN_GUARD_BEGIN
+    if (!out) return fail("out is null");
+    *out = nullptr;
+    if (dtype == TNN_DTYPE_FP16) return fail("fp16 networks are not implemented; use bf16");
+    if (dtype != TNN_DTYPE_BF16) return fail("Unsupported dtype. Only bf16 is supported");
+    if (width != 16 && width != 32 && width != 64 && width != 128)
+        return fail("Network width has to be a power of 2 between 16 and 128.");
+    if (input_width <= 0) return fail("Input width of " + std::to_string(input_width) + " is not supported. Value must be larger than 0.");
+    if (output_width <= 0) return fail("Output width of " + std::to_string(output_width) + " is not supported. Value must be larger than 0.");
+    if (input_width > width) return fail("Input width of " + std::to_string(input_width) + " is not supported. Value must be <= network width (" + std::to_string(width) + ").");
+    if (output_width > width) return fail("Output width of " + std::to_string(output_width) + " is not supported. Value must be <= network width (" + std::to_string(width) + ").");
+    if (n_hidden_layers <= 0) return fail("N hidden layers must be >= 1, i.e., 1 hidden layer and 1 output layer.");
+    if (!act_supported(activation)) return fail("activation must be ReLU, Sigmoid or None");
+    if (!act_supported(output_activation)) return fail("output activation must be ReLU, Sigmoid or None");
+    if (int rc = device_checks()) return rc;
+
+    auto *n = new tnn_network();
+    n->input_width = input_width;
+    n->output_width = output_width;
+    n->width = width;
+    n->n_hidden = n_hidden_layers;
+    n->n_mat = n_hidden_layers + 1;
+    n->act = activation;
+    n->out_act = output_activation;
+    n->use_bias = use_bias ? 1 : 0;
+    n->n_params = (size_t)n->n_mat * width * width;
+    if (n->one_padded_input() > width) {
+        delete n;
+        return fail("one_padded_input_width > padded_input_width, the input width is too small.");
+    }
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n->n_sm, cudaDevAttrMultiProcessorCount, dev);
+    const size_t bytes = n->n_params * sizeof(__nv_bfloat16);
+    cudaError_t e = cudaMalloc(&n->packed, bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&n->wimg, bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&n->wimg_t, bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&n->dw_slabs, (size_t)n->n_sm * n->n_params * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&n->status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(n->packed, 0, bytes);
+    if (e == cudaSuccess) e = cudaMemset(n->wimg, 0, bytes);
+    if (e == cudaSuccess) e = cudaMemset(n->wimg_t, 0, bytes);
+    if (e == cudaSuccess) e = cudaMemset(n->status, 0, sizeof(int));
+    if (e != cudaSuccess) {
+        tnn_network_destroy(n);
+        return fail(std::string("device allocation failed: ") + cudaGetErrorString(e), 2);
+    }
+    *out = n;
+    return 0;
+    TNN_GUARD_END
+}
+
+int tnn_network_destroy(tnn_network *n) {
+    if (!n) return 0;
+    cudaFree(n->packed);
+    cudaFree(n->wimg);
+    cudaFree(n->wimg_t);
+    cudaFree(n->dw_slabs);
+    cudaFree(n->status);
+    delete n;
+    return 0;
+}
+
+size_t tnn_network_n_params(const tnn_network *n) { return n ? n->n_params : 0; }
+int tnn_network_n_output_dims(const tnn_network *n) { return n ? n->width : 0; }
+int tnn_network_width(const tnn_network *n) { return n ? n->width : 0; }
+int tnn_network_n_hidden_layers(const tnn_network *n) { return n ? n->n_hidden : 0; }
+
+int tnn_network_set_variant(tnn_network *n, int variant) {
+    if (!n) return fail("network is null");
+    n->variant = variant;
+    return 0;
+}
+
+int tnn_network_set_params(tnn_network *n, const void *params, int dtype, int packed, void *stream) {
+    TNN_GUARD_BEGIN
+    if (!n || !params) return fail("null argument");
+    if (dtype != TNN_DTYPE_BF16 && dtype != TNN_DTYPE_FP32) return fail("params must be bf16 or fp32");
+    TNN_CUDA(tnn::launch_set_params(n->width, params, dtype == TNN_DTYPE_FP32, packed, n->n_mat, n->one_padded_input(),
+                                    n->output_width, n->packed, nullptr, n->wimg, n->wimg_t, (cudaStream_t)stream));
+    return 0;
+    TNN_GUARD_END
+}
+
+int tnn_network_initialize_params(tnn_network *n, uint64_t seed, void *stream) {
+    TNN_GUARD_BEGIN
+    if (!n) return fail("network is null");
+    std::mt19937 gen((uint32_t)seed);
+    std::vector<float> w(n->n_params);
+    size_t pos = 0;
+    const int W = n->width;
+    for (int l = 0; l < n->n_mat; ++l) {
+        int fan = W + W;
+        if (l == 0 || l + 1 == n->n_mat) fan = (n->input_width + 15) / 16 * 16 + W; // Network.h:278-286
+        const double bound = std::sqrt(6.0 / fan);
+        std::uniform_real_distribution<> dis(-bound, bound);
+        for (int i = 0; i < W * W; ++i, ++pos) w[pos] = (float)dis(gen);
+    }
+    float *tmp = nullptr;
+    TNN_CUDA(cudaMalloc(&tmp, w.size() * sizeof(float)));
+    cudaError_t e = cudaMemcpyAsync(tmp, w.data(), w.size() * sizeof(float), cudaMemcpyHostToDevice, (cudaStream_t)stream);
+    // the reference fills the matrices in their stored (packed) order
+    if (e == cudaSuccess)
+        e = tnn::launch_set_params(W, tmp, 1, 1, n->n_mat, n->one_padded_input(), n->output_width, n->packed, nullptr,
+                                   n->wimg, n->wimg_t, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    cudaFree(tmp);
+    TNN_CUDA(e);
+    return 0;
+    TNN_GUARD_END
+}
+
+int tnn_network_get_params(const tnn_network *n, void *out, void *stream) {
+    if (!n || !out) return fail("null argument");
+    TNN_CUDA(cudaMemcpyAsync(out, n->packed, n->n_params * sizeof(__nv_bfloat16), cudaMemcpyDeviceToDevice,
+                             (cudaStream_t)stream));
+    return 0;
+}
+
+static int run_forward(tnn_network *n, const void *x, void *y, void *interm, size_t batch, void *stream) {
+    TNN_GUARD_BEGIN
+    if (!n) return fail("network is null");
+    if (batch == 0) return 0;
+    if (!x) return fail("input is null");
+    if (batch % 8 != 0) return fail("Batch size is not divisible by 8."); // SwiftNetMLP.h:293-302
+    if (batch > (size_t)1 << 30) return fail("batch too large");
+    if (!y && !interm) return fail("forward needs y or interm_fwd");
+    tnn::FwdLaunch p{};
+    make_act_tmap(&p.tm_x, x, batch, n->width, 1);
+    if (y)
+        make_act_tmap(&p.tm_y, y, batch, n->width, 1);
+    else
+        p.tm_y = p.tm_x;
+    if (interm)
+        make_act_tmap(&p.tm_interm, interm, batch, n->width, n->n_mat + 1);
+    else
+        p.tm_interm = p.tm_x;
+    p.wimg = n->wimg;
+    p.wimg_t = n->wimg_t;
+    p.batch = batch;
+    p.width = n->width;
+    p.n_mat = n->n_mat;
+    p.act = n->act;
+    p.out_act = n->out_act;
+    p.store_all = interm ? 1 : 0;
+    p.write_y = y ? 1 : 0;
+    p.variant = n->variant;
+    p.n_sm = n->n_sm;
+    p.status = n->status;
+    p.stream = (cudaStream_t)stream;
+    if (interm) // matrix 0 of the forward workspace is a copy of the input (kernel_esimd.h:601-605)
+        TNN_CUDA(cudaMemcpyAsync(interm, x, batch * n->width * sizeof(__nv_bfloat16), cudaMemcpyDeviceToDevice, p.stream));
+    cudaError_t e = tnn::launch_mlp_fwd(p);
+    if (e == cudaErrorInvalidConfiguration)
+        return fail("this width / depth does not fit the on-chip weight staging of the forward kernel");
+    TNN_CUDA(e);
+    return 0;
+    TNN_GUARD_END
+}
+
+int tnn_network_inference(tnn_network *n, const void *x, void *y, size_t batch, void *stream) {
+    if (!y && batch) return fail("output is null");
+    return run_forward(n, x, y, nullptr, batch, stream);
+}
+
+int tnn_network_forward(tnn_network *n, const void *x, void *y, void *interm_fwd, size_t batch, void *stream) {
+    return run_forward(n, x, y, interm_fwd, batch, stream);
+}
+
+int tnn_network_backward(tnn_network *n, const void *dy, const void *interm_fwd, void *grads, int grads_dtype,
+                         int pack_transpose, void *dx, void *interm_bwd, size_t batch, void *stream) {
+    TNN_GUARD_BEGIN
+    if (!n) return fail("network is null");
+    if (!grads) return fail("grads is null");
+    if (grads_dtype != TNN_DTYPE_BF16 && grads_dtype != TNN_DTYPE_FP32) return fail("grads must be bf16 or fp32");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (batch == 0) {
+        const size_t esz = grads_dtype == TNN_DTYPE_FP32 ? 4 : 2;
+        TNN_CUDA(cudaMemsetAsync(grads, 0, n->n_params * esz, s));
+        return 0;
+    }
+    if (!dy || !interm_fwd) return fail("dy and interm_fwd are required");
+    if (batch % 8 != 0) return fail("Batch size is not divisible by 8.");
+    tnn::BwdLaunch p{};
+    make_act_tmap(&p.tm_dy, dy, batch, n->width, 1);
+    make_act_tmap(&p.tm_interm, interm_fwd, batch, n->width, n->n_mat + 1);
+    if (interm_bwd)
+        make_act_tmap(&p.tm_ibwd, interm_bwd, batch, n->width, n->n_mat);
+    else
+        p.tm_ibwd = p.tm_dy;
+    if (dx)
+        make_act_tmap(&p.tm_dx, dx, batch, n->width, 1);
+    else
+        p.tm_dx = p.tm_dy;
+    p.wimg = n->wimg;
+    p.wimg_t = n->wimg_t;
+    p.dw_partials = n->dw_slabs;
+    p.batch = batch;
+    p.width = n->width;
+    p.n_mat = n->n_mat;
+    p.act = n->act;
+    p.out_act = n->out_act;
+    p.store_bwd = interm_bwd ? 1 : 0;
+    p.want_dx = dx ? 1 : 0;
+    p.variant = n->variant;
+    p.n_sm = n->n_sm;
+    p.status = n->status;
+    p.stream = s;
+    cudaError_t e = tnn::launch_mlp_bwd(p);
+    if (e == cudaErrorInvalidConfiguration)
+        return fail("this width / depth does not fit the on-chip staging of the backward kernel");
+    TNN_CUDA(e);
+    TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, p.grid_out, n->n_mat, n->width, pack_transpose, 1.0f,
+                                   grads_dtype == TNN_DTYPE_FP32 ? (float *)grads : nullptr,
+                                   grads_dtype == TNN_DTYPE_BF16 ? (__nv_bfloat16 *)grads : nullptr, s));
+    return 0;
+    TNN_GUARD_END
+}
+
+int tnn_network_sync_status(tnn_network *n, int *status, void *stream) {
+    if (!n || !status) return fail("null argument");
+    TNN_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    TNN_CUDA(cudaMemcpy(status, n->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status != 0) TNN_CUDA(cudaMemset(n->status, 0, sizeof(int)));
+    return 0;
+}
+
+int tnn_network_adam_step(tnn_network *n, float *master, float *m, float *v, const float *grads, float grad_scale,
+                          int step, float lr, float beta1, float beta2, float eps, void *stream) {
+    TNN_GUARD_BEGIN
+    if (!n || !master || !m || !v || !grads) return fail("null argument");
+    if (step < 1) return fail("step counts from 1");
+    cudaStream_t s = (cudaStream_t)stream;
+    TNN_CUDA(tnn::launch_adam(master, m, v, grads, n->n_params, grad_scale, step, lr, beta1, beta2, eps, nullptr, s));
+    TNN_CUDA(tnn::launch_set_params(n->width, master, 1, 1, n->n_mat, n->one_padded_input(), n->output_width, n->packed,
+                                    nullptr, n->wimg, n->wimg_t, s));
+    return 0;
+    TNN_GUARD_END
+}
+
+int tnn_l2_loss(const void *pred, const float *target, int n_targets, float *values, void *grads, size_t batch,
+                int stride, float loss_scale, float *loss_sum, void *stream) {
+    TNN_GUARD_BEGIN
+    if (batch == 0) return 0;
+    if (!pred || !target) return fail("null argument");
+    if (n_targets <= 0 || n_targets > stride) return fail("n_targets must be in [1, stride]");
+    if (loss_scale == 0.0f) return fail("loss_scale must not be 0");
+    // partial sums live in a small per-call buffer carved from the caller's values array is not
+    // possible when values == nullptr, so the reduction buffer is owned by the library.
+    static float *partials = nullptr;
+    constexpr int kPartials = 1024;
+    if (loss_sum && !partials) TNN_CUDA(cudaMalloc(&partials, kPartials * sizeof(float)));
+    TNN_CUDA(tnn::launch_l2_loss((const __nv_bfloat16 *)pred, target, n_targets, values, (__nv_bfloat16 *)grads, batch,
+                                 stride, loss_scale, loss_sum ? partials : nullptr, kPartials, loss_sum,
+                                 (cudaStream_t)stream));
+    return 0;
+    TNN_GUARD_END
+}
+
+int tnn_adam_step(float *params, float *m, float *v, const float *grads, size_t n, float grad_scale, int step, float lr,
+                  float beta1, float beta2, float eps, void *stream) {
+    if (!params || !m || !v || !grads) return fail("null argument");
+    if (step < 1) return fail("step counts from 1");
+    TNN_CUDA(tnn::launch_adam(params, m, v, grads, n, grad_scale, step, lr, beta1, beta2, eps, nullptr,
+                              (cudaStream_t)stream));
+    return 0;
+}
+
+} // extern "C"
+
+// ======================================================================== encoding
+struct tnn_encoding {
+    bool is_grid = false;
+    int n_in = 0;
+    int n_out = 0;    // natural output width
+    int padded = 0;   // padded output width
+    float scale = 1.0f, offset = 0.0f; // identity
+    tnn::GridParams gp{};
+    size_t n_params = 0;
+    float *table = nullptr;
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+};
+
+namespace {
+
+int enum_value(const tnn::JsonObject &cfg, const char *key, const std::vector<const char *> &names, int dflt) {
+    if (!cfg.has(key)) return dflt;
+    const tnn::JsonValue &v = cfg.at(key);
+    if (v.is_string) {
+        for (size_t i = 0; i < names.size(); ++i)
+            if (v.str == names[i]) return (int)i;
+        throw std::runtime_error("Invalid enum value");
+    }
+    return (int)v.num;
+}
+
+} // namespace
+
+extern "C" {
+
+int tnn_encoding_create(const char *json_config, int padded_output_width, tnn_encoding **out) {
+    TNN_GUARD_BEGIN
+    if (!out || !json_config) return fail("null argument");
+    *out = nullptr;
+    tnn::JsonObject cfg = tnn::parse_json_object(json_config);
+    if (!cfg.has("otype")) return fail("Config needs to contain encoding, key otype");
+    const std::string name = cfg.at("otype").str;
+    if (int rc = device_checks()) return rc;
+    auto enc = std::make_unique<tnn_encoding>();
+    if (name == "Identity") {
+        if (!cfg.has("offset")) return fail("Config misses offset");
+        if (!cfg.has("scale")) return fail("Config misses scale");
+        if (!cfg.has("n_dims_to_encode")) return fail("Config misses n_dims_to_encode");
+        enc->n_in = (int)cfg.at("n_dims_to_encode").num;
+        enc->n_out = enc->n_in;
+        enc->scale = (float)cfg.at("scale").num;
+        enc->offset = (float)cfg.at("offset").num;
+    } else if (name == "HashGrid") {
+        enc->is_grid = true;
+        tnn::GridParams &g = enc->gp;
+        const uint32_t log2_hashmap = (uint32_t)cfg.number("log2_hashmap_size", 19);
+        g.n_dims = (uint32_t)cfg.number("n_dims_to_encode", 2);
+        g.features_per_level = (uint32_t)cfg.number("n_features_per_level", 2);
+        const uint32_t F = g.features_per_level;
+        if (F != 1 && F != 2 && F != 4 && F != 8) return fail("GridEncoding: n_features_per_level must be 1, 2, 4, or 8.");
+        if (cfg.has("n_features")) {
+            if (cfg.has("n_levels"))
+                return fail("GridEncoding: may not specify n_features and n_levels simultaneously (one determines the other)");
+            g.n_features = (uint32_t)cfg.at("n_features").num;
+        } else {
+            g.n_features = F * (uint32_t)cfg.number("n_levels", 16);
+        }
+        if (g.n_features % F != 0) return fail("GridEncoding: n_features must be a multiple of n_features_per_level");
+        g.n_levels = g.n_features / F;
+        if (g.n_levels == 0) return fail("Output width cannot be zero");
+        if (g.n_levels > tnn::kMaxGridLevels) return fail("GridEncoding: n_levels must be at most 128");
+        if (g.n_dims != 2 && g.n_dims != 3) return fail("GridEncoding: number of input dims must be 2 or 3.");
+        g.grid_type = enum_value(cfg, "type", {"Hash", "Dense", "Tiled"}, tnn::GRID_HASH);
+        g.hash_type = enum_value(cfg, "hash", {"Prime", "CoherentPrime", "ReversedPrime", "Rng"}, tnn::HASH_COHERENT_PRIME);
+        g.interpolation = enum_value(cfg, "interpolation", {"Nearest", "Linear", "Smoothstep"}, tnn::INTERP_LINEAR);
+        if (cfg.has("stochastic_interpolation") && cfg.at("stochastic_interpolation").truthy())
+            return fail("stochastic_interpolation is not implemented");
+        g.base_resolution = (uint32_t)cfg.number("base_resolution", 16);
+        float per_level_scale = 2.0f;
+        if (g.grid_type == tnn::GRID_DENSE && g.n_levels > 1)
+            per_level_scale = std::exp(std::log(256.0f / (float)g.base_resolution) / (float)(g.n_levels - 1));
+        per_level_scale = (float)cfg.number("per_level_scale", per_level_scale);
+        g.log2_per_level_scale = std::log2(per_level_scale);
+        g.max_level = 1000.0f;
+        const uint32_t entries = tnn::grid_build_level_table(g, log2_hashmap);
+        enc->n_params = (size_t)entries * F;
+        enc->n_in = (int)g.n_dims;
+        enc->n_out = (int)g.n_features;
+    } else if (name == "SphericalHarmonics" || name == "Frequency") {
+        return fail("encoding type " + name + " is outside the scope of this library (HashGrid and Identity only)");
+    } else {
+        return fail("Unknown encoding type: " + name);
+    }
+    enc->padded = padded_output_width > 0 ? padded_output_width : enc->n_out;
+    if (enc->n_in <= 0) return fail("Input width cannot be zero");
+    if (enc->padded < enc->n_out) return fail("Padded output width cannot be less than output width");
+    if (enc->is_grid) {
+        enc->gp.padded_width = (uint32_t)enc->padded;
+        TNN_CUDA(cudaMalloc(&enc->table, enc->n_params * sizeof(float)));
+        TNN_CUDA(cudaMemset(enc->table, 0, enc->n_params * sizeof(float)));
+    }
+    *out = enc.release();
+    return 0;
+    TNN_GUARD_END
+}
+
+int tnn_encoding_destroy(tnn_encoding *e) {
+    if (!e) return 0;
+    cudaFree(e->table);
+    cudaFree(e->scratch);
+    delete e;
+    return 0;
+}
+
+size_t tnn_encoding_n_params(const tnn_encoding *e) { return e ? e->n_params : 0; }
+int tnn_encoding_n_output_dims(const tnn_encoding *e) { return e ? e->padded : 0; }
+int tnn_encoding_n_input_dims(const tnn_encoding *e) { return e ? e->n_in : 0; }
+float *tnn_encoding_params_ptr(tnn_encoding *e) { return e ? e->table : nullptr; }
+
+int tnn_encoding_level_info(const tnn_encoding *e, int level, uint32_t *offset, uint32_t *size, float *scale,
+                            uint32_t *resolution) {
+    if (!e || !e->is_grid) return fail("not a grid encoding");
+    if (level < 0 || level >= (int)e->gp.n_levels) return fail("level out of range");
+    if (offset) *offset = e->gp.offsets[level];
+    if (size) *size = e->gp.offsets[level + 1] - e->gp.offsets[level];
+    if (scale) *scale = e->gp.scale[level];
+    if (resolution) *resolution = e->gp.resolution[level];
+    return 0;
+}
+
+int tnn_encoding_initialize_params(tnn_encoding *e, uint64_t seed, void *stream) {
+    TNN_GUARD_BEGIN
+    if (!e) return fail("encoding is null");
+    if (!e->n_params) return 0;
+    std::mt19937_64 gen(seed);
+    std::uniform_real_distribution<float> dis(-1e-4f, 1e-4f);
+    std::vector<float> h(e->n_params);
+    for (auto &v : h) v = dis(gen);
+    TNN_CUDA(cudaMemcpyAsync(e->table, h.data(), h.size() * sizeof(float), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    TNN_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return 0;
+    TNN_GUARD_END
+}
+
+int tnn_encoding_set_params(tnn_encoding *e, const float *params, void *stream) {
+    if (!e || !params) return fail("null argument");
+    if (!e->n_params) return fail("no encoding params to set");
+    TNN_CUDA(cudaMemcpyAsync(e->table, params, e->n_params * sizeof(float), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return 0;
+}
+
+int tnn_encoding_get_params(const tnn_encoding *e, float *out, void *stream) {
+    if (!e || !out) return fail("null argument");
+    if (!e->n_params) return 0;
+    TNN_CUDA(cudaMemcpyAsync(out, e->table, e->n_params * sizeof(float), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return 0;
+}
+
+int tnn_encoding_forward(tnn_encoding *e, const float *x, void *out, int out_dtype, size_t batch, void *stream) {
+    TNN_GUARD_BEGIN
+    if (!e) return fail("encoding is null");
+    if (batch == 0) return 0;
+    if (!x || !out) return fail("null argument");
+    if (out_dtype != TNN_DTYPE_FP32 && out_dtype != TNN_DTYPE_BF16) return fail("output must be fp32 or bf16");
+    if (batch > 0xFFFFFFFFull / 8) return fail("batch too large");
+    const int bf = out_dtype == TNN_DTYPE_BF16;
+    if (e->is_grid)
+        TNN_CUDA(tnn::launch_grid_fwd(e->gp, x, e->table, out, bf, batch, (cudaStream_t)stream));
+    else
+        TNN_CUDA(tnn::launch_identity_fwd(x, out, bf, batch, e->n_in, e->padded, e->scale, e->offset, (cudaStream_t)stream));
+    return 0;
+    TNN_GUARD_END
+}
+
+int tnn_encoding_backward(tnn_encoding *e, const float *x, const void *dy, int dy_dtype, float *grads, size_t batch,
+                          int deterministic, void *stream) {
+    TNN_GUARD_BEGIN
+    if (!e) return fail("encoding is null");
+    if (!e->n_params) return 0; // parameter-free encodings have no gradient (tnn_api.h:372-374)
+    if (!grads) return fail("grads is null");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (batch == 0) return fail("batch_size == 0"); // grid.h:744
+    if (!x || !dy) return fail("null argument");
+    if (dy_dtype != TNN_DTYPE_FP32 && dy_dtype != TNN_DTYPE_BF16) return fail("dy must be fp32 or bf16");
+    if (batch > 0xFFFFFFFFull / 8) return fail("batch too large");
+    size_t need = deterministic ? tnn::grid_bwd_scratch_bytes(e->gp, batch) : 0;
+    if (need > e->scratch_bytes) {
+        TNN_CUDA(cudaStreamSynchronize(s));
+        cudaFree(e->scratch);
+        e->scratch = nullptr;
+        e->scratch_bytes = 0;
+        TNN_CUDA(cudaMalloc(&e->scratch, need));
+        e->scratch_bytes = need;
+    }
+    TNN_CUDA(tnn::launch_grid_bwd(e->gp, x, dy, dy_dtype == TNN_DTYPE_BF16, grads, batch,
+                                  deterministic ? e->scratch : nullptr, e->scratch_bytes, s));
+    return 0;
+    TNN_GUARD_END
+}
+
+} // extern "C"

@@ -1,0 +1,211 @@
+// Small memory-bound kernels around the fused MLP: parameter layout conversion, identity
+// encoding, L2 loss, Adam, and the deterministic reduction of per-CTA weight-gradient slabs.
+#include "elementwise.h"
+#include "mlp_common.cuh"
+
+namespace tnn {
+
+// Packed ("VNNI") coordinate of element (i, j) of a rows x cols matrix: consecutive row pairs
+// are interleaved element-wise (reference source/common/common.cpp:33-42).
+__host__ __device__ inline int packed_coord(int i, int j, int cols) {
+    return (i & 1) == 0 ? i * cols + 2 * j : (i - 1) * cols + 2 * j + 1;
+}
+
+template <int W>
+__global__ void set_params_kernel(const void *__restrict__ src, int src_fp32, int src_packed, int n_mat,
+                                  int one_padded_in, int unpadded_out, __nv_bfloat16 *__restrict__ packed_out,
+                                  float *__restrict__ master_out, __nv_bfloat16 *__restrict__ wimg,
+                                  __nv_bfloat16 *__restrict__ wimg_t) {
+    using T = Tile<W>;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_mat * W * W) return;
+    const int l = idx / (W * W);
+    const int k = (idx / W) % W; // input feature (row of the in x out matrix)
+    const int n = idx % W;       // output feature
+    const int pk = l * W * W + packed_coord(k, n, W);
+    const int si = src_packed ? pk : idx;
+    float v = src_fp32 ? reinterpret_cast<const float *>(src)[si]
+                       : __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(src)[si]);
+    // rows of the first matrix beyond the (ones-padded) input and columns of the last matrix
+    // beyond the real output carry no signal: force them to zero (Network.h:171-233).
+    if (l == 0 && k >= one_padded_in) v = 0.0f;
+    if (l == n_mat - 1 && n >= unpadded_out) v = 0.0f;
+    const __nv_bfloat16 b = __float2bfloat16_rn(v);
+    packed_out[pk] = b;
+    if (master_out) master_out[pk] = v;
+    uint8_t *wi = reinterpret_cast<uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES;
+    uint8_t *wt = reinterpret_cast<uint8_t *>(wimg_t) + (size_t)l * T::WGT_BYTES;
+    *reinterpret_cast<__nv_bfloat16 *>(wi + T::elem_off(k, n, T::WGT_ATOM_BYTES)) = b;
+    *reinterpret_cast<__nv_bfloat16 *>(wt + T::elem_off(n, k, T::WGT_ATOM_BYTES)) = b;
+}
+
+cudaError_t launch_set_params(int width, const void *src, int src_fp32, int src_packed, int n_mat, int one_padded_in,
+                              int unpadded_out, __nv_bfloat16 *packed_out, float *master_out, __nv_bfloat16 *wimg,
+                              __nv_bfloat16 *wimg_t, cudaStream_t stream) {
+    const int n = n_mat * width * width;
+    const int blocks = (n + 255) / 256;
+#define TNN_CASE(WW)                                                                                                    \
+    case WW:                                                                                                            \
+        set_params_kernel<WW><<<blocks, 256, 0, stream>>>(src, src_fp32, src_packed, n_mat, one_padded_in, unpadded_out, \
+                                                          packed_out, master_out, wimg, wimg_t);                       \
+        break;
+    switch (width) {
+        TNN_CASE(16) TNN_CASE(32) TNN_CASE(64) TNN_CASE(128)
+    default: return cudaErrorInvalidValue;
+    }
+#undef TNN_CASE
+    return cudaGetLastError();
+}
+
+// Sum the per-CTA fp32 slabs [n_slabs][n_mat][W(out)][W(in)] in slab order (deterministic) and emit
+// the gradient in the requested layout: (out x in) row-major as the reference's gemm_batch leaves it
+// (kernel_esimd.h:234-239), or transposed to (in x out) and packed like the weights
+// (DeviceMatrix.h:469-488 PackAndTranspose).
+__global__ void reduce_dw_kernel(const float *__restrict__ slabs, int n_slabs, int n_mat, int W, int pack_transpose,
+                                 float scale, float *__restrict__ out_f32, __nv_bfloat16 *__restrict__ out_bf16) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    const int per = n_mat * W * W;
+    if (idx >= per) return;
+    float acc = 0.0f;
+    for (int s = 0; s < n_slabs; ++s) acc += slabs[(size_t)s * per + idx];
+    acc *= scale;
+    const int l = idx / (W * W);
+    const int o = (idx / W) % W; // output feature
+    const int i = idx % W;       // input feature
+    const int dst = pack_transpose ? l * W * W + packed_coord(i, o, W) : idx;
+    if (out_f32) out_f32[dst] = acc;
+    if (out_bf16) out_bf16[dst] = __float2bfloat16_rn(acc);
+}
+
+cudaError_t launch_reduce_dw(const float *slabs, int n_slabs, int n_mat, int width, int pack_transpose, float scale,
+                             float *out_f32, __nv_bfloat16 *out_bf16, cudaStream_t stream) {
+    const int n = n_mat * width * width;
+    reduce_dw_kernel<<<(n + 127) / 128, 128, 0, stream>>>(slabs, n_slabs, n_mat, width, pack_transpose, scale, out_f32,
+                                                         out_bf16);
+    return cudaGetLastError();
+}
+
+// Identity encoding (include/encodings/identity.h:63-77): out[i, j] = j < n_in ? x * scale + offset : 1.
+template <typename OutT>
+__global__ void identity_fwd_kernel(const float *__restrict__ x, OutT *__restrict__ out, size_t batch, int n_in,
+                                    int padded, float scale, float offset) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= batch * (size_t)padded) return;
+    const size_t row = idx / padded;
+    const int col = (int)(idx % padded);
+    const float v = col < n_in ? __fadd_rn(__fmul_rn(x[row * n_in + col], scale), offset) : 1.0f;
+    if constexpr (sizeof(OutT) == 2)
+        out[idx] = __float2bfloat16_rn(v);
+    else
+        out[idx] = v;
+}
+
+cudaError_t launch_identity_fwd(const float *x, void *out, int out_bf16, size_t batch, int n_in, int padded,
+                                float scale, float offset, cudaStream_t stream) {
+    const size_t n = batch * (size_t)padded;
+    if (n == 0) return cudaSuccess;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (out_bf16)
+        identity_fwd_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (__nv_bfloat16 *)out, batch, n_in, padded,
+                                                                       scale, offset);
+    else
+        identity_fwd_kernel<float><<<blocks, 256, 0, stream>>>(x, (float *)out, batch, n_in, padded, scale, offset);
+    return cudaGetLastError();
+}
+
+// L2 loss (include/losses/l2.h:19-41): value = (p - t)^2 / n, grad = scale * 2 (p - t) / n with
+// n = batch * stride.  Targets are [batch][n_targets]; prediction columns >= n_targets are padding and
+// compare against 0.  Per-block partial sums of the loss values go to `loss_partials` (fixed order).
+__global__ void l2_loss_kernel(const __nv_bfloat16 *__restrict__ pred, const float *__restrict__ target,
+                               int n_targets, float *__restrict__ values, __nv_bfloat16 *__restrict__ grads,
+                               size_t batch, int stride, float loss_scale, float *__restrict__ loss_partials) {
+    const size_t n_el = batch * (size_t)stride;
+    const float inv_n = 1.0f / (float)n_el;
+    float local = 0.0f;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n_el; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = idx / stride;
+        const int col = (int)(idx % stride);
+        const float t = col < n_targets ? target[row * n_targets + col] : 0.0f;
+        const float d = __bfloat162float(pred[idx]) - t;
+        const float v = d * d * inv_n;
+        if (values) values[idx] = v;
+        if (grads) grads[idx] = __float2bfloat16_rn(loss_scale * 2.0f * d * inv_n);
+        local += v;
+    }
+    __shared__ float red[256];
+    red[threadIdx.x] = local;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if ((int)threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && loss_partials) loss_partials[blockIdx.x] = red[0];
+}
+
+__global__ void sum_partials_kernel(const float *__restrict__ partials, int n, float *__restrict__ out) {
+    __shared__ float red[256];
+    float local = 0.0f;
+    for (int i = threadIdx.x; i < n; i += 256) local += partials[i];
+    red[threadIdx.x] = local;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if ((int)threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *out = red[0];
+}
+
+cudaError_t launch_l2_loss(const __nv_bfloat16 *pred, const float *target, int n_targets, float *values,
+                           __nv_bfloat16 *grads, size_t batch, int stride, float loss_scale, float *loss_partials,
+                           int n_partials, float *loss_sum, cudaStream_t stream) {
+    if (batch == 0) return cudaSuccess;
+    l2_loss_kernel<<<n_partials, 256, 0, stream>>>(pred, target, n_targets, values, grads, batch, stride, loss_scale,
+                                                   loss_partials);
+    if (loss_sum && loss_partials) sum_partials_kernel<<<1, 256, 0, stream>>>(loss_partials, n_partials, loss_sum);
+    return cudaGetLastError();
+}
+
+// Adam with torch.optim.Adam semantics (no weight decay, no amsgrad):
+//   m = b1 m + (1-b1) g;  v = b2 v + (1-b2) g^2;  p -= lr * (m / (1-b1^t)) / (sqrt(v / (1-b2^t)) + eps)
+// torch evaluates the update as  p -= (lr / bc1) * m / (sqrt(v) / sqrt(bc2) + eps); the same grouping is
+// used here.  Optionally refreshes the bf16 working copy in the same pass.
+__global__ void adam_kernel(float *__restrict__ p, float *__restrict__ m, float *__restrict__ v,
+                            const float *__restrict__ g, size_t n, float grad_scale, float lr, float b1, float b2,
+                            float eps, float bc1, float bc2_sqrt, __nv_bfloat16 *__restrict__ p_bf16) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float gi = g[i] * grad_scale;
+    const float mi = b1 * m[i] + (1.0f - b1) * gi;
+    const float vi = b2 * v[i] + (1.0f - b2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    const float denom = sqrtf(vi) / bc2_sqrt + eps;
+    const float pi = p[i] - (lr / bc1) * (mi / denom);
+    p[i] = pi;
+    if (p_bf16) p_bf16[i] = __float2bfloat16_rn(pi);
+}
+
+cudaError_t launch_adam(float *p, float *m, float *v, const float *g, size_t n, float grad_scale, int step, float lr,
+                        float b1, float b2, float eps, __nv_bfloat16 *p_bf16, cudaStream_t stream) {
+    if (n == 0) return cudaSuccess;
+    const float bc1 = 1.0f - powf(b1, (float)step);
+    const float bc2_sqrt = sqrtf(1.0f - powf(b2, (float)step));
+    adam_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p, m, v, g, n, grad_scale, lr, b1, b2, eps, bc1,
+                                                                 bc2_sqrt, p_bf16);
+    return cudaGetLastError();
+}
+
+template <typename A, typename B> __global__ void convert_kernel(const A *__restrict__ a, B *__restrict__ b, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) b[i] = (B)(float)a[i];
+}
+cudaError_t launch_f32_to_bf16(const float *a, __nv_bfloat16 *b, size_t n, cudaStream_t s) {
+    if (n) convert_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, b, n);
+    return cudaGetLastError();
+}
+cudaError_t launch_bf16_to_f32(const __nv_bfloat16 *a, float *b, size_t n, cudaStream_t s) {
+    if (n) convert_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, b, n);
+    return cudaGetLastError();
+}
+
+} // namespace tnn

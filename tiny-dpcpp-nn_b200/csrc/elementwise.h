@@ -1,0 +1,24 @@
+// Launchers of the small memory-bound kernels (parameter layout, identity encoding, loss, Adam).
+#pragma once
+#include <cstddef>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace tnn {
+
+cudaError_t launch_set_params(int width, const void *src, int src_fp32, int src_packed, int n_mat, int one_padded_in,
+                              int unpadded_out, __nv_bfloat16 *packed_out, float *master_out, __nv_bfloat16 *wimg,
+                              __nv_bfloat16 *wimg_t, cudaStream_t stream);
+cudaError_t launch_reduce_dw(const float *slabs, int n_slabs, int n_mat, int width, int pack_transpose, float scale,
+                             float *out_f32, __nv_bfloat16 *out_bf16, cudaStream_t stream);
+cudaError_t launch_identity_fwd(const float *x, void *out, int out_bf16, size_t batch, int n_in, int padded,
+                                float scale, float offset, cudaStream_t stream);
+cudaError_t launch_l2_loss(const __nv_bfloat16 *pred, const float *target, int n_targets, float *values,
+                           __nv_bfloat16 *grads, size_t batch, int stride, float loss_scale, float *loss_partials,
+                           int n_partials, float *loss_sum, cudaStream_t stream);
+cudaError_t launch_adam(float *p, float *m, float *v, const float *g, size_t n, float grad_scale, int step, float lr,
+                        float b1, float b2, float eps, __nv_bfloat16 *p_bf16, cudaStream_t stream);
+cudaError_t launch_f32_to_bf16(const float *a, __nv_bfloat16 *b, size_t n, cudaStream_t s);
+cudaError_t launch_bf16_to_f32(const __nv_bfloat16 *a, float *b, size_t n, cudaStream_t s);
+
+} // namespace tnn

@@ -1,0 +1,45 @@
+// Multi-resolution hash-grid encoding: level table and kernel launchers.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace tnn {
+
+constexpr int kMaxGridLevels = 128; // same cap as the reference (grid_interface.h:24)
+
+enum GridType : int { GRID_HASH = 0, GRID_DENSE = 1, GRID_TILED = 2 };
+enum HashType : int { HASH_PRIME = 0, HASH_COHERENT_PRIME = 1, HASH_REVERSED_PRIME = 2, HASH_RNG = 3 };
+enum InterpolationType : int { INTERP_NEAREST = 0, INTERP_LINEAR = 1, INTERP_SMOOTHSTEP = 2 };
+
+// Everything a grid kernel needs, passed by value.
+struct GridParams {
+    uint32_t n_levels;
+    uint32_t n_features; // n_levels * features_per_level
+    uint32_t features_per_level;
+    uint32_t n_dims;
+    uint32_t padded_width;
+    uint32_t base_resolution;
+    float log2_per_level_scale;
+    float max_level;
+    int interpolation;
+    int grid_type;
+    int hash_type;
+    uint32_t offsets[kMaxGridLevels + 1]; // first table entry of each level (in entries, not floats)
+    float scale[kMaxGridLevels];          // exp2(l * log2_per_level_scale) * base_resolution - 1
+    uint32_t resolution[kMaxGridLevels];  // ceil(scale) + 1
+};
+
+// Fills offsets / scale / resolution from the scalar fields (reference grid.h:588-659,
+// common_device.h:767-775).  Returns the total number of table entries.
+uint32_t grid_build_level_table(GridParams &p, uint32_t log2_hashmap_size);
+
+cudaError_t launch_grid_fwd(const GridParams &p, const float *x, const float *table, void *out, int out_bf16,
+                            size_t batch, cudaStream_t stream);
+
+// Scratch (bytes) the deterministic backward needs for `batch` samples.
+size_t grid_bwd_scratch_bytes(const GridParams &p, size_t batch);
+cudaError_t launch_grid_bwd(const GridParams &p, const float *x, const void *dy, int dy_bf16, float *grads,
+                            size_t batch, void *scratch, size_t scratch_bytes, cudaStream_t stream);
+
+} // namespace tnn

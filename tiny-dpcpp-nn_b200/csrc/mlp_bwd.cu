@@ -1,0 +1,433 @@
+// Fully fused MLP backward for sm_100a: delta chain, activation backward and the weight-gradient
+// batch reduction in one kernel.
+//
+// Replaces EsimdKernels::backward_impl of the reference (include/network/kernel_esimd.h:160-240),
+// i.e. the chain kernel *and* the oneMKL gemm_batch that follows it:
+//     delta_L   = dL/dy (.) act_out'(y)
+//     delta_l-1 = (delta_l W_l^T) (.) act'(a_l)          l = L..1, rounded to bf16 per layer
+//     dL/dx     = delta_0 W_0^T                          (optional)
+//     G_l       = delta_l^T a_l    (out x in)            l = 0..L, summed over the batch
+//
+// One persistent CTA per SM walks over 128-row batch tiles.  Per tile the forward activations
+// a_l arrive by TMA; delta tiles live in shared memory only.  Each delta tile is used twice by the
+// tensor cores without being moved: as the K-major A operand of the chain GEMM (M = batch rows) and
+// as the MN-major A operand of the weight-gradient GEMM (M = features, K = batch rows).  The
+// weight gradients of all layers accumulate in TMEM across all tiles of the CTA and are written
+// once, as one fp32 slab per CTA; a small second kernel adds the slabs in a fixed order.
+#include "mlp_common.cuh"
+#include "mlp_launch.h"
+
+namespace tnn {
+
+constexpr int kBwdRing = 3; // forward-activation tiles in flight
+
+template <int W> struct BwdSmem {
+    using T = Tile<W>;
+    static constexpr int DY = 0;                         // 2 tiles: dL/dy of this and the next tile
+    static constexpr int DP = DY + 2 * T::ACT_BYTES;     // 2 tiles: delta ping-pong
+    static constexpr int AR = DP + 2 * T::ACT_BYTES;     // kBwdRing forward-activation tiles
+    static constexpr int WBUF = AR + kBwdRing * T::ACT_BYTES;
+    static constexpr int DW_M = (W == 128) ? 128 : 64;   // UMMA M of the weight-gradient GEMM
+};
+
+struct BwdBarriers {
+    uint64_t w_full;
+    uint64_t dy_full[2];
+    uint64_t dy_empty[2];
+    uint64_t a_full[kBwdRing];
+    uint64_t a_empty[kBwdRing];
+    uint64_t d_ready;  // epilogue -> MMA: next delta tile is in shared memory / accumulator was read
+    uint64_t acc_full; // MMA -> epilogue: chain accumulator complete
+    uint64_t all_done; // MMA -> epilogue: every weight-gradient MMA of this CTA has completed
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+template <int W, bool B_MN_MAJOR>
+__global__ void __launch_bounds__(192, 1)
+mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_interm,
+               const __grid_constant__ CUtensorMap tm_ibwd, const __grid_constant__ CUtensorMap tm_dx,
+               const __nv_bfloat16 *__restrict__ wimg, float *__restrict__ dw_slabs, int n_tiles, int n_mat, int act,
+               int out_act, int store_bwd, int want_dx, int tmem_cols, int *status) {
+    using T = Tile<W>;
+    using S = BwdSmem<W>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ BwdBarriers bars;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int L = n_mat - 1;
+    const uint32_t smem_base = ptx::smem_u32(smem);
+    volatile uint32_t *abort_flag = &bars.abort_flag;
+    const bool has_oact = out_act != ACT_NONE;
+    const int loads_per_tile = n_mat + (has_oact ? 1 : 0); // a_L..a_0 (+ y for the output activation)
+    const int my_tiles = (n_tiles > (int)blockIdx.x) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bars.w_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(&bars.dy_full[b], 1);
+            ptx::mbar_init(&bars.dy_empty[b], 2); // MMA commit + epilogue leader
+        }
+        for (int r = 0; r < kBwdRing; ++r) {
+            ptx::mbar_init(&bars.a_full[r], 1);
+            ptx::mbar_init(&bars.a_empty[r], 129); // 128 epilogue threads + MMA commit
+        }
+        ptx::mbar_init(&bars.d_ready, 128);
+        ptx::mbar_init(&bars.acc_full, 1);
+        ptx::mbar_init(&bars.all_done, 1);
+        bars.abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tmap(&tm_dy);
+        ptx::prefetch_tmap(&tm_interm);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(&bars.tmem_base, (uint32_t)tmem_cols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = bars.tmem_base;
+    // TMEM columns: [0, W) chain accumulator, then one W-column weight-gradient accumulator per layer
+    const uint32_t acc_tmem = tmem_base;
+    auto dw_tmem = [&](int l) { return tmem_base + (uint32_t)(W + l * W); };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0 && my_tiles > 0) {
+            ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
+            for (int l = 0; l < n_mat; ++l)
+                ptx::bulk_load(smem + S::WBUF + l * T::WGT_BYTES,
+                               reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
+                               &bars.w_full);
+            int r = 0; // running index of forward-activation loads
+            bool ok = true;
+            for (int t = 0; ok && t < my_tiles; ++t) {
+                const int tile = blockIdx.x + t * gridDim.x;
+                const int b = t & 1;
+                if (t >= 2 && !ptx::mbar_wait(&bars.dy_empty[b], ((t >> 1) - 1) & 1, abort_flag)) {
+                    atomicExch(status, KS_TIMEOUT_PRODUCER | 1);
+                    break;
+                }
+                ptx::mbar_arrive_expect_tx(&bars.dy_full[b], T::ACT_BYTES);
+                for (int at = 0; at < T::KATOMS; ++at)
+                    ptx::tma_load_2d(smem + S::DY + b * T::ACT_BYTES + at * T::ACT_ATOM_BYTES, &tm_dy, at * T::ATOM_COLS,
+                                     tile * T::TM, &bars.dy_full[b]);
+                for (int j = 0; j < loads_per_tile; ++j, ++r) {
+                    // order of use: (y = a_{L+1} if the output activation needs it), a_L, ..., a_0
+                    const int mat = has_oact ? (L + 1 - j) : (L - j);
+                    const int slot = r % kBwdRing;
+                    if (r >= kBwdRing && !ptx::mbar_wait(&bars.a_empty[slot], ((r / kBwdRing) - 1) & 1, abort_flag)) {
+                        atomicExch(status, KS_TIMEOUT_PRODUCER | 2);
+                        ok = false;
+                        break;
+                    }
+                    ptx::mbar_arrive_expect_tx(&bars.a_full[slot], T::ACT_BYTES);
+                    for (int at = 0; at < T::KATOMS; ++at)
+                        ptx::tma_load_3d(smem + S::AR + slot * T::ACT_BYTES + at * T::ACT_ATOM_BYTES, &tm_interm,
+                                         at * T::ATOM_COLS, tile * T::TM, mat, &bars.a_full[slot]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0 && my_tiles > 0) {
+            constexpr uint32_t idesc_chain = ptx::make_idesc_bf16(128, W, 0, B_MN_MAJOR ? 1 : 0);
+            constexpr uint32_t idesc_dw = ptx::make_idesc_bf16(S::DW_M, W, 1, 1);
+            bool ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
+            if (!ok) atomicExch(status, KS_TIMEOUT_WEIGHTS);
+            int r = 0;  // forward-activation loads consumed
+            int dr = 0; // d_ready completions consumed
+            for (int t = 0; ok && t < my_tiles; ++t) {
+                const int b = t & 1;
+                if (!ptx::mbar_wait(&bars.dy_full[b], (t >> 1) & 1, abort_flag)) ok = false;
+                if (ok && has_oact) {
+                    // the epilogue rewrites dL/dy in place with the output-activation derivative; y's
+                    // ring slot is released by the epilogue threads plus this (empty) commit
+                    if (!ptx::mbar_wait(&bars.d_ready, dr & 1, abort_flag)) ok = false;
+                    ++dr;
+                    ptx::mma_commit(&bars.a_empty[r % kBwdRing]);
+                    ++r;
+                }
+                if (!ok) {
+                    atomicExch(status, KS_TIMEOUT_MMA | 1);
+                    break;
+                }
+                for (int l = L; ok && l >= 0; --l) {
+                    // delta_l: dL/dy buffer for l == L, else ping-pong buffer (L - 1 - l) & 1
+                    const uint32_t d_addr = (l == L) ? smem_base + S::DY + b * T::ACT_BYTES
+                                                     : smem_base + S::DP + ((L - 1 - l) & 1) * T::ACT_BYTES;
+                    if (l < L) {
+                        if (!ptx::mbar_wait(&bars.d_ready, dr & 1, abort_flag)) {
+                            atomicExch(status, KS_TIMEOUT_MMA | 2 | (l << 4));
+                            ok = false;
+                            break;
+                        }
+                        ++dr;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t w_addr = smem_base + S::WBUF + l * T::WGT_BYTES;
+                    if (l > 0 || want_dx) {
+                        // chain: acc[128 x W] = delta_l[128 x W] * W_l^T
+#pragma unroll
+                        for (int ks = 0; ks < T::KSTEPS; ++ks) {
+                            const uint64_t bdesc = B_MN_MAJOR ? T::desc_mnmajor(w_addr, ks, T::WGT_ATOM_BYTES)
+                                                              : T::desc_kmajor(w_addr, ks, T::WGT_ATOM_BYTES);
+                            ptx::mma_ss(acc_tmem, T::desc_kmajor(d_addr, ks, T::ACT_ATOM_BYTES), bdesc, idesc_chain, ks > 0);
+                        }
+                        ptx::mma_commit(&bars.acc_full);
+                    }
+                    // weight gradient: G_l[W x W] += delta_l^T[W x 128] * a_l[128 x W]
+                    const int slot = r % kBwdRing;
+                    if (!ptx::mbar_wait(&bars.a_full[slot], (r / kBwdRing) & 1, abort_flag)) {
+                        atomicExch(status, KS_TIMEOUT_MMA | 3 | (l << 4));
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_addr = smem_base + S::AR + slot * T::ACT_BYTES;
+#pragma unroll
+                    for (int ks = 0; ks < T::TM / 16; ++ks)
+                        ptx::mma_ss(dw_tmem(l), T::desc_mnmajor(d_addr, ks, T::ACT_ATOM_BYTES),
+                                    T::desc_mnmajor(a_addr, ks, T::ACT_ATOM_BYTES), idesc_dw, (t > 0 || ks > 0) ? 1u : 0u);
+                    ptx::mma_commit(&bars.a_empty[slot]);
+                    ++r;
+                    if (l == L) ptx::mma_commit(&bars.dy_empty[b]);
+                }
+                if (ok && want_dx) {
+                    // the accumulator holding dL/dx must be drained before the next tile reuses it
+                    if (!ptx::mbar_wait(&bars.d_ready, dr & 1, abort_flag)) {
+                        atomicExch(status, KS_TIMEOUT_MMA | 4);
+                        ok = false;
+                    }
+                    ++dr;
+                }
+            }
+            ptx::mma_commit(&bars.all_done);
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue group (4 warps)
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const bool leader = (warp == 2) && lane == 0;
+        const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+        bool ok = true;
+        int r = 0;  // forward-activation loads consumed
+        int ac = 0; // acc_full completions consumed
+        constexpr int CW = (W >= 32) ? 32 : 16;
+
+        for (int t = 0; ok && t < my_tiles; ++t) {
+            const int tile = blockIdx.x + t * gridDim.x;
+            const int b = t & 1;
+            uint8_t *dybuf = smem + S::DY + b * T::ACT_BYTES;
+            if (has_oact || store_bwd) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars.dy_full[b], (t >> 1) & 1, abort_flag))) {
+                    if (lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | 1);
+                    ok = false;
+                    break;
+                }
+            }
+            if (has_oact) {
+                // delta_L = dL/dy (.) act_out'(y), in place
+                const int slot = r % kBwdRing;
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars.a_full[slot], (r / kBwdRing) & 1, abort_flag))) {
+                    if (lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | 2);
+                    ok = false;
+                    break;
+                }
+                const uint8_t *ybuf = smem + S::AR + slot * T::ACT_BYTES;
+#pragma unroll
+                for (int c = 0; c < W; c += 8) {
+                    const int off = (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES + T::chunk_off(row, (c % T::ATOM_COLS) / 8);
+                    uint4 d = *reinterpret_cast<const uint4 *>(dybuf + off);
+                    const uint4 y = *reinterpret_cast<const uint4 *>(ybuf + off);
+                    d.x = act_bwd_pack(out_act, ptx::bf16lo_to_f32(d.x), ptx::bf16hi_to_f32(d.x), y.x);
+                    d.y = act_bwd_pack(out_act, ptx::bf16lo_to_f32(d.y), ptx::bf16hi_to_f32(d.y), y.y);
+                    d.z = act_bwd_pack(out_act, ptx::bf16lo_to_f32(d.z), ptx::bf16hi_to_f32(d.z), y.z);
+                    d.w = act_bwd_pack(out_act, ptx::bf16lo_to_f32(d.w), ptx::bf16hi_to_f32(d.w), y.w);
+                    *reinterpret_cast<uint4 *>(dybuf + off) = d;
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::mbar_arrive(&bars.d_ready);
+                ptx::mbar_arrive(&bars.a_empty[slot]);
+                ++r;
+            }
+            if (store_bwd) {
+                ptx::named_bar_sync(1, 128);
+                if (leader) {
+                    for (int at = 0; at < T::KATOMS; ++at)
+                        ptx::tma_store_3d(&tm_ibwd, dybuf + at * T::ACT_ATOM_BYTES, at * T::ATOM_COLS, tile * T::TM, L);
+                    ptx::tma_commit_group();
+                }
+            }
+            for (int l = L; l >= 0; --l) {
+                const int slot = r % kBwdRing;
+                const bool produce = (l > 0) || want_dx; // this step turns the accumulator into a bf16 tile
+                // delta_{l-1} goes to ping-pong buffer (L - l) & 1; dL/dx (l == 0) uses the same rule
+                uint8_t *dst = smem + S::DP + ((L - l) & 1) * T::ACT_BYTES;
+                if (produce) {
+                    if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars.acc_full, ac & 1, abort_flag))) {
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | 3 | (l << 4));
+                        ok = false;
+                        break;
+                    }
+                    ++ac;
+                    ptx::tc_fence_after_sync();
+                }
+                const bool need_a = (l > 0) && act != ACT_NONE;
+                if (need_a && !__all_sync(0xffffffffu, ptx::mbar_wait(&bars.a_full[slot], (r / kBwdRing) & 1, abort_flag))) {
+                    if (lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | 4 | (l << 4));
+                    ok = false;
+                    break;
+                }
+                if (produce) {
+                    if (store_bwd || want_dx) {
+                        // an earlier TMA store may still be reading the buffer that is written next
+                        // (with per-layer stores the newest one reads the other ping-pong buffer)
+                        if (leader) {
+                            if (store_bwd)
+                                ptx::tma_wait_group_read<1>();
+                            else
+                                ptx::tma_wait_group_read<0>();
+                        }
+                        ptx::named_bar_sync(1, 128);
+                    }
+                    const uint8_t *abuf = smem + S::AR + slot * T::ACT_BYTES;
+#pragma unroll
+                    for (int c0 = 0; c0 < W; c0 += CW) {
+                        uint32_t v[CW];
+                        if constexpr (CW == 32)
+                            ptx::tmem_ld32(acc_tmem + lane_addr + c0, v);
+                        else
+                            ptx::tmem_ld16(acc_tmem + lane_addr + c0, v);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int ch = 0; ch < CW / 8; ++ch) {
+                            const int c = c0 + ch * 8;
+                            const int off =
+                                (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES + T::chunk_off(row, (c % T::ATOM_COLS) / 8);
+                            uint4 f = make_uint4(0, 0, 0, 0);
+                            if (need_a) f = *reinterpret_cast<const uint4 *>(abuf + off);
+                            const int a = (l > 0) ? act : (int)ACT_NONE;
+                            uint4 o;
+                            o.x = act_bwd_pack(a, __uint_as_float(v[ch * 8 + 0]), __uint_as_float(v[ch * 8 + 1]), f.x);
+                            o.y = act_bwd_pack(a, __uint_as_float(v[ch * 8 + 2]), __uint_as_float(v[ch * 8 + 3]), f.y);
+                            o.z = act_bwd_pack(a, __uint_as_float(v[ch * 8 + 4]), __uint_as_float(v[ch * 8 + 5]), f.z);
+                            o.w = act_bwd_pack(a, __uint_as_float(v[ch * 8 + 6]), __uint_as_float(v[ch * 8 + 7]), f.w);
+                            *reinterpret_cast<uint4 *>(dst + off) = o;
+                        }
+                    }
+                    ptx::fence_proxy_async_smem();
+                    ptx::tc_fence_before_sync();
+                    ptx::mbar_arrive(&bars.d_ready);
+                }
+                ptx::mbar_arrive(&bars.a_empty[slot]);
+                ++r;
+                if (produce && (store_bwd || l == 0)) {
+                    ptx::named_bar_sync(1, 128);
+                    if (leader) {
+                        for (int at = 0; at < T::KATOMS; ++at) {
+                            if (l > 0) {
+                                if (store_bwd)
+                                    ptx::tma_store_3d(&tm_ibwd, dst + at * T::ACT_ATOM_BYTES, at * T::ATOM_COLS,
+                                                      tile * T::TM, l - 1);
+                            } else {
+                                ptx::tma_store_2d(&tm_dx, dst + at * T::ACT_ATOM_BYTES, at * T::ATOM_COLS, tile * T::TM);
+                            }
+                        }
+                        ptx::tma_commit_group();
+                    }
+                }
+            }
+            if (!ok) break;
+            if (leader) {
+                // dL/dy buffer b may be refilled once the store that read it (if any) is done
+                if (store_bwd) ptx::tma_wait_group_read<0>();
+                ptx::mbar_arrive(&bars.dy_empty[b]);
+            }
+        }
+        if (leader) ptx::tma_wait_group<0>();
+
+        // -------- drain the weight-gradient accumulators into this CTA's slab
+        if (ok && my_tiles > 0) {
+            if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars.all_done, 0, abort_flag))) {
+                if (lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | 5);
+                ok = false;
+            }
+        }
+        if (ok && my_tiles > 0) {
+            ptx::tc_fence_after_sync();
+            float *slab = dw_slabs + (size_t)blockIdx.x * n_mat * W * W;
+            for (int l = 0; l < n_mat; ++l) {
+                // M = 64 accumulators keep row m in lane (m % 16) + 32 * (m / 16); M = 128 in lane m
+                const int o = (S::DW_M == 64) ? quad * 16 + lane : quad * 32 + lane;
+                const bool valid = (S::DW_M == 64) ? (lane < 16 && o < W) : true;
+#pragma unroll
+                for (int c0 = 0; c0 < W; c0 += CW) {
+                    uint32_t v[CW];
+                    if constexpr (CW == 32)
+                        ptx::tmem_ld32(dw_tmem(l) + lane_addr + c0, v);
+                    else
+                        ptx::tmem_ld16(dw_tmem(l) + lane_addr + c0, v);
+                    ptx::tmem_ld_wait();
+                    if (valid) {
+                        float4 *dstp = reinterpret_cast<float4 *>(slab + ((size_t)l * W + o) * W + c0);
+#pragma unroll
+                        for (int q4 = 0; q4 < CW / 4; ++q4)
+                            dstp[q4] = make_float4(__uint_as_float(v[q4 * 4]), __uint_as_float(v[q4 * 4 + 1]),
+                                                   __uint_as_float(v[q4 * 4 + 2]), __uint_as_float(v[q4 * 4 + 3]));
+                    }
+                }
+            }
+        }
+    }
+
+    if (*abort_flag && threadIdx.x == 0) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(100);
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, (uint32_t)tmem_cols);
+    }
+}
+
+// ---------------------------------------------------------------------- host side
+template <int W, bool B_MN> static cudaError_t launch_bwd_variant(BwdLaunch &p) {
+    using T = Tile<W>;
+    using S = BwdSmem<W>;
+    const size_t smem = (size_t)S::WBUF + (size_t)p.n_mat * T::WGT_BYTES + 1024;
+    const int cols_needed = W + p.n_mat * W;
+    if (smem > 227 * 1024 || cols_needed > 512) return cudaErrorInvalidConfiguration;
+    int tmem_cols = 32;
+    while (tmem_cols < cols_needed) tmem_cols *= 2;
+    auto kern = mlp_bwd_kernel<W, B_MN>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
+    const int grid = n_tiles < p.n_sm ? n_tiles : p.n_sm;
+    p.grid_out = grid;
+    if (grid == 0) return cudaSuccess;
+    // K-major weights for the chain are rows = input feature; the MN-major variant reads the transposed image
+    kern<<<grid, 192, smem, p.stream>>>(p.tm_dy, p.tm_interm, p.tm_ibwd, p.tm_dx, B_MN ? p.wimg_t : p.wimg,
+                                        p.dw_partials, n_tiles, p.n_mat, p.act, p.out_act, p.store_bwd, p.want_dx,
+                                        tmem_cols, p.status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_mlp_bwd(BwdLaunch &p) {
+    const bool mn = (p.variant & 2) != 0;
+    switch (p.width) {
+    case 16: return mn ? launch_bwd_variant<16, true>(p) : launch_bwd_variant<16, false>(p);
+    case 32: return mn ? launch_bwd_variant<32, true>(p) : launch_bwd_variant<32, false>(p);
+    case 64: return mn ? launch_bwd_variant<64, true>(p) : launch_bwd_variant<64, false>(p);
+    case 128: return mn ? launch_bwd_variant<128, true>(p) : launch_bwd_variant<128, false>(p);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+} // namespace tnn

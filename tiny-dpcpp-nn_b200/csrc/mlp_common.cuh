@@ -1,0 +1,102 @@
+// Shared definitions of the fused-MLP kernels: tile geometry, the swizzled shared-memory
+// layout that both TMA and the tcgen05 descriptors agree on, and activation helpers.
+#pragma once
+#include "umma.cuh"
+
+namespace tnn {
+
+// Same enumerator order as the reference's `enum class Activation` (include/common/common.h:28-38).
+enum Activation : int {
+    ACT_RELU = 0,
+    ACT_LEAKY_RELU = 1,
+    ACT_EXPONENTIAL = 2,
+    ACT_SINE = 3,
+    ACT_SIGMOID = 4,
+    ACT_SQUAREPLUS = 5,
+    ACT_SOFTPLUS = 6,
+    ACT_TANH = 7,
+    ACT_NONE = 8,
+};
+
+// Error words written by a kernel that gave up on a bounded wait.
+enum KernelStatus : int {
+    KS_OK = 0,
+    KS_TIMEOUT_PRODUCER = 0x100,
+    KS_TIMEOUT_MMA = 0x200,
+    KS_TIMEOUT_EPILOGUE = 0x300,
+    KS_TIMEOUT_WEIGHTS = 0x400,
+};
+
+// Geometry of one batch tile (128 rows, the UMMA M) of a width-W network.
+//
+// A tile of `rows` x W bf16 is kept in shared memory as KATOMS column blocks ("atoms") of
+// `rows` x ATOM_COLS; inside an atom a row occupies ROW_BYTES contiguous bytes and its
+// 16-byte chunks are XOR-swizzled with the row index, exactly the pattern TMA writes for
+// CU_TENSOR_MAP_SWIZZLE_{32,64,128}B and the pattern a UMMA descriptor of the matching
+// swizzle mode reads.  The same bytes can be consumed
+//   * as a K-major operand  (MMA row = stored row,  K = stored column), or
+//   * as an MN-major operand (MMA row = stored column, K = stored row).
+template <int W> struct Tile {
+    static_assert(W == 16 || W == 32 || W == 64 || W == 128, "width must be 16, 32, 64 or 128");
+    static constexpr int TM = 128;
+    static constexpr int ROW_BYTES = (2 * W < 128) ? 2 * W : 128;
+    static constexpr int KATOMS = (2 * W) / ROW_BYTES;
+    static constexpr int ATOM_COLS = ROW_BYTES / 2;
+    static constexpr int CHUNKS = ROW_BYTES / 16;
+    static constexpr int ACT_ATOM_BYTES = TM * ROW_BYTES;
+    static constexpr int ACT_BYTES = ACT_ATOM_BYTES * KATOMS; // 128 x W bf16
+    static constexpr int WGT_ATOM_BYTES = W * ROW_BYTES;
+    static constexpr int WGT_BYTES = WGT_ATOM_BYTES * KATOMS; // W x W bf16
+    static constexpr uint32_t SWZ = ptx::swizzle_code(ROW_BYTES);
+    static constexpr int SBO = 8 * ROW_BYTES;
+    static constexpr int KSTEPS = W / 16; // one tcgen05.mma consumes K = 16 bf16
+
+    // byte offset of the 16-byte chunk `chunk` (0..CHUNKS-1) of row `r` inside an atom
+    __host__ __device__ static constexpr int chunk_off(int r, int chunk) {
+        return r * ROW_BYTES + ((chunk ^ (((r * ROW_BYTES) >> 7) & (CHUNKS - 1))) << 4);
+    }
+    // byte offset of element (r, c) of a `rows`-row tile
+    __host__ __device__ static constexpr int elem_off(int r, int c, int atom_bytes) {
+        return (c / ATOM_COLS) * atom_bytes + chunk_off(r, (c % ATOM_COLS) / 8) + (c % 8) * 2;
+    }
+
+    // Descriptor of k-step `ks` of a K-major operand stored at `base` (shared address).
+    __device__ static uint64_t desc_kmajor(uint32_t base, int ks, int atom_bytes) {
+        const int col = ks * 16;
+        const uint32_t start = base + (col / ATOM_COLS) * atom_bytes + (col % ATOM_COLS) * 2;
+        return ptx::make_smem_desc(start, 16, SBO, SWZ);
+    }
+    // Descriptor of k-step `ks` of an MN-major operand (K runs over the stored rows).
+    __device__ static uint64_t desc_mnmajor(uint32_t base, int ks, int atom_bytes) {
+        const uint32_t start = base + ks * 16 * ROW_BYTES;
+        return ptx::make_smem_desc(start, atom_bytes, SBO, SWZ);
+    }
+};
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+// Forward activation on two fp32 accumulators, rounded to a bf16 pair.  The reference rounds
+// to the storage type first and then clamps (kernel_esimd.h:443-458); max(bf16(x), 0) and
+// bf16(max(x, 0)) are the same value.  Sigmoid is evaluated in fp32 and then rounded.
+__device__ __forceinline__ uint32_t act_pack(int act, float lo, float hi) {
+    if (act == ACT_RELU) return ptx::pack_bf16x2_relu(lo, hi);
+    if (act == ACT_SIGMOID) return ptx::pack_bf16x2(sigmoidf_(lo), sigmoidf_(hi));
+    return ptx::pack_bf16x2(lo, hi);
+}
+
+// Backward activation (kernel_esimd.h:460-487): `fwd` holds the two stored forward
+// activations of the same elements.  ReLU zeroes where the stored activation is <= 0;
+// sigmoid multiplies by s (1 - s) in fp32.
+__device__ __forceinline__ uint32_t act_bwd_pack(int act, float lo, float hi, uint32_t fwd) {
+    if (act == ACT_RELU) {
+        if (!(ptx::bf16lo_to_f32(fwd) > 0.0f)) lo = 0.0f;
+        if (!(ptx::bf16hi_to_f32(fwd) > 0.0f)) hi = 0.0f;
+    } else if (act == ACT_SIGMOID) {
+        const float sl = ptx::bf16lo_to_f32(fwd), sh = ptx::bf16hi_to_f32(fwd);
+        lo *= sl * (1.0f - sl);
+        hi *= sh * (1.0f - sh);
+    }
+    return ptx::pack_bf16x2(lo, hi);
+}
+
+} // namespace tnn

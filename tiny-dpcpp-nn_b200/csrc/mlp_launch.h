@@ -1,0 +1,52 @@
+// Host-visible launch descriptors of the fused-MLP kernels (plain structs, no torch types).
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace tnn {
+
+struct FwdLaunch {
+    CUtensorMap tm_x;      // [batch][W] bf16 input, box 128 x min(W, 64)
+    CUtensorMap tm_y;      // [batch][W] bf16 output
+    CUtensorMap tm_interm; // [L+2][batch][W] bf16 activations (only read when store_all)
+    const __nv_bfloat16 *wimg;   // (L+1) swizzled tiles, rows = input feature, cols = output feature
+    const __nv_bfloat16 *wimg_t; // (L+1) swizzled tiles, rows = output feature, cols = input feature
+    size_t batch;
+    int width;
+    int n_mat; // number of weight matrices = n_hidden_layers + 1
+    int act, out_act;
+    int store_all;
+    int write_y;
+    int variant;
+    int n_sm;
+    int *status;
+    cudaStream_t stream;
+};
+cudaError_t launch_mlp_fwd(const FwdLaunch &p);
+
+struct BwdLaunch {
+    CUtensorMap tm_dy;      // [batch][W] bf16 dL/dy (after loss)
+    CUtensorMap tm_interm;  // [L+2][batch][W] bf16 forward activations (matrix 0 = input)
+    CUtensorMap tm_ibwd;    // [L+1][batch][W] bf16 deltas (written when store_bwd)
+    CUtensorMap tm_dx;      // [batch][W] bf16 dL/dx (written when want_dx)
+    const __nv_bfloat16 *wimg;
+    const __nv_bfloat16 *wimg_t;
+    float *dw_partials; // [grid][L+1][W][W] fp32, layout (out, in)
+    size_t batch;
+    int width;
+    int n_mat;
+    int act, out_act;
+    int store_bwd;
+    int want_dx;
+    int variant;
+    int n_sm;
+    int *status;
+    cudaStream_t stream;
+    int grid_out; // number of partial slabs written (set by the launcher)
+};
+cudaError_t launch_mlp_bwd(BwdLaunch &p);
+
+} // namespace tnn
