@@ -1,0 +1,381 @@
+"""Headline benchmark: samples/s of one SwiftNet training step (and of inference) at width 64,
+4 hidden layers, batch 2^22 per GPU, synthetic inputs.
+
+  python bench.py --gpus N --steps K --warmup W            # this library on N GPUs (N > 1: under torchrun)
+  python bench.py --impl reference --steps K --warmup W    # the reference's CPU path on the host cores
+
+A step = forward (activations kept for backward) -> L2 loss -> backward with fused weight-gradient
+reduction -> (N > 1: one NCCL all-reduce of the fp32 gradient buffer) -> Adam + weight refresh.
+Prints ONE JSON line.  `value` = whole-job training samples/s with inputs resident in HBM; `e2e` =
+the same through the public API from pinned HOST buffers (H2D of inputs and targets, D2H of the
+loss inside the timed region).  Extra keys: `infer` (inference throughput), `roofline` (dominant
+kernel of the step), `rooflines` (each kernel), `cpu_baseline`, `clocks`, `gpu_launches`.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "tiny-dpcpp-nn_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+
+WIDTH, N_HIDDEN, LOG2_BATCH = 64, 4, 22
+N_MAT = N_HIDDEN + 1
+METRIC = "train_samples_per_s"
+UNIT = "samples/s"
+# algorithmic work per sample (benchmarks/common_benchmarks.h:87-88, 120-121 of the reference)
+FLOPS_FWD = 2 * WIDTH * WIDTH * N_MAT            # 40 960
+FLOPS_BWD = 2 * FLOPS_FWD - 2 * WIDTH * WIDTH    # delta chain over L matrices + L+1 weight gradients
+FLOPS_TRAIN = 3 * FLOPS_FWD                      # 122 880 (the reference's 3x model)
+BYTES_INFER = 2 * WIDTH * 2                      # x in + y out, bf16
+
+
+def workload_name(batch_log2):
+    return (f"swiftnet_train_step_w{WIDTH}_l{N_HIDDEN}_relu_none_bf16_batch2^{batch_log2}_per_gpu "
+            "(L2 loss, Adam lr 1e-3 b 0.9/0.99 eps 1e-15; inputs/targets uniform[-1,1])")
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], tflops=p["bf16_tflops"], tflops_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [s for s, p in zip(sm, power) if p >= 0.5 * max(power)] or sm
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": max(smax), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------- CPU reference arm
+def _cpu_train_rate(n_samples, threads, seed=0):
+    """samples/s of forward + backward of the reference's own host MLP (test/mlp.h through oracle/_ref)
+    or, where that library is absent, of the oracle port, on `threads` host threads."""
+    from oracle import oracle as O  # the CPU legs are the one place bench.py runs the oracle
+
+    w = xavier_weights(N_MAT, WIDTH, 0).astype(np.float64)
+    rng = np.random.default_rng(100 + seed)
+    x = rng.uniform(-1, 1, (n_samples, WIDTH))
+    t = rng.uniform(-1, 1, (n_samples, WIDTH))
+    if O.ref_lib() is not None:
+        kind = "reference"
+        chunks = np.array_split(np.arange(n_samples), threads)
+        t0 = time.perf_counter()
+        ths = [threading.Thread(target=O.ref_mlp_run_batch,
+                                args=(WIDTH, N_MAT, "relu", "none", w, x[c], t[c], True)) for c in chunks if len(c)]
+        [th.start() for th in ths]
+        [th.join() for th in ths]
+        dt = time.perf_counter() - t0
+    else:
+        kind = "port"
+        t0 = time.perf_counter()
+        interm = O.mlp_forward(x, w, N_MAT, WIDTH, "relu", "none", bf16=True, n_threads=threads)
+        dy = (2 * (interm[-1] - t) / (n_samples * WIDTH)).astype(np.float32)
+        O.mlp_backward(dy, interm, w, N_MAT, WIDTH, "relu", "none", bf16=True, want_dx=False, n_threads=threads)
+        dt = time.perf_counter() - t0
+    return n_samples / dt, kind
+
+
+def cpu_baseline(target_seconds=12.0):
+    threads = os.cpu_count() or 1
+    rate, kind = _cpu_train_rate(256 * threads, threads)          # calibration
+    n = int(max(256 * threads, min(rate * target_seconds, 1 << 22)))
+    rate, kind = _cpu_train_rate(n, threads, seed=1)
+    return {"value": rate, "unit": UNIT, "cores": threads, "kind": kind,
+            "sample": f"{n} samples of the same training step (forward + L2 + backward, weights fixed) through "
+                      + ("the reference's test/mlp.h, double precision" if kind == "reference" else "the oracle port")}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rate0, kind = _cpu_train_rate(128 * threads, threads)
+    per_step = int(max(128 * threads, min(rate0 * 4.0, 1 << 20)))   # about 4 s of CPU work per step
+    for i in range(args.warmup):
+        _cpu_train_rate(max(per_step // 8, threads), threads, seed=10 + i)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        _cpu_train_rate(per_step, threads, seed=20 + i)
+    dt = time.perf_counter() - t0
+    value = per_step * args.steps / dt
+    sample = f"{per_step} samples per step of the batch-2^{LOG2_BATCH} step, {threads} host threads"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f64" if kind == "reference" else "bf16", "data": "synthetic",
+        "config": {"workload": workload_name(LOG2_BATCH), "l2_flush": "n/a (CPU)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# --------------------------------------------------------------------------------- GPU arm
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from tiny_dpcpp_nn import _lib as L
+    from tiny_dpcpp_nn.trainer import Trainer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    torch.cuda.set_device(local_rank)
+    pg = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        pg = dist.group.WORLD
+    batch = 1 << args.log2_batch
+    peaks = load_peaks()
+
+    # synthetic data of the configuration's shapes: weights Xavier-uniform seed 0 (same on every rank),
+    # inputs / targets uniform[-1, 1], per-rank seeds
+    w = xavier_weights(N_MAT, WIDTH, 0)
+    net = L.create_network(WIDTH, WIDTH, N_HIDDEN, 0, 8, WIDTH, "torch.bfloat16", True, seed=0)
+    net.set_params(torch.from_numpy(w.reshape(-1)).cuda(), False)
+    gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+    x = (torch.rand((batch, WIDTH), device="cuda", generator=gen) * 2 - 1).to(torch.bfloat16)
+    gen.manual_seed(1 + 1000 * rank)
+    targets = torch.rand((batch, WIDTH), device="cuda", generator=gen) * 2 - 1
+    trainer = Trainer(net, lr=1e-3, betas=(0.9, 0.99), eps=1e-15, process_group=pg, world_size=world)
+    trainer.set_master_params(torch.from_numpy(_packed(w)).cuda())
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync_all()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    # -------- training step, inputs resident in HBM (the per-step working set, 2.6 GiB of activations plus
+    # 1.5 GiB of inputs, is far larger than the 126 MB L2, so no explicit flush is needed)
+    step = lambda: trainer.training_step(x, targets)  # noqa: E731
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a moment to start: it runs from before the warm-up on
+    t_load = time.perf_counter()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ms_total = timed(step, args.steps)
+    # keep the same load on the GPU (untimed) until the sampler has seen about two seconds of it
+    while time.perf_counter() - t_load < 2.0:
+        for _ in range(10):
+            step()
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    status = net.status()
+    loss_value = float(trainer._loss.item())
+    ms_step = ms_total / args.steps
+    value = world * batch / (ms_step * 1e-3)
+
+    # -------- inference at the same batch
+    infer = lambda: net.inference(x)  # noqa: E731
+    for _ in range(3):
+        infer()
+    ms_inf = timed(infer, args.steps) / args.steps
+    infer_value = world * batch / (ms_inf * 1e-3)
+
+    # -------- per-kernel durations (CUDA events around one kernel at a time, same stream)
+    lib = L.load()
+    s = L.stream_ptr()
+    tr = trainer
+
+    def k_fwd():
+        L.check(lib.tnn_network_forward(net._h, L.dptr(x), None, L.dptr(tr._interm), batch, s))
+
+    def k_bwd():
+        L.check(lib.tnn_network_backward(net._h, L.dptr(tr._dy), L.dptr(tr._interm), L.dptr(tr.grads), L.DTYPE_FP32, 1,
+                                         None, None, batch, s))
+
+    def k_loss():
+        L.check(lib.tnn_l2_loss(L.dptr(tr._interm[N_MAT]), L.dptr(targets), WIDTH, None, L.dptr(tr._dy), batch, WIDTH,
+                                1.0, L.dptr(tr._loss), s))
+
+    kernel_ms = {}
+    for name, fn in (("mlp_fwd_store", k_fwd), ("l2_loss", k_loss), ("mlp_bwd", k_bwd), ("mlp_inference", infer)):
+        for _ in range(2):
+            fn()
+        kernel_ms[name] = timed(fn, args.steps) / args.steps
+
+    def roof(name, flops_per_sample, bytes_per_sample):
+        t = kernel_ms[name] * 1e-3
+        tf = flops_per_sample * batch / t * 1e-12
+        gb = bytes_per_sample * batch / t * 1e-9
+        return {"kernel": name, "ms": kernel_ms[name], "tflops": tf, "frac_tensor": tf / peaks["tflops"], "gbs": gb,
+                "frac_hbm": gb / peaks["hbm_gbs"]}
+
+    act_bytes = WIDTH * 2
+    rooflines = [
+        roof("mlp_inference", FLOPS_FWD, BYTES_INFER),
+        roof("mlp_fwd_store", FLOPS_FWD, act_bytes * (N_MAT + 2)),     # x in, x copy + every activation out
+        roof("mlp_bwd", FLOPS_BWD, act_bytes * (N_MAT + 1)),           # dy + a_L..a_0 in
+        roof("l2_loss", 0, act_bytes * 2 + WIDTH * 4),                 # y in, dy out, targets in
+    ]
+    dom = max(("mlp_fwd_store", "mlp_bwd", "l2_loss"), key=lambda k: kernel_ms[k])
+    dom_r = [r for r in rooflines if r["kernel"] == dom][0]
+    roofline = {"bound": "tensor", "kernel": dom, "achieved": dom_r["tflops"], "peak": peaks["tflops"],
+                "unit": "TFLOP/s", "frac": dom_r["frac_tensor"], "traffic": None, "peak_source": peaks["source"],
+                "hbm_frac_same_kernel": dom_r["frac_hbm"]}
+
+    # -------- end to end through the public API with HOST buffers
+    hx = torch.empty((batch, WIDTH), dtype=torch.bfloat16).pin_memory()
+    ht = torch.empty((batch, WIDTH), dtype=torch.float32).pin_memory()
+    hx.copy_(x.cpu()); ht.copy_(targets.cpu())
+    dx_, dt_ = torch.empty_like(x), torch.empty_like(targets)
+
+    def e2e_step():
+        dx_.copy_(hx, non_blocking=True)
+        dt_.copy_(ht, non_blocking=True)
+        loss = trainer.training_step(dx_, dt_)
+        return float(loss.item())  # device -> host read of the step's result
+
+    e2e_steps = max(2, min(args.steps, 5))
+    for _ in range(2):
+        e2e_step()
+    sync_all()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    sync_all()
+    dt_e2e = torch.tensor([time.perf_counter() - t0], device="cuda")
+    if world > 1:
+        dist.all_reduce(dt_e2e, op=dist.ReduceOp.MAX)
+    e2e_value = world * batch * e2e_steps / dt_e2e.item()
+
+    cpu = cpu_baseline() if (rank == 0 and world == 1 and not args.no_cpu) else None
+
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload_name(args.log2_batch), "global_batch": world * batch,
+                       "parallelism": f"dp{world}" if world > 1 else "single",
+                       "l2_flush": "inputs larger than L2 (4 GiB touched per step)"},
+            "train_tflops": FLOPS_TRAIN * value * 1e-12, "train_frac_of_bf16_peak": FLOPS_TRAIN * value * 1e-12 / world / peaks["tflops"],
+            "infer": {"value": infer_value, "unit": UNIT, "ms": ms_inf, "tflops": FLOPS_FWD * infer_value * 1e-12,
+                      "frac_of_bf16_peak": FLOPS_FWD * infer_value * 1e-12 / world / peaks["tflops"],
+                      "hbm_gbs": BYTES_INFER * infer_value * 1e-9 / world,
+                      "frac_of_hbm_peak": BYTES_INFER * infer_value * 1e-9 / world / peaks["hbm_gbs"]},
+            "roofline": roofline, "rooflines": rooflines,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": batch * WIDTH * (2 + 4),
+                    "d2h_bytes_per_step": 4, "steps": e2e_steps},
+            "gpu_launches": 7 * args.steps, "kernels_per_step": ["mlp_fwd_kernel", "l2_loss_kernel", "sum_partials_kernel",
+                                                                 "mlp_bwd_kernel", "reduce_dw_kernel", "adam_kernel",
+                                                                 "set_params_kernel"],
+            "clocks": clocks, "kernel_status": status, "final_loss_sum": loss_value,
+        }
+        if cpu is not None:
+            out["cpu_baseline"] = cpu
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def xavier_weights(n_mat, width, seed):
+    """n_mat matrices (in x out), uniform(+-sqrt(6 / (2 width))), numpy PCG64 - same draw as tests/synth.py."""
+    rng = np.random.default_rng(seed)
+    bound = np.sqrt(6.0 / (2 * width))
+    return rng.uniform(-bound, bound, (n_mat, width, width)).astype(np.float32)
+
+
+def _packed(w):
+    """(in x out) matrices -> the packed parameter order the optimiser sees."""
+    from tiny_dpcpp_nn.modules import to_packed_layout_coord
+
+    idx = np.array([to_packed_layout_coord(i, WIDTH, WIDTH) for i in range(WIDTH * WIDTH)])
+    flat = w.reshape(N_MAT, -1)
+    out = np.empty_like(flat)
+    out[:, idx] = flat
+    return out.reshape(-1)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--log2-batch", type=int, default=LOG2_BATCH)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -101,6 +101,11 @@ int tnn_network_sync_status(tnn_network *net, int *status, void *stream);
  * bit 1: MN-major weight operand).  Default 0.  No reference counterpart. */
 int tnn_network_set_variant(tnn_network *net, int variant);
 
+/* Kernel-tuning aid: with enable != 0 the inference kernel's first CTA records (code, clock) pairs
+ * per role into a device buffer; host_out (optional, n_words uint64) receives and clears it.
+ * enable == 0 frees the buffer.  Synchronises the device.  No reference counterpart. */
+int tnn_network_debug_timeline(tnn_network *net, int enable, unsigned long long *host_out, size_t n_words);
+
 /* ------------------------------------------------------------------------------------------
  * Encoding: replaces tnn::EncodingModule<float> (include/tnn_api.h:306-488) and create_encoding
  * (pybind_module.cpp:141-147, include/encodings/encoding_factory.h:109-176).

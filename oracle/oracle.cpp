@@ -272,6 +272,10 @@ uint32_t oracle_grid_init(OracleGrid *g, uint32_t n_levels, uint32_t F, uint32_t
                           uint32_t base_resolution, float per_level_scale, int grid_type, int hash_type,
                           int interpolation) {
     g->n_levels = n_levels, g->F = F, g->D = D, g->base_resolution = base_resolution;
+    if (per_level_scale <= 0.0f) // default of grid.h:1035-1041
+        per_level_scale = (grid_type == 1 && n_levels > 1)
+                              ? std::exp(std::log(256.0f / (float)base_resolution) / (n_levels - 1))
+                              : 2.0f;
     g->log2_per_level_scale = std::log2(per_level_scale);
     g->grid_type = grid_type, g->hash_type = hash_type, g->interpolation = interpolation;
     uint32_t offset = 0;

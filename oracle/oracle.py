@@ -160,7 +160,9 @@ class Grid:
     """Hash-grid oracle with the reference's configuration keys and defaults (grid.h:1010-1047)."""
 
     def __init__(self, n_dims_to_encode=2, n_levels=16, n_features_per_level=2, log2_hashmap_size=19,
-                 base_resolution=16, per_level_scale=2.0, type="Hash", hash="CoherentPrime", interpolation="Linear"):
+                 base_resolution=16, per_level_scale=None, type="Hash", hash="CoherentPrime", interpolation="Linear"):
+        if per_level_scale is None:
+            per_level_scale = 0.0  # oracle_grid_init then applies the default of grid.h:1035-1041
         self.s = _GridStruct()
         self.n_entries = lib().oracle_grid_init(ctypes.byref(self.s), ctypes.c_uint32(n_levels),
                                                 ctypes.c_uint32(n_features_per_level), ctypes.c_uint32(n_dims_to_encode),

@@ -19,6 +19,8 @@
 
 using mlp_cpp::MLP;
 
+static std::streambuf *const g_cout_buf = std::cout.rdbuf();
+
 static Activation to_act(int a) { return a == 0 ? Activation::ReLU : a == 4 ? Activation::Sigmoid : Activation::None; }
 
 extern "C" {
@@ -74,6 +76,7 @@ int ref_mlp_sample(int in_dim, int width, int out_dim, int n_mat, int batch, int
         std::cout.rdbuf(old);
         return 0;
     } catch (const std::exception &e) {
+        std::cout.rdbuf(g_cout_buf);
         std::cerr << "ref_mlp_sample: " << e.what() << std::endl;
         return 1;
     }
@@ -83,8 +86,7 @@ int ref_mlp_sample(int in_dim, int width, int out_dim, int n_mat, int batch, int
 // do_backward != 0) of one shared MLP instance; returns the number of samples processed.
 long ref_mlp_run_batch(int width, int n_mat, int act, int out_act, const double *weights, const double *x,
                        const double *target, long batch, int do_backward, double *checksum) {
-    std::ostringstream sink;
-    auto *old = std::cout.rdbuf(sink.rdbuf());
+    // called from several threads at once: std::cout is left alone here (with equal widths mlp.h prints nothing)
     MLP<double> mlp(width, width, width, n_mat, 1, to_act(act), to_act(out_act), mlp_cpp::WeightInitMode::constant);
     for (int l = 0; l < n_mat; ++l)
         for (int k = 0; k < width; ++k)
@@ -104,7 +106,6 @@ long ref_mlp_run_batch(int width, int n_mat, int act, int out_act, const double 
             acc += wg[0].data[0][0];
         }
     }
-    std::cout.rdbuf(old);
     if (checksum) *checksum = acc;
     return batch;
 }

@@ -10,6 +10,7 @@
 #include "mlp_common.cuh"
 #include "mlp_launch.h"
 
+#include <algorithm>
 #include <cmath>
 #include <cstring>
 #include <memory>
@@ -100,6 +101,7 @@ struct tnn_network {
     __nv_bfloat16 *wimg_t = nullptr; // swizzled operand images, rows = output feature
     float *dw_slabs = nullptr;       // per-CTA weight-gradient partial sums
     int *status = nullptr;
+    unsigned long long *prof = nullptr; // timeline buffer for kernel tuning (see tnn_network_debug_timeline)
 
     int one_padded_input() const {
         // rows of the first matrix that can carry signal: the real inputs, plus (with bias) the
@@ -176,6 +178,7 @@ int tnn_network_destroy(tnn_network *n) {
     cudaFree(n->wimg_t);
     cudaFree(n->dw_slabs);
     cudaFree(n->status);
+    cudaFree(n->prof);
     delete n;
     return 0;
 }
@@ -267,6 +270,7 @@ static int run_forward(tnn_network *n, const void *x, void *y, void *interm, siz
     p.n_sm = n->n_sm;
     p.status = n->status;
     p.stream = (cudaStream_t)stream;
+    p.prof = interm ? nullptr : n->prof;
     if (interm) // matrix 0 of the forward workspace is a copy of the input (kernel_esimd.h:601-605)
         TNN_CUDA(cudaMemcpyAsync(interm, x, batch * n->width * sizeof(__nv_bfloat16), cudaMemcpyDeviceToDevice, p.stream));
     cudaError_t e = tnn::launch_mlp_fwd(p);
@@ -344,6 +348,25 @@ int tnn_network_sync_status(tnn_network *n, int *status, void *stream) {
     return 0;
 }
 
+int tnn_network_debug_timeline(tnn_network *n, int enable, unsigned long long *host_out, size_t n_words) {
+    if (!n) return fail("network is null");
+    constexpr size_t kWords = 6 * 2048 * 2;
+    if (enable && !n->prof) {
+        TNN_CUDA(cudaMalloc(&n->prof, kWords * sizeof(unsigned long long)));
+        TNN_CUDA(cudaMemset(n->prof, 0, kWords * sizeof(unsigned long long)));
+    }
+    if (host_out && n->prof) {
+        TNN_CUDA(cudaDeviceSynchronize());
+        TNN_CUDA(cudaMemcpy(host_out, n->prof, std::min(n_words, kWords) * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+        TNN_CUDA(cudaMemset(n->prof, 0, kWords * sizeof(unsigned long long)));
+    }
+    if (!enable && n->prof) {
+        cudaFree(n->prof);
+        n->prof = nullptr;
+    }
+    return 0;
+}
+
 int tnn_network_adam_step(tnn_network *n, float *master, float *m, float *v, const float *grads, float grad_scale,
                           int step, float lr, float beta1, float beta2, float eps, void *stream) {
     TNN_GUARD_BEGIN
@@ -364,8 +387,8 @@ int tnn_l2_loss(const void *pred, const float *target, int n_targets, float *val
     if (!pred || !target) return fail("null argument");
     if (n_targets <= 0 || n_targets > stride) return fail("n_targets must be in [1, stride]");
     if (loss_scale == 0.0f) return fail("loss_scale must not be 0");
-    // partial sums live in a small per-call buffer carved from the caller's values array is not
-    // possible when values == nullptr, so the reduction buffer is owned by the library.
+    if (stride % 16 != 0) return fail("stride must be a multiple of 16 (network widths are)");
+    // per-block partial sums of the loss; the buffer is owned by the library (one per process)
     static float *partials = nullptr;
     constexpr int kPartials = 1024;
     if (loss_sum && !partials) TNN_CUDA(cudaMalloc(&partials, kPartials * sizeof(float)));
@@ -425,7 +448,6 @@ int tnn_encoding_create(const char *json_config, int padded_output_width, tnn_en
     tnn::JsonObject cfg = tnn::parse_json_object(json_config);
     if (!cfg.has("otype")) return fail("Config needs to contain encoding, key otype");
     const std::string name = cfg.at("otype").str;
-    if (int rc = device_checks()) return rc;
     auto enc = std::make_unique<tnn_encoding>();
     if (name == "Identity") {
         if (!cfg.has("offset")) return fail("Config misses offset");
@@ -479,6 +501,7 @@ int tnn_encoding_create(const char *json_config, int padded_output_width, tnn_en
     enc->padded = padded_output_width > 0 ? padded_output_width : enc->n_out;
     if (enc->n_in <= 0) return fail("Input width cannot be zero");
     if (enc->padded < enc->n_out) return fail("Padded output width cannot be less than output width");
+    if (int rc = device_checks()) return rc; // configuration errors above are reported even without a device
     if (enc->is_grid) {
         enc->gp.padded_width = (uint32_t)enc->padded;
         TNN_CUDA(cudaMalloc(&enc->table, enc->n_params * sizeof(float)));

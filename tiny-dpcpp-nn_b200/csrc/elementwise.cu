@@ -116,21 +116,48 @@ cudaError_t launch_identity_fwd(const float *x, void *out, int out_bf16, size_t 
 // L2 loss (include/losses/l2.h:19-41): value = (p - t)^2 / n, grad = scale * 2 (p - t) / n with
 // n = batch * stride.  Targets are [batch][n_targets]; prediction columns >= n_targets are padding and
 // compare against 0.  Per-block partial sums of the loss values go to `loss_partials` (fixed order).
-__global__ void l2_loss_kernel(const __nv_bfloat16 *__restrict__ pred, const float *__restrict__ target,
-                               int n_targets, float *__restrict__ values, __nv_bfloat16 *__restrict__ grads,
-                               size_t batch, int stride, float loss_scale, float *__restrict__ loss_partials) {
+__global__ void __launch_bounds__(256)
+l2_loss_kernel(const __nv_bfloat16 *__restrict__ pred, const float *__restrict__ target, int n_targets,
+               float *__restrict__ values, __nv_bfloat16 *__restrict__ grads, size_t batch, int stride,
+               float loss_scale, float *__restrict__ loss_partials) {
+    // one thread handles 8 consecutive columns of one row (16 bytes of bf16); stride is a multiple of 16
     const size_t n_el = batch * (size_t)stride;
+    const size_t n_vec = n_el / 8;
     const float inv_n = 1.0f / (float)n_el;
+    const bool full_targets = n_targets == stride;
     float local = 0.0f;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n_el; idx += (size_t)gridDim.x * blockDim.x) {
+    for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < n_vec; v += (size_t)gridDim.x * blockDim.x) {
+        const size_t idx = v * 8;
         const size_t row = idx / stride;
         const int col = (int)(idx % stride);
-        const float t = col < n_targets ? target[row * n_targets + col] : 0.0f;
-        const float d = __bfloat162float(pred[idx]) - t;
-        const float v = d * d * inv_n;
-        if (values) values[idx] = v;
-        if (grads) grads[idx] = __float2bfloat16_rn(loss_scale * 2.0f * d * inv_n);
-        local += v;
+        const uint4 p4 = *reinterpret_cast<const uint4 *>(pred + idx);
+        const uint32_t pw[4] = {p4.x, p4.y, p4.z, p4.w};
+        float t[8];
+        if (full_targets) {
+            const float4 a = *reinterpret_cast<const float4 *>(target + idx);
+            const float4 b = *reinterpret_cast<const float4 *>(target + idx + 4);
+            t[0] = a.x, t[1] = a.y, t[2] = a.z, t[3] = a.w, t[4] = b.x, t[5] = b.y, t[6] = b.z, t[7] = b.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[j] = (col + j) < n_targets ? target[row * n_targets + col + j] : 0.0f;
+        }
+        float g[8], val[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float p = (j & 1) ? ptx::bf16hi_to_f32(pw[j >> 1]) : ptx::bf16lo_to_f32(pw[j >> 1]);
+            const float d = p - t[j];
+            val[j] = d * d * inv_n;
+            g[j] = loss_scale * 2.0f * d * inv_n;
+            local += val[j];
+        }
+        if (values) {
+            *reinterpret_cast<float4 *>(values + idx) = make_float4(val[0], val[1], val[2], val[3]);
+            *reinterpret_cast<float4 *>(values + idx + 4) = make_float4(val[4], val[5], val[6], val[7]);
+        }
+        if (grads)
+            *reinterpret_cast<uint4 *>(grads + idx) =
+                make_uint4(ptx::pack_bf16x2(g[0], g[1]), ptx::pack_bf16x2(g[2], g[3]), ptx::pack_bf16x2(g[4], g[5]),
+                           ptx::pack_bf16x2(g[6], g[7]));
     }
     __shared__ float red[256];
     red[threadIdx.x] = local;

@@ -136,6 +136,12 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
         if (lane == 0 && my_tiles > 0) {
             constexpr uint32_t idesc_chain = ptx::make_idesc_bf16(128, W, 0, B_MN_MAJOR ? 1 : 0);
             constexpr uint32_t idesc_dw = ptx::make_idesc_bf16(S::DW_M, W, 1, 1);
+            // base descriptors; buffers and k-steps are reached with constant adds
+            const uint64_t dk_desc0 = T::kdesc_base(smem_base + S::DY);                        // delta tiles, K-major
+            const uint64_t dmn_desc0 = T::mndesc_base(smem_base + S::DY, T::ACT_ATOM_BYTES);   // delta tiles, MN-major
+            const uint64_t amn_desc0 = T::mndesc_base(smem_base + S::AR, T::ACT_ATOM_BYTES);   // activations, MN-major
+            const uint64_t w_desc0 = B_MN_MAJOR ? T::mndesc_base(smem_base + S::WBUF, T::WGT_ATOM_BYTES)
+                                                : T::kdesc_base(smem_base + S::WBUF);
             bool ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
             if (!ok) atomicExch(status, KS_TIMEOUT_WEIGHTS);
             int r = 0;  // forward-activation loads consumed
@@ -157,8 +163,8 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                 }
                 for (int l = L; ok && l >= 0; --l) {
                     // delta_l: dL/dy buffer for l == L, else ping-pong buffer (L - 1 - l) & 1
-                    const uint32_t d_addr = (l == L) ? smem_base + S::DY + b * T::ACT_BYTES
-                                                     : smem_base + S::DP + ((L - 1 - l) & 1) * T::ACT_BYTES;
+                    // (index into the four contiguous delta tiles DY[0], DY[1], DP[0], DP[1])
+                    const int d_idx = (l == L) ? b : 2 + ((L - 1 - l) & 1);
                     if (l < L) {
                         if (!ptx::mbar_wait(&bars.d_ready, dr & 1, abort_flag)) {
                             atomicExch(status, KS_TIMEOUT_MMA | 2 | (l << 4));
@@ -168,15 +174,10 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                         ++dr;
                     }
                     ptx::tc_fence_after_sync();
-                    const uint32_t w_addr = smem_base + S::WBUF + l * T::WGT_BYTES;
                     if (l > 0 || want_dx) {
                         // chain: acc[128 x W] = delta_l[128 x W] * W_l^T
-#pragma unroll
-                        for (int ks = 0; ks < T::KSTEPS; ++ks) {
-                            const uint64_t bdesc = B_MN_MAJOR ? T::desc_mnmajor(w_addr, ks, T::WGT_ATOM_BYTES)
-                                                              : T::desc_kmajor(w_addr, ks, T::WGT_ATOM_BYTES);
-                            ptx::mma_ss(acc_tmem, T::desc_kmajor(d_addr, ks, T::ACT_ATOM_BYTES), bdesc, idesc_chain, ks > 0);
-                        }
+                        T::template issue_chain<B_MN_MAJOR>(acc_tmem, dk_desc0 + (uint64_t)(d_idx * T::ACT_UNITS),
+                                                            w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc_chain);
                         ptx::mma_commit(&bars.acc_full);
                     }
                     // weight gradient: G_l[W x W] += delta_l^T[W x 128] * a_l[128 x W]
@@ -187,11 +188,8 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    const uint32_t a_addr = smem_base + S::AR + slot * T::ACT_BYTES;
-#pragma unroll
-                    for (int ks = 0; ks < T::TM / 16; ++ks)
-                        ptx::mma_ss(dw_tmem(l), T::desc_mnmajor(d_addr, ks, T::ACT_ATOM_BYTES),
-                                    T::desc_mnmajor(a_addr, ks, T::ACT_ATOM_BYTES), idesc_dw, (t > 0 || ks > 0) ? 1u : 0u);
+                    T::issue_outer(dw_tmem(l), dmn_desc0 + (uint64_t)(d_idx * T::ACT_UNITS),
+                                   amn_desc0 + (uint64_t)(slot * T::ACT_UNITS), idesc_dw, t > 0 ? 1u : 0u);
                     ptx::mma_commit(&bars.a_empty[slot]);
                     ++r;
                     if (l == L) ptx::mma_commit(&bars.dy_empty[b]);
@@ -295,27 +293,31 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                         ptx::named_bar_sync(1, 128);
                     }
                     const uint8_t *abuf = smem + S::AR + slot * T::ACT_BYTES;
+                    constexpr int NLD = W / CW;
+                    uint32_t v[NLD][CW];
 #pragma unroll
-                    for (int c0 = 0; c0 < W; c0 += CW) {
-                        uint32_t v[CW];
+                    for (int i = 0; i < NLD; ++i) {
                         if constexpr (CW == 32)
-                            ptx::tmem_ld32(acc_tmem + lane_addr + c0, v);
+                            ptx::tmem_ld32(acc_tmem + lane_addr + i * CW, v[i]);
                         else
-                            ptx::tmem_ld16(acc_tmem + lane_addr + c0, v);
-                        ptx::tmem_ld_wait();
+                            ptx::tmem_ld16(acc_tmem + lane_addr + i * CW, v[i]);
+                    }
+                    ptx::tmem_ld_wait();
+                    const int a = (l > 0) ? act : (int)ACT_NONE;
+#pragma unroll
+                    for (int i = 0; i < NLD; ++i) {
 #pragma unroll
                         for (int ch = 0; ch < CW / 8; ++ch) {
-                            const int c = c0 + ch * 8;
+                            const int c = i * CW + ch * 8;
                             const int off =
                                 (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES + T::chunk_off(row, (c % T::ATOM_COLS) / 8);
                             uint4 f = make_uint4(0, 0, 0, 0);
                             if (need_a) f = *reinterpret_cast<const uint4 *>(abuf + off);
-                            const int a = (l > 0) ? act : (int)ACT_NONE;
                             uint4 o;
-                            o.x = act_bwd_pack(a, __uint_as_float(v[ch * 8 + 0]), __uint_as_float(v[ch * 8 + 1]), f.x);
-                            o.y = act_bwd_pack(a, __uint_as_float(v[ch * 8 + 2]), __uint_as_float(v[ch * 8 + 3]), f.y);
-                            o.z = act_bwd_pack(a, __uint_as_float(v[ch * 8 + 4]), __uint_as_float(v[ch * 8 + 5]), f.z);
-                            o.w = act_bwd_pack(a, __uint_as_float(v[ch * 8 + 6]), __uint_as_float(v[ch * 8 + 7]), f.w);
+                            o.x = act_bwd_pack(a, __uint_as_float(v[i][ch * 8 + 0]), __uint_as_float(v[i][ch * 8 + 1]), f.x);
+                            o.y = act_bwd_pack(a, __uint_as_float(v[i][ch * 8 + 2]), __uint_as_float(v[i][ch * 8 + 3]), f.y);
+                            o.z = act_bwd_pack(a, __uint_as_float(v[i][ch * 8 + 4]), __uint_as_float(v[i][ch * 8 + 5]), f.z);
+                            o.w = act_bwd_pack(a, __uint_as_float(v[i][ch * 8 + 6]), __uint_as_float(v[i][ch * 8 + 7]), f.w);
                             *reinterpret_cast<uint4 *>(dst + off) = o;
                         }
                     }

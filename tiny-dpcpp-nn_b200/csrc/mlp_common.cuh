@@ -60,16 +60,50 @@ template <int W> struct Tile {
         return (c / ATOM_COLS) * atom_bytes + chunk_off(r, (c % ATOM_COLS) / 8) + (c % 8) * 2;
     }
 
-    // Descriptor of k-step `ks` of a K-major operand stored at `base` (shared address).
-    __device__ static uint64_t desc_kmajor(uint32_t base, int ks, int atom_bytes) {
-        const int col = ks * 16;
-        const uint32_t start = base + (col / ATOM_COLS) * atom_bytes + (col % ATOM_COLS) * 2;
-        return ptx::make_smem_desc(start, 16, SBO, SWZ);
+    // Descriptor arithmetic.  A descriptor's low 14 bits hold (address >> 4), so stepping to the next
+    // k-step or the next buffer is a plain 64-bit add of a compile-time constant to a base descriptor;
+    // the MMA issuer is a single thread, every instruction it saves shortens the layer-to-layer chain.
+    static constexpr int KPA = ATOM_COLS / 16;              // k-steps inside one K-major atom
+    static constexpr uint32_t K_STEP = 2;                    // 32 bytes: one k-step inside a K-major row
+    static constexpr uint32_t MN_STEP = ROW_BYTES;           // 16 stored rows: one k-step of an MN-major operand
+    static constexpr uint32_t ACT_UNITS = ACT_BYTES >> 4;    // one activation tile, in descriptor units
+    static constexpr uint32_t WGT_UNITS = WGT_BYTES >> 4;
+    __device__ static uint64_t kdesc_base(uint32_t base) { return ptx::make_smem_desc(base, 16, SBO, SWZ); }
+    __device__ static uint64_t mndesc_base(uint32_t base, int atom_bytes) {
+        return ptx::make_smem_desc(base, atom_bytes, SBO, SWZ);
     }
-    // Descriptor of k-step `ks` of an MN-major operand (K runs over the stored rows).
-    __device__ static uint64_t desc_mnmajor(uint32_t base, int ks, int atom_bytes) {
-        const uint32_t start = base + ks * 16 * ROW_BYTES;
-        return ptx::make_smem_desc(start, atom_bytes, SBO, SWZ);
+    // D[128 x W] = A[128 x W] * B, A K-major in an activation tile, B a weight tile (K- or MN-major).
+    template <bool B_MN> __device__ static void issue_chain(uint32_t d_tmem, uint64_t a_base, uint64_t w_base,
+                                                            uint32_t idesc) {
+#pragma unroll
+        for (int at = 0; at < KATOMS; ++at) {
+            const uint64_t a0 = a_base + (uint64_t)(at * (ACT_ATOM_BYTES >> 4));
+            const uint64_t b0 = w_base + (uint64_t)(B_MN ? at * KPA * MN_STEP : at * (WGT_ATOM_BYTES >> 4));
+#pragma unroll
+            for (int k = 0; k < KPA; ++k)
+                ptx::mma_ss(d_tmem, a0 + (uint64_t)(k * K_STEP), b0 + (uint64_t)(k * (B_MN ? MN_STEP : K_STEP)), idesc,
+                            (at > 0 || k > 0) ? 1u : 0u);
+        }
+    }
+    // same with the A operand in tensor memory (two bf16 per 32-bit column: 8 columns per k-step)
+    template <bool B_MN> __device__ static void issue_chain_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t w_base,
+                                                               uint32_t idesc) {
+#pragma unroll
+        for (int at = 0; at < KATOMS; ++at) {
+            const uint64_t b0 = w_base + (uint64_t)(B_MN ? at * KPA * MN_STEP : at * (WGT_ATOM_BYTES >> 4));
+#pragma unroll
+            for (int k = 0; k < KPA; ++k)
+                ptx::mma_ts(d_tmem, a_tmem + (at * KPA + k) * 8, b0 + (uint64_t)(k * (B_MN ? MN_STEP : K_STEP)), idesc,
+                            (at > 0 || k > 0) ? 1u : 0u);
+        }
+    }
+    // D[M x W] (+)= A^T B over the 128 stored rows of two activation tiles, both MN-major.
+    __device__ static void issue_outer(uint32_t d_tmem, uint64_t a_base, uint64_t b_base, uint32_t idesc,
+                                       uint32_t accumulate) {
+#pragma unroll
+        for (int k = 0; k < TM / 16; ++k)
+            ptx::mma_ss(d_tmem, a_base + (uint64_t)(k * MN_STEP), b_base + (uint64_t)(k * MN_STEP), idesc,
+                        (k > 0) ? 1u : accumulate);
     }
 };
 

@@ -19,11 +19,14 @@
 
 namespace tnn {
 
-template <int W, int NSLOT, bool TMEM_A> struct FwdSmem {
+template <int W, int NSLOT, bool TMEM_A, bool STORE_ALL> struct FwdSmem {
     using T = Tile<W>;
+    // activation buffers per slot: two (ping-pong) when every layer is also streamed out by TMA,
+    // one when the next layer's MMA is the only reader
+    static constexpr int NABUF = STORE_ALL ? 2 : 1;
     static constexpr int XBUF = 0;                                     // NSLOT input tiles
-    static constexpr int ABUF = XBUF + NSLOT * T::ACT_BYTES;           // NSLOT x 2 activation tiles
-    static constexpr int WBUF = ABUF + NSLOT * 2 * T::ACT_BYTES;       // (L+1) weight tiles follow
+    static constexpr int ABUF = XBUF + NSLOT * T::ACT_BYTES;           // NSLOT x NABUF activation tiles
+    static constexpr int WBUF = ABUF + NSLOT * NABUF * T::ACT_BYTES;   // (L+1) weight tiles follow
     static constexpr int tmem_cols_needed = NSLOT * (W + (TMEM_A ? W / 2 : 0));
     static constexpr int tmem_cols =
         tmem_cols_needed <= 32 ? 32 : tmem_cols_needed <= 64 ? 64 : tmem_cols_needed <= 128 ? 128
@@ -41,13 +44,29 @@ struct FwdBarriers {
     uint32_t abort_flag;
 };
 
-template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN_MAJOR>
+// Timeline probe for tuning: CTA 0 appends (code, clock64) pairs per role into `prof`
+// (region r starts at prof + r * 2 * kProfRegion).  Compiled in only for PROFILE instantiations.
+constexpr int kProfRegion = 2048;
+#define TNN_PROF(region, code)                                                                                         \
+    do {                                                                                                               \
+        if constexpr (PROFILE) {                                                                                       \
+            if (blockIdx.x == 0 && prof && prof_n < kProfRegion) {                                                     \
+                prof[((region) * kProfRegion + prof_n) * 2] = (unsigned long long)(code);                             \
+                prof[((region) * kProfRegion + prof_n) * 2 + 1] = (unsigned long long)clock64();                      \
+                ++prof_n;                                                                                              \
+            }                                                                                                          \
+        }                                                                                                              \
+    } while (0)
+
+template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN_MAJOR, bool PROFILE = false>
 __global__ void __launch_bounds__(64 + 128 * NSLOT, 1)
 mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                const __grid_constant__ CUtensorMap tm_interm, const __nv_bfloat16 *__restrict__ wimg,
-               int n_tiles, int n_mat, int act, int out_act, int write_y, int *status) {
+               int n_tiles, int n_mat, int act, int out_act, int write_y, int *status,
+               unsigned long long *prof = nullptr) {
+    [[maybe_unused]] int prof_n = 0;
     using T = Tile<W>;
-    using S = FwdSmem<W, NSLOT, TMEM_A>;
+    using S = FwdSmem<W, NSLOT, TMEM_A, STORE_ALL>;
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment (swizzle span)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -104,12 +123,18 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                 for (int a = 0; a < T::KATOMS; ++a)
                     ptx::tma_load_2d(smem + S::XBUF + s * T::ACT_BYTES + a * T::ACT_ATOM_BYTES, &tm_x,
                                      a * T::ATOM_COLS, tile * T::TM, &bars.x_full[s]);
+                TNN_PROF(0, (j << 8) | 1);
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0 && my_tiles > 0) {
             constexpr uint32_t idesc = ptx::make_idesc_bf16(128, W, 0, B_MN_MAJOR ? 1 : 0);
+            // base descriptors, stepped with constant adds inside the loop
+            const uint64_t x_desc0 = T::kdesc_base(smem_base + S::XBUF);
+            const uint64_t a_desc0 = T::kdesc_base(smem_base + S::ABUF);
+            const uint64_t w_desc0 = B_MN_MAJOR ? T::mndesc_base(smem_base + S::WBUF, T::WGT_ATOM_BYTES)
+                                                : T::kdesc_base(smem_base + S::WBUF);
             bool ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
             if (!ok) atomicExch(status, KS_TIMEOUT_WEIGHTS);
             const int rounds = (my_tiles + NSLOT - 1) / NSLOT;
@@ -120,6 +145,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                         // a_ready completion that must precede this MMA: the epilogue of
                         // (t, l-1), or for l == 0 the last epilogue of the previous tile.
                         const int n = t * n_mat + l - 1;
+                        TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 0);
                         if (l == 0 && !ptx::mbar_wait(&bars.x_full[s], t & 1, abort_flag)) ok = false;
                         if (ok && n >= 0 && !ptx::mbar_wait(&bars.a_ready[s], n & 1, abort_flag)) ok = false;
                         if (!ok) {
@@ -127,23 +153,31 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                             break;
                         }
                         ptx::tc_fence_after_sync();
+                        TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 1);
                         const uint32_t d_tmem = tmem_base + s * W;
-                        const uint32_t w_addr = smem_base + S::WBUF + l * T::WGT_BYTES;
-                        const uint32_t a_addr = (l == 0) ? smem_base + S::XBUF + s * T::ACT_BYTES
-                                                         : smem_base + S::ABUF + (s * 2 + ((l - 1) & 1)) * T::ACT_BYTES;
-#pragma unroll
-                        for (int ks = 0; ks < T::KSTEPS; ++ks) {
-                            const uint64_t bdesc = B_MN_MAJOR ? T::desc_mnmajor(w_addr, ks, T::WGT_ATOM_BYTES)
-                                                              : T::desc_kmajor(w_addr, ks, T::WGT_ATOM_BYTES);
-                            if (TMEM_A && l > 0) {
-                                const uint32_t a_tmem = tmem_base + NSLOT * W + s * (W / 2) + ks * 8;
-                                ptx::mma_ts(d_tmem, a_tmem, bdesc, idesc, ks > 0);
+                        const uint64_t w_desc = w_desc0 + (uint64_t)(l * T::WGT_UNITS);
+                        if (TMEM_A && l > 0) {
+                            T::template issue_chain_ts<B_MN_MAJOR>(d_tmem, tmem_base + NSLOT * W + s * (W / 2), w_desc, idesc);
+                        } else {
+                            const uint64_t a_desc =
+                                (l == 0) ? x_desc0 + (uint64_t)(s * T::ACT_UNITS)
+                                         : a_desc0 + (uint64_t)((s * S::NABUF + ((l - 1) & (S::NABUF - 1))) * T::ACT_UNITS);
+                            if constexpr (PROFILE) {
+                                ptx::mma_ss(d_tmem, a_desc, w_desc, idesc, 0u);
+                                TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 5);
+                                ptx::mma_ss(d_tmem, a_desc + 2, w_desc + 2, idesc, 1u);
+                                TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 6);
+                                ptx::mma_ss(d_tmem, a_desc + 4, w_desc + 4, idesc, 1u);
+                                ptx::mma_ss(d_tmem, a_desc + 6, w_desc + 6, idesc, 1u);
+                                TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 7);
                             } else {
-                                ptx::mma_ss(d_tmem, T::desc_kmajor(a_addr, ks, T::ACT_ATOM_BYTES), bdesc, idesc, ks > 0);
+                                T::template issue_chain<B_MN_MAJOR>(d_tmem, a_desc, w_desc, idesc);
                             }
                         }
                         ptx::mma_commit(&bars.acc_full[s]);
+                        TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 8);
                         if (l == 0) ptx::mma_commit(&bars.x_empty[s]);
+                        TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 2);
                     }
                 }
             }
@@ -168,10 +202,12 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                     break;
                 }
                 ptx::tc_fence_after_sync();
+                if (threadIdx.x == 64 + 128 * g) TNN_PROF(2 + g, (t << 16) | (l << 8) | 1);
                 const int a = (l == L) ? out_act : act;
                 const bool to_tmem = TMEM_A && l < L;
-                uint8_t *abuf = smem + S::ABUF + (s * 2 + (l & 1)) * T::ACT_BYTES;
+                uint8_t *abuf = smem + S::ABUF + (s * S::NABUF + (l & (S::NABUF - 1))) * T::ACT_BYTES;
                 if (!to_tmem && (STORE_ALL || TMEM_A || l == 0)) {
+                    // (single-buffer modes: only the previous tile's output store can still be reading it)
                     // the buffer about to be overwritten may still be read by an earlier TMA store
                     if (leader) {
                         if (STORE_ALL && l > 0)
@@ -182,18 +218,23 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                     ptx::named_bar_sync(1 + g, 128);
                 }
                 constexpr int CW = (W >= 32) ? 32 : 16; // columns per TMEM load
+                constexpr int NLD = W / CW;
+                uint32_t v[NLD][CW];
 #pragma unroll
-                for (int c0 = 0; c0 < W; c0 += CW) {
-                    uint32_t v[CW];
+                for (int i = 0; i < NLD; ++i) {
                     if constexpr (CW == 32)
-                        ptx::tmem_ld32(tmem_base + lane_addr + s * W + c0, v);
+                        ptx::tmem_ld32(tmem_base + lane_addr + s * W + i * CW, v[i]);
                     else
-                        ptx::tmem_ld16(tmem_base + lane_addr + s * W + c0, v);
-                    ptx::tmem_ld_wait();
+                        ptx::tmem_ld16(tmem_base + lane_addr + s * W + i * CW, v[i]);
+                }
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < NLD; ++i) {
+                    const int c0 = i * CW;
                     uint32_t p[CW / 2];
 #pragma unroll
-                    for (int i = 0; i < CW / 2; ++i)
-                        p[i] = act_pack(a, __uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                    for (int j = 0; j < CW / 2; ++j)
+                        p[j] = act_pack(a, __uint_as_float(v[i][2 * j]), __uint_as_float(v[i][2 * j + 1]));
                     if (to_tmem) {
                         if constexpr (CW == 32) {
                             ptx::tmem_st16(tmem_base + lane_addr + NSLOT * W + s * (W / 2) + c0 / 2, p);
@@ -209,12 +250,14 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                         }
                     }
                 }
+                if (threadIdx.x == 64 + 128 * g) TNN_PROF(2 + g, (t << 16) | (l << 8) | 2);
                 if (to_tmem)
                     ptx::tmem_st_wait();
                 else
                     ptx::fence_proxy_async_smem();
                 ptx::tc_fence_before_sync();
                 ptx::mbar_arrive(&bars.a_ready[s]);
+                if (threadIdx.x == 64 + 128 * g) TNN_PROF(2 + g, (t << 16) | (l << 8) | 3);
                 if (!to_tmem && (STORE_ALL || l == L)) {
                     ptx::named_bar_sync(1 + g, 128);
                     if (leader) {
@@ -249,13 +292,13 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
 }
 
 // ---------------------------------------------------------------------- host side
-template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN>
+template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN, bool PROFILE = false>
 static cudaError_t launch_variant(const FwdLaunch &p) {
     using T = Tile<W>;
-    using S = FwdSmem<W, NSLOT, TMEM_A>;
+    using S = FwdSmem<W, NSLOT, TMEM_A, STORE_ALL>;
     const size_t smem = (size_t)S::WBUF + (size_t)p.n_mat * T::WGT_BYTES + 1024;
     if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
-    auto kern = mlp_fwd_kernel<W, NSLOT, STORE_ALL, TMEM_A, B_MN>;
+    auto kern = mlp_fwd_kernel<W, NSLOT, STORE_ALL, TMEM_A, B_MN, PROFILE>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
@@ -263,7 +306,7 @@ static cudaError_t launch_variant(const FwdLaunch &p) {
     if (grid == 0) return cudaSuccess;
     kern<<<grid, 64 + 128 * NSLOT, smem, p.stream>>>(p.tm_x, p.tm_y, p.tm_interm,
                                                     B_MN ? p.wimg : p.wimg_t, n_tiles, p.n_mat, p.act, p.out_act,
-                                                    p.write_y, p.status);
+                                                    p.write_y, p.status, p.prof);
     return cudaGetLastError();
 }
 
@@ -271,6 +314,12 @@ template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
     // variant bits: 1 = keep hidden activations in TMEM (inference only), 2 = MN-major weights
     if (p.store_all) {
         return (p.variant & 2) ? launch_variant<W, 2, true, false, true>(p) : launch_variant<W, 2, true, false, false>(p);
+    }
+    if constexpr (W == 64) {
+        if (p.prof) return launch_variant<W, 2, false, false, false, true>(p);
+    }
+    if constexpr (W <= 64) {
+        if (p.variant & 8) return launch_variant<W, 4, false, false, false>(p); // four tiles in flight per CTA
     }
     if constexpr (W >= 32) {
         if (p.variant & 1)

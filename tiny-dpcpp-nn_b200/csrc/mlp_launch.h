@@ -24,6 +24,7 @@ struct FwdLaunch {
     int n_sm;
     int *status;
     cudaStream_t stream;
+    unsigned long long *prof; // optional timeline buffer (tuning builds only), else nullptr
 };
 cudaError_t launch_mlp_fwd(const FwdLaunch &p);
 

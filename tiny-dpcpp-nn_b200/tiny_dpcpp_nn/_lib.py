@@ -12,6 +12,7 @@ import ctypes
 import enum
 import json
 import os
+import sys
 
 import torch
 
@@ -39,6 +40,7 @@ _SIGNATURES = {
     "tnn_network_backward": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _vp, _vp, _c.c_size_t, _vp]),
     "tnn_network_sync_status": (_c.c_int, [_vp, _c.POINTER(_c.c_int), _vp]),
     "tnn_network_set_variant": (_c.c_int, [_vp, _c.c_int]),
+    "tnn_network_debug_timeline": (_c.c_int, [_vp, _c.c_int, _vp, _c.c_size_t]),
     "tnn_encoding_create": (_c.c_int, [_c.c_char_p, _c.c_int, _c.POINTER(_vp)]),
     "tnn_encoding_destroy": (_c.c_int, [_vp]),
     "tnn_encoding_n_params": (_c.c_size_t, [_vp]),
@@ -157,9 +159,13 @@ class NetworkModule:
         check(lib.tnn_network_initialize_params(self._h, seed, stream_ptr()))
 
     def __del__(self):
-        if getattr(self, "_h", None):
-            self._lib.tnn_network_destroy(self._h)
-            self._h = None
+        # at interpreter shutdown the CUDA runtime may already be gone; the process exit frees the memory
+        try:
+            if getattr(self, "_h", None) and not sys.is_finalizing():
+                self._lib.tnn_network_destroy(self._h)
+                self._h = None
+        except Exception:  # module globals are already torn down
+            pass
 
     def n_params(self):
         return int(self._lib.tnn_network_n_params(self._h))
@@ -263,9 +269,12 @@ class EncodingModule:
             check(lib.tnn_encoding_initialize_params(self._h, seed, stream_ptr()))
 
     def __del__(self):
-        if getattr(self, "_h", None):
-            self._lib.tnn_encoding_destroy(self._h)
-            self._h = None
+        try:
+            if getattr(self, "_h", None) and not sys.is_finalizing():
+                self._lib.tnn_encoding_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
 
     def n_params(self):
         return int(self._lib.tnn_encoding_n_params(self._h))

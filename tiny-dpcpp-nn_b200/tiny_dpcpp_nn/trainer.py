@@ -1,0 +1,66 @@
+"""Training step for a Network: forward -> L2 loss -> backward -> (gradient all-reduce) -> Adam.
+
+The reference's Trainer<T>::training_step (include/trainer.h:23-46) runs forward_pass and
+backward_pass only ("no optimisation as we run benchmarking", trainer.h:39); its Python training
+loops add torch's loss and torch.optim.Adam around the module.  This class is the device-resident
+equivalent of that whole loop body: nothing leaves the GPU between the kernels, the parameter
+vector keeps the packed layout the reference exposes to optimisers (modules.py:169-175), and in
+data-parallel runs the only communication is one all-reduce of the fp32 weight-gradient buffer.
+"""
+import torch
+
+from . import _lib
+
+
+class Trainer:
+    def __init__(self, network, lr=1e-3, betas=(0.9, 0.99), eps=1e-15, loss_scale=1.0, process_group=None,
+                 world_size=1):
+        """network: a _lib.NetworkModule.  process_group: torch.distributed group for data parallelism
+        (None = single GPU); gradients are averaged over world_size ranks."""
+        self.net = network
+        self.lr, self.betas, self.eps = lr, betas, eps
+        self.loss_scale = loss_scale
+        self.pg = process_group
+        self.world_size = world_size
+        n = network.n_params()
+        self.master = network.get_params().float().reshape(-1).contiguous()  # fp32 master copy, packed layout
+        self.m = torch.zeros(n, dtype=torch.float32, device="cuda")
+        self.v = torch.zeros(n, dtype=torch.float32, device="cuda")
+        self.grads = torch.zeros(n, dtype=torch.float32, device="cuda")
+        self.step = 0
+        self._interm = None
+        self._dy = None
+        self._loss = torch.zeros(1, dtype=torch.float32, device="cuda")
+
+    def set_master_params(self, packed_fp32):
+        self.master.copy_(packed_fp32.reshape(-1))
+        self.net.set_params(self.master, True)
+
+    def forward_backward(self, x, targets):
+        """x: batch x width bf16, targets: batch x n_targets fp32.  Leaves the loss sum in self._loss
+        and the (packed, transposed) fp32 gradient of the mean loss in self.grads."""
+        net, lib = self.net, _lib.load()
+        batch = x.shape[0]
+        if self._interm is None or self._interm.shape[1] != batch:
+            self._interm = torch.empty((net.n_mat + 1, batch, net.width), dtype=torch.bfloat16, device="cuda")
+            self._dy = torch.empty((batch, net.width), dtype=torch.bfloat16, device="cuda")
+        s = _lib.stream_ptr()
+        _lib.check(lib.tnn_network_forward(net._h, _lib.dptr(x), None, _lib.dptr(self._interm), batch, s))
+        pred = self._interm[net.n_mat]
+        _lib.check(lib.tnn_l2_loss(_lib.dptr(pred), _lib.dptr(targets), targets.shape[1], None, _lib.dptr(self._dy),
+                                   batch, net.width, float(self.loss_scale), _lib.dptr(self._loss), s))
+        _lib.check(lib.tnn_network_backward(net._h, _lib.dptr(self._dy), _lib.dptr(self._interm),
+                                            _lib.dptr(self.grads), _lib.DTYPE_FP32, 1, None, None, batch, s))
+        return self._loss
+
+    def optimizer_step(self):
+        if self.pg is not None and self.world_size > 1:
+            torch.distributed.all_reduce(self.grads, group=self.pg)
+        self.step += 1
+        self.net.adam_step(self.master, self.m, self.v, self.grads, self.step, self.lr, self.betas[0], self.betas[1],
+                           self.eps, grad_scale=1.0 / (self.loss_scale * self.world_size))
+
+    def training_step(self, x, targets):
+        loss = self.forward_backward(x, targets)
+        self.optimizer_step()
+        return loss
