@@ -93,18 +93,25 @@ int tnn_network_forward(tnn_network *net, const void *x, void *y, void *interm_f
 int tnn_network_backward(tnn_network *net, const void *dy, const void *interm_fwd, void *grads,
                          int grads_dtype, int pack_transpose, void *dx, void *interm_bwd,
                          size_t batch, void *stream);
+/* Trainer<T>::training_step - include/trainer.h:23-46 (forward_pass then backward_pass), with the L2
+ * loss of include/losses/l2.h:19-41 evaluated in between as the reference's training loops do:
+ * forward, loss, backward and the weight-gradient reduction in one pass.  x: batch x width bf16;
+ * targets: batch x n_targets fp32 (output columns >= n_targets compare against 0); the loss is
+ * normalised by batch * width.  grads as in tnn_network_backward; loss_sum (optional): one fp32.
+ * Where width and depth allow (all activations of a 128-row tile resident on the SM) this is a single
+ * kernel; otherwise the forward, loss and backward kernels run one after another on a workspace
+ * owned by the handle. */
+int tnn_network_train_step(tnn_network *net, const void *x, const float *targets, int n_targets,
+                           size_t batch, float loss_scale, void *grads, int grads_dtype,
+                           int pack_transpose, float *loss_sum, void *stream);
 /* Waits for `stream` and returns the kernels' status word in *status (0 = fine; non-zero = a
  * bounded device-side wait gave up, results are invalid).  No reference counterpart: the
  * reference kernels have no device-side waits. */
 int tnn_network_sync_status(tnn_network *net, int *status, void *stream);
-/* Selects a kernel variant for experiments (bit 0: hidden activations via TMEM in inference,
- * bit 1: MN-major weight operand).  Default 0.  No reference counterpart. */
+/* Selects a kernel variant for tuning experiments (bit 0: hidden activations through TMEM in
+ * inference, bit 1: MN-major weight operand, bit 2: fewer tiles in flight, bit 4: unfused training path).  Default 0.
+ * No reference counterpart. */
 int tnn_network_set_variant(tnn_network *net, int variant);
-
-/* Kernel-tuning aid: with enable != 0 the inference kernel's first CTA records (code, clock) pairs
- * per role into a device buffer; host_out (optional, n_words uint64) receives and clears it.
- * enable == 0 frees the buffer.  Synchronises the device.  No reference counterpart. */
-int tnn_network_debug_timeline(tnn_network *net, int enable, unsigned long long *host_out, size_t n_words);
 
 /* ------------------------------------------------------------------------------------------
  * Encoding: replaces tnn::EncodingModule<float> (include/tnn_api.h:306-488) and create_encoding

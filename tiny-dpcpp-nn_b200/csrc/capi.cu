@@ -100,8 +100,12 @@ struct tnn_network {
     __nv_bfloat16 *wimg = nullptr;   // swizzled operand images, rows = input feature
     __nv_bfloat16 *wimg_t = nullptr; // swizzled operand images, rows = output feature
     float *dw_slabs = nullptr;       // per-CTA weight-gradient partial sums
+    float *loss_partials = nullptr;  // per-CTA loss partial sums of the fused training kernel
     int *status = nullptr;
-    unsigned long long *prof = nullptr; // timeline buffer for kernel tuning (see tnn_network_debug_timeline)
+    // workspace of the unfused training path (grown on demand, like the reference's module workspaces)
+    __nv_bfloat16 *ws_interm = nullptr;
+    __nv_bfloat16 *ws_dy = nullptr;
+    size_t ws_batch = 0;
 
     int one_padded_input() const {
         // rows of the first matrix that can carry signal: the real inputs, plus (with bias) the
@@ -157,6 +161,7 @@ int tnn_network_create(int input_width, int output_width, int n_hidden_layers, i
     if (e == cudaSuccess) e = cudaMalloc(&n->wimg, bytes);
     if (e == cudaSuccess) e = cudaMalloc(&n->wimg_t, bytes);
     if (e == cudaSuccess) e = cudaMalloc(&n->dw_slabs, (size_t)n->n_sm * n->n_params * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&n->loss_partials, 1024 * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&n->status, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(n->packed, 0, bytes);
     if (e == cudaSuccess) e = cudaMemset(n->wimg, 0, bytes);
@@ -177,8 +182,10 @@ int tnn_network_destroy(tnn_network *n) {
     cudaFree(n->wimg);
     cudaFree(n->wimg_t);
     cudaFree(n->dw_slabs);
+    cudaFree(n->loss_partials);
+    cudaFree(n->ws_interm);
+    cudaFree(n->ws_dy);
     cudaFree(n->status);
-    cudaFree(n->prof);
     delete n;
     return 0;
 }
@@ -270,7 +277,6 @@ static int run_forward(tnn_network *n, const void *x, void *y, void *interm, siz
     p.n_sm = n->n_sm;
     p.status = n->status;
     p.stream = (cudaStream_t)stream;
-    p.prof = interm ? nullptr : n->prof;
     if (interm) // matrix 0 of the forward workspace is a copy of the input (kernel_esimd.h:601-605)
         TNN_CUDA(cudaMemcpyAsync(interm, x, batch * n->width * sizeof(__nv_bfloat16), cudaMemcpyDeviceToDevice, p.stream));
     cudaError_t e = tnn::launch_mlp_fwd(p);
@@ -340,30 +346,73 @@ int tnn_network_backward(tnn_network *n, const void *dy, const void *interm_fwd,
     TNN_GUARD_END
 }
 
+int tnn_network_train_step(tnn_network *n, const void *x, const float *targets, int n_targets, size_t batch,
+                           float loss_scale, void *grads, int grads_dtype, int pack_transpose, float *loss_sum,
+                           void *stream) {
+    TNN_GUARD_BEGIN
+    if (!n) return fail("network is null");
+    if (!grads) return fail("grads is null");
+    if (grads_dtype != TNN_DTYPE_BF16 && grads_dtype != TNN_DTYPE_FP32) return fail("grads must be bf16 or fp32");
+    if (batch == 0) return fail("batch_size == 0");
+    if (!x || !targets) return fail("x and targets are required");
+    if (batch % 8 != 0) return fail("Batch size is not divisible by 8.");
+    if (n_targets <= 0 || n_targets > n->width) return fail("n_targets must be in [1, width]");
+    if (loss_scale == 0.0f) return fail("loss_scale must not be 0");
+    cudaStream_t s = (cudaStream_t)stream;
+    float *gf = grads_dtype == TNN_DTYPE_FP32 ? (float *)grads : nullptr;
+    __nv_bfloat16 *gb = grads_dtype == TNN_DTYPE_BF16 ? (__nv_bfloat16 *)grads : nullptr;
+
+    if (!(n->variant & 16)) { // fused single-kernel path
+        tnn::TrainLaunch p{};
+        make_act_tmap(&p.tm_x, x, batch, n->width, 1);
+        p.wimg = n->wimg;
+        p.targets = targets;
+        p.n_targets = n_targets;
+        p.dw_partials = n->dw_slabs;
+        p.loss_partials = n->loss_partials;
+        p.batch = batch;
+        p.width = n->width;
+        p.n_mat = n->n_mat;
+        p.act = n->act;
+        p.out_act = n->out_act;
+        p.loss_scale = loss_scale;
+        p.n_sm = n->n_sm;
+        p.status = n->status;
+        p.stream = s;
+        p.prof = (n->variant & 32) ? reinterpret_cast<long long *>(n->loss_partials) : nullptr; // non-null = print cycle accounting
+        cudaError_t e = tnn::launch_mlp_train(p);
+        if (e == cudaSuccess) {
+            if (loss_sum) TNN_CUDA(tnn::launch_sum_partials(n->loss_partials, p.grid_out, loss_sum, s));
+            TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, p.grid_out, n->n_mat, n->width, pack_transpose, 1.0f, gf, gb, s));
+            return 0;
+        }
+        if (e != cudaErrorInvalidConfiguration) TNN_CUDA(e);
+        cudaGetLastError(); // the fused kernel does not cover this width / depth: use the three-kernel path
+    }
+    if (batch > n->ws_batch) {
+        TNN_CUDA(cudaStreamSynchronize(s));
+        cudaFree(n->ws_interm);
+        cudaFree(n->ws_dy);
+        n->ws_interm = n->ws_dy = nullptr;
+        n->ws_batch = 0;
+        TNN_CUDA(cudaMalloc(&n->ws_interm, (size_t)(n->n_mat + 1) * batch * n->width * sizeof(__nv_bfloat16)));
+        TNN_CUDA(cudaMalloc(&n->ws_dy, batch * n->width * sizeof(__nv_bfloat16)));
+        n->ws_batch = batch;
+    }
+    if (int rc = tnn_network_forward(n, x, nullptr, n->ws_interm, batch, stream)) return rc;
+    const __nv_bfloat16 *pred = n->ws_interm + (size_t)n->n_mat * batch * n->width;
+    if (int rc = tnn_l2_loss(pred, targets, n_targets, nullptr, n->ws_dy, batch, n->width, loss_scale, loss_sum, stream))
+        return rc;
+    return tnn_network_backward(n, n->ws_dy, n->ws_interm, grads, grads_dtype, pack_transpose, nullptr, nullptr, batch,
+                                stream);
+    TNN_GUARD_END
+}
+
 int tnn_network_sync_status(tnn_network *n, int *status, void *stream) {
     if (!n || !status) return fail("null argument");
     TNN_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     TNN_CUDA(cudaMemcpy(status, n->status, sizeof(int), cudaMemcpyDeviceToHost));
     if (*status != 0) TNN_CUDA(cudaMemset(n->status, 0, sizeof(int)));
-    return 0;
-}
-
-int tnn_network_debug_timeline(tnn_network *n, int enable, unsigned long long *host_out, size_t n_words) {
-    if (!n) return fail("network is null");
-    constexpr size_t kWords = 6 * 2048 * 2;
-    if (enable && !n->prof) {
-        TNN_CUDA(cudaMalloc(&n->prof, kWords * sizeof(unsigned long long)));
-        TNN_CUDA(cudaMemset(n->prof, 0, kWords * sizeof(unsigned long long)));
-    }
-    if (host_out && n->prof) {
-        TNN_CUDA(cudaDeviceSynchronize());
-        TNN_CUDA(cudaMemcpy(host_out, n->prof, std::min(n_words, kWords) * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
-        TNN_CUDA(cudaMemset(n->prof, 0, kWords * sizeof(unsigned long long)));
-    }
-    if (!enable && n->prof) {
-        cudaFree(n->prof);
-        n->prof = nullptr;
-    }
     return 0;
 }
 

@@ -182,6 +182,11 @@ __global__ void sum_partials_kernel(const float *__restrict__ partials, int n, f
     if (threadIdx.x == 0) *out = red[0];
 }
 
+cudaError_t launch_sum_partials(const float *partials, int n, float *out, cudaStream_t stream) {
+    sum_partials_kernel<<<1, 256, 0, stream>>>(partials, n, out);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_l2_loss(const __nv_bfloat16 *pred, const float *target, int n_targets, float *values,
                            __nv_bfloat16 *grads, size_t batch, int stride, float loss_scale, float *loss_partials,
                            int n_partials, float *loss_sum, cudaStream_t stream) {

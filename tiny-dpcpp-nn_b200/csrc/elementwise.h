@@ -16,6 +16,7 @@ cudaError_t launch_identity_fwd(const float *x, void *out, int out_bf16, size_t 
 cudaError_t launch_l2_loss(const __nv_bfloat16 *pred, const float *target, int n_targets, float *values,
                            __nv_bfloat16 *grads, size_t batch, int stride, float loss_scale, float *loss_partials,
                            int n_partials, float *loss_sum, cudaStream_t stream);
+cudaError_t launch_sum_partials(const float *partials, int n, float *out, cudaStream_t stream);
 cudaError_t launch_adam(float *p, float *m, float *v, const float *g, size_t n, float grad_scale, int step, float lr,
                         float b1, float b2, float eps, __nv_bfloat16 *p_bf16, cudaStream_t stream);
 cudaError_t launch_f32_to_bf16(const float *a, __nv_bfloat16 *b, size_t n, cudaStream_t s);

@@ -236,17 +236,20 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                     break;
                 }
                 const uint8_t *ybuf = smem + S::AR + slot * T::ACT_BYTES;
+                dispatch_act(out_act, [&](auto tag) {
+                    constexpr int ACT = decltype(tag)::value;
 #pragma unroll
-                for (int c = 0; c < W; c += 8) {
-                    const int off = (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES + T::chunk_off(row, (c % T::ATOM_COLS) / 8);
-                    uint4 d = *reinterpret_cast<const uint4 *>(dybuf + off);
-                    const uint4 y = *reinterpret_cast<const uint4 *>(ybuf + off);
-                    d.x = act_bwd_pack(out_act, ptx::bf16lo_to_f32(d.x), ptx::bf16hi_to_f32(d.x), y.x);
-                    d.y = act_bwd_pack(out_act, ptx::bf16lo_to_f32(d.y), ptx::bf16hi_to_f32(d.y), y.y);
-                    d.z = act_bwd_pack(out_act, ptx::bf16lo_to_f32(d.z), ptx::bf16hi_to_f32(d.z), y.z);
-                    d.w = act_bwd_pack(out_act, ptx::bf16lo_to_f32(d.w), ptx::bf16hi_to_f32(d.w), y.w);
-                    *reinterpret_cast<uint4 *>(dybuf + off) = d;
-                }
+                    for (int c = 0; c < W; c += 8) {
+                        const int off = (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES + T::chunk_off(row, (c % T::ATOM_COLS) / 8);
+                        uint4 d = *reinterpret_cast<const uint4 *>(dybuf + off);
+                        const uint4 y = *reinterpret_cast<const uint4 *>(ybuf + off);
+                        d.x = act_bwd_pack_t<ACT>(ptx::bf16lo_to_f32(d.x), ptx::bf16hi_to_f32(d.x), y.x);
+                        d.y = act_bwd_pack_t<ACT>(ptx::bf16lo_to_f32(d.y), ptx::bf16hi_to_f32(d.y), y.y);
+                        d.z = act_bwd_pack_t<ACT>(ptx::bf16lo_to_f32(d.z), ptx::bf16hi_to_f32(d.z), y.z);
+                        d.w = act_bwd_pack_t<ACT>(ptx::bf16lo_to_f32(d.w), ptx::bf16hi_to_f32(d.w), y.w);
+                        *reinterpret_cast<uint4 *>(dybuf + off) = d;
+                    }
+                });
                 ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(&bars.d_ready);
                 ptx::mbar_arrive(&bars.a_empty[slot]);
@@ -303,24 +306,26 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                             ptx::tmem_ld16(acc_tmem + lane_addr + i * CW, v[i]);
                     }
                     ptx::tmem_ld_wait();
-                    const int a = (l > 0) ? act : (int)ACT_NONE;
+                    dispatch_act((l > 0) ? act : (int)ACT_NONE, [&](auto tag) {
+                        constexpr int ACT = decltype(tag)::value;
 #pragma unroll
-                    for (int i = 0; i < NLD; ++i) {
+                        for (int i = 0; i < NLD; ++i) {
 #pragma unroll
-                        for (int ch = 0; ch < CW / 8; ++ch) {
-                            const int c = i * CW + ch * 8;
-                            const int off =
-                                (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES + T::chunk_off(row, (c % T::ATOM_COLS) / 8);
-                            uint4 f = make_uint4(0, 0, 0, 0);
-                            if (need_a) f = *reinterpret_cast<const uint4 *>(abuf + off);
-                            uint4 o;
-                            o.x = act_bwd_pack(a, __uint_as_float(v[i][ch * 8 + 0]), __uint_as_float(v[i][ch * 8 + 1]), f.x);
-                            o.y = act_bwd_pack(a, __uint_as_float(v[i][ch * 8 + 2]), __uint_as_float(v[i][ch * 8 + 3]), f.y);
-                            o.z = act_bwd_pack(a, __uint_as_float(v[i][ch * 8 + 4]), __uint_as_float(v[i][ch * 8 + 5]), f.z);
-                            o.w = act_bwd_pack(a, __uint_as_float(v[i][ch * 8 + 6]), __uint_as_float(v[i][ch * 8 + 7]), f.w);
-                            *reinterpret_cast<uint4 *>(dst + off) = o;
+                            for (int ch = 0; ch < CW / 8; ++ch) {
+                                const int c = i * CW + ch * 8;
+                                const int off =
+                                    (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES + T::chunk_off(row, (c % T::ATOM_COLS) / 8);
+                                uint4 f = make_uint4(0, 0, 0, 0);
+                                if constexpr (ACT != ACT_NONE) f = *reinterpret_cast<const uint4 *>(abuf + off);
+                                uint4 o;
+                                o.x = act_bwd_pack_t<ACT>(__uint_as_float(v[i][ch * 8 + 0]), __uint_as_float(v[i][ch * 8 + 1]), f.x);
+                                o.y = act_bwd_pack_t<ACT>(__uint_as_float(v[i][ch * 8 + 2]), __uint_as_float(v[i][ch * 8 + 3]), f.y);
+                                o.z = act_bwd_pack_t<ACT>(__uint_as_float(v[i][ch * 8 + 4]), __uint_as_float(v[i][ch * 8 + 5]), f.z);
+                                o.w = act_bwd_pack_t<ACT>(__uint_as_float(v[i][ch * 8 + 6]), __uint_as_float(v[i][ch * 8 + 7]), f.w);
+                                *reinterpret_cast<uint4 *>(dst + off) = o;
+                            }
                         }
-                    }
+                    });
                     ptx::fence_proxy_async_smem();
                     ptx::tc_fence_before_sync();
                     ptx::mbar_arrive(&bars.d_ready);

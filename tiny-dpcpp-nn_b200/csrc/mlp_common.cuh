@@ -109,6 +109,36 @@ template <int W> struct Tile {
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
 
+// Compile-time activation tags.  The epilogues select the activation ONCE per tile step with a
+// uniform branch and then run a straight-line body specialised for it: a run-time `act` inside the
+// per-element code makes the compiler evaluate every activation (including the exp and the division
+// of the sigmoid) for every element and select afterwards, which multiplied the epilogue's length.
+template <int A> struct ActTag { static constexpr int value = A; };
+template <class F> __device__ __forceinline__ void dispatch_act(int act, F &&f) {
+    if (act == ACT_RELU)
+        f(ActTag<ACT_RELU>{});
+    else if (act == ACT_SIGMOID)
+        f(ActTag<ACT_SIGMOID>{});
+    else
+        f(ActTag<ACT_NONE>{});
+}
+template <int A> __device__ __forceinline__ uint32_t act_pack_t(float lo, float hi) {
+    if constexpr (A == ACT_RELU) return ptx::pack_bf16x2_relu(lo, hi);
+    if constexpr (A == ACT_SIGMOID) return ptx::pack_bf16x2(1.0f / (1.0f + __expf(-lo)), 1.0f / (1.0f + __expf(-hi)));
+    return ptx::pack_bf16x2(lo, hi);
+}
+template <int A> __device__ __forceinline__ uint32_t act_bwd_pack_t(float lo, float hi, uint32_t fwd) {
+    if constexpr (A == ACT_RELU) {
+        if (!(ptx::bf16lo_to_f32(fwd) > 0.0f)) lo = 0.0f;
+        if (!(ptx::bf16hi_to_f32(fwd) > 0.0f)) hi = 0.0f;
+    } else if constexpr (A == ACT_SIGMOID) {
+        const float sl = ptx::bf16lo_to_f32(fwd), sh = ptx::bf16hi_to_f32(fwd);
+        lo *= sl * (1.0f - sl);
+        hi *= sh * (1.0f - sh);
+    }
+    return ptx::pack_bf16x2(lo, hi);
+}
+
 // Forward activation on two fp32 accumulators, rounded to a bf16 pair.  The reference rounds
 // to the storage type first and then clamps (kernel_esimd.h:443-458); max(bf16(x), 0) and
 // bf16(max(x, 0)) are the same value.  Sigmoid is evaluated in fp32 and then rounded.

@@ -4,16 +4,21 @@
 // (include/network/kernel_esimd.h:565-640): y = act_out(... act(act(x W0) W1) ... WL), all
 // matrices W x W, bf16 operands, fp32 accumulation, rounding to bf16 after every layer.
 //
-// One persistent CTA per SM walks over 128-row batch tiles.  Roles:
-//   warp 0      : TMA producer - stages the weights once, then streams input tiles
-//   warp 1      : MMA issuer   - owns TMEM, issues tcgen05.mma for every (tile, layer)
-//   warps 2...  : NSLOT epilogue groups of 4 warps; group g owns pipeline slot g
-// A slot is one tile in flight: its input buffer, two activation buffers and one fp32
-// accumulator of W TMEM columns.  Per layer the group pulls the accumulator out of TMEM,
-// applies the activation, rounds to bf16 and writes the next layer's A operand straight
-// back to swizzled shared memory (or, with TMEM_A, back to TMEM), so activations never
-// leave the SM.  With STORE_ALL every layer's activation is also written to global memory
-// by TMA for a later backward pass.
+// One persistent CTA per SM walks over 128-row batch tiles with NSLOT tiles in flight.  Roles:
+//   warp 0            : TMA producer - stages the weights once, then streams input tiles
+//   warps 1..NSLOT    : one MMA issuer per slot (a single elected lane issues tcgen05.mma)
+//   then NSLOT groups : 4 epilogue warps per slot
+// A slot is one tile in flight: its input buffer, its activation buffer(s) and one fp32
+// accumulator of W TMEM columns.  Per layer the slot's epilogue group pulls the accumulator out
+// of TMEM, applies the activation, rounds to bf16 and writes the next layer's A operand straight
+// back to swizzled shared memory (or, with TMEM_A, back to TMEM), so activations never leave the
+// SM.  With STORE_ALL every layer's activation is also written to global memory by TMA for a
+// later backward pass.
+//
+// The layer-to-layer chain of one tile is strictly serial (MMA -> epilogue -> MMA ...), and a
+// single thread's dependent instructions cost several cycles each, so throughput comes from
+// running the chains of several slots side by side: every slot has its own issuer warp and its
+// own epilogue group, and nothing but the tensor pipe and shared memory is shared between them.
 #include "mlp_common.cuh"
 #include "mlp_launch.h"
 
@@ -24,49 +29,37 @@ template <int W, int NSLOT, bool TMEM_A, bool STORE_ALL> struct FwdSmem {
     // activation buffers per slot: two (ping-pong) when every layer is also streamed out by TMA,
     // one when the next layer's MMA is the only reader
     static constexpr int NABUF = STORE_ALL ? 2 : 1;
-    static constexpr int XBUF = 0;                                     // NSLOT input tiles
-    static constexpr int ABUF = XBUF + NSLOT * T::ACT_BYTES;           // NSLOT x NABUF activation tiles
-    static constexpr int WBUF = ABUF + NSLOT * NABUF * T::ACT_BYTES;   // (L+1) weight tiles follow
+    static constexpr int XBUF = 0;                                   // NSLOT input tiles
+    static constexpr int ABUF = XBUF + NSLOT * T::ACT_BYTES;         // NSLOT x NABUF activation tiles
+    static constexpr int WBUF = ABUF + NSLOT * NABUF * T::ACT_BYTES; // (L+1) weight tiles follow
     static constexpr int tmem_cols_needed = NSLOT * (W + (TMEM_A ? W / 2 : 0));
     static constexpr int tmem_cols =
         tmem_cols_needed <= 32 ? 32 : tmem_cols_needed <= 64 ? 64 : tmem_cols_needed <= 128 ? 128
                                                               : tmem_cols_needed <= 256 ? 256 : 512;
     static_assert(tmem_cols_needed <= 512, "TMEM overflow");
+    static constexpr int THREADS = 32 * (1 + NSLOT) + 128 * NSLOT;
 };
+
+constexpr int kMaxSlots = 4;
 
 struct FwdBarriers {
     uint64_t w_full;
-    uint64_t x_full[4];
-    uint64_t x_empty[4];
-    uint64_t a_ready[4];
-    uint64_t acc_full[4];
+    uint64_t x_full[kMaxSlots];
+    uint64_t x_empty[kMaxSlots];
+    uint64_t a_ready[kMaxSlots];
+    uint64_t acc_full[kMaxSlots];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
 
-// Timeline probe for tuning: CTA 0 appends (code, clock64) pairs per role into `prof`
-// (region r starts at prof + r * 2 * kProfRegion).  Compiled in only for PROFILE instantiations.
-constexpr int kProfRegion = 2048;
-#define TNN_PROF(region, code)                                                                                         \
-    do {                                                                                                               \
-        if constexpr (PROFILE) {                                                                                       \
-            if (blockIdx.x == 0 && prof && prof_n < kProfRegion) {                                                     \
-                prof[((region) * kProfRegion + prof_n) * 2] = (unsigned long long)(code);                             \
-                prof[((region) * kProfRegion + prof_n) * 2 + 1] = (unsigned long long)clock64();                      \
-                ++prof_n;                                                                                              \
-            }                                                                                                          \
-        }                                                                                                              \
-    } while (0)
-
-template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN_MAJOR, bool PROFILE = false>
-__global__ void __launch_bounds__(64 + 128 * NSLOT, 1)
+template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN_MAJOR>
+__global__ void __launch_bounds__(FwdSmem<W, NSLOT, TMEM_A, STORE_ALL>::THREADS, 1)
 mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                const __grid_constant__ CUtensorMap tm_interm, const __nv_bfloat16 *__restrict__ wimg,
-               int n_tiles, int n_mat, int act, int out_act, int write_y, int *status,
-               unsigned long long *prof = nullptr) {
-    [[maybe_unused]] int prof_n = 0;
+               int n_tiles, int n_mat, int act, int out_act, int write_y, int *status) {
     using T = Tile<W>;
     using S = FwdSmem<W, NSLOT, TMEM_A, STORE_ALL>;
+    static_assert(NSLOT <= kMaxSlots, "too many slots");
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment (swizzle span)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -78,7 +71,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     const uint32_t smem_base = ptx::smem_u32(smem);
     volatile uint32_t *abort_flag = &bars.abort_flag;
 
-    // tiles handled by this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
+    // tiles handled by this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; local tile j runs in slot j % NSLOT
     const int my_tiles = (n_tiles > (int)blockIdx.x) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
     if (threadIdx.x == 0) {
@@ -123,143 +116,144 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                 for (int a = 0; a < T::KATOMS; ++a)
                     ptx::tma_load_2d(smem + S::XBUF + s * T::ACT_BYTES + a * T::ACT_ATOM_BYTES, &tm_x,
                                      a * T::ATOM_COLS, tile * T::TM, &bars.x_full[s]);
-                TNN_PROF(0, (j << 8) | 1);
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0 && my_tiles > 0) {
+    } else if (warp <= NSLOT) {
+        // ------------------------------------------------------------ MMA issuer of slot s
+        const int s = warp - 1;
+        if (lane == 0 && my_tiles > s) {
             constexpr uint32_t idesc = ptx::make_idesc_bf16(128, W, 0, B_MN_MAJOR ? 1 : 0);
-            // base descriptors, stepped with constant adds inside the loop
-            const uint64_t x_desc0 = T::kdesc_base(smem_base + S::XBUF);
-            const uint64_t a_desc0 = T::kdesc_base(smem_base + S::ABUF);
+            // every descriptor this thread will ever need, as bases that are stepped by constants
+            const uint64_t x_desc = T::kdesc_base(smem_base + S::XBUF + s * T::ACT_BYTES);
+            const uint64_t a_desc0 = T::kdesc_base(smem_base + S::ABUF + s * S::NABUF * T::ACT_BYTES);
             const uint64_t w_desc0 = B_MN_MAJOR ? T::mndesc_base(smem_base + S::WBUF, T::WGT_ATOM_BYTES)
                                                 : T::kdesc_base(smem_base + S::WBUF);
+            const uint32_t d_tmem = tmem_base + s * W;
+            [[maybe_unused]] const uint32_t a_tmem = tmem_base + NSLOT * W + s * (W / 2);
+            uint64_t *const a_ready = &bars.a_ready[s];
+            uint64_t *const acc_full = &bars.acc_full[s];
             bool ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
             if (!ok) atomicExch(status, KS_TIMEOUT_WEIGHTS);
-            const int rounds = (my_tiles + NSLOT - 1) / NSLOT;
-            for (int t = 0; ok && t < rounds; ++t) {
-                for (int l = 0; ok && l <= L; ++l) {
-                    for (int s = 0; s < NSLOT; ++s) {
-                        if (t * NSLOT + s >= my_tiles) break;
-                        // a_ready completion that must precede this MMA: the epilogue of
-                        // (t, l-1), or for l == 0 the last epilogue of the previous tile.
-                        const int n = t * n_mat + l - 1;
-                        TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 0);
-                        if (l == 0 && !ptx::mbar_wait(&bars.x_full[s], t & 1, abort_flag)) ok = false;
-                        if (ok && n >= 0 && !ptx::mbar_wait(&bars.a_ready[s], n & 1, abort_flag)) ok = false;
-                        if (!ok) {
-                            atomicExch(status, KS_TIMEOUT_MMA | (l << 4) | s);
-                            break;
-                        }
-                        ptx::tc_fence_after_sync();
-                        TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 1);
-                        const uint32_t d_tmem = tmem_base + s * W;
-                        const uint64_t w_desc = w_desc0 + (uint64_t)(l * T::WGT_UNITS);
-                        if (TMEM_A && l > 0) {
-                            T::template issue_chain_ts<B_MN_MAJOR>(d_tmem, tmem_base + NSLOT * W + s * (W / 2), w_desc, idesc);
-                        } else {
-                            const uint64_t a_desc =
-                                (l == 0) ? x_desc0 + (uint64_t)(s * T::ACT_UNITS)
-                                         : a_desc0 + (uint64_t)((s * S::NABUF + ((l - 1) & (S::NABUF - 1))) * T::ACT_UNITS);
-                            if constexpr (PROFILE) {
-                                ptx::mma_ss(d_tmem, a_desc, w_desc, idesc, 0u);
-                                TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 5);
-                                ptx::mma_ss(d_tmem, a_desc + 2, w_desc + 2, idesc, 1u);
-                                TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 6);
-                                ptx::mma_ss(d_tmem, a_desc + 4, w_desc + 4, idesc, 1u);
-                                ptx::mma_ss(d_tmem, a_desc + 6, w_desc + 6, idesc, 1u);
-                                TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 7);
-                            } else {
-                                T::template issue_chain<B_MN_MAJOR>(d_tmem, a_desc, w_desc, idesc);
-                            }
-                        }
-                        ptx::mma_commit(&bars.acc_full[s]);
-                        TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 8);
-                        if (l == 0) ptx::mma_commit(&bars.x_empty[s]);
-                        TNN_PROF(1, (t << 16) | (l << 8) | (s << 4) | 2);
+            uint32_t ar_parity = 0; // parity of the next a_ready completion to wait for
+            uint32_t xf_parity = 0;
+            const int my_slot_tiles = (my_tiles - s + NSLOT - 1) / NSLOT;
+            for (int t = 0; ok && t < my_slot_tiles; ++t) {
+                // layer 0: needs the input tile and (from the second tile on) the drained accumulator
+                ok = ptx::mbar_wait(&bars.x_full[s], xf_parity, abort_flag);
+                xf_parity ^= 1u;
+                if (ok && t > 0) {
+                    ok = ptx::mbar_wait(a_ready, ar_parity, abort_flag);
+                    ar_parity ^= 1u;
+                }
+                if (!ok) {
+                    atomicExch(status, KS_TIMEOUT_MMA | s);
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                T::template issue_chain<B_MN_MAJOR>(d_tmem, x_desc, w_desc0, idesc);
+                ptx::mma_commit(acc_full);
+                ptx::mma_commit(&bars.x_empty[s]);
+                uint64_t w_desc = w_desc0;
+                for (int l = 1; l <= L; ++l) {
+                    w_desc += T::WGT_UNITS;
+                    if (!ptx::mbar_wait(a_ready, ar_parity, abort_flag)) {
+                        atomicExch(status, KS_TIMEOUT_MMA | (l << 4) | s);
+                        ok = false;
+                        break;
                     }
+                    ar_parity ^= 1u;
+                    ptx::tc_fence_after_sync();
+                    if constexpr (TMEM_A) {
+                        T::template issue_chain_ts<B_MN_MAJOR>(d_tmem, a_tmem, w_desc, idesc);
+                    } else {
+                        const uint64_t a_desc = a_desc0 + (uint64_t)(((l - 1) & (S::NABUF - 1)) * T::ACT_UNITS);
+                        T::template issue_chain<B_MN_MAJOR>(d_tmem, a_desc, w_desc, idesc);
+                    }
+                    ptx::mma_commit(acc_full);
                 }
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue groups
-        const int g = (warp - 2) >> 2;   // slot owned by this group
-        const int quad = warp & 3;       // TMEM lane quarter this warp may touch
-        const int row = quad * 32 + lane; // tile row owned by this thread
-        const bool leader = ((warp - 2) & 3) == 0 && lane == 0;
-        const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-        const int s = g;
+        // ------------------------------------------------------------ epilogue group of slot s
+        const int ew = warp - (1 + NSLOT);  // epilogue warp index
+        const int s = ew >> 2;              // slot owned by this group
+        const int quad = warp & 3;          // TMEM lane quarter this warp may touch
+        const int row = quad * 32 + lane;   // tile row owned by this thread
+        const bool leader = (ew & 3) == 0 && lane == 0;
+        const uint32_t acc_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + s * W;
+        [[maybe_unused]] const uint32_t a_tmem = tmem_base + ((uint32_t)(quad * 32) << 16) + NSLOT * W + s * (W / 2);
+        uint64_t *const a_ready = &bars.a_ready[s];
+        uint64_t *const acc_full = &bars.acc_full[s];
+        uint32_t af_parity = 0;
         bool ok = true;
-        for (int t = 0; ok && t * NSLOT + s < my_tiles; ++t) {
-            const int tile = blockIdx.x + (t * NSLOT + s) * gridDim.x;
+        for (int j = s; ok && j < my_tiles; j += NSLOT) {
+            const int tile = blockIdx.x + j * gridDim.x;
             for (int l = 0; l <= L; ++l) {
-                const int n = t * n_mat + l;
                 // the verdict must be warp-uniform: the TMEM accesses below are .aligned
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars.acc_full[s], n & 1, abort_flag))) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(acc_full, af_parity, abort_flag))) {
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | (l << 4) | s);
                     ok = false;
                     break;
                 }
+                af_parity ^= 1u;
                 ptx::tc_fence_after_sync();
-                if (threadIdx.x == 64 + 128 * g) TNN_PROF(2 + g, (t << 16) | (l << 8) | 1);
                 const int a = (l == L) ? out_act : act;
                 const bool to_tmem = TMEM_A && l < L;
                 uint8_t *abuf = smem + S::ABUF + (s * S::NABUF + (l & (S::NABUF - 1))) * T::ACT_BYTES;
-                if (!to_tmem && (STORE_ALL || TMEM_A || l == 0)) {
-                    // (single-buffer modes: only the previous tile's output store can still be reading it)
-                    // the buffer about to be overwritten may still be read by an earlier TMA store
-                    if (leader) {
-                        if (STORE_ALL && l > 0)
-                            ptx::tma_wait_group_read<1>();
-                        else
-                            ptx::tma_wait_group_read<0>();
-                    }
-                    ptx::named_bar_sync(1 + g, 128);
-                }
                 constexpr int CW = (W >= 32) ? 32 : 16; // columns per TMEM load
                 constexpr int NLD = W / CW;
                 uint32_t v[NLD][CW];
 #pragma unroll
                 for (int i = 0; i < NLD; ++i) {
                     if constexpr (CW == 32)
-                        ptx::tmem_ld32(tmem_base + lane_addr + s * W + i * CW, v[i]);
+                        ptx::tmem_ld32(acc_addr + i * CW, v[i]);
                     else
-                        ptx::tmem_ld16(tmem_base + lane_addr + s * W + i * CW, v[i]);
+                        ptx::tmem_ld16(acc_addr + i * CW, v[i]);
+                }
+                if (!to_tmem && (STORE_ALL || TMEM_A || l == 0)) {
+                    // the buffer about to be overwritten may still be read by an earlier TMA store: with
+                    // per-layer stores the newest one reads the other ping-pong buffer, otherwise only the
+                    // previous tile's output store can be pending
+                    if (leader) {
+                        if (STORE_ALL && l > 0)
+                            ptx::tma_wait_group_read<1>();
+                        else
+                            ptx::tma_wait_group_read<0>();
+                    }
+                    ptx::named_bar_sync(1 + s, 128);
                 }
                 ptx::tmem_ld_wait();
+                dispatch_act(a, [&](auto tag) {
+                    constexpr int ACT = decltype(tag)::value;
 #pragma unroll
-                for (int i = 0; i < NLD; ++i) {
-                    const int c0 = i * CW;
-                    uint32_t p[CW / 2];
+                    for (int i = 0; i < NLD; ++i) {
+                        const int c0 = i * CW;
+                        uint32_t p[CW / 2];
 #pragma unroll
-                    for (int j = 0; j < CW / 2; ++j)
-                        p[j] = act_pack(a, __uint_as_float(v[i][2 * j]), __uint_as_float(v[i][2 * j + 1]));
-                    if (to_tmem) {
-                        if constexpr (CW == 32) {
-                            ptx::tmem_st16(tmem_base + lane_addr + NSLOT * W + s * (W / 2) + c0 / 2, p);
-                        }
-                    } else {
+                        for (int q = 0; q < CW / 2; ++q)
+                            p[q] = act_pack_t<ACT>(__uint_as_float(v[i][2 * q]), __uint_as_float(v[i][2 * q + 1]));
+                        if (to_tmem) {
+                            if constexpr (CW == 32) ptx::tmem_st16(a_tmem + c0 / 2, p);
+                        } else {
 #pragma unroll
-                        for (int ch = 0; ch < CW / 8; ++ch) {
-                            const int c = c0 + ch * 8;
-                            uint8_t *dst = abuf + (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES +
-                                           T::chunk_off(row, (c % T::ATOM_COLS) / 8);
-                            *reinterpret_cast<uint4 *>(dst) =
-                                make_uint4(p[ch * 4], p[ch * 4 + 1], p[ch * 4 + 2], p[ch * 4 + 3]);
+                            for (int ch = 0; ch < CW / 8; ++ch) {
+                                const int c = c0 + ch * 8;
+                                uint8_t *dst = abuf + (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES +
+                                               T::chunk_off(row, (c % T::ATOM_COLS) / 8);
+                                *reinterpret_cast<uint4 *>(dst) =
+                                    make_uint4(p[ch * 4], p[ch * 4 + 1], p[ch * 4 + 2], p[ch * 4 + 3]);
+                            }
                         }
                     }
-                }
-                if (threadIdx.x == 64 + 128 * g) TNN_PROF(2 + g, (t << 16) | (l << 8) | 2);
+                });
                 if (to_tmem)
                     ptx::tmem_st_wait();
                 else
                     ptx::fence_proxy_async_smem();
                 ptx::tc_fence_before_sync();
-                ptx::mbar_arrive(&bars.a_ready[s]);
-                if (threadIdx.x == 64 + 128 * g) TNN_PROF(2 + g, (t << 16) | (l << 8) | 3);
+                ptx::mbar_arrive(a_ready);
                 if (!to_tmem && (STORE_ALL || l == L)) {
-                    ptx::named_bar_sync(1 + g, 128);
+                    ptx::named_bar_sync(1 + s, 128);
                     if (leader) {
                         for (int at = 0; at < T::KATOMS; ++at) {
                             if (STORE_ALL)
@@ -292,41 +286,43 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
 }
 
 // ---------------------------------------------------------------------- host side
-template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN, bool PROFILE = false>
+template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN>
 static cudaError_t launch_variant(const FwdLaunch &p) {
     using T = Tile<W>;
     using S = FwdSmem<W, NSLOT, TMEM_A, STORE_ALL>;
     const size_t smem = (size_t)S::WBUF + (size_t)p.n_mat * T::WGT_BYTES + 1024;
     if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
-    auto kern = mlp_fwd_kernel<W, NSLOT, STORE_ALL, TMEM_A, B_MN, PROFILE>;
+    auto kern = mlp_fwd_kernel<W, NSLOT, STORE_ALL, TMEM_A, B_MN>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
     const int grid = n_tiles < p.n_sm ? n_tiles : p.n_sm;
     if (grid == 0) return cudaSuccess;
-    kern<<<grid, 64 + 128 * NSLOT, smem, p.stream>>>(p.tm_x, p.tm_y, p.tm_interm,
-                                                    B_MN ? p.wimg : p.wimg_t, n_tiles, p.n_mat, p.act, p.out_act,
-                                                    p.write_y, p.status, p.prof);
+    kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, p.tm_y, p.tm_interm, B_MN ? p.wimg : p.wimg_t, n_tiles, p.n_mat,
+                                               p.act, p.out_act, p.write_y, p.status);
     return cudaGetLastError();
 }
 
 template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
-    // variant bits: 1 = keep hidden activations in TMEM (inference only), 2 = MN-major weights
+    // variant bits (tuning): 1 = hidden activations through TMEM (inference only), 2 = MN-major weight
+    // operand, 4 = two instead of four tiles in flight
     if (p.store_all) {
-        return (p.variant & 2) ? launch_variant<W, 2, true, false, true>(p) : launch_variant<W, 2, true, false, false>(p);
+        cudaError_t e = cudaErrorInvalidConfiguration;
+        if (!(p.variant & 4)) e = launch_variant<W, 3, true, false, false>(p);
+        if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, true, false, false>(p);
+        return e;
     }
-    if constexpr (W == 64) {
-        if (p.prof) return launch_variant<W, 2, false, false, false, true>(p);
-    }
-    if constexpr (W <= 64) {
-        if (p.variant & 8) return launch_variant<W, 4, false, false, false>(p); // four tiles in flight per CTA
-    }
+    if (p.variant & 2) return launch_variant<W, 2, false, false, true>(p);
     if constexpr (W >= 32) {
         if (p.variant & 1)
-            return (p.variant & 2) ? launch_variant<W, 2, false, true, true>(p)
-                                   : launch_variant<W, 2, false, true, false>(p);
+            return (p.variant & 4) ? launch_variant<W, 2, false, true, false>(p)
+                                   : launch_variant<W, 4, false, true, false>(p);
     }
-    return (p.variant & 2) ? launch_variant<W, 2, false, false, true>(p) : launch_variant<W, 2, false, false, false>(p);
+    if (p.variant & 8) return launch_variant<W, 3, false, false, false>(p);
+    cudaError_t e = cudaErrorInvalidConfiguration;
+    if (!(p.variant & 4)) e = launch_variant<W, 4, false, false, false>(p);
+    if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, false, false, false>(p);
+    return e;
 }
 
 cudaError_t launch_mlp_fwd(const FwdLaunch &p) {

@@ -24,7 +24,6 @@ struct FwdLaunch {
     int n_sm;
     int *status;
     cudaStream_t stream;
-    unsigned long long *prof; // optional timeline buffer (tuning builds only), else nullptr
 };
 cudaError_t launch_mlp_fwd(const FwdLaunch &p);
 
@@ -49,5 +48,26 @@ struct BwdLaunch {
     int grid_out; // number of partial slabs written (set by the launcher)
 };
 cudaError_t launch_mlp_bwd(BwdLaunch &p);
+
+struct TrainLaunch {
+    CUtensorMap tm_x;       // [batch][W] bf16 input
+    const __nv_bfloat16 *wimg;
+    const float *targets;   // [batch][n_targets] fp32
+    int n_targets;
+    float *dw_partials;     // [grid][L+1][W][W] fp32, layout (out, in)
+    float *loss_partials;   // [grid] fp32
+    size_t batch;
+    int width;
+    int n_mat;
+    int act, out_act;
+    float loss_scale;
+    int n_sm;
+    int *status;
+    cudaStream_t stream;
+    int grid_out;
+    long long *prof; // cycle-accounting buffer of tuning builds, normally nullptr
+};
+// cudaErrorInvalidConfiguration when the network does not fit the on-chip budget of the fused kernel.
+cudaError_t launch_mlp_train(TrainLaunch &p);
 
 } // namespace tnn

@@ -49,6 +49,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred P;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+                 "selp.b32 %0, 1, 0, P;\n\t}"
+                 : "=r"(ok)
+                 : "r"(smem_u32(bar)), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
+
 // Spin budget of one bounded wait.  try_wait itself blocks for a hardware-defined
 // slice, so this is on the order of a second before the kernel gives up.
 constexpr uint32_t kSpinLimit = 1u << 20;
@@ -59,6 +70,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     for (uint32_t it = 0; it < kSpinLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 63u && *abort_flag) return false;
+    }
+    *abort_flag = 1u;
+    return false;
+}
+
+// Same contract, but polls without letting the hardware suspend the thread: lower wake-up latency for
+// the few threads that sit on the layer-to-layer critical path.
+constexpr uint32_t kBusySpinLimit = 1u << 26;
+__device__ __forceinline__ bool mbar_wait_busy(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag) {
+    for (uint32_t it = 0; it < kBusySpinLimit; ++it) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((it & 1023u) == 1023u && *abort_flag) return false;
     }
     *abort_flag = 1u;
     return false;
@@ -209,6 +232,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
                    "=r"(r[15])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr)
                  : "memory");
 }

@@ -38,9 +38,10 @@ _SIGNATURES = {
     "tnn_network_inference": (_c.c_int, [_vp, _vp, _vp, _c.c_size_t, _vp]),
     "tnn_network_forward": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_size_t, _vp]),
     "tnn_network_backward": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _vp, _vp, _c.c_size_t, _vp]),
+    "tnn_network_train_step": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _c.c_size_t, _c.c_float, _vp, _c.c_int, _c.c_int,
+                                          _vp, _vp]),
     "tnn_network_sync_status": (_c.c_int, [_vp, _c.POINTER(_c.c_int), _vp]),
     "tnn_network_set_variant": (_c.c_int, [_vp, _c.c_int]),
-    "tnn_network_debug_timeline": (_c.c_int, [_vp, _c.c_int, _vp, _c.c_size_t]),
     "tnn_encoding_create": (_c.c_int, [_c.c_char_p, _c.c_int, _c.POINTER(_vp)]),
     "tnn_encoding_destroy": (_c.c_int, [_vp]),
     "tnn_encoding_n_params": (_c.c_size_t, [_vp]),

@@ -28,8 +28,6 @@ class Trainer:
         self.v = torch.zeros(n, dtype=torch.float32, device="cuda")
         self.grads = torch.zeros(n, dtype=torch.float32, device="cuda")
         self.step = 0
-        self._interm = None
-        self._dy = None
         self._loss = torch.zeros(1, dtype=torch.float32, device="cuda")
 
     def set_master_params(self, packed_fp32):
@@ -38,19 +36,12 @@ class Trainer:
 
     def forward_backward(self, x, targets):
         """x: batch x width bf16, targets: batch x n_targets fp32.  Leaves the loss sum in self._loss
-        and the (packed, transposed) fp32 gradient of the mean loss in self.grads."""
+        and the (packed, transposed) fp32 gradient of the mean loss in self.grads.  One call into the
+        library: forward, L2 loss, backward and the weight-gradient reduction are fused."""
         net, lib = self.net, _lib.load()
-        batch = x.shape[0]
-        if self._interm is None or self._interm.shape[1] != batch:
-            self._interm = torch.empty((net.n_mat + 1, batch, net.width), dtype=torch.bfloat16, device="cuda")
-            self._dy = torch.empty((batch, net.width), dtype=torch.bfloat16, device="cuda")
-        s = _lib.stream_ptr()
-        _lib.check(lib.tnn_network_forward(net._h, _lib.dptr(x), None, _lib.dptr(self._interm), batch, s))
-        pred = self._interm[net.n_mat]
-        _lib.check(lib.tnn_l2_loss(_lib.dptr(pred), _lib.dptr(targets), targets.shape[1], None, _lib.dptr(self._dy),
-                                   batch, net.width, float(self.loss_scale), _lib.dptr(self._loss), s))
-        _lib.check(lib.tnn_network_backward(net._h, _lib.dptr(self._dy), _lib.dptr(self._interm),
-                                            _lib.dptr(self.grads), _lib.DTYPE_FP32, 1, None, None, batch, s))
+        _lib.check(lib.tnn_network_train_step(net._h, _lib.dptr(x), _lib.dptr(targets), targets.shape[1], x.shape[0],
+                                              float(self.loss_scale), _lib.dptr(self.grads), _lib.DTYPE_FP32, 1,
+                                              _lib.dptr(self._loss), _lib.stream_ptr()))
         return self._loss
 
     def optimizer_step(self):
