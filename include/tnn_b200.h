@@ -109,7 +109,7 @@ int tnn_network_train_step(tnn_network *net, const void *x, const float *targets
  * reference kernels have no device-side waits. */
 int tnn_network_sync_status(tnn_network *net, int *status, void *stream);
 /* Selects a kernel variant for tuning experiments (bit 0: hidden activations through TMEM in
- * inference, bit 1: MN-major weight operand, bit 2: fewer tiles in flight, bit 4: unfused training path).  Default 0.
+ * inference, bit 1: MN-major weight operand, bit 2: fewer tiles in flight, bit 4: unfused training path, bit 6: single-tile fused training kernel).  Default 0.
  * No reference counterpart. */
 int tnn_network_set_variant(tnn_network *net, int variant);
 

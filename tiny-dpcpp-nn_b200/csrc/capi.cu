@@ -380,7 +380,12 @@ int tnn_network_train_step(tnn_network *n, const void *x, const float *targets, 
         p.status = n->status;
         p.stream = s;
         p.prof = (n->variant & 32) ? reinterpret_cast<long long *>(n->loss_partials) : nullptr; // non-null = print cycle accounting
-        cudaError_t e = tnn::launch_mlp_train(p);
+        // widest-overlap kernel first; the single-tile kernel covers deeper networks
+        cudaError_t e = (n->variant & 64) ? cudaErrorInvalidConfiguration : tnn::launch_mlp_train_pipe(p);
+        if (e == cudaErrorInvalidConfiguration) {
+            cudaGetLastError();
+            e = tnn::launch_mlp_train(p);
+        }
         if (e == cudaSuccess) {
             if (loss_sum) TNN_CUDA(tnn::launch_sum_partials(n->loss_partials, p.grid_out, loss_sum, s));
             TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, p.grid_out, n->n_mat, n->width, pack_transpose, 1.0f, gf, gb, s));

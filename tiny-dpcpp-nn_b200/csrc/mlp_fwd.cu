@@ -314,9 +314,7 @@ template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
     }
     if (p.variant & 2) return launch_variant<W, 2, false, false, true>(p);
     if constexpr (W >= 32) {
-        if (p.variant & 1)
-            return (p.variant & 4) ? launch_variant<W, 2, false, true, false>(p)
-                                   : launch_variant<W, 4, false, true, false>(p);
+        if (p.variant & 1) return launch_variant<W, 2, false, true, false>(p);
     }
     if (p.variant & 8) return launch_variant<W, 3, false, false, false>(p);
     cudaError_t e = cudaErrorInvalidConfiguration;

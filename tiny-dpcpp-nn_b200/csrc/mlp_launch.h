@@ -69,5 +69,7 @@ struct TrainLaunch {
 };
 // cudaErrorInvalidConfiguration when the network does not fit the on-chip budget of the fused kernel.
 cudaError_t launch_mlp_train(TrainLaunch &p);
+// Same pass with the forward stage of one tile overlapped with the backward stage of the previous one.
+cudaError_t launch_mlp_train_pipe(TrainLaunch &p);
 
 } // namespace tnn

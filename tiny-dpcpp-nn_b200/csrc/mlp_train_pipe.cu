@@ -1,0 +1,540 @@
+// Fused training pass, pipelined over two tiles: while the backward pass of tile t runs, the forward
+// pass (and L2 loss) of tile t+1 runs on the same SM.  Same arithmetic as mlp_train.cu - forward
+// (reference include/network/kernel_esimd.h:565-640), L2 loss (include/losses/l2.h:19-41), backward chain
+// and weight-gradient reduction (kernel_esimd.h:160-240) with no activation ever leaving the SM.
+//
+// A tile's layer-to-layer chain is strictly serial (GEMM -> epilogue -> GEMM ...), so one tile alone
+// leaves the tensor pipe idle most of the time.  Two tiles do not fit in shared memory side by side,
+// but a forward pass *fills* its activation buffers in the order 1..L while the backward pass of the
+// tile before it *releases* them in the order L..1.  Consecutive tiles therefore use the L+1 activation
+// buffers in opposite directions and share them:
+//     even tile: a_j -> buffer j-1            odd tile: a_j -> buffer L+1-j
+// When the forward stage of tile t+1 reaches layer k it needs exactly the buffer the backward stage of
+// tile t released one step earlier.  Per-buffer mbarriers make that hand-over exact.
+//
+// Roles (640 threads, one CTA per SM):
+//   warp 0      TMA producer (weights once, input tiles double-buffered)
+//   warp 1      issuer of the forward chain GEMMs       (accumulator F; owns TMEM)
+//   warp 2      issuer of the backward chain GEMMs      (accumulator B)
+//   warp 3      issuer of the weight-gradient GEMMs     (one accumulator per layer, kept across all tiles)
+//   warps 4-11  forward-stage epilogue, two threads per row: activation, bf16, next A operand; L2 loss
+//   warps 12-19 backward-stage epilogue, two threads per row: activation backward, next delta tile
+#include "mlp_common.cuh"
+#include "mlp_launch.h"
+
+namespace tnn {
+
+constexpr int kPipeMaxMat = 6; // (L + 3) * W TMEM columns and L + 6 tiles of shared memory must fit
+
+template <int W> struct PipeSmem {
+    using T = Tile<W>;
+    // delta tiles first (see mlp_train.cu: the M = 64 weight-gradient GEMM over-reads past them for W < 64)
+    static constexpr int DL = 0;                                  // delta_L: forward stage -> backward stage
+    __host__ __device__ static constexpr int DP(int p) { return (1 + p) * T::ACT_BYTES; } // delta ping-pong
+    __host__ __device__ static constexpr int X(int b) { return (3 + b) * T::ACT_BYTES; }  // input tiles
+    __host__ __device__ static constexpr int AB(int i) { return (5 + i) * T::ACT_BYTES; } // L + 1 shared activation buffers
+    __host__ __device__ static constexpr int WBUF(int n_mat) { return (5 + n_mat) * T::ACT_BYTES; }
+    static constexpr int GROUP_THREADS = 256; // one epilogue stage: two threads per tile row
+    static constexpr int GROUP_WARPS = GROUP_THREADS / 32;
+    static constexpr int THREADS = 128 + 2 * GROUP_THREADS;
+    static constexpr int CPT = W / 2; // columns per epilogue thread
+};
+
+struct PipeBarriers {
+    uint64_t w_full;
+    uint64_t x_full[2], x_empty[2];
+    uint64_t f_ready, accf_full;       // forward stage <-> its issuer
+    uint64_t b_ready, accb_full;       // backward stage <-> its issuer
+    uint64_t dl_ready, dl_free;        // delta_L hand-over between the stages
+    uint64_t dwgo_f;                   // forward stage -> weight-gradient issuer (delta_L)
+    uint64_t dwgo_b[2];                // backward stage -> weight-gradient issuer (alternating, see mlp_train.cu)
+    uint64_t chain_issued[2];          // backward issuer -> weight-gradient issuer (alternating)
+    uint64_t dp_free[2];               // weight-gradient GEMM that read delta ping-pong buffer p is complete
+    uint64_t ab_free[kPipeMaxMat + 1]; // activation buffer i: mask read by the backward stage and weight-gradient GEMM done
+    uint64_t all_done;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+    float loss_red[8];
+};
+
+template <int W>
+__global__ void __launch_bounds__(PipeSmem<W>::THREADS, 1)
+mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *__restrict__ wimg,
+                      const float *__restrict__ targets, int n_targets, float *__restrict__ dw_slabs,
+                      float *__restrict__ loss_partials, size_t batch, int n_tiles, int n_mat, int act, int out_act,
+                      float loss_scale, float inv_n, int *status) {
+    using T = Tile<W>;
+    using S = PipeSmem<W>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ PipeBarriers bars;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int L = n_mat - 1;
+    const uint32_t smem_base = ptx::smem_u32(smem);
+    volatile uint32_t *abort_flag = &bars.abort_flag;
+    const int my_tiles = (n_tiles > (int)blockIdx.x) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    constexpr uint32_t kTmemCols = 512;
+
+    // activation buffer of a_j (j = 1..L) of this CTA's t-th tile
+    auto ab_index = [L](int t, int j) { return (t & 1) ? L + 1 - j : j - 1; };
+    // number of times buffer i was used by the tiles before tile t
+    auto ab_prior_uses = [L](int t, int i) { return i == 0 ? (t + 1) / 2 : (i == L ? t / 2 : t); };
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bars.w_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(&bars.x_full[b], 1);
+            ptx::mbar_init(&bars.x_empty[b], 2);
+            ptx::mbar_init(&bars.dwgo_b[b], S::GROUP_WARPS);
+            ptx::mbar_init(&bars.chain_issued[b], 1);
+            ptx::mbar_init(&bars.dp_free[b], 1);
+        }
+        ptx::mbar_init(&bars.f_ready, S::GROUP_WARPS);
+        ptx::mbar_init(&bars.accf_full, 1);
+        ptx::mbar_init(&bars.b_ready, S::GROUP_WARPS);
+        ptx::mbar_init(&bars.accb_full, 1);
+        ptx::mbar_init(&bars.dl_ready, S::GROUP_WARPS);
+        ptx::mbar_init(&bars.dl_free, 2); // backward chain GEMM + weight-gradient GEMM of layer L
+        ptx::mbar_init(&bars.dwgo_f, S::GROUP_WARPS);
+        for (int i = 0; i <= kPipeMaxMat; ++i) ptx::mbar_init(&bars.ab_free[i], S::GROUP_WARPS + 1);
+        ptx::mbar_init(&bars.all_done, 1);
+        bars.abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tmap(&tm_x);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(&bars.tmem_base, kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = bars.tmem_base;
+    const uint32_t accf_tmem = tmem_base;     // columns [0, W)
+    const uint32_t accb_tmem = tmem_base + W; // columns [W, 2W); weight gradients of layer l at 2W + l W
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0 && my_tiles > 0) {
+            ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
+            for (int l = 0; l < n_mat; ++l)
+                ptx::bulk_load(smem + S::WBUF(n_mat) + l * T::WGT_BYTES,
+                               reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
+                               &bars.w_full);
+            for (int t = 0; t < my_tiles; ++t) {
+                const int tile = blockIdx.x + t * gridDim.x;
+                const int b = t & 1;
+                if (t >= 2 && !ptx::mbar_wait(&bars.x_empty[b], ((t >> 1) - 1) & 1, abort_flag)) {
+                    atomicExch(status, KS_TIMEOUT_PRODUCER | 1);
+                    break;
+                }
+                ptx::mbar_arrive_expect_tx(&bars.x_full[b], T::ACT_BYTES);
+                for (int at = 0; at < T::KATOMS; ++at)
+                    ptx::tma_load_2d(smem + S::X(b) + at * T::ACT_ATOM_BYTES, &tm_x, at * T::ATOM_COLS, tile * T::TM,
+                                     &bars.x_full[b]);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ forward chain issuer
+        if (lane == 0 && my_tiles > 0) {
+            constexpr uint32_t idesc = ptx::make_idesc_bf16(128, W, 0, 1); // B = W_l read MN-major
+            const uint64_t x_desc0 = T::kdesc_base(smem_base + S::X(0));
+            const uint64_t ab_desc0 = T::kdesc_base(smem_base + S::AB(0));
+            const uint64_t w_desc0 = T::mndesc_base(smem_base + S::WBUF(n_mat), T::WGT_ATOM_BYTES);
+            bool ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
+            if (!ok) atomicExch(status, KS_TIMEOUT_WEIGHTS);
+            uint32_t fr_parity = 0;
+            for (int t = 0; ok && t < my_tiles; ++t) {
+                const int b = t & 1;
+                if (t > 0) { // the loss step of the previous tile has drained the accumulator
+                    ok = ptx::mbar_wait_busy(&bars.f_ready, fr_parity, abort_flag);
+                    fr_parity ^= 1u;
+                }
+                if (ok) ok = ptx::mbar_wait_busy(&bars.x_full[b], (t >> 1) & 1, abort_flag);
+                if (!ok) {
+                    atomicExch(status, KS_TIMEOUT_MMA | 1);
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                T::template issue_chain<true>(accf_tmem, x_desc0 + (uint64_t)(b * T::ACT_UNITS), w_desc0, idesc);
+                ptx::mma_commit(&bars.accf_full);
+                ptx::mma_commit(&bars.x_empty[b]);
+                for (int l = 1; l <= L; ++l) {
+                    if (!ptx::mbar_wait_busy(&bars.f_ready, fr_parity, abort_flag)) {
+                        atomicExch(status, KS_TIMEOUT_MMA | 2 | (l << 4));
+                        ok = false;
+                        break;
+                    }
+                    fr_parity ^= 1u;
+                    ptx::tc_fence_after_sync();
+                    T::template issue_chain<true>(accf_tmem, ab_desc0 + (uint64_t)(ab_index(t, l) * T::ACT_UNITS),
+                                                  w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
+                    ptx::mma_commit(&bars.accf_full);
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // ------------------------------------------------------------ backward chain issuer
+        if (lane == 0 && my_tiles > 0) {
+            constexpr uint32_t idesc = ptx::make_idesc_bf16(128, W, 0, 0); // B = W_l read K-major
+            const uint64_t dl_desc = T::kdesc_base(smem_base + S::DL);
+            const uint64_t dp_desc0 = T::kdesc_base(smem_base + S::DP(0));
+            const uint64_t w_desc0 = T::kdesc_base(smem_base + S::WBUF(n_mat));
+            bool ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
+            uint32_t br_parity = 0, ci_count = 0;
+            for (int t = 0; ok && t < my_tiles; ++t) {
+                ok = ptx::mbar_wait_busy(&bars.dl_ready, t & 1, abort_flag);
+                if (ok && t > 0) { // delta_0 of the previous tile is out: accumulator B is drained
+                    ok = ptx::mbar_wait_busy(&bars.b_ready, br_parity, abort_flag);
+                    br_parity ^= 1u;
+                }
+                if (!ok) {
+                    atomicExch(status, KS_TIMEOUT_MMA | 3);
+                    break;
+                }
+                for (int l = L; l >= 1; --l) {
+                    if (l < L) {
+                        if (!ptx::mbar_wait_busy(&bars.b_ready, br_parity, abort_flag)) {
+                            atomicExch(status, KS_TIMEOUT_MMA | 4 | (l << 4));
+                            ok = false;
+                            break;
+                        }
+                        br_parity ^= 1u;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint64_t d_desc = (l == L) ? dl_desc : dp_desc0 + (uint64_t)(((L - 1 - l) & 1) * T::ACT_UNITS);
+                    T::template issue_chain<false>(accb_tmem, d_desc, w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
+                    ptx::mma_commit(&bars.accb_full);
+                    if (l == L) ptx::mma_commit(&bars.dl_free);
+                    ptx::mbar_arrive(&bars.chain_issued[ci_count & 1u]); // the weight-gradient GEMM of layer l may follow
+                    ++ci_count;
+                }
+            }
+        }
+    } else if (warp == 3) {
+        // ------------------------------------------------------------ weight-gradient issuer
+        if (lane == 0 && my_tiles > 0) {
+            constexpr int DW_M = (W == 128) ? 128 : 64;
+            constexpr uint32_t idesc = ptx::make_idesc_bf16(DW_M, W, 1, 1);
+            const uint64_t x_desc0 = T::mndesc_base(smem_base + S::X(0), T::ACT_ATOM_BYTES);
+            const uint64_t ab_desc0 = T::mndesc_base(smem_base + S::AB(0), T::ACT_ATOM_BYTES);
+            const uint64_t dl_desc = T::mndesc_base(smem_base + S::DL, T::ACT_ATOM_BYTES);
+            const uint64_t dp_desc0 = T::mndesc_base(smem_base + S::DP(0), T::ACT_ATOM_BYTES);
+            uint32_t kb = 0; // backward-stage hand-overs consumed
+            uint32_t kc = 0; // chain_issued signals consumed
+            bool ok = true;
+            for (int t = 0; ok && t < my_tiles; ++t) {
+                const int b = t & 1;
+                for (int l = L; l >= 0; --l) {
+                    if (l == L) {
+                        ok = ptx::mbar_wait(&bars.dwgo_f, t & 1, abort_flag);
+                    } else {
+                        ok = ptx::mbar_wait(&bars.dwgo_b[kb & 1u], (kb >> 1) & 1u, abort_flag);
+                        ++kb;
+                    }
+                    if (ok && l >= 1) { // stay behind the chain GEMM that consumes the same delta tile
+                        ok = ptx::mbar_wait(&bars.chain_issued[kc & 1u], (kc >> 1) & 1u, abort_flag);
+                        ++kc;
+                    }
+                    if (!ok) {
+                        atomicExch(status, KS_TIMEOUT_MMA | 5 | (l << 4));
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const int p = (L - 1 - l) & 1;
+                    const uint64_t d_desc = (l == L) ? dl_desc : dp_desc0 + (uint64_t)(p * T::ACT_UNITS);
+                    const int ai = (l >= 1) ? ab_index(t, l) : 0;
+                    const uint64_t a_desc = (l >= 1) ? ab_desc0 + (uint64_t)(ai * T::ACT_UNITS)
+                                                     : x_desc0 + (uint64_t)(b * T::ACT_UNITS);
+                    T::issue_outer(tmem_base + (uint32_t)(2 * W + l * W), d_desc, a_desc, idesc, t > 0 ? 1u : 0u);
+                    if (l == L)
+                        ptx::mma_commit(&bars.dl_free);
+                    else
+                        ptx::mma_commit(&bars.dp_free[p]);
+                    if (l >= 1)
+                        ptx::mma_commit(&bars.ab_free[ai]);
+                    else
+                        ptx::mma_commit(&bars.x_empty[b]);
+                }
+            }
+            ptx::mma_commit(&bars.all_done);
+        }
+    } else if (warp < 4 + S::GROUP_WARPS) {
+        // ------------------------------------------------------------ forward-stage epilogue
+        const int gw = warp - 4;
+        const int quad = warp & 3;
+        const int half = gw >> 2;
+        const int row = quad * 32 + lane;
+        const int col0 = half * S::CPT;
+        constexpr int CPT = S::CPT;
+        const uint32_t acc_addr = accf_tmem + ((uint32_t)(quad * 32) << 16) + col0;
+        uint32_t af_parity = 0;
+        float loss_local = 0.0f;
+        bool ok = true;
+        auto chunk_at = [&](int ch) {
+            const int c = col0 + ch * 8;
+            return (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES + T::chunk_off(row, (c % T::ATOM_COLS) / 8);
+        };
+        auto wait_u = [&](uint64_t *bar, uint32_t parity, int code) { // warp-uniform bounded wait
+            const bool r = __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag));
+            if (!r && lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | code);
+            return r;
+        };
+        auto load_acc = [&](uint32_t (&v)[CPT]) {
+            if constexpr (CPT == 32)
+                ptx::tmem_ld32(acc_addr, v);
+            else
+                ptx::tmem_ld16(acc_addr, v);
+            ptx::tmem_ld_wait();
+        };
+        for (int t = 0; ok && t < my_tiles; ++t) {
+            const int tile = blockIdx.x + t * gridDim.x;
+            const size_t grow = (size_t)tile * T::TM + row;
+            const bool row_valid = grow < batch;
+            for (int l = 0; l < L && ok; ++l) {
+                if (!wait_u(&bars.accf_full, af_parity, 1 | (l << 4))) {
+                    ok = false;
+                    break;
+                }
+                af_parity ^= 1u;
+                ptx::tc_fence_after_sync();
+                uint32_t v[CPT];
+                load_acc(v);
+                const int bi = ab_index(t, l + 1);
+                const int uses = ab_prior_uses(t, bi);
+                if (uses > 0 && !wait_u(&bars.ab_free[bi], (uses - 1) & 1, 2 | (l << 4))) {
+                    ok = false;
+                    break;
+                }
+                uint8_t *dst = smem + S::AB(bi);
+                dispatch_act(act, [&](auto tag) {
+                    constexpr int ACT = decltype(tag)::value;
+#pragma unroll
+                    for (int ch = 0; ch < CPT / 8; ++ch) {
+                        uint4 o;
+                        o.x = act_pack_t<ACT>(__uint_as_float(v[ch * 8 + 0]), __uint_as_float(v[ch * 8 + 1]));
+                        o.y = act_pack_t<ACT>(__uint_as_float(v[ch * 8 + 2]), __uint_as_float(v[ch * 8 + 3]));
+                        o.z = act_pack_t<ACT>(__uint_as_float(v[ch * 8 + 4]), __uint_as_float(v[ch * 8 + 5]));
+                        o.w = act_pack_t<ACT>(__uint_as_float(v[ch * 8 + 6]), __uint_as_float(v[ch * 8 + 7]));
+                        *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) = o;
+                    }
+                });
+                ptx::fence_proxy_async_smem();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&bars.f_ready);
+            }
+            if (!ok) break;
+            // ---- output layer + L2 loss.  The target slice is requested before the wait for the last GEMM.
+            float tg[CPT];
+            if (row_valid && n_targets == W) {
+#pragma unroll
+                for (int q4 = 0; q4 < CPT / 4; ++q4) {
+                    const float4 t4 = __ldg(reinterpret_cast<const float4 *>(targets + grow * W + col0) + q4);
+                    tg[q4 * 4 + 0] = t4.x, tg[q4 * 4 + 1] = t4.y, tg[q4 * 4 + 2] = t4.z, tg[q4 * 4 + 3] = t4.w;
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < CPT; ++q)
+                    tg[q] = (row_valid && col0 + q < n_targets) ? __ldg(targets + grow * n_targets + col0 + q) : 0.0f;
+            }
+            if (!wait_u(&bars.accf_full, af_parity, 3)) {
+                ok = false;
+                break;
+            }
+            af_parity ^= 1u;
+            ptx::tc_fence_after_sync();
+            uint32_t v[CPT];
+            load_acc(v);
+            // delta_L of the previous tile must have been consumed by its two GEMMs
+            if (t > 0 && !wait_u(&bars.dl_free, (t - 1) & 1, 4)) {
+                ok = false;
+                break;
+            }
+            uint8_t *dst = smem + S::DL;
+            dispatch_act(out_act, [&](auto tag) {
+                constexpr int ACT = decltype(tag)::value;
+#pragma unroll
+                for (int ch = 0; ch < CPT / 8; ++ch) {
+                    uint32_t o[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        // the prediction as the network stores it (bf16), then the loss on that value
+                        const uint32_t y16 = act_pack_t<ACT>(__uint_as_float(v[ch * 8 + 2 * q]),
+                                                              __uint_as_float(v[ch * 8 + 2 * q + 1]));
+                        float d0 = ptx::bf16lo_to_f32(y16) - tg[ch * 8 + 2 * q];
+                        float d1 = ptx::bf16hi_to_f32(y16) - tg[ch * 8 + 2 * q + 1];
+                        if (!row_valid) d0 = d1 = 0.0f;
+                        loss_local += d0 * d0 * inv_n + d1 * d1 * inv_n;
+                        const uint32_t g16 =
+                            ptx::pack_bf16x2(loss_scale * 2.0f * d0 * inv_n, loss_scale * 2.0f * d1 * inv_n);
+                        o[q] = (ACT == ACT_NONE)
+                                   ? g16
+                                   : act_bwd_pack_t<ACT>(ptx::bf16lo_to_f32(g16), ptx::bf16hi_to_f32(g16), y16);
+                    }
+                    *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            });
+            ptx::fence_proxy_async_smem();
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                ptx::mbar_arrive(&bars.f_ready);  // accumulator F is free for the next tile
+                ptx::mbar_arrive(&bars.dl_ready); // backward chain may start
+                ptx::mbar_arrive(&bars.dwgo_f);   // weight gradient of the output layer may start
+            }
+        }
+        // loss partial of this CTA (fixed summation order)
+        for (int o = 16; o > 0; o >>= 1) loss_local += __shfl_xor_sync(0xffffffffu, loss_local, o);
+        if (lane == 0) bars.loss_red[gw] = loss_local;
+        ptx::named_bar_sync(1, S::GROUP_THREADS);
+        if (gw == 0 && lane == 0 && loss_partials) {
+            float s = 0.0f;
+            for (int i = 0; i < S::GROUP_WARPS; ++i) s += bars.loss_red[i];
+            loss_partials[blockIdx.x] = s;
+        }
+    } else {
+        // ------------------------------------------------------------ backward-stage epilogue
+        const int gw = warp - (4 + S::GROUP_WARPS);
+        const int quad = warp & 3;
+        const int half = gw >> 2;
+        const int row = quad * 32 + lane;
+        const int col0 = half * S::CPT;
+        constexpr int CPT = S::CPT;
+        const uint32_t acc_addr = accb_tmem + ((uint32_t)(quad * 32) << 16) + col0;
+        uint32_t ab_parity = 0;
+        uint32_t dp_parity[2] = {0, 0};
+        int dp_writes[2] = {0, 0};
+        uint32_t go_count = 0;
+        bool ok = true;
+        auto chunk_at = [&](int ch) {
+            const int c = col0 + ch * 8;
+            return (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES + T::chunk_off(row, (c % T::ATOM_COLS) / 8);
+        };
+        auto wait_u = [&](uint64_t *bar, uint32_t parity, int code) {
+            const bool r = __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag));
+            if (!r && lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | code);
+            return r;
+        };
+        for (int t = 0; ok && t < my_tiles; ++t) {
+            for (int l = L; l >= 1 && ok; --l) {
+                if (!wait_u(&bars.accb_full, ab_parity, 5 | (l << 4))) {
+                    ok = false;
+                    break;
+                }
+                ab_parity ^= 1u;
+                ptx::tc_fence_after_sync();
+                uint32_t v[CPT];
+                if constexpr (CPT == 32)
+                    ptx::tmem_ld32(acc_addr, v);
+                else
+                    ptx::tmem_ld16(acc_addr, v);
+                ptx::tmem_ld_wait();
+                const int p = (L - l) & 1; // delta_{l-1} goes to ping-pong buffer (L - l) & 1
+                if (dp_writes[p] > 0) {     // all but the first write wait for the GEMM that read the buffer
+                    if (!wait_u(&bars.dp_free[p], dp_parity[p], 6 | (l << 4))) {
+                        ok = false;
+                        break;
+                    }
+                    dp_parity[p] ^= 1u;
+                }
+                ++dp_writes[p];
+                const int ai = ab_index(t, l);
+                const uint8_t *abuf = smem + S::AB(ai);
+                uint8_t *dst = smem + S::DP(p);
+                dispatch_act(act, [&](auto tag) {
+                    constexpr int ACT = decltype(tag)::value;
+#pragma unroll
+                    for (int ch = 0; ch < CPT / 8; ++ch) {
+                        const int off = chunk_at(ch);
+                        uint4 f = make_uint4(0, 0, 0, 0);
+                        if constexpr (ACT != ACT_NONE) f = *reinterpret_cast<const uint4 *>(abuf + off);
+                        uint4 o;
+                        o.x = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 0]), __uint_as_float(v[ch * 8 + 1]), f.x);
+                        o.y = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 2]), __uint_as_float(v[ch * 8 + 3]), f.y);
+                        o.z = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 4]), __uint_as_float(v[ch * 8 + 5]), f.z);
+                        o.w = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 6]), __uint_as_float(v[ch * 8 + 7]), f.w);
+                        *reinterpret_cast<uint4 *>(dst + off) = o;
+                    }
+                });
+                ptx::fence_proxy_async_smem();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(&bars.b_ready);
+                    ptx::mbar_arrive(&bars.dwgo_b[go_count & 1u]);
+                    ptx::mbar_arrive(&bars.ab_free[ai]); // this stage is done with a_l
+                }
+                ++go_count;
+            }
+        }
+        // ---- drain the weight-gradient accumulators into this CTA's slab
+        if (ok && my_tiles > 0 && !wait_u(&bars.all_done, 0, 7)) ok = false;
+        if (ok && my_tiles > 0) {
+            ptx::tc_fence_after_sync();
+            float *slab = dw_slabs + (size_t)blockIdx.x * n_mat * W * W;
+            const int o = quad * 16 + lane; // M = 64 accumulators keep row m in lane (m % 16) + 32 * (m / 16)
+            const bool valid = lane < 16 && o < W;
+            for (int l = 0; l < n_mat; ++l) {
+                uint32_t v[CPT];
+                const uint32_t addr = tmem_base + ((uint32_t)(quad * 32) << 16) + 2 * W + l * W + col0;
+                if constexpr (CPT == 32)
+                    ptx::tmem_ld32(addr, v);
+                else
+                    ptx::tmem_ld16(addr, v);
+                ptx::tmem_ld_wait();
+                if (valid) {
+                    float4 *dstp = reinterpret_cast<float4 *>(slab + ((size_t)l * W + o) * W + col0);
+#pragma unroll
+                    for (int q4 = 0; q4 < CPT / 4; ++q4)
+                        dstp[q4] = make_float4(__uint_as_float(v[q4 * 4]), __uint_as_float(v[q4 * 4 + 1]),
+                                               __uint_as_float(v[q4 * 4 + 2]), __uint_as_float(v[q4 * 4 + 3]));
+                }
+            }
+        }
+    }
+
+    if (*abort_flag && threadIdx.x == 0) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(100);
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------- host side
+template <int W> static cudaError_t launch_pipe_w(TrainLaunch &p) {
+    using T = Tile<W>;
+    using S = PipeSmem<W>;
+    const size_t smem = (size_t)S::WBUF(p.n_mat) + (size_t)p.n_mat * T::WGT_BYTES + 1024;
+    const int cols_needed = 2 * W + p.n_mat * W;
+    if (smem > 227 * 1024 || cols_needed > 512 || p.n_mat > kPipeMaxMat) return cudaErrorInvalidConfiguration;
+    auto kern = mlp_train_pipe_kernel<W>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
+    const int grid = n_tiles < p.n_sm ? n_tiles : p.n_sm;
+    p.grid_out = grid;
+    if (grid == 0) return cudaSuccess;
+    const float inv_n = 1.0f / ((float)p.batch * (float)W);
+    kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, p.wimg, p.targets, p.n_targets, p.dw_partials, p.loss_partials,
+                                               p.batch, n_tiles, p.n_mat, p.act, p.out_act, p.loss_scale, inv_n,
+                                               p.status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_mlp_train_pipe(TrainLaunch &p) {
+    switch (p.width) {
+    case 32: return launch_pipe_w<32>(p);
+    case 64: return launch_pipe_w<64>(p);
+    default: return cudaErrorInvalidConfiguration;
+    }
+}
+
+} // namespace tnn
