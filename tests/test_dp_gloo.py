@@ -1,0 +1,71 @@
+"""CPU test of the data-parallel semantics with two gloo ranks: every rank computes the gradient of ITS
+mean loss on its row shard (here with the oracle standing in for the GPU kernel), the ranks all-reduce
+(sum) the gradient buffer and scale by 1 / world - the result must equal the gradient of the mean loss
+over the whole batch, and every rank must hold the same bits afterwards."""
+import os
+import socket
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+W, NH, BATCH, WORLD = 32, 2, 512, 2
+
+
+def _grads(x, t, w):
+    from oracle import oracle as O
+
+    interm = O.mlp_forward(x, w, NH + 1, W, "relu", "none", bf16=True)
+    _, dy = O.l2_loss(interm[-1], t, 1.0, bf16_grads=True)
+    return O.mlp_backward(dy, interm, w, NH + 1, W, "relu", "none", bf16=True, want_dx=False)[1]
+
+
+def _worker(rank, port, out_dir):
+    for p in (ROOT, os.path.join(ROOT, "tiny-dpcpp-nn_b200")):
+        sys.path.insert(0, p)
+    from tests import synth
+    from tiny_dpcpp_nn.parallel import allreduce_sum_, shard_rows
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    w, x = synth.mlp_case(W, NH, BATCH, w_seed=6)
+    t = synth.uniform_inputs(BATCH, W, seed=1)
+    a, b = shard_rows(BATCH, rank, WORLD)
+    g = torch.from_numpy(_grads(x[a:b], t[a:b], w).astype(np.float32).reshape(-1))
+    allreduce_sum_(g, dist.group.WORLD)
+    g /= WORLD
+    np.save(os.path.join(out_dir, f"g{rank}.npy"), g.numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_gradient_average_equals_full_batch_gradient(tmp_path):
+    from oracle import oracle as O
+    from tests import synth
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker, args=(port, str(tmp_path)), nprocs=WORLD, join=True)
+    g0, g1 = np.load(tmp_path / "g0.npy"), np.load(tmp_path / "g1.npy")
+    assert np.array_equal(g0, g1)
+    w, x = synth.mlp_case(W, NH, BATCH, w_seed=6)
+    t = synth.uniform_inputs(BATCH, W, seed=1)
+    full = _grads(x, t, w).reshape(-1)
+    # the per-shard dL/dy is rounded to bf16 at a different scale than the full-batch one: 1e-2 like the kernels
+    ok, rel = O.within_tolerance(g0, full, 1e-2)
+    assert ok, rel
+
+
+def test_shard_rows_cover_the_batch():
+    from tiny_dpcpp_nn.parallel import shard_rows
+
+    for n, world in ((1 << 22, 8), (1000 * 8, 3), (64, 4)):
+        edges = [shard_rows(n, r, world) for r in range(world)]
+        assert edges[0][0] == 0 and edges[-1][1] == n
+        for (a0, b0), (a1, b1) in zip(edges, edges[1:]):
+            assert b0 == a1 and (b0 - a0) % 8 == 0

@@ -10,6 +10,7 @@ data-parallel runs the only communication is one all-reduce of the fp32 weight-g
 import torch
 
 from . import _lib
+from .parallel import allreduce_sum_
 
 
 class Trainer:
@@ -45,8 +46,8 @@ class Trainer:
         return self._loss
 
     def optimizer_step(self):
-        if self.pg is not None and self.world_size > 1:
-            torch.distributed.all_reduce(self.grads, group=self.pg)
+        if self.world_size > 1:
+            allreduce_sum_(self.grads, self.pg)
         self.step += 1
         self.net.adam_step(self.master, self.m, self.v, self.grads, self.step, self.lr, self.betas[0], self.betas[1],
                            self.eps, grad_scale=1.0 / (self.loss_scale * self.world_size))
