@@ -163,6 +163,21 @@ int tnn_encoding_backward(tnn_encoding *enc, const float *x, const void *dy, int
  * loss_sum (optional): one fp32 = sum of values. */
 int tnn_l2_loss(const void *pred, const float *target, int n_targets, float *values, void *grads,
                 size_t batch, int stride, float loss_scale, float *loss_sum, void *stream);
+/* No counterpart in the reference.  Same computation and arguments as tnn_l2_loss for callers that must
+ * not allocate device memory - e.g. a plug-in inside a host application whose allocator already owns all
+ * free device memory, or a latency-critical loop that cannot afford the device-wide synchronisation an
+ * allocation implies.  It calls no cudaMalloc / cudaFree and no allocating library routine: the per-block
+ * partial sums live in a fixed 16 KiB array inside the library image (present on every GPU that loads
+ * the library until the process exits).  Limits and rules that follow from that:
+ *   - batch * stride must not exceed 2^27 elements (4096 partial sums x 32768 elements); larger inputs
+ *     are rejected with an error, use tnn_l2_loss or split the batch;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current); make that first call before any stream capture;
+ *   - all calls on a device share the array: calls that overlap on the GPU (different streams) race on it.
+ *     The array keeps the previous call's contents, which is harmless - every slot a call reads is first
+ *     overwritten by that call. */
+int tnn_l2_loss_static(const void *pred, const float *target, int n_targets, float *values, void *grads,
+                       size_t batch, int stride, float loss_scale, float *loss_sum, void *stream);
 /* Optimizer::step - include/optimizers/optimizer.h; arithmetic is torch.optim.Adam's (the optimiser
  * every runnable reference path uses: test/python/test_compare_torch_dpcpp.py:37), not the vestigial
  * source/optimizers/adam.cpp.  `step` counts from 1.  grads are multiplied by grad_scale first. */

@@ -88,6 +88,11 @@ bool act_supported(int a) { return a == tnn::ACT_RELU || a == tnn::ACT_SIGMOID |
 
 } // namespace
 
+namespace tnn {
+// error recording for translation units that implement further entry points
+int api_fail(const std::string &msg, int code) { return fail(msg, code); }
+} // namespace tnn
+
 // ======================================================================== network
 struct tnn_network {
     int input_width = 0, output_width = 0; // as requested (unpadded)

@@ -56,6 +56,7 @@ _SIGNATURES = {
     "tnn_encoding_forward": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _c.c_size_t, _vp]),
     "tnn_encoding_backward": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _vp, _c.c_size_t, _c.c_int, _vp]),
     "tnn_l2_loss": (_c.c_int, [_vp, _vp, _c.c_int, _vp, _vp, _c.c_size_t, _c.c_int, _c.c_float, _vp, _vp]),
+    "tnn_l2_loss_static": (_c.c_int, [_vp, _vp, _c.c_int, _vp, _vp, _c.c_size_t, _c.c_int, _c.c_float, _vp, _vp]),
     "tnn_adam_step": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_size_t, _c.c_float, _c.c_int, _c.c_float, _c.c_float,
                                  _c.c_float, _c.c_float, _vp]),
     "tnn_network_adam_step": (_c.c_int, [_vp, _vp, _vp, _vp, _vp, _c.c_float, _c.c_int, _c.c_float, _c.c_float,
@@ -370,6 +371,15 @@ def l2_loss(pred, target, loss_scale=1.0, want_values=False):
     check(lib.tnn_l2_loss(dptr(pred), dptr(target), target.shape[1], dptr(values), dptr(grads), batch, stride,
                           float(loss_scale), dptr(loss_sum), stream_ptr()))
     return loss_sum, grads, values
+
+
+def l2_loss_static(pred, target, loss_sum, grads, values=None, loss_scale=1.0):
+    """tnn_l2_loss_static: every buffer comes from the caller and the library allocates nothing (its scratch
+    is a fixed array inside the library).  Raises TnnError beyond 2^27 elements."""
+    lib = load()
+    batch, stride = pred.shape
+    check(lib.tnn_l2_loss_static(dptr(pred), dptr(target), target.shape[1], dptr(values), dptr(grads), batch, stride,
+                                 float(loss_scale), dptr(loss_sum), stream_ptr()))
 
 
 def adam_step(params, m, v, grads, step, lr=1e-3, beta1=0.9, beta2=0.99, eps=1e-15, grad_scale=1.0):
