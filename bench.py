@@ -4,8 +4,8 @@
   python bench.py --gpus N --steps K --warmup W            # this library on N GPUs (N > 1: under torchrun)
   python bench.py --impl reference --steps K --warmup W    # the reference's CPU path on the host cores
 
-A step = forward (activations kept for backward) -> L2 loss -> backward with fused weight-gradient
-reduction -> (N > 1: one NCCL all-reduce of the fp32 gradient buffer) -> Adam + weight refresh.
+A step = one fused kernel (forward -> L2 loss -> backward -> weight-gradient reduction, activations never
+leave the SM) -> (N > 1: one NCCL all-reduce of the fp32 gradient buffer) -> Adam + weight refresh.
 Prints ONE JSON line.  `value` = whole-job training samples/s with inputs resident in HBM; `e2e` =
 the same through the public API from pinned HOST buffers (H2D of inputs and targets, D2H of the
 loss inside the timed region).  Extra keys: `infer` (inference throughput), `roofline` (dominant
@@ -219,8 +219,8 @@ def run_gpu_arm(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item()
 
-    # -------- training step, inputs resident in HBM (the per-step working set, 2.6 GiB of activations plus
-    # 1.5 GiB of inputs, is far larger than the 126 MB L2, so no explicit flush is needed)
+    # -------- training step, inputs resident in HBM (every step streams 1.5 GiB of inputs and targets, far
+    # more than the 126 MB L2, so no explicit flush is needed)
     step = lambda: trainer.training_step(x, targets)  # noqa: E731
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -247,47 +247,56 @@ def run_gpu_arm(args):
     ms_inf = timed(infer, args.steps) / args.steps
     infer_value = world * batch / (ms_inf * 1e-3)
 
-    # -------- per-kernel durations (CUDA events around one kernel at a time, same stream)
+    # -------- per-kernel durations (CUDA events around one call at a time, same stream)
     lib = L.load()
     s = L.stream_ptr()
     tr = trainer
+    interm = torch.empty((N_MAT + 1, batch, WIDTH), dtype=torch.bfloat16, device="cuda")
+    dy = torch.empty((batch, WIDTH), dtype=torch.bfloat16, device="cuda")
+
+    def k_train():  # the fused kernel (+ two tiny reductions: loss partials, gradient slabs)
+        L.check(lib.tnn_network_train_step(net._h, L.dptr(x), L.dptr(targets), WIDTH, batch, 1.0, L.dptr(tr.grads),
+                                           L.DTYPE_FP32, 1, L.dptr(tr._loss), s))
 
     def k_fwd():
-        L.check(lib.tnn_network_forward(net._h, L.dptr(x), None, L.dptr(tr._interm), batch, s))
+        L.check(lib.tnn_network_forward(net._h, L.dptr(x), None, L.dptr(interm), batch, s))
 
     def k_bwd():
-        L.check(lib.tnn_network_backward(net._h, L.dptr(tr._dy), L.dptr(tr._interm), L.dptr(tr.grads), L.DTYPE_FP32, 1,
-                                         None, None, batch, s))
+        L.check(lib.tnn_network_backward(net._h, L.dptr(dy), L.dptr(interm), L.dptr(tr.grads), L.DTYPE_FP32, 1, None,
+                                         None, batch, s))
 
     def k_loss():
-        L.check(lib.tnn_l2_loss(L.dptr(tr._interm[N_MAT]), L.dptr(targets), WIDTH, None, L.dptr(tr._dy), batch, WIDTH,
-                                1.0, L.dptr(tr._loss), s))
+        L.check(lib.tnn_l2_loss(L.dptr(interm[N_MAT]), L.dptr(targets), WIDTH, None, L.dptr(dy), batch, WIDTH, 1.0,
+                                L.dptr(tr._loss), s))
 
     kernel_ms = {}
-    for name, fn in (("mlp_fwd_store", k_fwd), ("l2_loss", k_loss), ("mlp_bwd", k_bwd), ("mlp_inference", infer)):
+    for name, fn in (("mlp_train_fused", k_train), ("mlp_inference", infer), ("mlp_fwd_store", k_fwd),
+                     ("l2_loss", k_loss), ("mlp_bwd", k_bwd)):
         for _ in range(2):
             fn()
         kernel_ms[name] = timed(fn, args.steps) / args.steps
 
-    def roof(name, flops_per_sample, bytes_per_sample):
+    def roof(name, flops_per_sample, bytes_per_sample, note):
         t = kernel_ms[name] * 1e-3
         tf = flops_per_sample * batch / t * 1e-12
         gb = bytes_per_sample * batch / t * 1e-9
         return {"kernel": name, "ms": kernel_ms[name], "tflops": tf, "frac_tensor": tf / peaks["tflops"], "gbs": gb,
-                "frac_hbm": gb / peaks["hbm_gbs"]}
+                "frac_hbm": gb / peaks["hbm_gbs"], "note": note}
 
     act_bytes = WIDTH * 2
     rooflines = [
-        roof("mlp_inference", FLOPS_FWD, BYTES_INFER),
-        roof("mlp_fwd_store", FLOPS_FWD, act_bytes * (N_MAT + 2)),     # x in, x copy + every activation out
-        roof("mlp_bwd", FLOPS_BWD, act_bytes * (N_MAT + 1)),           # dy + a_L..a_0 in
-        roof("l2_loss", 0, act_bytes * 2 + WIDTH * 4),                 # y in, dy out, targets in
+        roof("mlp_train_fused", FLOPS_TRAIN, act_bytes + WIDTH * 4, "the step's kernel: x in, targets in"),
+        roof("mlp_inference", FLOPS_FWD, BYTES_INFER, "x in, y out"),
+        roof("mlp_fwd_store", FLOPS_FWD, act_bytes * (N_MAT + 2), "unfused path: x in, input copy + every activation out"),
+        roof("mlp_bwd", FLOPS_BWD, act_bytes * (N_MAT + 1), "unfused path: dy + a_L..a_0 in"),
+        roof("l2_loss", 0, act_bytes * 2 + WIDTH * 4, "unfused path: y in, dy out, targets in"),
     ]
-    dom = max(("mlp_fwd_store", "mlp_bwd", "l2_loss"), key=lambda k: kernel_ms[k])
-    dom_r = [r for r in rooflines if r["kernel"] == dom][0]
-    roofline = {"bound": "tensor", "kernel": dom, "achieved": dom_r["tflops"], "peak": peaks["tflops"],
+    dom_r = rooflines[0]
+    roofline = {"bound": "tensor", "kernel": "mlp_train_pipe_kernel", "achieved": dom_r["tflops"], "peak": peaks["tflops"],
                 "unit": "TFLOP/s", "frac": dom_r["frac_tensor"], "traffic": None, "peak_source": peaks["source"],
+                "frac_of_sustained_peak": dom_r["tflops"] / peaks["tflops_sustained"],
                 "hbm_frac_same_kernel": dom_r["frac_hbm"]}
+    del interm, dy
 
     # -------- end to end through the public API with HOST buffers
     hx = torch.empty((batch, WIDTH), dtype=torch.bfloat16).pin_memory()
@@ -323,7 +332,7 @@ def run_gpu_arm(args):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload_name(args.log2_batch), "global_batch": world * batch,
                        "parallelism": f"dp{world}" if world > 1 else "single",
-                       "l2_flush": "inputs larger than L2 (4 GiB touched per step)"},
+                       "l2_flush": "inputs larger than L2 (1.5 GiB streamed per step)"},
             "train_tflops": FLOPS_TRAIN * value * 1e-12, "train_frac_of_bf16_peak": FLOPS_TRAIN * value * 1e-12 / world / peaks["tflops"],
             "infer": {"value": infer_value, "unit": UNIT, "ms": ms_inf, "tflops": FLOPS_FWD * infer_value * 1e-12,
                       "frac_of_bf16_peak": FLOPS_FWD * infer_value * 1e-12 / world / peaks["tflops"],
@@ -332,9 +341,9 @@ def run_gpu_arm(args):
             "roofline": roofline, "rooflines": rooflines,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": batch * WIDTH * (2 + 4),
                     "d2h_bytes_per_step": 4, "steps": e2e_steps},
-            "gpu_launches": 7 * args.steps, "kernels_per_step": ["mlp_fwd_kernel", "l2_loss_kernel", "sum_partials_kernel",
-                                                                 "mlp_bwd_kernel", "reduce_dw_kernel", "adam_kernel",
-                                                                 "set_params_kernel"],
+            "gpu_launches": 5 * args.steps,
+            "kernels_per_step": ["mlp_train_pipe_kernel", "sum_partials_kernel", "reduce_dw_kernel", "adam_kernel",
+                                 "set_params_kernel"] + (["ncclAllReduce (80 KiB)"] if world > 1 else []),
             "clocks": clocks, "kernel_status": status, "final_loss_sum": loss_value,
         }
         if cpu is not None:
