@@ -4,20 +4,21 @@
 // (include/encodings/grid.h:137-245), so its sums have no fixed order.  Here the same sum is
 // evaluated as a segmented reduction with a fixed order, in three kernels per group of levels:
 //
-//   partition  every CTA takes a tile of 8192 consecutive contributions (sample-major, corner-minor)
+//   partition  every CTA takes a tile of 16384 consecutive contributions (sample-major, corner-minor)
 //              of one level, computes their table indices and weighted gradients, and writes them
 //              *stably sorted by bucket* (a bucket = 2^shift consecutive table entries) into the
 //              tile's own record area, together with the tile's bucket offsets.  Ranks come from
 //              warp match/ballot arithmetic and per-warp counters - no atomics, order preserved.
-//   accumulate one warp per (bucket, tile group): walks the bucket's segments of its tiles in tile
-//              order and adds each record into a warp-private shared-memory accumulator; the lane
-//              that owns an entry (entry mod 32) is the only one that touches it, and it does so in
-//              record order.  The result goes straight to the gradient table, or to a per-group
-//              partial table when coarse levels are split over several groups for parallelism.
+//   accumulate one warp per (bucket, tile group): walks the bucket's segments of its tiles and adds the
+//              records, 32 per round, into a warp-private shared-memory accumulator; records of one
+//              round that hit the same entry are ranked by lane and added one after the other, so
+//              every entry sees its additions in an order fixed by the record layout.  The result
+//              goes straight to the gradient table, or to a per-group partial table when coarse
+//              levels are split over several groups for parallelism.
 //   combine    adds the per-group partial tables in group order.
 //
-// Summation order per table entry = ascending (sample, corner): independent of scheduling, so two
-// runs give identical bits.
+// The summation order per table entry depends only on the record layout (itself a pure function of
+// the inputs), never on scheduling, so two runs give identical bits.
 #include "grid.h"
 #include "grid_device.cuh"
 
@@ -29,10 +30,11 @@ namespace tnn {
 
 namespace {
 
-constexpr int kTile = 8192;      // contributions per partition CTA
+constexpr int kTile = 16384;     // contributions per partition CTA
 constexpr int kWarpsA = 8;       // warps of a partition CTA
 constexpr int kRounds = kTile / (kWarpsA * 32);
-constexpr int kMaxBuckets = 4096;
+constexpr int kMaxBuckets = 1024; // per level; keeps the per-warp counters small enough for 4 CTAs per SM
+constexpr int kTargetUnits = 4096; // accumulate warps wanted per level
 constexpr int kPassLevels = 16;  // levels handled by one launch triple
 constexpr int kWarpsB = 8;       // warps (= units) of an accumulate CTA
 constexpr size_t kScratchCap = (size_t)1 << 30;
@@ -53,7 +55,7 @@ struct DetPass {
     int n_levels;
     uint32_t n_tiles;
     uint32_t total_units;
-    uint32_t corners;         // contributions per sample
+    uint32_t corner_shift;    // log2(contributions per sample)
     uint64_t n_contrib;       // batch * corners
     DetLevel lv[kPassLevels];
 };
@@ -68,7 +70,7 @@ LevelPlan plan_level(uint32_t T, uint32_t F, uint32_t n_tiles) {
     lp.shift = 7;
     while (((T + (1u << lp.shift) - 1) >> lp.shift) > (uint32_t)kMaxBuckets) ++lp.shift;
     lp.n_buckets = (T + (1u << lp.shift) - 1) >> lp.shift;
-    uint32_t g = (kMaxBuckets + lp.n_buckets - 1) / lp.n_buckets;
+    uint32_t g = (kTargetUnits + lp.n_buckets - 1) / lp.n_buckets;
     g = std::max(1u, std::min(g, n_tiles));
     lp.tiles_per_group = (n_tiles + g - 1) / g;
     lp.groups = (n_tiles + lp.tiles_per_group - 1) / lp.tiles_per_group;
@@ -85,19 +87,19 @@ uint32_t corners_of(const GridParams &p) { return p.interpolation == INTERP_NEAR
 // table index and weighted gradient of contribution c of one level
 template <int D, int F, typename DyT>
 __device__ __forceinline__ bool contribution(const GridParams &p, uint32_t level, uint32_t hsize, uint32_t res,
-                                             float scale, uint64_t c, uint64_t n_contrib, uint32_t corners,
+                                             float scale, uint64_t c, uint64_t n_contrib, uint32_t corner_shift,
                                              const float *__restrict__ x, const DyT *__restrict__ dy, uint32_t &index,
                                              float (&val)[F]) {
     if (c >= n_contrib) return false;
-    const uint64_t i = c / corners;
-    const uint32_t corner = (uint32_t)(c % corners);
+    const uint64_t i = c >> corner_shift;
+    const uint32_t corner = (uint32_t)c & ((1u << corner_shift) - 1u);
     float w[D], xin[D];
     uint32_t g[D];
 #pragma unroll
     for (int d = 0; d < D; ++d) xin[d] = __ldg(x + i * D + d);
     grid_pos<D>(xin, scale, p.interpolation, w, g);
     float weight = 1.0f;
-    if (corners > 1) {
+    if (corner_shift > 0) {
 #pragma unroll
         for (int d = 0; d < D; ++d) {
             if ((corner & (1u << d)) == 0) {
@@ -122,9 +124,11 @@ grid_bwd_partition_kernel(const GridParams p, const DetPass ps, const float *__r
     const DetLevel lv = ps.lv[blockIdx.y];
     const uint32_t NB = lv.n_buckets; // bucket NB collects the padding of the last tile
     uint16_t *cnt = reinterpret_cast<uint16_t *>(sm_raw);                           // [kWarpsA][NB + 1]
-    uint32_t *seg = reinterpret_cast<uint32_t *>(sm_raw + (((size_t)kWarpsA * (NB + 1) * 2 + 15) & ~(size_t)15)); // [NB + 2]
+    const size_t cnt_bytes = ((size_t)kWarpsA * (NB + 1) * 2 + 15) & ~(size_t)15;
+    uint32_t *seg = reinterpret_cast<uint32_t *>(sm_raw + cnt_bytes);                // [NB + 2]
+    const size_t seg_bytes = ((size_t)(NB + 2) * 4 + 15) & ~(size_t)15;
+    uint16_t *ranks = reinterpret_cast<uint16_t *>(sm_raw + cnt_bytes + seg_bytes);  // [kRounds][threads]
     __shared__ uint32_t chunk_sum[kWarpsA * 32];
-    __shared__ uint16_t ranks[kTile]; // rank of every contribution of the tile, [round][thread]
 
     const uint32_t tile = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -143,7 +147,7 @@ grid_bwd_partition_kernel(const GridParams p, const DetPass ps, const float *__r
         uint32_t index;
         float val[F];
         const bool valid = contribution<D, F, DyT>(p, lv.level, hsize, res, scale, c0 + r * 32 + lane, ps.n_contrib,
-                                                    ps.corners, x, dy, index, val);
+                                                    ps.corner_shift, x, dy, index, val);
         const uint32_t bucket = valid ? (index >> lv.shift) : NB;
         const uint32_t peers = __match_any_sync(0xffffffffu, bucket);
         const uint32_t below = __popc(peers & ((1u << lane) - 1u));
@@ -199,22 +203,22 @@ grid_bwd_partition_kernel(const GridParams p, const DetPass ps, const float *__r
     for (uint32_t b = threadIdx.x; b < n_b; b += blockDim.x) offs[b] = seg[b];
 
     // ---- phase 3: recompute and write every record to its sorted position inside the tile's area
-    uint32_t *rec_meta = reinterpret_cast<uint32_t *>(scratch + lv.rec_off);
-    float *rec_val = reinterpret_cast<float *>(scratch + lv.rec_off) + (size_t)ps.n_tiles * kTile;
-    const size_t n_rec = (size_t)ps.n_tiles * kTile;
+    // a record = {entry index inside its bucket, F weighted gradients}, stored contiguously
+    uint32_t *rec = reinterpret_cast<uint32_t *>(scratch + lv.rec_off);
 #pragma unroll 1
     for (int r = 0; r < kRounds; ++r) {
         uint32_t index;
         float val[F];
         const bool valid = contribution<D, F, DyT>(p, lv.level, hsize, res, scale, c0 + r * 32 + lane, ps.n_contrib,
-                                                    ps.corners, x, dy, index, val);
+                                                    ps.corner_shift, x, dy, index, val);
         if (!valid) continue;
         const uint32_t bucket = index >> lv.shift;
         const uint32_t rk = ranks[r * (kWarpsA * 32) + threadIdx.x];
         const size_t pos = (size_t)tile * kTile + seg[bucket] + wcnt[bucket] + rk;
-        rec_meta[pos] = index & ((1u << lv.shift) - 1u);
+        uint32_t *r_out = rec + pos * (1 + F);
+        r_out[0] = index & ((1u << lv.shift) - 1u);
 #pragma unroll
-        for (int f = 0; f < F; ++f) rec_val[(size_t)f * n_rec + pos] = val[f];
+        for (int f = 0; f < F; ++f) r_out[1 + f] = __float_as_uint(val[f]);
     }
 }
 
@@ -242,83 +246,75 @@ grid_bwd_accumulate_kernel(const GridParams p, const DetPass ps, const uint8_t *
 
     const uint32_t n_b = lv.n_buckets + 1;
     const uint32_t *offs = reinterpret_cast<const uint32_t *>(scratch + lv.offs_off);
-    const uint32_t *rec_meta = reinterpret_cast<const uint32_t *>(scratch + lv.rec_off);
-    const size_t n_rec = (size_t)ps.n_tiles * kTile;
-    const float *rec_val = reinterpret_cast<const float *>(scratch + lv.rec_off) + n_rec;
+    const uint32_t *rec = reinterpret_cast<const uint32_t *>(scratch + lv.rec_off);
     const uint32_t t0 = g * lv.tiles_per_group;
     const uint32_t t1 = min(t0 + lv.tiles_per_group, ps.n_tiles);
 
-    auto apply = [&](uint32_t m, const float (&v)[F]) {
-        if ((m & 31u) == (uint32_t)lane) {
+    // One round adds up to 32 records (one per lane) into the accumulator.  Lanes whose records hit the
+    // same entry are ranked by lane and take turns, so the additions into an entry happen in lane order;
+    // lanes with distinct entries add at once.  The order is a fixed function of the record layout.
+    auto add_round = [&](bool active, uint32_t m, const float (&v)[F]) {
+        const uint32_t key = active ? m : (0x80000000u | (uint32_t)lane);
+        const uint32_t peers = __match_any_sync(0xffffffffu, key);
+        const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
+        const uint32_t max_rank = __reduce_max_sync(0xffffffffu, active ? rank : 0u);
+        for (uint32_t r = 0; r <= max_rank; ++r) {
+            if (active && rank == r) {
 #pragma unroll
-            for (int f = 0; f < F; ++f) acc[m * F + f] += v[f];
+                for (int f = 0; f < F; ++f) acc[m * F + f] += v[f];
+            }
+            __syncwarp();
         }
     };
 
+    constexpr int R = 8; // records of its segment every lane pre-loads
     for (uint32_t tb = t0; tb < t1; tb += 32) {
-        // every lane looks up the segment of one tile and pre-loads its first two records
+        // every lane looks up the segment of one tile and pre-loads its first R records
         const uint32_t my_tile = tb + lane;
         uint32_t s = 0, n = 0;
         if (my_tile < t1) {
-            s = offs[(size_t)my_tile * n_b + b];
-            n = offs[(size_t)my_tile * n_b + b + 1] - s;
+            s = __ldg(offs + (size_t)my_tile * n_b + b);
+            n = __ldg(offs + (size_t)my_tile * n_b + b + 1) - s;
         }
-        uint32_t m0 = 0, m1 = 0;
-        float v0[F], v1[F];
+        uint32_t mr[R];
+        float vr[R][F];
+        const uint32_t *seg_rec = rec + ((size_t)my_tile * kTile + s) * (1 + F);
 #pragma unroll
-        for (int f = 0; f < F; ++f) v0[f] = v1[f] = 0.0f;
-        const size_t base = (size_t)my_tile * kTile + s;
-        if (n > 0) {
-            m0 = rec_meta[base];
+        for (int k = 0; k < R; ++k) {
+            mr[k] = 0;
 #pragma unroll
-            for (int f = 0; f < F; ++f) v0[f] = rec_val[(size_t)f * n_rec + base];
-        }
-        if (n > 1) {
-            m1 = rec_meta[base + 1];
+            for (int f = 0; f < F; ++f) vr[k][f] = 0.0f;
+            if ((uint32_t)k < n) {
+                mr[k] = __ldg(seg_rec + k * (1 + F));
 #pragma unroll
-            for (int f = 0; f < F; ++f) v1[f] = rec_val[(size_t)f * n_rec + base + 1];
-        }
-        const uint32_t tiles_here = min(32u, t1 - tb);
-        for (uint32_t t = 0; t < tiles_here; ++t) {
-            const uint32_t nt = __shfl_sync(0xffffffffu, n, t);
-            if (nt == 0) continue;
-            {
-                const uint32_t m = __shfl_sync(0xffffffffu, m0, t);
-                float v[F];
-#pragma unroll
-                for (int f = 0; f < F; ++f) v[f] = __shfl_sync(0xffffffffu, v0[f], t);
-                apply(m, v);
+                for (int f = 0; f < F; ++f) vr[k][f] = __uint_as_float(__ldg(seg_rec + k * (1 + F) + 1 + f));
             }
-            if (nt > 1) {
-                const uint32_t m = __shfl_sync(0xffffffffu, m1, t);
-                float v[F];
+        }
+        const uint32_t n_max = __reduce_max_sync(0xffffffffu, n);
 #pragma unroll
-                for (int f = 0; f < F; ++f) v[f] = __shfl_sync(0xffffffffu, v1[f], t);
-                apply(m, v);
-            }
-            if (nt > 2) {
-                // long segment (coarse levels): stream the rest 32 records at a time
+        for (int k = 0; k < R; ++k)
+            if ((uint32_t)k < n_max) add_round((uint32_t)k < n, mr[k], vr[k]); // k-th record of each segment, in tile order
+        if (n_max > (uint32_t)R) {
+            // long segments (coarse levels): stream the rest of each, 32 records per round
+            const uint32_t tiles_here = min(32u, t1 - tb);
+            for (uint32_t t = 0; t < tiles_here; ++t) {
+                const uint32_t nt = __shfl_sync(0xffffffffu, n, t);
+                if (nt <= (uint32_t)R) continue;
                 const uint32_t st = __shfl_sync(0xffffffffu, s, t);
-                const size_t tbase = (size_t)(tb + t) * kTile;
-                for (uint32_t i = st + 2; i < st + nt; i += 32) {
+                const uint32_t *trec = rec + (size_t)(tb + t) * kTile * (1 + F);
+                for (uint32_t i = st + R; i < st + nt; i += 32) {
                     const uint32_t idx = i + lane;
+                    const bool act = idx < st + nt;
                     uint32_t mm = 0;
                     float vv[F];
 #pragma unroll
                     for (int f = 0; f < F; ++f) vv[f] = 0.0f;
-                    if (idx < st + nt) {
-                        mm = rec_meta[tbase + idx];
+                    if (act) {
+                        mm = __ldg(trec + (size_t)idx * (1 + F));
 #pragma unroll
-                        for (int f = 0; f < F; ++f) vv[f] = rec_val[(size_t)f * n_rec + tbase + idx];
+                        for (int f = 0; f < F; ++f) vv[f] = __uint_as_float(__ldg(trec + (size_t)idx * (1 + F) + 1 + f));
                     }
-                    const uint32_t cnt = min(32u, st + nt - i);
-                    for (uint32_t j = 0; j < cnt; ++j) {
-                        const uint32_t m = __shfl_sync(0xffffffffu, mm, j);
-                        float v[F];
-#pragma unroll
-                        for (int f = 0; f < F; ++f) v[f] = __shfl_sync(0xffffffffu, vv[f], j);
-                        apply(m, v);
-                    }
+                    add_round(act, mm, vv);
                 }
             }
         }
@@ -392,7 +388,7 @@ cudaError_t run_det(const GridParams &p, const float *x, const void *dy, int dy_
         DetPass ps{};
         ps.n_levels = (int)std::min<size_t>(lay.levels_per_pass, active.size() - first);
         ps.n_tiles = n_tiles;
-        ps.corners = corners;
+        ps.corner_shift = (p.interpolation == INTERP_NEAREST) ? 0u : p.n_dims;
         ps.n_contrib = n_contrib;
         uint32_t units = 0, nb_max = 0, e_max = 0;
         bool any_groups = false;
@@ -414,7 +410,8 @@ cudaError_t run_det(const GridParams &p, const float *x, const void *dy, int dy_
             t_max = std::max(t_max, T);
         }
         ps.total_units = units;
-        const size_t smem_a = (((size_t)kWarpsA * (nb_max + 1) * 2 + 15) & ~(size_t)15) + (size_t)(nb_max + 2) * 4;
+        const size_t smem_a = (((size_t)kWarpsA * (nb_max + 1) * 2 + 15) & ~(size_t)15) +
+                              (((size_t)(nb_max + 2) * 4 + 15) & ~(size_t)15) + (size_t)kTile * 2;
         const size_t smem_b = (size_t)kWarpsB * e_max * F * sizeof(float);
         if (smem_a > 200 * 1024 || smem_b > 200 * 1024) return cudaErrorInvalidConfiguration;
         dim3 grid_a(n_tiles, ps.n_levels);

@@ -39,6 +39,8 @@ __device__ __forceinline__ uint32_t grid_index(int grid_type, int hash_type, uin
         }
     }
     if (grid_type == GRID_HASH && hashmap_size < stride) index = grid_hash<D>(hash_type, g);
+    // same value as index % hashmap_size; table sizes are powers of two on all but the coarsest levels
+    if ((hashmap_size & (hashmap_size - 1u)) == 0u) return index & (hashmap_size - 1u);
     return index % hashmap_size;
 }
 
