@@ -74,6 +74,18 @@ void make_act_tmap(CUtensorMap *m, const void *base, size_t rows, int width, int
     if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
 }
 
+// fp32 targets [rows][width] as 128-row boxes of 32 columns (128 bytes, the swizzle span)
+void make_tgt_tmap(CUtensorMap *m, const float *base, size_t rows, int width) {
+    cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)width * sizeof(float)};
+    cuuint32_t box[2] = {32, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = get_encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+}
+
 int device_checks() {
     int dev = 0;
     TNN_CUDA(cudaGetDevice(&dev));
@@ -373,6 +385,8 @@ int tnn_network_train_step(tnn_network *n, const void *x, const float *targets, 
         p.wimg = n->wimg;
         p.targets = targets;
         p.n_targets = n_targets;
+        p.tgt_tma = (n_targets == n->width && n->width >= 32 && reinterpret_cast<uintptr_t>(targets) % 16 == 0) ? 1 : 0;
+        if (p.tgt_tma) make_tgt_tmap(&p.tm_tgt, targets, batch, n->width);
         p.dw_partials = n->dw_slabs;
         p.loss_partials = n->loss_partials;
         p.batch = batch;

@@ -129,8 +129,10 @@ template <int A> __device__ __forceinline__ uint32_t act_pack_t(float lo, float 
 }
 template <int A> __device__ __forceinline__ uint32_t act_bwd_pack_t(float lo, float hi, uint32_t fwd) {
     if constexpr (A == ACT_RELU) {
-        if (!(ptx::bf16lo_to_f32(fwd) > 0.0f)) lo = 0.0f;
-        if (!(ptx::bf16hi_to_f32(fwd) > 0.0f)) hi = 0.0f;
+        // keep the gradient where the stored activation is > 0: one packed compare gives 0xffff per kept half
+        __nv_bfloat162 f2;
+        memcpy(&f2, &fwd, sizeof(f2));
+        return ptx::pack_bf16x2(lo, hi) & __hgt2_mask(f2, __floats2bfloat162_rn(0.0f, 0.0f));
     } else if constexpr (A == ACT_SIGMOID) {
         const float sl = ptx::bf16lo_to_f32(fwd), sh = ptx::bf16hi_to_f32(fwd);
         lo *= sl * (1.0f - sl);

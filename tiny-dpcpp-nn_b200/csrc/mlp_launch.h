@@ -54,6 +54,8 @@ struct TrainLaunch {
     const __nv_bfloat16 *wimg;
     const float *targets;   // [batch][n_targets] fp32
     int n_targets;
+    CUtensorMap tm_tgt;     // the same targets as a tiled map, box 128 x 32 fp32 (valid when tgt_tma)
+    int tgt_tma;            // targets are as wide as the network and 16-byte aligned: stage them with TMA
     float *dw_partials;     // [grid][L+1][W][W] fp32, layout (out, in)
     float *loss_partials;   // [grid] fp32
     size_t batch;

@@ -22,18 +22,25 @@
 #include "mlp_common.cuh"
 #include "mlp_launch.h"
 
+#include <cstdio>
+
 namespace tnn {
 
 constexpr int kPipeMaxMat = 6; // (L + 3) * W TMEM columns and L + 6 tiles of shared memory must fit
 
-template <int W> struct PipeSmem {
+// TGT: the fp32 targets of a tile (128 x W, twice the bytes of a bf16 tile) are staged by TMA into the delta_L
+// buffer plus one more tile right behind it; the loss step pulls its slice into registers before delta_L is written.
+template <int W, bool TGT> struct PipeSmem {
     using T = Tile<W>;
     // delta tiles first (see mlp_train.cu: the M = 64 weight-gradient GEMM over-reads past them for W < 64)
     static constexpr int DL = 0;                                  // delta_L: forward stage -> backward stage
-    __host__ __device__ static constexpr int DP(int p) { return (1 + p) * T::ACT_BYTES; } // delta ping-pong
-    __host__ __device__ static constexpr int X(int b) { return (3 + b) * T::ACT_BYTES; }  // input tiles
-    __host__ __device__ static constexpr int AB(int i) { return (5 + i) * T::ACT_BYTES; } // L + 1 shared activation buffers
-    __host__ __device__ static constexpr int WBUF(int n_mat) { return (5 + n_mat) * T::ACT_BYTES; }
+    static constexpr int NB = TGT ? 2 : 1;                        // tiles in front of the ping-pong buffers
+    static constexpr int TGT_BOX_BYTES = 128 * 128;               // one box: 128 rows x 32 fp32
+    static constexpr int TGT_BOXES = W / 32;
+    __host__ __device__ static constexpr int DP(int p) { return (NB + p) * T::ACT_BYTES; } // delta ping-pong
+    __host__ __device__ static constexpr int X(int b) { return (NB + 2 + b) * T::ACT_BYTES; }  // input tiles
+    __host__ __device__ static constexpr int AB(int i) { return (NB + 4 + i) * T::ACT_BYTES; } // L + 1 shared activation buffers
+    __host__ __device__ static constexpr int WBUF(int n_mat) { return (NB + 4 + n_mat) * T::ACT_BYTES; }
     static constexpr int GROUP_THREADS = 256; // one epilogue stage: two threads per tile row
     static constexpr int GROUP_WARPS = GROUP_THREADS / 32;
     static constexpr int THREADS = 128 + 2 * GROUP_THREADS;
@@ -52,22 +59,44 @@ struct PipeBarriers {
     uint64_t dp_free[2];               // weight-gradient GEMM that read delta ping-pong buffer p is complete
     uint64_t ab_free[kPipeMaxMat + 1]; // activation buffer i: mask read by the backward stage and weight-gradient GEMM done
     uint64_t all_done;
+    uint64_t tgt_full;                 // targets of the current tile have landed
+    uint64_t tgt_read;                 // every warp of the forward stage has pulled its targets into registers
     uint32_t tmem_base;
     uint32_t abort_flag;
     float loss_red[8];
 };
 
-template <int W>
-__global__ void __launch_bounds__(PipeSmem<W>::THREADS, 1)
-mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *__restrict__ wimg,
+// Cycle accounting for tuning (PROF instantiations only): CTA 0 prints how many cycles one thread of every
+// role spent in each region.
+#define TNN_TIC() ([&]() { if constexpr (PROF) return (long long)clock64(); else return 0ll; }())
+#define TNN_TOC(slot, t0) do { if constexpr (PROF) prof_acc[slot] += (long long)clock64() - (t0); } while (0)
+// Time stamp of one event of the tile kProfTile of CTA 0 (all roles share the SM's clock).
+constexpr int kProfTile = 10;
+// PROF only: the issuer waits for the completion of the GEMM it just issued and stamps it.
+#define TNN_DONE(t, which, cnt, id) do { if constexpr (PROF) { if (blockIdx.x == 0) { ptx::mma_commit(&prof_bar[which]); \
+    ptx::mbar_wait_busy(&prof_bar[which], (cnt) & 1u, abort_flag); ++(cnt); TNN_EV(t, id); } } } while (0)
+#define TNN_EV(t, id) do { if constexpr (PROF) { if ((t) == kProfTile && blockIdx.x == 0) prof_ev[id] = (long long)clock64(); } } while (0)
+
+template <int W, bool TGT, bool PROF = false>
+__global__ void __launch_bounds__(PipeSmem<W, TGT>::THREADS, 1)
+mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_tgt,
+                      const __nv_bfloat16 *__restrict__ wimg,
                       const float *__restrict__ targets, int n_targets, float *__restrict__ dw_slabs,
                       float *__restrict__ loss_partials, size_t batch, int n_tiles, int n_mat, int act, int out_act,
                       float loss_scale, float inv_n, int *status) {
     using T = Tile<W>;
-    using S = PipeSmem<W>;
+    using S = PipeSmem<W, TGT>;
+    [[maybe_unused]] long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    [[maybe_unused]] const long long prof_t_all = TNN_TIC();
+    [[maybe_unused]] uint32_t prof_cnt = 0;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ PipeBarriers bars;
+    __shared__ long long prof_ev[PROF ? 96 : 1];
+    __shared__ uint64_t prof_bar[3];
+    if constexpr (PROF) {
+        if (threadIdx.x < 96) prof_ev[threadIdx.x] = 0;
+    }
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -100,9 +129,15 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
         ptx::mbar_init(&bars.dwgo_f, S::GROUP_WARPS);
         for (int i = 0; i <= kPipeMaxMat; ++i) ptx::mbar_init(&bars.ab_free[i], S::GROUP_WARPS + 1);
         ptx::mbar_init(&bars.all_done, 1);
+        ptx::mbar_init(&bars.tgt_full, 1);
+        ptx::mbar_init(&bars.tgt_read, S::GROUP_WARPS);
+        if constexpr (PROF) {
+            for (int i = 0; i < 3; ++i) ptx::mbar_init(&prof_bar[i], 1);
+        }
         bars.abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tmap(&tm_x);
+        if constexpr (TGT) ptx::prefetch_tmap(&tm_tgt);
     }
     if (warp == 1) {
         ptx::tmem_alloc(&bars.tmem_base, kTmemCols);
@@ -134,50 +169,82 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
                 for (int at = 0; at < T::KATOMS; ++at)
                     ptx::tma_load_2d(smem + S::X(b) + at * T::ACT_ATOM_BYTES, &tm_x, at * T::ATOM_COLS, tile * T::TM,
                                      &bars.x_full[b]);
+                if constexpr (TGT) {
+                    // the staging area overlaps delta_L: both GEMMs that read delta_L of the previous tile are complete
+                    if (t > 0 && !ptx::mbar_wait(&bars.dl_free, (t - 1) & 1, abort_flag)) {
+                        atomicExch(status, KS_TIMEOUT_PRODUCER | 2);
+                        break;
+                    }
+                    ptx::mbar_arrive_expect_tx(&bars.tgt_full, (uint32_t)(S::TGT_BOXES * S::TGT_BOX_BYTES));
+                    for (int bx = 0; bx < S::TGT_BOXES; ++bx)
+                        ptx::tma_load_2d(smem + S::DL + bx * S::TGT_BOX_BYTES, &tm_tgt, bx * 32, tile * T::TM,
+                                         &bars.tgt_full);
+                }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ forward chain issuer
-        if (lane == 0 && my_tiles > 0) {
+        if (my_tiles > 0) { // all lanes run the loop, one elected lane issues (see ptx::elect_one)
             constexpr uint32_t idesc = ptx::make_idesc_bf16(128, W, 0, 1); // B = W_l read MN-major
             const uint64_t x_desc0 = T::kdesc_base(smem_base + S::X(0));
             const uint64_t ab_desc0 = T::kdesc_base(smem_base + S::AB(0));
             const uint64_t w_desc0 = T::mndesc_base(smem_base + S::WBUF(n_mat), T::WGT_ATOM_BYTES);
             bool ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
-            if (!ok) atomicExch(status, KS_TIMEOUT_WEIGHTS);
+            if (!ok && lane == 0) atomicExch(status, KS_TIMEOUT_WEIGHTS);
             uint32_t fr_parity = 0;
             for (int t = 0; ok && t < my_tiles; ++t) {
                 const int b = t & 1;
+                const long long t_w0 = TNN_TIC();
                 if (t > 0) { // the loss step of the previous tile has drained the accumulator
                     ok = ptx::mbar_wait_busy(&bars.f_ready, fr_parity, abort_flag);
                     fr_parity ^= 1u;
                 }
+                TNN_TOC(0, t_w0);
                 if (ok) ok = ptx::mbar_wait_busy(&bars.x_full[b], (t >> 1) & 1, abort_flag);
                 if (!ok) {
-                    atomicExch(status, KS_TIMEOUT_MMA | 1);
+                    if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 1);
                     break;
                 }
                 ptx::tc_fence_after_sync();
-                T::template issue_chain<true>(accf_tmem, x_desc0 + (uint64_t)(b * T::ACT_UNITS), w_desc0, idesc);
-                ptx::mma_commit(&bars.accf_full);
-                ptx::mma_commit(&bars.x_empty[b]);
+                if (ptx::elect_one()) {
+                    TNN_EV(t, 40);
+                    T::template issue_chain<true>(accf_tmem, x_desc0 + (uint64_t)(b * T::ACT_UNITS), w_desc0, idesc);
+                    ptx::mma_commit(&bars.accf_full);
+                    ptx::mma_commit(&bars.x_empty[b]);
+                    TNN_EV(t, 45);
+                    TNN_DONE(t, 0, prof_cnt, 80);
+                }
+                __syncwarp();
                 for (int l = 1; l <= L; ++l) {
+                    const long long t_w = TNN_TIC();
                     if (!ptx::mbar_wait_busy(&bars.f_ready, fr_parity, abort_flag)) {
-                        atomicExch(status, KS_TIMEOUT_MMA | 2 | (l << 4));
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 2 | (l << 4));
                         ok = false;
                         break;
                     }
+                    TNN_TOC(0, t_w);
                     fr_parity ^= 1u;
                     ptx::tc_fence_after_sync();
-                    T::template issue_chain<true>(accf_tmem, ab_desc0 + (uint64_t)(ab_index(t, l) * T::ACT_UNITS),
-                                                  w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
-                    ptx::mma_commit(&bars.accf_full);
+                    if (ptx::elect_one()) {
+                        TNN_EV(t, 40 + l);
+                        T::template issue_chain<true>(accf_tmem, ab_desc0 + (uint64_t)(ab_index(t, l) * T::ACT_UNITS),
+                                                      w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
+                        ptx::mma_commit(&bars.accf_full);
+                        TNN_EV(t, 45 + l);
+                        TNN_DONE(t, 0, prof_cnt, 80 + l);
+                    }
+                    __syncwarp();
                 }
+            }
+            if constexpr (PROF) {
+                if (blockIdx.x == 0 && lane == 0)
+                    printf("[pipe prof] fwd issuer: tiles %d, waiting %lld of %lld cycles\n", my_tiles, prof_acc[0],
+                           (long long)clock64() - prof_t_all);
             }
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------ backward chain issuer
-        if (lane == 0 && my_tiles > 0) {
+        if (my_tiles > 0) {
             constexpr uint32_t idesc = ptx::make_idesc_bf16(128, W, 0, 0); // B = W_l read K-major
             const uint64_t dl_desc = T::kdesc_base(smem_base + S::DL);
             const uint64_t dp_desc0 = T::kdesc_base(smem_base + S::DP(0));
@@ -191,13 +258,13 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
                     br_parity ^= 1u;
                 }
                 if (!ok) {
-                    atomicExch(status, KS_TIMEOUT_MMA | 3);
+                    if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 3);
                     break;
                 }
                 for (int l = L; l >= 1; --l) {
                     if (l < L) {
                         if (!ptx::mbar_wait_busy(&bars.b_ready, br_parity, abort_flag)) {
-                            atomicExch(status, KS_TIMEOUT_MMA | 4 | (l << 4));
+                            if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 4 | (l << 4));
                             ok = false;
                             break;
                         }
@@ -205,17 +272,23 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
                     }
                     ptx::tc_fence_after_sync();
                     const uint64_t d_desc = (l == L) ? dl_desc : dp_desc0 + (uint64_t)(((L - 1 - l) & 1) * T::ACT_UNITS);
-                    T::template issue_chain<false>(accb_tmem, d_desc, w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
-                    ptx::mma_commit(&bars.accb_full);
-                    if (l == L) ptx::mma_commit(&bars.dl_free);
-                    ptx::mbar_arrive(&bars.chain_issued[ci_count & 1u]); // the weight-gradient GEMM of layer l may follow
+                    if (ptx::elect_one()) {
+                        TNN_EV(t, 50 + L - l);
+                        T::template issue_chain<false>(accb_tmem, d_desc, w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
+                        ptx::mma_commit(&bars.accb_full);
+                        if (l == L) ptx::mma_commit(&bars.dl_free);
+                        ptx::mbar_arrive(&bars.chain_issued[ci_count & 1u]); // the weight-gradient GEMM of layer l may follow
+                        TNN_EV(t, 55 + L - l);
+                        TNN_DONE(t, 1, prof_cnt, 85 + L - l);
+                    }
+                    __syncwarp();
                     ++ci_count;
                 }
             }
         }
     } else if (warp == 3) {
         // ------------------------------------------------------------ weight-gradient issuer
-        if (lane == 0 && my_tiles > 0) {
+        if (my_tiles > 0) {
             constexpr int DW_M = (W == 128) ? 128 : 64;
             constexpr uint32_t idesc = ptx::make_idesc_bf16(DW_M, W, 1, 1);
             const uint64_t x_desc0 = T::mndesc_base(smem_base + S::X(0), T::ACT_ATOM_BYTES);
@@ -239,7 +312,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
                         ++kc;
                     }
                     if (!ok) {
-                        atomicExch(status, KS_TIMEOUT_MMA | 5 | (l << 4));
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 5 | (l << 4));
                         break;
                     }
                     ptx::tc_fence_after_sync();
@@ -248,18 +321,25 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
                     const int ai = (l >= 1) ? ab_index(t, l) : 0;
                     const uint64_t a_desc = (l >= 1) ? ab_desc0 + (uint64_t)(ai * T::ACT_UNITS)
                                                      : x_desc0 + (uint64_t)(b * T::ACT_UNITS);
-                    T::issue_outer(tmem_base + (uint32_t)(2 * W + l * W), d_desc, a_desc, idesc, t > 0 ? 1u : 0u);
-                    if (l == L)
-                        ptx::mma_commit(&bars.dl_free);
-                    else
-                        ptx::mma_commit(&bars.dp_free[p]);
-                    if (l >= 1)
-                        ptx::mma_commit(&bars.ab_free[ai]);
-                    else
-                        ptx::mma_commit(&bars.x_empty[b]);
+                    if (ptx::elect_one()) {
+                        TNN_EV(t, 60 + L - l);
+                        T::issue_outer(tmem_base + (uint32_t)(2 * W + l * W), d_desc, a_desc, idesc, t > 0 ? 1u : 0u);
+                        if (l == L)
+                            ptx::mma_commit(&bars.dl_free);
+                        else
+                            ptx::mma_commit(&bars.dp_free[p]);
+                        if (l >= 1)
+                            ptx::mma_commit(&bars.ab_free[ai]);
+                        else
+                            ptx::mma_commit(&bars.x_empty[b]);
+                        TNN_EV(t, 66 + L - l);
+                        TNN_DONE(t, 2, prof_cnt, 90 + L - l);
+                    }
+                    __syncwarp();
                 }
             }
-            ptx::mma_commit(&bars.all_done);
+            if (ptx::elect_one()) ptx::mma_commit(&bars.all_done);
+            __syncwarp();
         }
     } else if (warp < 4 + S::GROUP_WARPS) {
         // ------------------------------------------------------------ forward-stage epilogue
@@ -294,20 +374,29 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
             const size_t grow = (size_t)tile * T::TM + row;
             const bool row_valid = grow < batch;
             for (int l = 0; l < L && ok; ++l) {
+                const long long t_a = TNN_TIC();
                 if (!wait_u(&bars.accf_full, af_parity, 1 | (l << 4))) {
                     ok = false;
                     break;
                 }
+                TNN_TOC(1, t_a);
+                if (threadIdx.x == 128) TNN_EV(t, l * 4);
                 af_parity ^= 1u;
                 ptx::tc_fence_after_sync();
                 uint32_t v[CPT];
+                const long long t_l = TNN_TIC();
                 load_acc(v);
+                TNN_TOC(2, t_l);
                 const int bi = ab_index(t, l + 1);
                 const int uses = ab_prior_uses(t, bi);
+                const long long t_f = TNN_TIC();
                 if (uses > 0 && !wait_u(&bars.ab_free[bi], (uses - 1) & 1, 2 | (l << 4))) {
                     ok = false;
                     break;
                 }
+                TNN_TOC(3, t_f);
+                if (threadIdx.x == 128) TNN_EV(t, l * 4 + 1);
+                const long long t_p = TNN_TIC();
                 uint8_t *dst = smem + S::AB(bi);
                 dispatch_act(act, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
@@ -321,15 +410,39 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
                         *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) = o;
                     }
                 });
+                TNN_TOC(4, t_p);
+                const long long t_h = TNN_TIC();
                 ptx::fence_proxy_async_smem();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&bars.f_ready);
+                TNN_TOC(5, t_h);
+                if (threadIdx.x == 128) TNN_EV(t, l * 4 + 2);
             }
             if (!ok) break;
+            const long long t_loss = TNN_TIC();
             // ---- output layer + L2 loss.  The target slice is requested before the wait for the last GEMM.
             float tg[CPT];
-            if (row_valid && n_targets == W) {
+            if constexpr (TGT) {
+                if (!wait_u(&bars.tgt_full, t & 1, 8)) {
+                    ok = false;
+                    break;
+                }
+                const uint8_t *src = smem + S::DL + (col0 / 32) * S::TGT_BOX_BYTES + row * 128;
+#pragma unroll
+                for (int q4 = 0; q4 < CPT / 4; ++q4) {
+                    const int chunk = (col0 % 32) / 4 + q4;
+                    const float4 t4 = *reinterpret_cast<const float4 *>(src + ((chunk ^ (row & 7)) << 4));
+                    tg[q4 * 4 + 0] = t4.x, tg[q4 * 4 + 1] = t4.y, tg[q4 * 4 + 2] = t4.z, tg[q4 * 4 + 3] = t4.w;
+                }
+                // every thread of the stage holds its targets before the first one overwrites the area with delta_L
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&bars.tgt_read);
+                if (!wait_u(&bars.tgt_read, t & 1, 9)) {
+                    ok = false;
+                    break;
+                }
+            } else if (row_valid && n_targets == W) {
 #pragma unroll
                 for (int q4 = 0; q4 < CPT / 4; ++q4) {
                     const float4 t4 = __ldg(reinterpret_cast<const float4 *>(targets + grow * W + col0) + q4);
@@ -345,14 +458,17 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
                 break;
             }
             af_parity ^= 1u;
+            if (threadIdx.x == 128) TNN_EV(t, 16);
             ptx::tc_fence_after_sync();
             uint32_t v[CPT];
             load_acc(v);
-            // delta_L of the previous tile must have been consumed by its two GEMMs
-            if (t > 0 && !wait_u(&bars.dl_free, (t - 1) & 1, 4)) {
-                ok = false;
-                break;
+            if constexpr (!TGT) { // delta_L of the previous tile must have been consumed by its two GEMMs
+                if (t > 0 && !wait_u(&bars.dl_free, (t - 1) & 1, 4)) {
+                    ok = false;
+                    break;
+                }
             }
+            if (threadIdx.x == 128) TNN_EV(t, 17);
             uint8_t *dst = smem + S::DL;
             dispatch_act(out_act, [&](auto tag) {
                 constexpr int ACT = decltype(tag)::value;
@@ -385,6 +501,15 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
                 ptx::mbar_arrive(&bars.dl_ready); // backward chain may start
                 ptx::mbar_arrive(&bars.dwgo_f);   // weight gradient of the output layer may start
             }
+            TNN_TOC(6, t_loss);
+            if (threadIdx.x == 128) TNN_EV(t, 18);
+        }
+        if constexpr (PROF) {
+            if (blockIdx.x == 0 && threadIdx.x == 128)
+                printf("[pipe prof] fwd epilogue: wait acc %lld, tmem ld %lld, wait buffer %lld, pack+store %lld, "
+                       "hand-over %lld, loss step (incl. its wait) %lld, total %lld cycles\n",
+                       prof_acc[1], prof_acc[2], prof_acc[3], prof_acc[4], prof_acc[5], prof_acc[6],
+                       (long long)clock64() - prof_t_all);
         }
         // loss partial of this CTA (fixed summation order)
         for (int o = 16; o > 0; o >>= 1) loss_local += __shfl_xor_sync(0xffffffffu, loss_local, o);
@@ -405,8 +530,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
         constexpr int CPT = S::CPT;
         const uint32_t acc_addr = accb_tmem + ((uint32_t)(quad * 32) << 16) + col0;
         uint32_t ab_parity = 0;
-        uint32_t dp_parity[2] = {0, 0};
-        int dp_writes[2] = {0, 0};
+        uint32_t dp_parity = 0, dp_written = 0; // bit p: phase to wait for / buffer p was written before
         uint32_t go_count = 0;
         bool ok = true;
         auto chunk_at = [&](int ch) {
@@ -420,10 +544,13 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
         };
         for (int t = 0; ok && t < my_tiles; ++t) {
             for (int l = L; l >= 1 && ok; --l) {
+                const long long t_a = TNN_TIC();
                 if (!wait_u(&bars.accb_full, ab_parity, 5 | (l << 4))) {
                     ok = false;
                     break;
                 }
+                TNN_TOC(1, t_a);
+                if (gw == 0 && lane == 0) TNN_EV(t, 20 + (L - l) * 4);
                 ab_parity ^= 1u;
                 ptx::tc_fence_after_sync();
                 uint32_t v[CPT];
@@ -433,14 +560,18 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
                     ptx::tmem_ld16(acc_addr, v);
                 ptx::tmem_ld_wait();
                 const int p = (L - l) & 1; // delta_{l-1} goes to ping-pong buffer (L - l) & 1
-                if (dp_writes[p] > 0) {     // all but the first write wait for the GEMM that read the buffer
-                    if (!wait_u(&bars.dp_free[p], dp_parity[p], 6 | (l << 4))) {
+                const long long t_f = TNN_TIC();
+                if ((dp_written >> p) & 1u) { // all but the first write wait for the GEMM that read the buffer
+                    if (!wait_u(&bars.dp_free[p], (dp_parity >> p) & 1u, 6 | (l << 4))) {
                         ok = false;
                         break;
                     }
-                    dp_parity[p] ^= 1u;
+                    dp_parity ^= 1u << p;
                 }
-                ++dp_writes[p];
+                dp_written |= 1u << p;
+                TNN_TOC(3, t_f);
+                if (gw == 0 && lane == 0) TNN_EV(t, 20 + (L - l) * 4 + 1);
+                const long long t_p = TNN_TIC();
                 const int ai = ab_index(t, l);
                 const uint8_t *abuf = smem + S::AB(ai);
                 uint8_t *dst = smem + S::DP(p);
@@ -459,6 +590,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
                         *reinterpret_cast<uint4 *>(dst + off) = o;
                     }
                 });
+                TNN_TOC(4, t_p);
                 ptx::fence_proxy_async_smem();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
@@ -467,8 +599,14 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
                     ptx::mbar_arrive(&bars.dwgo_b[go_count & 1u]);
                     ptx::mbar_arrive(&bars.ab_free[ai]); // this stage is done with a_l
                 }
+                if (gw == 0 && lane == 0) TNN_EV(t, 20 + (L - l) * 4 + 2);
                 ++go_count;
             }
+        }
+        if constexpr (PROF) {
+            if (blockIdx.x == 0 && threadIdx.x == 128 + S::GROUP_THREADS)
+                printf("[pipe prof] bwd epilogue: wait acc %lld, wait delta buffer %lld, mask+pack+store %lld, total %lld "
+                       "cycles\n", prof_acc[1], prof_acc[3], prof_acc[4], (long long)clock64() - prof_t_all);
         }
         // ---- drain the weight-gradient accumulators into this CTA's slab
         if (ok && my_tiles > 0 && !wait_u(&bars.all_done, 0, 7)) ok = false;
@@ -501,6 +639,15 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if constexpr (PROF) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            long long t0 = 0;
+            for (int i = 0; i < 96; ++i)
+                if (prof_ev[i] && (!t0 || prof_ev[i] < t0)) t0 = prof_ev[i];
+            for (int i = 0; i < 96; ++i)
+                if (prof_ev[i]) printf("[pipe ev] %d %lld\n", i, prof_ev[i] - t0);
+        }
+    }
     if (warp == 1) {
         __syncwarp();
         ptx::tc_fence_after_sync();
@@ -509,13 +656,20 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloa
 }
 
 // ---------------------------------------------------------------------- host side
-template <int W> static cudaError_t launch_pipe_w(TrainLaunch &p) {
+// 227 KB per CTA minus the statically allocated barriers
+constexpr size_t kPipeSmemLimit = 227 * 1024 - 2048;
+
+template <int W, bool TGT> static cudaError_t launch_pipe_w(TrainLaunch &p) {
     using T = Tile<W>;
-    using S = PipeSmem<W>;
+    using S = PipeSmem<W, TGT>;
     const size_t smem = (size_t)S::WBUF(p.n_mat) + (size_t)p.n_mat * T::WGT_BYTES + 1024;
     const int cols_needed = 2 * W + p.n_mat * W;
-    if (smem > 227 * 1024 || cols_needed > 512 || p.n_mat > kPipeMaxMat) return cudaErrorInvalidConfiguration;
-    auto kern = mlp_train_pipe_kernel<W>;
+    if (smem > kPipeSmemLimit || cols_needed > 512 || p.n_mat > kPipeMaxMat) return cudaErrorInvalidConfiguration;
+    void (*kern)(const CUtensorMap, const CUtensorMap, const __nv_bfloat16 *, const float *, int, float *, float *, size_t,
+                 int, int, int, int, float, float, int *) = mlp_train_pipe_kernel<W, TGT, false>;
+    if constexpr (W == 64 && TGT) {
+        if (p.prof) kern = mlp_train_pipe_kernel<W, TGT, true>;
+    }
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
@@ -523,18 +677,19 @@ template <int W> static cudaError_t launch_pipe_w(TrainLaunch &p) {
     p.grid_out = grid;
     if (grid == 0) return cudaSuccess;
     const float inv_n = 1.0f / ((float)p.batch * (float)W);
-    kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, p.wimg, p.targets, p.n_targets, p.dw_partials, p.loss_partials,
+    kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, TGT ? p.tm_tgt : p.tm_x, p.wimg, p.targets, p.n_targets, p.dw_partials, p.loss_partials,
                                                p.batch, n_tiles, p.n_mat, p.act, p.out_act, p.loss_scale, inv_n,
                                                p.status);
     return cudaGetLastError();
 }
 
 cudaError_t launch_mlp_train_pipe(TrainLaunch &p) {
-    switch (p.width) {
-    case 32: return launch_pipe_w<32>(p);
-    case 64: return launch_pipe_w<64>(p);
-    default: return cudaErrorInvalidConfiguration;
-    }
+    // staged targets need one more tile of shared memory: without room for it the per-thread loads remain
+    cudaError_t e = cudaErrorInvalidConfiguration;
+    if (p.tgt_tma) e = (p.width == 64) ? launch_pipe_w<64, true>(p) : (p.width == 32) ? launch_pipe_w<32, true>(p) : e;
+    if (e == cudaErrorInvalidConfiguration)
+        e = (p.width == 64) ? launch_pipe_w<64, false>(p) : (p.width == 32) ? launch_pipe_w<32, false>(p) : e;
+    return e;
 }
 
 } // namespace tnn

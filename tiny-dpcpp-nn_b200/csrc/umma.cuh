@@ -17,13 +17,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred = 0;
-    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.b32 %0, 1, 0, P;\n\t}"
-                 : "=r"(pred));
-    return pred != 0;
-}
-
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -85,6 +78,15 @@ __device__ __forceinline__ bool mbar_wait_busy(uint64_t *bar, uint32_t parity, v
     }
     *abort_flag = 1u;
     return false;
+}
+
+// One lane of a converged warp.  An issuing warp runs its loop with all 32 lanes and elects only around the
+// tcgen05 instructions: descriptors and loop state then live in uniform registers, which is what those
+// instructions take, and a burst of MMAs issues at the rate the tensor pipe drains it.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.b32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+    return pred != 0;
 }
 
 // ---------------------------------------------------------------- proxies / fences
