@@ -6,14 +6,16 @@
 //
 // One persistent CTA per SM walks over 128-row batch tiles with NSLOT tiles in flight.  Roles:
 //   warp 0            : TMA producer - stages the weights once, then streams input tiles
-//   warps 1..NSLOT    : one MMA issuer per slot (a single elected lane issues tcgen05.mma)
+//   warps 1..NSLOT    : one MMA issuer per slot (the warp runs converged, an elected lane issues tcgen05.mma)
 //   then NSLOT groups : 4 epilogue warps per slot
 // A slot is one tile in flight: its input buffer, its activation buffer(s) and one fp32
 // accumulator of W TMEM columns.  Per layer the slot's epilogue group pulls the accumulator out
-// of TMEM, applies the activation, rounds to bf16 and writes the next layer's A operand straight
-// back to swizzled shared memory (or, with TMEM_A, back to TMEM), so activations never leave the
-// SM.  With STORE_ALL every layer's activation is also written to global memory by TMA for a
-// later backward pass.
+// of TMEM, applies the activation, rounds to bf16 and writes the next layer's A operand back to TMEM
+// (TMEM_A, the inference default) or to swizzled shared memory, so activations never leave the SM.
+// With the A operand in TMEM a 128 x 64 x 16 MMA reads only its 2 KB weight slice from shared memory
+// and runs in 32 cycles; with both operands in shared memory the 6 KB of operand traffic make it 48
+// cycles and compete with the epilogue's stores.  With STORE_ALL every layer's activation is also
+// written to global memory by TMA for a later backward pass.
 //
 // The layer-to-layer chain of one tile is strictly serial (MMA -> epilogue -> MMA ...), and a
 // single thread's dependent instructions cost several cycles each, so throughput comes from
@@ -36,7 +38,7 @@ template <int W, int NSLOT, bool TMEM_A, bool STORE_ALL> struct FwdSmem {
     static constexpr int tmem_cols =
         tmem_cols_needed <= 32 ? 32 : tmem_cols_needed <= 64 ? 64 : tmem_cols_needed <= 128 ? 128
                                                               : tmem_cols_needed <= 256 ? 256 : 512;
-    static_assert(tmem_cols_needed <= 512, "TMEM overflow");
+    static constexpr bool fits_tmem = tmem_cols_needed <= 512;
     static constexpr int THREADS = 32 * (1 + NSLOT) + 128 * NSLOT;
 };
 
@@ -79,7 +81,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         for (int s = 0; s < NSLOT; ++s) {
             ptx::mbar_init(&bars.x_full[s], 1);
             ptx::mbar_init(&bars.x_empty[s], 1);
-            ptx::mbar_init(&bars.a_ready[s], 128);
+            ptx::mbar_init(&bars.a_ready[s], 4); // one arrival per epilogue warp
             ptx::mbar_init(&bars.acc_full[s], 1);
         }
         bars.abort_flag = 0;
@@ -121,7 +123,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     } else if (warp <= NSLOT) {
         // ------------------------------------------------------------ MMA issuer of slot s
         const int s = warp - 1;
-        if (lane == 0 && my_tiles > s) {
+        if (my_tiles > s) { // all lanes run the loop, one elected lane issues (see ptx::elect_one)
             constexpr uint32_t idesc = ptx::make_idesc_bf16(128, W, 0, B_MN_MAJOR ? 1 : 0);
             // every descriptor this thread will ever need, as bases that are stepped by constants
             const uint64_t x_desc = T::kdesc_base(smem_base + S::XBUF + s * T::ACT_BYTES);
@@ -133,7 +135,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
             uint64_t *const a_ready = &bars.a_ready[s];
             uint64_t *const acc_full = &bars.acc_full[s];
             bool ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
-            if (!ok) atomicExch(status, KS_TIMEOUT_WEIGHTS);
+            if (!ok && lane == 0) atomicExch(status, KS_TIMEOUT_WEIGHTS);
             uint32_t ar_parity = 0; // parity of the next a_ready completion to wait for
             uint32_t xf_parity = 0;
             const int my_slot_tiles = (my_tiles - s + NSLOT - 1) / NSLOT;
@@ -146,30 +148,36 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                     ar_parity ^= 1u;
                 }
                 if (!ok) {
-                    atomicExch(status, KS_TIMEOUT_MMA | s);
+                    if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | s);
                     break;
                 }
                 ptx::tc_fence_after_sync();
-                T::template issue_chain<B_MN_MAJOR>(d_tmem, x_desc, w_desc0, idesc);
-                ptx::mma_commit(acc_full);
-                ptx::mma_commit(&bars.x_empty[s]);
+                if (ptx::elect_one()) {
+                    T::template issue_chain<B_MN_MAJOR>(d_tmem, x_desc, w_desc0, idesc);
+                    ptx::mma_commit(acc_full);
+                    ptx::mma_commit(&bars.x_empty[s]);
+                }
+                __syncwarp();
                 uint64_t w_desc = w_desc0;
                 for (int l = 1; l <= L; ++l) {
                     w_desc += T::WGT_UNITS;
                     if (!ptx::mbar_wait(a_ready, ar_parity, abort_flag)) {
-                        atomicExch(status, KS_TIMEOUT_MMA | (l << 4) | s);
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | (l << 4) | s);
                         ok = false;
                         break;
                     }
                     ar_parity ^= 1u;
                     ptx::tc_fence_after_sync();
-                    if constexpr (TMEM_A) {
-                        T::template issue_chain_ts<B_MN_MAJOR>(d_tmem, a_tmem, w_desc, idesc);
-                    } else {
-                        const uint64_t a_desc = a_desc0 + (uint64_t)(((l - 1) & (S::NABUF - 1)) * T::ACT_UNITS);
-                        T::template issue_chain<B_MN_MAJOR>(d_tmem, a_desc, w_desc, idesc);
+                    if (ptx::elect_one()) {
+                        if constexpr (TMEM_A) {
+                            T::template issue_chain_ts<B_MN_MAJOR>(d_tmem, a_tmem, w_desc, idesc);
+                        } else {
+                            const uint64_t a_desc = a_desc0 + (uint64_t)(((l - 1) & (S::NABUF - 1)) * T::ACT_UNITS);
+                            T::template issue_chain<B_MN_MAJOR>(d_tmem, a_desc, w_desc, idesc);
+                        }
+                        ptx::mma_commit(acc_full);
                     }
-                    ptx::mma_commit(acc_full);
+                    __syncwarp();
                 }
             }
         }
@@ -251,7 +259,8 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                 else
                     ptx::fence_proxy_async_smem();
                 ptx::tc_fence_before_sync();
-                ptx::mbar_arrive(a_ready);
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(a_ready);
                 if (!to_tmem && (STORE_ALL || l == L)) {
                     ptx::named_bar_sync(1 + s, 128);
                     if (leader) {
@@ -291,7 +300,7 @@ static cudaError_t launch_variant(const FwdLaunch &p) {
     using T = Tile<W>;
     using S = FwdSmem<W, NSLOT, TMEM_A, STORE_ALL>;
     const size_t smem = (size_t)S::WBUF + (size_t)p.n_mat * T::WGT_BYTES + 1024;
-    if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
+    if (smem > 227 * 1024 - 1024 || !S::fits_tmem) return cudaErrorInvalidConfiguration;
     auto kern = mlp_fwd_kernel<W, NSLOT, STORE_ALL, TMEM_A, B_MN>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
@@ -304,8 +313,8 @@ static cudaError_t launch_variant(const FwdLaunch &p) {
 }
 
 template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
-    // variant bits (tuning): 1 = hidden activations through TMEM (inference only), 2 = MN-major weight
-    // operand, 4 = two instead of four tiles in flight
+    // variant bits (tuning): 1 = hidden activations through shared memory instead of TMEM (inference),
+    // 2 = MN-major weight operand, 4 = two instead of four tiles in flight, 8 = three tiles in flight
     if (p.store_all) {
         cudaError_t e = cudaErrorInvalidConfiguration;
         if (!(p.variant & 4)) e = launch_variant<W, 3, true, false, false>(p);
@@ -313,11 +322,16 @@ template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
         return e;
     }
     if (p.variant & 2) return launch_variant<W, 2, false, false, true>(p);
+    cudaError_t e = cudaErrorInvalidConfiguration;
     if constexpr (W >= 32) {
-        if (p.variant & 1) return launch_variant<W, 2, false, true, false>(p);
+        if (!(p.variant & 1)) {
+            if (p.variant & 8) e = launch_variant<W, 3, false, true, false>(p);
+            if (e == cudaErrorInvalidConfiguration && !(p.variant & 4)) e = launch_variant<W, 4, false, true, false>(p);
+            if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, false, true, false>(p);
+            if (e != cudaErrorInvalidConfiguration) return e;
+        }
     }
     if (p.variant & 8) return launch_variant<W, 3, false, false, false>(p);
-    cudaError_t e = cudaErrorInvalidConfiguration;
     if (!(p.variant & 4)) e = launch_variant<W, 4, false, false, false>(p);
     if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, false, false, false>(p);
     return e;

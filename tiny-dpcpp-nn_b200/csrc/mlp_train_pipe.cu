@@ -374,6 +374,18 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
             const size_t grow = (size_t)tile * T::TM + row;
             const bool row_valid = grow < batch;
             for (int l = 0; l < L && ok; ++l) {
+                // Every wait is a shared-memory round trip that queues behind the operand traffic of running
+                // GEMMs even when it passes, so the wait for the destination buffer comes first: its latency
+                // then hides under the GEMM this step waits for anyway.
+                const int bi = ab_index(t, l + 1);
+                const int uses = ab_prior_uses(t, bi);
+                const long long t_f = TNN_TIC();
+                if (uses > 0 && !wait_u(&bars.ab_free[bi], (uses - 1) & 1, 2 | (l << 4))) {
+                    ok = false;
+                    break;
+                }
+                TNN_TOC(3, t_f);
+                if (threadIdx.x == 128) TNN_EV(t, l * 4 + 1);
                 const long long t_a = TNN_TIC();
                 if (!wait_u(&bars.accf_full, af_parity, 1 | (l << 4))) {
                     ok = false;
@@ -387,15 +399,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 const long long t_l = TNN_TIC();
                 load_acc(v);
                 TNN_TOC(2, t_l);
-                const int bi = ab_index(t, l + 1);
-                const int uses = ab_prior_uses(t, bi);
-                const long long t_f = TNN_TIC();
-                if (uses > 0 && !wait_u(&bars.ab_free[bi], (uses - 1) & 1, 2 | (l << 4))) {
-                    ok = false;
-                    break;
-                }
-                TNN_TOC(3, t_f);
-                if (threadIdx.x == 128) TNN_EV(t, l * 4 + 1);
                 const long long t_p = TNN_TIC();
                 uint8_t *dst = smem + S::AB(bi);
                 dispatch_act(act, [&](auto tag) {
@@ -543,22 +546,15 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
             return r;
         };
         for (int t = 0; ok && t < my_tiles; ++t) {
+            // the forward stage has finished this tile: its stored activations may be fetched ahead of the GEMMs
+            if (!wait_u(&bars.dl_ready, t & 1, 10)) {
+                ok = false;
+                break;
+            }
             for (int l = L; l >= 1 && ok; --l) {
-                const long long t_a = TNN_TIC();
-                if (!wait_u(&bars.accb_full, ab_parity, 5 | (l << 4))) {
-                    ok = false;
-                    break;
-                }
-                TNN_TOC(1, t_a);
-                if (gw == 0 && lane == 0) TNN_EV(t, 20 + (L - l) * 4);
-                ab_parity ^= 1u;
-                ptx::tc_fence_after_sync();
-                uint32_t v[CPT];
-                if constexpr (CPT == 32)
-                    ptx::tmem_ld32(acc_addr, v);
-                else
-                    ptx::tmem_ld16(acc_addr, v);
-                ptx::tmem_ld_wait();
+                // The destination buffer and the stored forward activations are ready long before the GEMM of
+                // this step completes: wait for the former and fetch the latter first, so that both
+                // shared-memory round trips hide under the GEMM (see the forward stage).
                 const int p = (L - l) & 1; // delta_{l-1} goes to ping-pong buffer (L - l) & 1
                 const long long t_f = TNN_TIC();
                 if ((dp_written >> p) & 1u) { // all but the first write wait for the GEMM that read the buffer
@@ -571,17 +567,37 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 dp_written |= 1u << p;
                 TNN_TOC(3, t_f);
                 if (gw == 0 && lane == 0) TNN_EV(t, 20 + (L - l) * 4 + 1);
-                const long long t_p = TNN_TIC();
                 const int ai = ab_index(t, l);
                 const uint8_t *abuf = smem + S::AB(ai);
                 uint8_t *dst = smem + S::DP(p);
+                uint4 fa[CPT / 8];
+#pragma unroll
+                for (int ch = 0; ch < CPT / 8; ++ch)
+                    fa[ch] = (act != ACT_NONE) ? *reinterpret_cast<const uint4 *>(abuf + chunk_at(ch)) : make_uint4(0, 0, 0, 0);
+                const long long t_a = TNN_TIC();
+                if (!wait_u(&bars.accb_full, ab_parity, 5 | (l << 4))) {
+                    ok = false;
+                    break;
+                }
+                TNN_TOC(1, t_a);
+                if (gw == 0 && lane == 0) TNN_EV(t, 20 + (L - l) * 4);
+                ab_parity ^= 1u;
+                ptx::tc_fence_after_sync();
+                uint32_t v[CPT];
+                const long long t_l = TNN_TIC();
+                if constexpr (CPT == 32)
+                    ptx::tmem_ld32(acc_addr, v);
+                else
+                    ptx::tmem_ld16(acc_addr, v);
+                ptx::tmem_ld_wait();
+                TNN_TOC(2, t_l);
+                const long long t_p = TNN_TIC();
                 dispatch_act(act, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
 #pragma unroll
                     for (int ch = 0; ch < CPT / 8; ++ch) {
                         const int off = chunk_at(ch);
-                        uint4 f = make_uint4(0, 0, 0, 0);
-                        if constexpr (ACT != ACT_NONE) f = *reinterpret_cast<const uint4 *>(abuf + off);
+                        const uint4 f = fa[ch];
                         uint4 o;
                         o.x = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 0]), __uint_as_float(v[ch * 8 + 1]), f.x);
                         o.y = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 2]), __uint_as_float(v[ch * 8 + 3]), f.y);
@@ -605,8 +621,8 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
         }
         if constexpr (PROF) {
             if (blockIdx.x == 0 && threadIdx.x == 128 + S::GROUP_THREADS)
-                printf("[pipe prof] bwd epilogue: wait acc %lld, wait delta buffer %lld, mask+pack+store %lld, total %lld "
-                       "cycles\n", prof_acc[1], prof_acc[3], prof_acc[4], (long long)clock64() - prof_t_all);
+                printf("[pipe prof] bwd epilogue: wait acc %lld, tmem ld %lld, wait delta buffer %lld, mask+pack+store %lld, total %lld "
+                       "cycles\n", prof_acc[1], prof_acc[2], prof_acc[3], prof_acc[4], (long long)clock64() - prof_t_all);
         }
         // ---- drain the weight-gradient accumulators into this CTA's slab
         if (ok && my_tiles > 0 && !wait_u(&bars.all_done, 0, 7)) ok = false;
