@@ -68,12 +68,16 @@ struct PipeBarriers {
 
 // Cycle accounting for tuning (PROF instantiations only): CTA 0 prints how many cycles one thread of every
 // role spent in each region.
-#define TNN_TIC() ([&]() { if constexpr (PROF) return (long long)clock64(); else return 0ll; }())
-#define TNN_TOC(slot, t0) do { if constexpr (PROF) prof_acc[slot] += (long long)clock64() - (t0); } while (0)
+// (region sums and event stamps disturb each other: TNN_PROF_ACC selects which of the two a PROF build records)
+#ifndef TNN_PROF_ACC
+#define TNN_PROF_ACC 0
+#endif
+#define TNN_TIC() ([&]() { if constexpr (PROF && TNN_PROF_ACC) return (long long)clock64(); else return 0ll; }())
+#define TNN_TOC(slot, t0) do { if constexpr (PROF && TNN_PROF_ACC) prof_acc[slot] += (long long)clock64() - (t0); } while (0)
 // Time stamp of one event of the tile kProfTile of CTA 0 (all roles share the SM's clock).
 constexpr int kProfTile = 10;
 // PROF only: the issuer waits for the completion of the GEMM it just issued and stamps it.
-#define TNN_DONE(t, which, cnt, id) do { if constexpr (PROF) { if (blockIdx.x == 0) { ptx::mma_commit(&prof_bar[which]); \
+#define TNN_DONE(t, which, cnt, id) do { if constexpr (PROF && TNN_PROF_ACC) { if (blockIdx.x == 0) { ptx::mma_commit(&prof_bar[which]); \
     ptx::mbar_wait_busy(&prof_bar[which], (cnt) & 1u, abort_flag); ++(cnt); TNN_EV(t, id); } } } while (0)
 #define TNN_EV(t, id) do { if constexpr (PROF) { if ((t) == kProfTile && blockIdx.x == 0) prof_ev[id] = (long long)clock64(); } } while (0)
 
@@ -202,11 +206,11 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 const int b = t & 1;
                 const long long t_w0 = TNN_TIC();
                 if (t > 0) { // the loss step of the previous tile has drained the accumulator
-                    ok = ptx::mbar_wait_busy(&bars.f_ready, fr_parity, abort_flag);
+                    ok = ptx::mbar_wait(&bars.f_ready, fr_parity, abort_flag);
                     fr_parity ^= 1u;
                 }
                 TNN_TOC(0, t_w0);
-                if (ok) ok = ptx::mbar_wait_busy(&bars.x_full[b], (t >> 1) & 1, abort_flag);
+                if (ok) ok = ptx::mbar_wait(&bars.x_full[b], (t >> 1) & 1, abort_flag);
                 if (!ok) {
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 1);
                     break;
@@ -223,7 +227,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 __syncwarp();
                 for (int l = 1; l <= L; ++l) {
                     const long long t_w = TNN_TIC();
-                    if (!ptx::mbar_wait_busy(&bars.f_ready, fr_parity, abort_flag)) {
+                    if (!ptx::mbar_wait(&bars.f_ready, fr_parity, abort_flag)) {
                         if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 2 | (l << 4));
                         ok = false;
                         break;
@@ -261,9 +265,9 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
             bool ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
             uint32_t br_parity = 0, ci_count = 0;
             for (int t = 0; ok && t < my_tiles; ++t) {
-                ok = ptx::mbar_wait_busy(&bars.dl_ready, t & 1, abort_flag);
+                ok = ptx::mbar_wait(&bars.dl_ready, t & 1, abort_flag);
                 if (ok && t > 0) { // delta_0 of the previous tile is out: accumulator B is drained
-                    ok = ptx::mbar_wait_busy(&bars.b_ready, br_parity, abort_flag);
+                    ok = ptx::mbar_wait(&bars.b_ready, br_parity, abort_flag);
                     br_parity ^= 1u;
                 }
                 if (!ok) {
@@ -272,7 +276,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 }
                 for (int l = L; l >= 1; --l) {
                     if (l < L) {
-                        if (!ptx::mbar_wait_busy(&bars.b_ready, br_parity, abort_flag)) {
+                        if (!ptx::mbar_wait(&bars.b_ready, br_parity, abort_flag)) {
                             if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 4 | (l << 4));
                             ok = false;
                             break;
