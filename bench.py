@@ -6,6 +6,8 @@
 
 A step = one fused kernel (forward -> L2 loss -> backward -> weight-gradient reduction, activations never
 leave the SM) -> (N > 1: one NCCL all-reduce of the fp32 gradient buffer) -> Adam + weight refresh.
+`--only train|infer|grid` runs just that kernel a few times and prints a short line: the small, single-kernel
+command the profiler captures are taken from (with `--log2-batch` below the headline size).
 Prints ONE JSON line.  `value` = whole-job training samples/s with inputs resident in HBM; `e2e` =
 the same through the public API from pinned HOST buffers (H2D of inputs and targets, D2H of the
 loss inside the timed region).  Extra keys: `infer` (inference throughput), `roofline` (dominant
@@ -35,6 +37,10 @@ FLOPS_FWD = 2 * WIDTH * WIDTH * N_MAT            # 40 960
 FLOPS_BWD = 2 * FLOPS_FWD - 2 * WIDTH * WIDTH    # delta chain over L matrices + L+1 weight gradients
 FLOPS_TRAIN = 3 * FLOPS_FWD                      # 122 880 (the reference's 3x model)
 BYTES_INFER = 2 * WIDTH * 2                      # x in + y out, bf16
+# DRAM bytes (read + write) per sample of the fused training kernel from a profiler capture at batch 2^19
+# (the traffic is proportional to the batch: inputs and targets are read once, nothing else is streamed)
+TRAIN_DRAM_BYTES_PER_SAMPLE = 391.0
+TRAIN_DRAM_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum at batch 2^19, scaled by the batch"
 
 
 def workload_name(batch_log2):
@@ -167,6 +173,71 @@ def run_reference_arm(args):
     }))
 
 
+# --------------------------------------------------------------------------------- single-kernel runs
+GRID_CFG = dict(otype="HashGrid", n_dims_to_encode=3, n_levels=16, n_features_per_level=2, log2_hashmap_size=19,
+                base_resolution=16, per_level_scale=2.0)
+
+
+def grid_leg(L, torch, batch, steps, timed):
+    """Forward and parameter-gradient backward of the 16-level hash grid (3-D inputs, 2 features per level)."""
+    enc = L.create_encoding("HashGrid", GRID_CFG, 32, seed=3)
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    pos = torch.rand((batch, 3), device="cuda", generator=gen)
+    dy = torch.rand((batch, 32), device="cuda", generator=gen) - 0.5
+    res = {}
+    fwd = lambda: enc.fwd(pos)  # noqa: E731
+    for name, fn in (("grid_fwd", fwd),
+                     ("grid_bwd_deterministic", lambda: enc.bwd_with_encoding_grad(dy, pos, False, False, deterministic=True)),
+                     ("grid_bwd_atomic", lambda: enc.bwd_with_encoding_grad(dy, pos, False, False, deterministic=False))):
+        for _ in range(2):
+            fn()
+        res[name] = timed(fn, steps) / steps
+    return res
+
+
+def run_only(args):
+    """One kernel, few launches: what a profiler capture is taken from."""
+    import torch
+
+    from tiny_dpcpp_nn import _lib as L
+    from tiny_dpcpp_nn.trainer import Trainer
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    batch = 1 << args.log2_batch
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    out = {"only": args.only, "log2_batch": args.log2_batch, "steps": args.steps}
+    if args.only == "grid":
+        out.update(grid_leg(L, torch, batch, args.steps, timed))
+    else:
+        w = xavier_weights(N_MAT, WIDTH, 0)
+        net = L.create_network(WIDTH, WIDTH, N_HIDDEN, 0, 8, WIDTH, "torch.bfloat16", True, seed=0)
+        net.set_params(torch.from_numpy(w.reshape(-1)).cuda(), False)
+        gen = torch.Generator(device="cuda").manual_seed(100)
+        x = (torch.rand((batch, WIDTH), device="cuda", generator=gen) * 2 - 1).to(torch.bfloat16)
+        if args.only == "infer":
+            fn = lambda: net.inference(x)  # noqa: E731
+        else:
+            targets = torch.rand((batch, WIDTH), device="cuda", generator=gen) * 2 - 1
+            tr = Trainer(net)
+            fn = lambda: tr.forward_backward(x, targets)  # noqa: E731
+        for _ in range(max(args.warmup, 1)):
+            fn()
+        out["ms"] = timed(fn, args.steps) / args.steps
+        out["kernel_status"] = net.status()
+    print(json.dumps(out))
+
+
 # --------------------------------------------------------------------------------- GPU arm
 def run_gpu_arm(args):
     import torch
@@ -291,9 +362,20 @@ def run_gpu_arm(args):
         roof("mlp_bwd", FLOPS_BWD, act_bytes * (N_MAT + 1), "unfused path: dy + a_L..a_0 in"),
         roof("l2_loss", 0, act_bytes * 2 + WIDTH * 4, "unfused path: y in, dy out, targets in"),
     ]
+    grid_batch = 1 << 20
+    grid_ms = grid_leg(L, torch, grid_batch, max(3, min(args.steps, 10)), timed) if rank == 0 else {}
+    # per sample and level: 8 corners x 2 features (4 B each) read, position read once, 2 features written
+    grid_fwd_bytes = 16 * (8 * 2 * 4) + 3 * 4 + 32 * 4
+    grid_rooflines = [{"kernel": k, "ms": v, "batch": grid_batch,
+                       "gbs": grid_fwd_bytes * grid_batch / (v * 1e-3) * 1e-9,
+                       "frac_hbm": grid_fwd_bytes * grid_batch / (v * 1e-3) * 1e-9 / peaks["hbm_gbs"],
+                       "note": "16 levels x 8 corners x 2 fp32 features gathered (or scattered) per sample; "
+                               "the fine levels' tables exceed L2"} for k, v in grid_ms.items()]
     dom_r = rooflines[0]
     roofline = {"bound": "tensor", "kernel": "mlp_train_pipe_kernel", "achieved": dom_r["tflops"], "peak": peaks["tflops"],
-                "unit": "TFLOP/s", "frac": dom_r["frac_tensor"], "traffic": None, "peak_source": peaks["source"],
+                "unit": "TFLOP/s", "frac": dom_r["frac_tensor"],
+                "traffic": TRAIN_DRAM_BYTES_PER_SAMPLE * batch, "traffic_source": TRAIN_DRAM_SOURCE,
+                "peak_source": peaks["source"],
                 "frac_of_sustained_peak": dom_r["tflops"] / peaks["tflops_sustained"],
                 "hbm_frac_same_kernel": dom_r["frac_hbm"]}
     del interm, dy
@@ -338,7 +420,7 @@ def run_gpu_arm(args):
                       "frac_of_bf16_peak": FLOPS_FWD * infer_value * 1e-12 / world / peaks["tflops"],
                       "hbm_gbs": BYTES_INFER * infer_value * 1e-9 / world,
                       "frac_of_hbm_peak": BYTES_INFER * infer_value * 1e-9 / world / peaks["hbm_gbs"]},
-            "roofline": roofline, "rooflines": rooflines,
+            "roofline": roofline, "rooflines": rooflines, "grid_rooflines": grid_rooflines,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": batch * WIDTH * (2 + 4),
                     "d2h_bytes_per_step": 4, "steps": e2e_steps},
             "gpu_launches": 5 * args.steps,
@@ -379,9 +461,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--log2-batch", type=int, default=LOG2_BATCH)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--only", choices=["train", "infer", "grid"], help="run one kernel only (profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.only:
+        run_only(args)
     else:
         run_gpu_arm(args)
 
