@@ -1,7 +1,8 @@
 """Builds libtnn_b200.so (sm_100a only) next to this file with plain nvcc.
 
-Usage: python build.py [--force]
+Usage: python build.py [--force] [-v] [--microbench]
 The library has no torch dependency: it exports the C ABI of include/tnn_b200.h.
+--microbench also builds the stand-alone tcgen05 microbenchmark (csrc/umma_microbench.cu) next to the library.
 """
 import os
 import subprocess
@@ -61,5 +62,17 @@ def build(force=False, verbose=False):
     return OUT
 
 
+def build_microbench():
+    out = os.path.join(HERE, "umma_microbench")
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", out,
+           os.path.join(CSRC, "umma_microbench.cu")]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed for umma_microbench.cu:\n{r.stdout}\n{r.stderr}")
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--microbench" in sys.argv:
+        print(build_microbench())
