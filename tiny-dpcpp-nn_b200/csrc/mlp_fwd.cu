@@ -17,6 +17,10 @@
 // cycles and compete with the epilogue's stores.  With STORE_ALL every layer's activation is also
 // written to global memory by TMA for a later backward pass.
 //
+// Networks whose weights do not fit beside the tiles (width 128, or many layers) run with STREAM_W: every slot
+// owns a ring of two weight tiles and its issuer fetches the weights of the next layer (from L2) right before it
+// issues the GEMM of the current one, i.e. as soon as the GEMM that read that ring stage is known to be complete.
+//
 // The layer-to-layer chain of one tile is strictly serial (MMA -> epilogue -> MMA ...), and a
 // single thread's dependent instructions cost several cycles each, so throughput comes from
 // running the chains of several slots side by side: every slot has its own issuer warp and its
@@ -26,7 +30,7 @@
 
 namespace tnn {
 
-template <int W, int NSLOT, bool TMEM_A, bool STORE_ALL> struct FwdSmem {
+template <int W, int NSLOT, bool TMEM_A, bool STORE_ALL, bool STREAM_W = false> struct FwdSmem {
     using T = Tile<W>;
     // activation buffers per slot: two (ping-pong) when every layer is also streamed out by TMA,
     // one when the next layer's MMA is the only reader
@@ -40,6 +44,8 @@ template <int W, int NSLOT, bool TMEM_A, bool STORE_ALL> struct FwdSmem {
                                                               : tmem_cols_needed <= 256 ? 256 : 512;
     static constexpr bool fits_tmem = tmem_cols_needed <= 512;
     static constexpr int THREADS = 32 * (1 + NSLOT) + 128 * NSLOT;
+    // weight tiles behind WBUF: all n_mat of them, or a ring of two per slot
+    __host__ __device__ static constexpr int weight_tiles(int n_mat) { return STREAM_W ? 2 * NSLOT : n_mat; }
 };
 
 constexpr int kMaxSlots = 4;
@@ -50,17 +56,18 @@ struct FwdBarriers {
     uint64_t x_empty[kMaxSlots];
     uint64_t a_ready[kMaxSlots];
     uint64_t acc_full[kMaxSlots];
+    uint64_t wring_full[kMaxSlots][2]; // STREAM_W: weight ring stages of every slot
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
 
-template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN_MAJOR>
+template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN_MAJOR, bool STREAM_W = false>
 __global__ void __launch_bounds__(FwdSmem<W, NSLOT, TMEM_A, STORE_ALL>::THREADS, 1)
 mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                const __grid_constant__ CUtensorMap tm_interm, const __nv_bfloat16 *__restrict__ wimg,
                int n_tiles, int n_mat, int act, int out_act, int write_y, int *status) {
     using T = Tile<W>;
-    using S = FwdSmem<W, NSLOT, TMEM_A, STORE_ALL>;
+    using S = FwdSmem<W, NSLOT, TMEM_A, STORE_ALL, STREAM_W>;
     static_assert(NSLOT <= kMaxSlots, "too many slots");
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment (swizzle span)
@@ -83,6 +90,8 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
             ptx::mbar_init(&bars.x_empty[s], 1);
             ptx::mbar_init(&bars.a_ready[s], 4); // one arrival per epilogue warp
             ptx::mbar_init(&bars.acc_full[s], 1);
+            ptx::mbar_init(&bars.wring_full[s][0], 1);
+            ptx::mbar_init(&bars.wring_full[s][1], 1);
         }
         bars.abort_flag = 0;
         ptx::fence_barrier_init();
@@ -102,11 +111,13 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (lane == 0 && my_tiles > 0) {
-            ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
-            for (int l = 0; l < n_mat; ++l)
-                ptx::bulk_load(smem + S::WBUF + l * T::WGT_BYTES,
-                               reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
-                               &bars.w_full);
+            if constexpr (!STREAM_W) {
+                ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
+                for (int l = 0; l < n_mat; ++l)
+                    ptx::bulk_load(smem + S::WBUF + l * T::WGT_BYTES,
+                                   reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
+                                   &bars.w_full);
+            }
             for (int j = 0; j < my_tiles; ++j) {
                 const int s = j % NSLOT, t = j / NSLOT;
                 const int tile = blockIdx.x + j * gridDim.x;
@@ -128,13 +139,28 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
             // every descriptor this thread will ever need, as bases that are stepped by constants
             const uint64_t x_desc = T::kdesc_base(smem_base + S::XBUF + s * T::ACT_BYTES);
             const uint64_t a_desc0 = T::kdesc_base(smem_base + S::ABUF + s * S::NABUF * T::ACT_BYTES);
-            const uint64_t w_desc0 = B_MN_MAJOR ? T::mndesc_base(smem_base + S::WBUF, T::WGT_ATOM_BYTES)
-                                                : T::kdesc_base(smem_base + S::WBUF);
+            // resident weights: tile l of the image; streamed: stage 0 of this slot's ring
+            const uint32_t w_smem0 = smem_base + S::WBUF + (STREAM_W ? s * 2 * T::WGT_BYTES : 0);
+            const uint64_t w_desc0 =
+                B_MN_MAJOR ? T::mndesc_base(w_smem0, T::WGT_ATOM_BYTES) : T::kdesc_base(w_smem0);
+            [[maybe_unused]] uint32_t wg = 0; // STREAM_W: GEMMs issued so far = ring position of the current weights
+            [[maybe_unused]] auto fetch_weights = [&](int l, uint32_t g) { // W_l into ring stage g & 1 (elected lane)
+                uint64_t *bar = &bars.wring_full[s][g & 1u];
+                ptx::mbar_arrive_expect_tx(bar, (uint32_t)T::WGT_BYTES);
+                ptx::bulk_load(smem + S::WBUF + (s * 2 + (g & 1u)) * T::WGT_BYTES,
+                               reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES, bar);
+            };
             const uint32_t d_tmem = tmem_base + s * W;
             [[maybe_unused]] const uint32_t a_tmem = tmem_base + NSLOT * W + s * (W / 2);
             uint64_t *const a_ready = &bars.a_ready[s];
             uint64_t *const acc_full = &bars.acc_full[s];
-            bool ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
+            bool ok = true;
+            if constexpr (STREAM_W) {
+                if (ptx::elect_one()) fetch_weights(0, 0);
+                __syncwarp();
+            } else {
+                ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
+            }
             if (!ok && lane == 0) atomicExch(status, KS_TIMEOUT_WEIGHTS);
             uint32_t ar_parity = 0; // parity of the next a_ready completion to wait for
             uint32_t xf_parity = 0;
@@ -151,13 +177,27 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | s);
                     break;
                 }
+                if constexpr (STREAM_W) {
+                    // the GEMM that read the other ring stage is complete (its accumulator was drained): refill it
+                    // (next in this slot's sequence: W_1, or W_0 of its next tile for a single-matrix network)
+                    if (L >= 1 || t + 1 < my_slot_tiles) {
+                        if (ptx::elect_one()) fetch_weights(L >= 1 ? 1 : 0, wg + 1);
+                        __syncwarp();
+                    }
+                    if (!ptx::mbar_wait(&bars.wring_full[s][wg & 1u], (wg >> 1) & 1u, abort_flag)) {
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_WEIGHTS | 1);
+                        break;
+                    }
+                }
                 ptx::tc_fence_after_sync();
                 if (ptx::elect_one()) {
-                    T::template issue_chain<B_MN_MAJOR>(d_tmem, x_desc, w_desc0, idesc);
+                    T::template issue_chain<B_MN_MAJOR>(d_tmem, x_desc,
+                                                        w_desc0 + (STREAM_W ? (uint64_t)((wg & 1u) * T::WGT_UNITS) : 0), idesc);
                     ptx::mma_commit(acc_full);
                     ptx::mma_commit(&bars.x_empty[s]);
                 }
                 __syncwarp();
+                ++wg;
                 uint64_t w_desc = w_desc0;
                 for (int l = 1; l <= L; ++l) {
                     w_desc += T::WGT_UNITS;
@@ -167,6 +207,19 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                         break;
                     }
                     ar_parity ^= 1u;
+                    if constexpr (STREAM_W) {
+                        // next in this slot's sequence: W_{l+1}, or W_0 for its next tile
+                        if (l < L || t + 1 < my_slot_tiles) {
+                            if (ptx::elect_one()) fetch_weights(l < L ? l + 1 : 0, wg + 1);
+                            __syncwarp();
+                        }
+                        if (!ptx::mbar_wait(&bars.wring_full[s][wg & 1u], (wg >> 1) & 1u, abort_flag)) {
+                            if (lane == 0) atomicExch(status, KS_TIMEOUT_WEIGHTS | 2);
+                            ok = false;
+                            break;
+                        }
+                        w_desc = w_desc0 + (uint64_t)((wg & 1u) * T::WGT_UNITS);
+                    }
                     ptx::tc_fence_after_sync();
                     if (ptx::elect_one()) {
                         if constexpr (TMEM_A) {
@@ -178,6 +231,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                         ptx::mma_commit(acc_full);
                     }
                     __syncwarp();
+                    ++wg;
                 }
             }
         }
@@ -295,13 +349,13 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
 }
 
 // ---------------------------------------------------------------------- host side
-template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN>
+template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN, bool STREAM_W = false>
 static cudaError_t launch_variant(const FwdLaunch &p) {
     using T = Tile<W>;
-    using S = FwdSmem<W, NSLOT, TMEM_A, STORE_ALL>;
-    const size_t smem = (size_t)S::WBUF + (size_t)p.n_mat * T::WGT_BYTES + 1024;
+    using S = FwdSmem<W, NSLOT, TMEM_A, STORE_ALL, STREAM_W>;
+    const size_t smem = (size_t)S::WBUF + (size_t)S::weight_tiles(p.n_mat) * T::WGT_BYTES + 1024;
     if (smem > 227 * 1024 - 1024 || !S::fits_tmem) return cudaErrorInvalidConfiguration;
-    auto kern = mlp_fwd_kernel<W, NSLOT, STORE_ALL, TMEM_A, B_MN>;
+    auto kern = mlp_fwd_kernel<W, NSLOT, STORE_ALL, TMEM_A, B_MN, STREAM_W>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
@@ -315,10 +369,22 @@ static cudaError_t launch_variant(const FwdLaunch &p) {
 template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
     // variant bits (tuning): 1 = hidden activations through shared memory instead of TMEM (inference),
     // 2 = MN-major weight operand, 4 = two instead of four tiles in flight, 8 = three tiles in flight
+    // bit 256 = stream the weights even if they would fit
+    const bool force_stream = (p.variant & 256) != 0;
     if (p.store_all) {
         cudaError_t e = cudaErrorInvalidConfiguration;
-        if (!(p.variant & 4)) e = launch_variant<W, 3, true, false, false>(p);
-        if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, true, false, false>(p);
+        if (!force_stream) {
+            if (!(p.variant & 4)) e = launch_variant<W, 3, true, false, false>(p);
+            if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, true, false, false>(p);
+        }
+        // weights do not fit beside the tiles: per-slot weight rings
+        if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, true, false, false, true>(p);
+        if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 1, true, false, false, true>(p);
+        return e;
+    }
+    if (force_stream) {
+        cudaError_t e = launch_variant<W, 2, false, W >= 32, false, true>(p);
+        if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 1, false, W >= 32, false, true>(p);
         return e;
     }
     if (p.variant & 2) return launch_variant<W, 2, false, false, true>(p);
@@ -334,6 +400,8 @@ template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
     if (p.variant & 8) return launch_variant<W, 3, false, false, false>(p);
     if (!(p.variant & 4)) e = launch_variant<W, 4, false, false, false>(p);
     if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, false, false, false>(p);
+    if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, false, W >= 32, false, true>(p);
+    if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 1, false, W >= 32, false, true>(p);
     return e;
 }
 
