@@ -70,6 +70,37 @@ def test_forward_backward_matrix(tnn_lib, W, nh, act, oact):
         _check(dxg.float().cpu().numpy().reshape(batch, W), dx)
 
 
+@pytest.mark.parametrize("W,nh,variant", [(128, 2, 0), (128, 4, 0), (128, 8, 0), (64, 8, 0), (32, 8, 0), (16, 8, 0),
+                                          (64, 4, 256), (32, 2, 256)])
+def test_wide_and_deep_networks(tnn_lib, W, nh, variant):
+    """The reference's sweep (benchmarks/benchmark_all.cpp: widths 16..128, up to 8+ hidden layers): networks whose
+    weights do not stay resident (streamed through per-slot rings; variant 256 forces that path) and whose weight
+    gradients need more than one pass over the tensor-memory accumulators."""
+    act, oact = "relu", "none"
+    for batch in (64, 128 * 150 + 8):
+        w, x = synth.mlp_case(W, nh, batch, w_seed=3, x_seed=200 + batch)
+        n_mat = nh + 1
+        net = _net(tnn_lib, W, nh, act, oact, w)
+        net.set_variant(variant)
+        interm = O.mlp_forward(x, w, n_mat, W, act, oact, bf16=True)
+        xt = _bf16(x)
+        _check(net.inference(xt).float().cpu().numpy(), interm[-1])
+        net.fwd(xt)
+        ig = net.interm_fwd().float().cpu().numpy()
+        for l in range(1, n_mat + 1):
+            _check(ig[l], interm[l])
+        dy = O.bf16_round((np.random.default_rng(9).uniform(-1, 1, (batch, W)) / batch).astype(np.float32))
+        ib, gr, dx = O.mlp_backward(dy, ig, w, n_mat, W, act, oact, bf16=True)
+        dxg, g = net.bwd_no_encoding_grad(_bf16(dy), False, True, want_interm_bwd=True, grads_dtype=torch.float32)
+        assert net.status() == 0
+        g = g.cpu().numpy().reshape(n_mat, W, W)
+        ibg = net._interm_bwd.float().cpu().numpy()
+        for l in range(n_mat):
+            _check(ibg[l], ib[l])
+            _check(g[l], gr[l])
+        _check(dxg.float().cpu().numpy().reshape(batch, W), dx)
+
+
 def test_inference_benchmark_self_check(tnn_lib):
     """benchmarks/benchmark_inference.h:39-48, 71: weights 1 / W, input 0.1, linear => every output is 0.1."""
     W, nh, batch = 64, 4, 1 << 12
@@ -148,8 +179,6 @@ def test_reference_fixture_through_the_device(tnn_lib):
     for ci in range(len([k for k in z.files if k.endswith("_cfg")])):
         k = f"c{ci}"
         W, nh, a, oa = [int(v) for v in z[k + "_cfg"]]
-        if W == 128:
-            continue
         w = synth.xavier_weights(nh + 1, W, int(z[k + "_wseed"][0]))
         net = _net(tnn_lib, W, nh, names[a], names[oa], w)
         x = np.zeros((8, W), np.float32)

@@ -37,6 +37,9 @@ def _oracle_step(x, t, w, W, nh, act, oact):
     (32, 4, "relu", "none", 4096, 32),
     (32, 2, "sigmoid", "none", 4096, 5),
     (16, 2, "relu", "none", 4096, 16),
+    (64, 8, "relu", "none", 4096, 64),
+    (128, 2, "relu", "none", 4096, 128),
+    (128, 4, "relu", "none", 128 * 150 + 8, 128),
 ])
 def test_train_step_matches_oracle(tnn_lib, variant, W, nh, act, oact, batch, nt):
     from tiny_dpcpp_nn.trainer import Trainer

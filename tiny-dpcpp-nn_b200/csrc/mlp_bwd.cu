@@ -14,28 +14,38 @@
 // as the MN-major A operand of the weight-gradient GEMM (M = features, K = batch rows).  The
 // weight gradients of all layers accumulate in TMEM across all tiles of the CTA and are written
 // once, as one fp32 slab per CTA; a small second kernel adds the slabs in a fixed order.
+//
+// TMEM holds the chain accumulator plus one accumulator per layer, 512 columns in all.  Networks with more
+// layers than fit (width 128: three, width 64: seven) run the kernel in several passes; every pass repeats the
+// chain and reduces the weight gradients of its own group of layers [dw_lo, dw_hi).  With BIG (width 128, or
+// weights that do not fit beside the tiles) the weights are not resident: the issuer streams W_l through a ring
+// of two tiles, fetching the next one when it issues a chain GEMM, and fewer tiles are kept in flight.
 #include "mlp_common.cuh"
 #include "mlp_launch.h"
 
 namespace tnn {
 
-constexpr int kBwdRing = 3; // forward-activation tiles in flight
+constexpr int kBwdMaxRing = 3;
 
-template <int W> struct BwdSmem {
+template <int W, bool BIG> struct BwdSmem {
     using T = Tile<W>;
-    static constexpr int DY = 0;                         // 2 tiles: dL/dy of this and the next tile
-    static constexpr int DP = DY + 2 * T::ACT_BYTES;     // 2 tiles: delta ping-pong
-    static constexpr int AR = DP + 2 * T::ACT_BYTES;     // kBwdRing forward-activation tiles
-    static constexpr int WBUF = AR + kBwdRing * T::ACT_BYTES;
+    static constexpr int NDY = BIG ? 1 : 2;              // dL/dy tiles (this and the next tile)
+    static constexpr int RING = BIG ? 2 : 3;             // forward-activation tiles in flight
+    static constexpr int DY = 0;
+    static constexpr int DP = DY + NDY * T::ACT_BYTES;   // 2 tiles: delta ping-pong (directly behind DY)
+    static constexpr int AR = DP + 2 * T::ACT_BYTES;     // RING forward-activation tiles
+    static constexpr int WBUF = AR + RING * T::ACT_BYTES;
     static constexpr int DW_M = (W == 128) ? 128 : 64;   // UMMA M of the weight-gradient GEMM
+    __host__ __device__ static constexpr int weight_tiles(int n_mat) { return BIG ? 2 : n_mat; }
 };
 
 struct BwdBarriers {
     uint64_t w_full;
     uint64_t dy_full[2];
     uint64_t dy_empty[2];
-    uint64_t a_full[kBwdRing];
-    uint64_t a_empty[kBwdRing];
+    uint64_t a_full[kBwdMaxRing];
+    uint64_t a_empty[kBwdMaxRing];
+    uint64_t wring_full[2]; // BIG: weight ring stages
     uint64_t d_ready;  // epilogue -> MMA: next delta tile is in shared memory / accumulator was read
     uint64_t acc_full; // MMA -> epilogue: chain accumulator complete
     uint64_t all_done; // MMA -> epilogue: every weight-gradient MMA of this CTA has completed
@@ -43,14 +53,16 @@ struct BwdBarriers {
     uint32_t abort_flag;
 };
 
-template <int W, bool B_MN_MAJOR>
+template <int W, bool B_MN_MAJOR, bool BIG>
 __global__ void __launch_bounds__(192, 1)
 mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_interm,
                const __grid_constant__ CUtensorMap tm_ibwd, const __grid_constant__ CUtensorMap tm_dx,
                const __nv_bfloat16 *__restrict__ wimg, float *__restrict__ dw_slabs, int n_tiles, int n_mat, int act,
-               int out_act, int store_bwd, int want_dx, int tmem_cols, int *status) {
+               int out_act, int store_bwd, int want_dx, int tmem_cols, int dw_lo, int dw_hi, int *status) {
     using T = Tile<W>;
-    using S = BwdSmem<W>;
+    using S = BwdSmem<W, BIG>;
+    constexpr int kBwdRing = S::RING;
+    constexpr int NDY = S::NDY;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ BwdBarriers bars;
@@ -69,6 +81,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(&bars.dy_full[b], 1);
             ptx::mbar_init(&bars.dy_empty[b], 2); // MMA commit + epilogue leader
+            ptx::mbar_init(&bars.wring_full[b], 1);
         }
         for (int r = 0; r < kBwdRing; ++r) {
             ptx::mbar_init(&bars.a_full[r], 1);
@@ -92,22 +105,24 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
     const uint32_t tmem_base = bars.tmem_base;
     // TMEM columns: [0, W) chain accumulator, then one W-column weight-gradient accumulator per layer
     const uint32_t acc_tmem = tmem_base;
-    auto dw_tmem = [&](int l) { return tmem_base + (uint32_t)(W + l * W); };
+    auto dw_tmem = [&](int l) { return tmem_base + (uint32_t)(W + (l - dw_lo) * W); }; // dw_lo <= l < dw_hi
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (lane == 0 && my_tiles > 0) {
-            ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
-            for (int l = 0; l < n_mat; ++l)
-                ptx::bulk_load(smem + S::WBUF + l * T::WGT_BYTES,
-                               reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
-                               &bars.w_full);
+            if constexpr (!BIG) {
+                ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
+                for (int l = 0; l < n_mat; ++l)
+                    ptx::bulk_load(smem + S::WBUF + l * T::WGT_BYTES,
+                                   reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
+                                   &bars.w_full);
+            }
             int r = 0; // running index of forward-activation loads
             bool ok = true;
             for (int t = 0; ok && t < my_tiles; ++t) {
                 const int tile = blockIdx.x + t * gridDim.x;
-                const int b = t & 1;
-                if (t >= 2 && !ptx::mbar_wait(&bars.dy_empty[b], ((t >> 1) - 1) & 1, abort_flag)) {
+                const int b = t % NDY;
+                if (t >= NDY && !ptx::mbar_wait(&bars.dy_empty[b], ((t / NDY) - 1) & 1, abort_flag)) {
                     atomicExch(status, KS_TIMEOUT_PRODUCER | 1);
                     break;
                 }
@@ -133,7 +148,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0 && my_tiles > 0) {
+        if (my_tiles > 0) { // all lanes run the loop, one elected lane issues (see ptx::elect_one)
             constexpr uint32_t idesc_chain = ptx::make_idesc_bf16(128, W, 0, B_MN_MAJOR ? 1 : 0);
             constexpr uint32_t idesc_dw = ptx::make_idesc_bf16(S::DW_M, W, 1, 1);
             // base descriptors; buffers and k-steps are reached with constant adds
@@ -142,68 +157,112 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
             const uint64_t amn_desc0 = T::mndesc_base(smem_base + S::AR, T::ACT_ATOM_BYTES);   // activations, MN-major
             const uint64_t w_desc0 = B_MN_MAJOR ? T::mndesc_base(smem_base + S::WBUF, T::WGT_ATOM_BYTES)
                                                 : T::kdesc_base(smem_base + S::WBUF);
-            bool ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
-            if (!ok) atomicExch(status, KS_TIMEOUT_WEIGHTS);
+            // BIG: chain GEMM number g reads ring stage g & 1; its weights are fetched while GEMM g - 1 is issued
+            const int last_chain = want_dx ? 0 : 1; // lowest layer with a chain GEMM
+            [[maybe_unused]] uint32_t wg = 0;
+            [[maybe_unused]] auto fetch_weights = [&](int l, uint32_t g) {
+                uint64_t *bar = &bars.wring_full[g & 1u];
+                ptx::mbar_arrive_expect_tx(bar, (uint32_t)T::WGT_BYTES);
+                ptx::bulk_load(smem + S::WBUF + (g & 1u) * T::WGT_BYTES,
+                               reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES, bar);
+            };
+            bool ok = true;
+            if constexpr (BIG) {
+                if (L >= last_chain) {
+                    if (ptx::elect_one()) fetch_weights(L, 0);
+                    __syncwarp();
+                }
+            } else {
+                ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
+            }
+            if (!ok && lane == 0) atomicExch(status, KS_TIMEOUT_WEIGHTS);
             int r = 0;  // forward-activation loads consumed
             int dr = 0; // d_ready completions consumed
             for (int t = 0; ok && t < my_tiles; ++t) {
-                const int b = t & 1;
-                if (!ptx::mbar_wait(&bars.dy_full[b], (t >> 1) & 1, abort_flag)) ok = false;
+                const int b = t % NDY;
+                if (!ptx::mbar_wait(&bars.dy_full[b], (t / NDY) & 1, abort_flag)) ok = false;
                 if (ok && has_oact) {
                     // the epilogue rewrites dL/dy in place with the output-activation derivative; y's
                     // ring slot is released by the epilogue threads plus this (empty) commit
                     if (!ptx::mbar_wait(&bars.d_ready, dr & 1, abort_flag)) ok = false;
                     ++dr;
-                    ptx::mma_commit(&bars.a_empty[r % kBwdRing]);
+                    if (ptx::elect_one()) ptx::mma_commit(&bars.a_empty[r % kBwdRing]);
+                    __syncwarp();
                     ++r;
                 }
                 if (!ok) {
-                    atomicExch(status, KS_TIMEOUT_MMA | 1);
+                    if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 1);
                     break;
                 }
                 for (int l = L; ok && l >= 0; --l) {
                     // delta_l: dL/dy buffer for l == L, else ping-pong buffer (L - 1 - l) & 1
                     // (index into the four contiguous delta tiles DY[0], DY[1], DP[0], DP[1])
-                    const int d_idx = (l == L) ? b : 2 + ((L - 1 - l) & 1);
+                    const int d_idx = (l == L) ? b : NDY + ((L - 1 - l) & 1);
                     if (l < L) {
                         if (!ptx::mbar_wait(&bars.d_ready, dr & 1, abort_flag)) {
-                            atomicExch(status, KS_TIMEOUT_MMA | 2 | (l << 4));
+                            if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 2 | (l << 4));
                             ok = false;
                             break;
                         }
                         ++dr;
                     }
+                    const bool chain = l > 0 || want_dx;
+                    uint64_t w_desc = w_desc0 + (uint64_t)(l * T::WGT_UNITS);
+                    if constexpr (BIG) {
+                        if (chain) {
+                            // every earlier chain GEMM is complete (its accumulator was consumed): refill the other
+                            // stage with the weights of the next chain GEMM of this CTA, if there is one
+                            const int next_l = (l > last_chain) ? l - 1 : L;
+                            if (l > last_chain || t + 1 < my_tiles) {
+                                if (ptx::elect_one()) fetch_weights(next_l, wg + 1);
+                                __syncwarp();
+                            }
+                            if (!ptx::mbar_wait(&bars.wring_full[wg & 1u], (wg >> 1) & 1u, abort_flag)) {
+                                if (lane == 0) atomicExch(status, KS_TIMEOUT_WEIGHTS | 1);
+                                ok = false;
+                                break;
+                            }
+                            w_desc = w_desc0 + (uint64_t)((wg & 1u) * T::WGT_UNITS);
+                            ++wg;
+                        }
+                    }
                     ptx::tc_fence_after_sync();
-                    if (l > 0 || want_dx) {
+                    if (chain && ptx::elect_one()) {
                         // chain: acc[128 x W] = delta_l[128 x W] * W_l^T
-                        T::template issue_chain<B_MN_MAJOR>(acc_tmem, dk_desc0 + (uint64_t)(d_idx * T::ACT_UNITS),
-                                                            w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc_chain);
+                        T::template issue_chain<B_MN_MAJOR>(acc_tmem, dk_desc0 + (uint64_t)(d_idx * T::ACT_UNITS), w_desc,
+                                                            idesc_chain);
                         ptx::mma_commit(&bars.acc_full);
                     }
+                    __syncwarp();
                     // weight gradient: G_l[W x W] += delta_l^T[W x 128] * a_l[128 x W]
                     const int slot = r % kBwdRing;
                     if (!ptx::mbar_wait(&bars.a_full[slot], (r / kBwdRing) & 1, abort_flag)) {
-                        atomicExch(status, KS_TIMEOUT_MMA | 3 | (l << 4));
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 3 | (l << 4));
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    T::issue_outer(dw_tmem(l), dmn_desc0 + (uint64_t)(d_idx * T::ACT_UNITS),
-                                   amn_desc0 + (uint64_t)(slot * T::ACT_UNITS), idesc_dw, t > 0 ? 1u : 0u);
-                    ptx::mma_commit(&bars.a_empty[slot]);
+                    if (ptx::elect_one()) {
+                        if (l >= dw_lo && l < dw_hi) // layers of other passes only release their buffers
+                            T::issue_outer(dw_tmem(l), dmn_desc0 + (uint64_t)(d_idx * T::ACT_UNITS),
+                                           amn_desc0 + (uint64_t)(slot * T::ACT_UNITS), idesc_dw, t > 0 ? 1u : 0u);
+                        ptx::mma_commit(&bars.a_empty[slot]);
+                        if (l == L) ptx::mma_commit(&bars.dy_empty[b]);
+                    }
+                    __syncwarp();
                     ++r;
-                    if (l == L) ptx::mma_commit(&bars.dy_empty[b]);
                 }
                 if (ok && want_dx) {
                     // the accumulator holding dL/dx must be drained before the next tile reuses it
                     if (!ptx::mbar_wait(&bars.d_ready, dr & 1, abort_flag)) {
-                        atomicExch(status, KS_TIMEOUT_MMA | 4);
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 4);
                         ok = false;
                     }
                     ++dr;
                 }
             }
-            ptx::mma_commit(&bars.all_done);
+            if (ptx::elect_one()) ptx::mma_commit(&bars.all_done);
+            __syncwarp();
         }
     } else {
         // ------------------------------------------------------------ epilogue group (4 warps)
@@ -218,10 +277,10 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
 
         for (int t = 0; ok && t < my_tiles; ++t) {
             const int tile = blockIdx.x + t * gridDim.x;
-            const int b = t & 1;
+            const int b = t % NDY;
             uint8_t *dybuf = smem + S::DY + b * T::ACT_BYTES;
             if (has_oact || store_bwd) {
-                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars.dy_full[b], (t >> 1) & 1, abort_flag))) {
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(&bars.dy_full[b], (t / NDY) & 1, abort_flag))) {
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | 1);
                     ok = false;
                     break;
@@ -367,7 +426,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
         if (ok && my_tiles > 0) {
             ptx::tc_fence_after_sync();
             float *slab = dw_slabs + (size_t)blockIdx.x * n_mat * W * W;
-            for (int l = 0; l < n_mat; ++l) {
+            for (int l = dw_lo; l < dw_hi; ++l) {
                 // M = 64 accumulators keep row m in lane (m % 16) + 32 * (m / 16); M = 128 in lane m
                 const int o = (S::DW_M == 64) ? quad * 16 + lane : quad * 32 + lane;
                 const bool valid = (S::DW_M == 64) ? (lane < 16 && o < W) : true;
@@ -404,35 +463,50 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------- host side
-template <int W, bool B_MN> static cudaError_t launch_bwd_variant(BwdLaunch &p) {
+template <int W, bool B_MN, bool BIG> static cudaError_t launch_bwd_variant(BwdLaunch &p) {
     using T = Tile<W>;
-    using S = BwdSmem<W>;
-    const size_t smem = (size_t)S::WBUF + (size_t)p.n_mat * T::WGT_BYTES + 1024;
-    const int cols_needed = W + p.n_mat * W;
-    if (smem > 227 * 1024 || cols_needed > 512) return cudaErrorInvalidConfiguration;
-    int tmem_cols = 32;
-    while (tmem_cols < cols_needed) tmem_cols *= 2;
-    auto kern = mlp_bwd_kernel<W, B_MN>;
+    using S = BwdSmem<W, BIG>;
+    const size_t smem = (size_t)S::WBUF + (size_t)S::weight_tiles(p.n_mat) * T::WGT_BYTES + 1024;
+    if (smem > 227 * 1024 - 512) return cudaErrorInvalidConfiguration;
+    auto kern = mlp_bwd_kernel<W, B_MN, BIG>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
     const int grid = n_tiles < p.n_sm ? n_tiles : p.n_sm;
     p.grid_out = grid;
     if (grid == 0) return cudaSuccess;
-    // K-major weights for the chain are rows = input feature; the MN-major variant reads the transposed image
-    kern<<<grid, 192, smem, p.stream>>>(p.tm_dy, p.tm_interm, p.tm_ibwd, p.tm_dx, B_MN ? p.wimg_t : p.wimg,
-                                        p.dw_partials, n_tiles, p.n_mat, p.act, p.out_act, p.store_bwd, p.want_dx,
-                                        tmem_cols, p.status);
-    return cudaGetLastError();
+    // weight-gradient accumulators that fit beside the chain accumulator: layers per pass
+    const int per_pass = (512 - W) / W;
+    for (int lo = 0; lo < p.n_mat; lo += per_pass) {
+        const int hi = lo + per_pass < p.n_mat ? lo + per_pass : p.n_mat;
+        const int cols_needed = W + (hi - lo) * W;
+        int tmem_cols = 32;
+        while (tmem_cols < cols_needed) tmem_cols *= 2;
+        const int first = lo == 0; // deltas and dL/dx are the same in every pass: store them once
+        // K-major weights for the chain are rows = input feature; the MN-major variant reads the transposed image
+        kern<<<grid, 192, smem, p.stream>>>(p.tm_dy, p.tm_interm, p.tm_ibwd, p.tm_dx, B_MN ? p.wimg_t : p.wimg,
+                                            p.dw_partials, n_tiles, p.n_mat, p.act, p.out_act, first ? p.store_bwd : 0,
+                                            first ? p.want_dx : 0, tmem_cols, lo, hi, p.status);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+template <int W> static cudaError_t launch_bwd_w(BwdLaunch &p) {
+    const bool mn = (p.variant & 2) != 0;
+    if (mn) return launch_bwd_variant<W, true, false>(p);
+    cudaError_t e = (p.variant & 256) ? cudaErrorInvalidConfiguration : launch_bwd_variant<W, false, false>(p);
+    if (e == cudaErrorInvalidConfiguration) e = launch_bwd_variant<W, false, true>(p); // streamed weights
+    return e;
 }
 
 cudaError_t launch_mlp_bwd(BwdLaunch &p) {
-    const bool mn = (p.variant & 2) != 0;
     switch (p.width) {
-    case 16: return mn ? launch_bwd_variant<16, true>(p) : launch_bwd_variant<16, false>(p);
-    case 32: return mn ? launch_bwd_variant<32, true>(p) : launch_bwd_variant<32, false>(p);
-    case 64: return mn ? launch_bwd_variant<64, true>(p) : launch_bwd_variant<64, false>(p);
-    case 128: return mn ? launch_bwd_variant<128, true>(p) : launch_bwd_variant<128, false>(p);
+    case 16: return launch_bwd_w<16>(p);
+    case 32: return launch_bwd_w<32>(p);
+    case 64: return launch_bwd_w<64>(p);
+    case 128: return launch_bwd_w<128>(p);
     default: return cudaErrorInvalidValue;
     }
 }
