@@ -219,6 +219,34 @@ def run_only(args):
     out = {"only": args.only, "log2_batch": args.log2_batch, "steps": args.steps}
     if args.only == "grid":
         out.update(grid_leg(L, torch, batch, args.steps, timed))
+    elif args.only == "sweep":
+        # the reference's sweep (benchmarks/benchmark_all.cpp): widths 16..128, 2 / 4 / 8 hidden layers
+        peaks = load_peaks()
+        rows = []
+        for width in (16, 32, 64, 128):
+            gen = torch.Generator(device="cuda").manual_seed(100)
+            x = (torch.rand((batch, width), device="cuda", generator=gen) * 2 - 1).to(torch.bfloat16)
+            targets = torch.rand((batch, width), device="cuda", generator=gen) * 2 - 1
+            for n_hidden in (2, 4, 8):
+                net = L.create_network(width, width, n_hidden, 0, 8, width, "torch.bfloat16", True, seed=0)
+                net.set_params(torch.from_numpy(xavier_weights(n_hidden + 1, width, 0).reshape(-1)).cuda(), False)
+                tr = Trainer(net)
+                inf = lambda: net.inference(x)  # noqa: E731
+                trn = lambda: tr.forward_backward(x, targets)  # noqa: E731
+                for fn in (inf, trn):
+                    for _ in range(2):
+                        fn()
+                ms_i = timed(inf, args.steps) / args.steps
+                ms_t = timed(trn, args.steps) / args.steps
+                flops = 2 * width * width * (n_hidden + 1)
+                rows.append({"width": width, "n_hidden": n_hidden, "infer_ms": ms_i, "train_ms": ms_t,
+                             "infer_samples_per_s": batch / ms_i * 1e3, "train_samples_per_s": batch / ms_t * 1e3,
+                             "infer_tflops": flops * batch / ms_i * 1e-9, "train_tflops": 3 * flops * batch / ms_t * 1e-9,
+                             "infer_frac_hbm": 4 * width * batch / ms_i * 1e-6 / peaks["hbm_gbs"],
+                             "status": net.status()})
+                del tr, net
+            del x, targets
+        out["sweep"] = rows
     else:
         w = xavier_weights(N_MAT, WIDTH, 0)
         net = L.create_network(WIDTH, WIDTH, N_HIDDEN, 0, 8, WIDTH, "torch.bfloat16", True, seed=0)
@@ -461,7 +489,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--log2-batch", type=int, default=LOG2_BATCH)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--only", choices=["train", "infer", "grid"], help="run one kernel only (profiler captures)")
+    ap.add_argument("--only", choices=["train", "infer", "grid", "sweep"],
+                    help="run one kernel only (profiler captures), or the width / depth sweep")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
