@@ -108,8 +108,15 @@ int tnn_network_train_step(tnn_network *net, const void *x, const float *targets
  * bounded device-side wait gave up, results are invalid).  No reference counterpart: the
  * reference kernels have no device-side waits. */
 int tnn_network_sync_status(tnn_network *net, int *status, void *stream);
-/* Selects a kernel variant for tuning experiments (bit 0: hidden activations through TMEM in
- * inference, bit 1: MN-major weight operand, bit 2: fewer tiles in flight, bit 4: unfused training path, bit 6: single-tile fused training kernel).  Default 0.
+/* Selects a kernel variant for tuning experiments.  Default 0 (the fastest measured choice everywhere).
+ *   1    inference keeps hidden activations in shared memory instead of tensor memory
+ *   2    MN-major weight operand in the forward / backward kernels
+ *   4    fewer tiles in flight in the forward kernel        8    three tiles in flight (inference)
+ *   16   training through the forward / loss / backward kernels instead of a fused kernel
+ *   32   the pipelined training kernel prints event time stamps of one tile (tuning build)
+ *   64   single-tile instead of pipelined fused training kernel
+ *   128  fused training kernel feeds its chain GEMMs from tensor memory
+ *   256  stream the weights through per-slot rings even if they would fit on chip
  * No reference counterpart. */
 int tnn_network_set_variant(tnn_network *net, int variant);
 
