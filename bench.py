@@ -329,10 +329,14 @@ def run_gpu_arm(args):
         step()
     ms_total = timed(step, args.steps)
     # keep the same load on the GPU (untimed) until the sampler has seen about two seconds of it
-    while time.perf_counter() - t_load < 2.0:
-        for _ in range(10):
-            step()
-        torch.cuda.synchronize()
+    # (the number of extra steps is agreed between the ranks: a step holds a collective)
+    remaining = torch.tensor([2.0 - (time.perf_counter() - t_load)], device="cuda")
+    if world > 1:
+        dist.all_reduce(remaining, op=dist.ReduceOp.MAX)
+    ms_guess = max(ms_total / args.steps, 1e-3)
+    for _ in range(int(min(max(remaining.item(), 0.0) * 1e3 / ms_guess, 20000))):
+        step()
+    torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
     status = net.status()
     loss_value = float(trainer._loss.item())
@@ -390,8 +394,19 @@ def run_gpu_arm(args):
         roof("mlp_bwd", FLOPS_BWD, act_bytes * (N_MAT + 1), "unfused path: dy + a_L..a_0 in"),
         roof("l2_loss", 0, act_bytes * 2 + WIDTH * 4, "unfused path: y in, dy out, targets in"),
     ]
+    # (rank 0 only, so it is timed locally: `timed` holds collectives that every rank would have to join)
+    def timed_local(fn, steps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
     grid_batch = 1 << 20
-    grid_ms = grid_leg(L, torch, grid_batch, max(3, min(args.steps, 10)), timed) if rank == 0 else {}
+    grid_ms = grid_leg(L, torch, grid_batch, max(3, min(args.steps, 10)), timed_local) if rank == 0 else {}
     # per sample and level: 8 corners x 2 features (4 B each) read, position read once, 2 features written
     grid_fwd_bytes = 16 * (8 * 2 * 4) + 3 * 4 + 32 * 4
     grid_rooflines = [{"kernel": k, "ms": v, "batch": grid_batch,
@@ -481,7 +496,20 @@ def _packed(w):
     return out.reshape(-1)
 
 
+def _watchdog(seconds):
+    """A run that is still going after `seconds` is stuck (a rank that never joined a collective): leave loudly."""
+    def fire():
+        sys.stderr.write(f"bench.py: still running after {seconds} s, giving up\n")
+        sys.stderr.flush()
+        os._exit(3)
+
+    t = threading.Timer(seconds, fire)
+    t.daemon = True
+    t.start()
+
+
 def main():
+    _watchdog(1200)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
