@@ -10,6 +10,26 @@
 
 namespace tnn {
 
+// grad[0..F) += v[0..F) at one table entry.  sm_90+ has vector reductions: one `red` per 2 or 4 features instead
+// of one per feature (each element is still added atomically on its own; entries are F * 4 bytes apart, so the
+// vector forms are naturally aligned).
+template <int F> __device__ __forceinline__ void red_add_entry(float *dst, const float (&v)[F]) {
+    if constexpr (F % 4 == 0) {
+#pragma unroll
+        for (int f = 0; f < F; f += 4)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + f), "f"(v[f]), "f"(v[f + 1]),
+                         "f"(v[f + 2]), "f"(v[f + 3])
+                         : "memory");
+    } else if constexpr (F % 2 == 0) {
+#pragma unroll
+        for (int f = 0; f < F; f += 2)
+            asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(dst + f), "f"(v[f]), "f"(v[f + 1]) : "memory");
+    } else {
+#pragma unroll
+        for (int f = 0; f < F; ++f) atomicAdd(dst + f, v[f]);
+    }
+}
+
 template <int D, int F, typename DyT>
 __global__ void __launch_bounds__(256) grid_bwd_atomic_kernel(const GridParams p, const float *__restrict__ x,
                                                                const DyT *__restrict__ dy, float *__restrict__ grads,
@@ -36,8 +56,7 @@ __global__ void __launch_bounds__(256) grid_bwd_atomic_kernel(const GridParams p
 
     if (p.interpolation == INTERP_NEAREST) {
         const uint32_t e = grid_index<D>(p.grid_type, p.hash_type, hsize, res, g);
-#pragma unroll
-        for (int f = 0; f < F; ++f) atomicAdd(gl + (size_t)e * F + f, gr[f]);
+        red_add_entry<F>(gl + (size_t)e * F, gr);
         return;
     }
 #pragma unroll
@@ -55,8 +74,10 @@ __global__ void __launch_bounds__(256) grid_bwd_atomic_kernel(const GridParams p
             }
         }
         const uint32_t e = grid_index<D>(p.grid_type, p.hash_type, hsize, res, gc);
+        float contrib[F];
 #pragma unroll
-        for (int f = 0; f < F; ++f) atomicAdd(gl + (size_t)e * F + f, __fmul_rn(weight, gr[f]));
+        for (int f = 0; f < F; ++f) contrib[f] = __fmul_rn(weight, gr[f]);
+        red_add_entry<F>(gl + (size_t)e * F, contrib);
     }
 }
 
