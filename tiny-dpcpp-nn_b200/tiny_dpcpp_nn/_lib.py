@@ -309,7 +309,14 @@ class EncodingModule:
     def bwd_no_encoding_grad(self, grad_output, pack_gradient, get_dl_dinput):
         raise TnnError("backward_pass needs input_from_fwd")
 
-    def bwd_with_encoding_grad(self, grad_output, input_from_fwd, pack_gradient, get_dl_dinput, deterministic=True):
+    #: default summation of the table gradient: False = floating-point reductions in memory like the reference's
+    #: kernel_grid_backward (grid.h:177-183, order not fixed, fastest); True = the atomic-free pipeline whose
+    #: result repeats bit for bit (about 7x slower at the benchmark grid)
+    deterministic_backward = False
+
+    def bwd_with_encoding_grad(self, grad_output, input_from_fwd, pack_gradient, get_dl_dinput, deterministic=None):
+        if deterministic is None:
+            deterministic = self.deterministic_backward
         if self.n_params() == 0:
             return None, None
         if pack_gradient:
