@@ -115,7 +115,6 @@ int tnn_network_sync_status(tnn_network *net, int *status, void *stream);
  *   16   training through the forward / loss / backward kernels instead of a fused kernel
  *   32   the pipelined training kernel prints event time stamps of one tile (tuning build)
  *   64   single-tile instead of pipelined fused training kernel
- *   128  fused training kernel feeds its chain GEMMs from tensor memory
  *   256  stream the weights through per-slot rings even if they would fit on chip
  * No reference counterpart. */
 int tnn_network_set_variant(tnn_network *net, int variant);

@@ -398,7 +398,6 @@ int tnn_network_train_step(tnn_network *n, const void *x, const float *targets, 
         p.n_sm = n->n_sm;
         p.status = n->status;
         p.stream = s;
-        p.ts = (n->variant & 128) ? 1 : 0;
         p.prof = (n->variant & 32) ? reinterpret_cast<long long *>(n->loss_partials) : nullptr; // non-null = print cycle accounting
         // widest-overlap kernel first; the single-tile kernel covers deeper networks
         cudaError_t e = (n->variant & 64) ? cudaErrorInvalidConfiguration : tnn::launch_mlp_train_pipe(p);

@@ -68,7 +68,6 @@ struct TrainLaunch {
     cudaStream_t stream;
     int grid_out;
     long long *prof; // cycle-accounting buffer of tuning builds, normally nullptr
-    int ts;          // tuning: chain operands through tensor memory (measured slower than shared memory here)
 };
 // cudaErrorInvalidConfiguration when the network does not fit the on-chip budget of the fused kernel.
 cudaError_t launch_mlp_train(TrainLaunch &p);

@@ -81,11 +81,11 @@ constexpr int kProfTile = 10;
     ptx::mbar_wait_busy(&prof_bar[which], (cnt) & 1u, abort_flag); ++(cnt); TNN_EV(t, id); } } } while (0)
 #define TNN_EV(t, id) do { if constexpr (PROF) { if ((t) == kProfTile && blockIdx.x == 0) prof_ev[id] = (long long)clock64(); } } while (0)
 
-// TS: the hidden-layer chain GEMMs of both stages take their A operand (the bf16 activations / deltas the
-// epilogue just produced) from tensor memory instead of shared memory.  A 128 x 64 x 16 MMA then reads 2 KB
-// instead of 6 KB of shared memory and runs in 32 instead of 48 cycles.  The shared-memory copies are still
-// written: the weight-gradient GEMMs and the activation backward read them.  Needs (n_mat + 3) W columns.
-template <int W, bool TGT, bool TS, bool PROF = false>
+// (The chain GEMMs read both operands from shared memory.  Feeding their A operand from tensor memory, as the
+// inference kernel does, was measured slower here: the activations must be in shared memory anyway for the
+// weight-gradient GEMMs and the activation backward, and the extra tcgen05.st in every epilogue step costs more
+// than the shorter GEMMs save.)
+template <int W, bool TGT, bool PROF = false>
 __global__ void __launch_bounds__(PipeSmem<W, TGT>::THREADS, 1)
 mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_tgt,
                       const __nv_bfloat16 *__restrict__ wimg,
@@ -157,8 +157,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
     const uint32_t tmem_base = bars.tmem_base;
     const uint32_t accf_tmem = tmem_base;     // columns [0, W)
     const uint32_t accb_tmem = tmem_base + W; // columns [W, 2W); weight gradients of layer l at 2W + l W
-    [[maybe_unused]] const uint32_t af_tmem = tmem_base + 2 * W + n_mat * W; // TS: A operand of the forward chain
-    [[maybe_unused]] const uint32_t ab_tmem = af_tmem + W / 2;               // TS: A operand of the backward chain
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
@@ -237,11 +235,8 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     ptx::tc_fence_after_sync();
                     if (ptx::elect_one()) {
                         TNN_EV(t, 40 + l);
-                        if constexpr (TS)
-                            T::template issue_chain_ts<true>(accf_tmem, af_tmem, w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
-                        else
-                            T::template issue_chain<true>(accf_tmem, ab_desc0 + (uint64_t)(ab_index(t, l) * T::ACT_UNITS),
-                                                          w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
+                        T::template issue_chain<true>(accf_tmem, ab_desc0 + (uint64_t)(ab_index(t, l) * T::ACT_UNITS),
+                                                      w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
                         ptx::mma_commit(&bars.accf_full);
                         TNN_EV(t, 45 + l);
                         TNN_DONE(t, 0, prof_cnt, 80 + l);
@@ -287,10 +282,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     const uint64_t d_desc = (l == L) ? dl_desc : dp_desc0 + (uint64_t)(((L - 1 - l) & 1) * T::ACT_UNITS);
                     if (ptx::elect_one()) {
                         TNN_EV(t, 50 + L - l);
-                        if (TS && l < L) // delta_L comes from the forward stage through shared memory
-                            T::template issue_chain_ts<false>(accb_tmem, ab_tmem, w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
-                        else
-                            T::template issue_chain<false>(accb_tmem, d_desc, w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
+                        T::template issue_chain<false>(accb_tmem, d_desc, w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
                         ptx::mma_commit(&bars.accb_full);
                         if (l == L) ptx::mma_commit(&bars.dl_free);
                         ptx::mbar_arrive(&bars.chain_issued[ci_count & 1u]); // the weight-gradient GEMM of layer l may follow
@@ -366,13 +358,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
         const int col0 = half * S::CPT;
         constexpr int CPT = S::CPT;
         const uint32_t acc_addr = accf_tmem + ((uint32_t)(quad * 32) << 16) + col0;
-        [[maybe_unused]] const uint32_t a_st_addr = af_tmem + ((uint32_t)(quad * 32) << 16) + col0 / 2;
-        auto store_a = [](uint32_t addr, const uint32_t (&pk)[S::CPT / 2]) {
-            if constexpr (S::CPT == 32)
-                ptx::tmem_st16(addr, pk);
-            else
-                ptx::tmem_st8(addr, pk);
-        };
         uint32_t af_parity = 0;
         float loss_local = 0.0f;
         bool ok = true;
@@ -430,13 +415,11 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
 #pragma unroll
                     for (int q = 0; q < CPT / 2; ++q)
                         pk[q] = act_pack_t<ACT>(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
-                    if constexpr (TS) store_a(a_st_addr, pk);
 #pragma unroll
                     for (int ch = 0; ch < CPT / 8; ++ch)
                         *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) =
                             make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
                 });
-                if constexpr (TS) ptx::tmem_st_wait();
                 TNN_TOC(4, t_p);
                 const long long t_h = TNN_TIC();
                 ptx::fence_proxy_async_smem();
@@ -562,7 +545,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
         const int col0 = half * S::CPT;
         constexpr int CPT = S::CPT;
         const uint32_t acc_addr = accb_tmem + ((uint32_t)(quad * 32) << 16) + col0;
-        [[maybe_unused]] const uint32_t a_st_addr = ab_tmem + ((uint32_t)(quad * 32) << 16) + col0 / 2;
         uint32_t ab_parity = 0;
         uint32_t dp_parity = 0, dp_written = 0; // bit p: phase to wait for / buffer p was written before
         uint32_t go_count = 0;
@@ -634,20 +616,11 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                         pk[ch * 4 + 2] = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 4]), __uint_as_float(v[ch * 8 + 5]), f.z);
                         pk[ch * 4 + 3] = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 6]), __uint_as_float(v[ch * 8 + 7]), f.w);
                     }
-                    if constexpr (TS) {
-                        if (l > 1) { // delta_0 feeds no further chain GEMM
-                            if constexpr (CPT == 32)
-                                ptx::tmem_st16(a_st_addr, pk);
-                            else
-                                ptx::tmem_st8(a_st_addr, pk);
-                        }
-                    }
 #pragma unroll
                     for (int ch = 0; ch < CPT / 8; ++ch)
                         *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) =
                             make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
                 });
-                if constexpr (TS) ptx::tmem_st_wait();
                 TNN_TOC(4, t_p);
                 ptx::fence_proxy_async_smem();
                 ptx::tc_fence_before_sync();
@@ -717,16 +690,16 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
 // 227 KB per CTA minus the statically allocated barriers
 constexpr size_t kPipeSmemLimit = 227 * 1024 - 2048;
 
-template <int W, bool TGT, bool TS> static cudaError_t launch_pipe_w(TrainLaunch &p) {
+template <int W, bool TGT> static cudaError_t launch_pipe_w(TrainLaunch &p) {
     using T = Tile<W>;
     using S = PipeSmem<W, TGT>;
     const size_t smem = (size_t)S::WBUF(p.n_mat) + (size_t)p.n_mat * T::WGT_BYTES + 1024;
-    const int cols_needed = (TS ? 3 : 2) * W + p.n_mat * W;
+    const int cols_needed = 2 * W + p.n_mat * W;
     if (smem > kPipeSmemLimit || cols_needed > 512 || p.n_mat > kPipeMaxMat) return cudaErrorInvalidConfiguration;
     void (*kern)(const CUtensorMap, const CUtensorMap, const __nv_bfloat16 *, const float *, int, float *, float *, size_t,
-                 int, int, int, int, float, float, int *) = mlp_train_pipe_kernel<W, TGT, TS, false>;
-    if constexpr (W == 64 && TGT && !TS) {
-        if (p.prof) kern = mlp_train_pipe_kernel<W, TGT, TS, true>;
+                 int, int, int, int, float, float, int *) = mlp_train_pipe_kernel<W, TGT, false>;
+    if constexpr (W == 64 && TGT) {
+        if (p.prof) kern = mlp_train_pipe_kernel<W, TGT, true>;
     }
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
@@ -743,16 +716,11 @@ template <int W, bool TGT, bool TS> static cudaError_t launch_pipe_w(TrainLaunch
 
 cudaError_t launch_mlp_train_pipe(TrainLaunch &p) {
     // staged targets need one more tile of shared memory: without room for it the per-thread loads remain
-    // and the chain operands go through tensor memory while its 512 columns hold them beside the accumulators
     cudaError_t e = cudaErrorInvalidConfiguration;
     if (p.width != 64 && p.width != 32) return e;
     const bool w64 = p.width == 64;
-    if (p.tgt_tma && p.ts) e = w64 ? launch_pipe_w<64, true, true>(p) : launch_pipe_w<32, true, true>(p);
-    if (e == cudaErrorInvalidConfiguration && p.tgt_tma)
-        e = w64 ? launch_pipe_w<64, true, false>(p) : launch_pipe_w<32, true, false>(p);
-    if (e == cudaErrorInvalidConfiguration && p.ts)
-        e = w64 ? launch_pipe_w<64, false, true>(p) : launch_pipe_w<32, false, true>(p);
-    if (e == cudaErrorInvalidConfiguration) e = w64 ? launch_pipe_w<64, false, false>(p) : launch_pipe_w<32, false, false>(p);
+    if (p.tgt_tma) e = w64 ? launch_pipe_w<64, true>(p) : launch_pipe_w<32, true>(p);
+    if (e == cudaErrorInvalidConfiguration) e = w64 ? launch_pipe_w<64, false>(p) : launch_pipe_w<32, false>(p);
     return e;
 }
 
