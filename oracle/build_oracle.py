@@ -2,7 +2,7 @@
 
   liboracle.so        - this repository's restatement (oracle.cpp), always built
   _ref/libref_mlp.so  - the reference's own host MLP (test/mlp.h), compiled unmodified from the
-                        reference checkout when one is present (TNN_REFERENCE_ROOT or /root/reference);
+                        reference checkout when one is present (environment variable TNN_REFERENCE_ROOT, else the default below);
                         on machines without the checkout the prebuilt file is used as is.
 """
 import os

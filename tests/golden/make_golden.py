@@ -2,7 +2,7 @@
 
   mlp_ref_vectors.npz - outputs of the reference's own host MLP (test/mlp.h, double precision) for
       seeded weights and inputs, produced through oracle/_ref/libref_mlp.so.  Needs the reference
-      checkout (TNN_REFERENCE_ROOT or /root/reference) to build that library; the fixture itself
+      checkout (see oracle/build_oracle.py: TNN_REFERENCE_ROOT) to build that library; the fixture itself
       travels with the repository.
   grid_kat.json / packing_kat.json hold literal vectors of the reference's tests and are not generated:
       test/doctest_encodings.cpp:234-285 and test/python/test_packing.py:9-27.
