@@ -245,6 +245,26 @@ void oracle_identity_forward(const float *x, size_t batch, int n_in, int padded,
 }
 
 // ---------------------------------------------------------------------------------------------
+// Frequency encoding: include/encodings/frequency.h:63-80.  The reference forms the argument as
+// float * size_t (float) * M_PI (double) + phase (float) and rounds it to float before the sine.
+// ---------------------------------------------------------------------------------------------
+void oracle_frequency_forward(const float *x, size_t batch, int n_in, int n_freq, int padded, float *out) {
+    const int n_out = n_in * n_freq * 2;
+    for (size_t b = 0; b < batch; ++b)
+        for (int j = 0; j < padded; ++j) {
+            if (j >= n_out) {
+                out[b * padded + j] = 1.0f;
+                continue;
+            }
+            const int feature = j / (n_freq * 2);
+            const int log2_frequency = (j / 2) % n_freq;
+            const float phase_shift = (float)((j % 2) * (M_PI / 2.0));
+            const float arg = (float)((double)(x[b * n_in + feature] * (float)((size_t)1 << log2_frequency)) * M_PI + phase_shift);
+            out[b * padded + j] = std::sin(arg);
+        }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Hash grid.  Level table: include/encodings/grid.h:588-659; scale / resolution:
 // include/common/common_device.h:767-775; hash and index: common_device.h:700-765 (all uint32,
 // wrapping); forward: grid.h:37-135; backward: grid.h:137-245.

@@ -149,6 +149,16 @@ def identity_forward(x, padded, scale=1.0, offset=0.0):
     return out
 
 
+def frequency_forward(x, n_frequencies, padded=None):
+    """include/encodings/frequency.h:63-80: sin / cos pairs of n_frequencies octaves per input feature, padded with 1."""
+    x = _f32(x)
+    padded = padded or x.shape[1] * n_frequencies * 2
+    out = np.empty((x.shape[0], padded), dtype=np.float32)
+    lib().oracle_frequency_forward(_ptr(x), ctypes.c_size_t(x.shape[0]), ctypes.c_int(x.shape[1]),
+                                   ctypes.c_int(n_frequencies), ctypes.c_int(padded), _ptr(out))
+    return out
+
+
 class _GridStruct(ctypes.Structure):
     _fields_ = [("n_levels", ctypes.c_uint32), ("F", ctypes.c_uint32), ("D", ctypes.c_uint32),
                 ("base_resolution", ctypes.c_uint32), ("log2_per_level_scale", ctypes.c_float),

@@ -46,6 +46,17 @@ def test_argument_errors_need_no_device(tnn_lib):
     assert lib.tnn_encoding_create(b'{"otype": "Nope"}', 0, ctypes.byref(e)) != 0
     assert b"Unknown encoding type" in lib.tnn_last_error()
     assert lib.tnn_encoding_create(b'{"n_levels": 4}', 0, ctypes.byref(e)) != 0
+    # frequency encoding (test/doctest_encodings.cpp:357-404): missing / zero / negative n_frequencies, zero input
+    # dims, padded width below the natural width
+    for cfg, pad in ((b'{"otype": "Frequency", "n_dims_to_encode": 1}', 0),
+                     (b'{"otype": "Frequency", "n_dims_to_encode": 1, "n_frequencies": 0}', 0),
+                     (b'{"otype": "Frequency", "n_dims_to_encode": 1, "n_frequencies": -1}', 0),
+                     (b'{"otype": "Frequency", "n_dims_to_encode": 0, "n_frequencies": 1}', 0),
+                     (b'{"otype": "Frequency", "n_dims_to_encode": 1, "n_frequencies": 1}', 1)):
+        assert lib.tnn_encoding_create(cfg, pad, ctypes.byref(e)) != 0, cfg
+    assert lib.tnn_encoding_create(b'{"otype": "SphericalHarmonics", "n_dims_to_encode": 3, "degree": 4}', 0,
+                                   ctypes.byref(e)) != 0
+    assert b"outside the scope" in lib.tnn_last_error()
 
 
 def test_no_device_means_loud_failure(tnn_lib):

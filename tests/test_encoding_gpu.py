@@ -133,9 +133,30 @@ def test_identity_encoding(tnn_lib):
     assert np.array_equal(out16, O.bf16_round(O.identity_forward(x, 64)))
 
 
+def test_frequency_encoding(tnn_lib):
+    """include/encodings/frequency.h:63-80; expectations of test/doctest_encodings.cpp:486-560 (1e-4)."""
+    import math
+    enc = tnn_lib.create_encoding("Frequency", dict(otype="Frequency", n_frequencies=1, n_dims_to_encode=1), 4)
+    assert enc.n_params() == 0 and enc.n_output_dims() == 4
+    out = enc.fwd(_t(np.array([[1.234]], np.float32))).cpu().numpy()
+    assert np.allclose(out[0], [math.sin(math.pi * 1.234), math.cos(math.pi * 1.234), 1, 1], atol=1e-4)
+    enc = tnn_lib.create_encoding("Frequency", dict(otype="Frequency", n_frequencies=2, n_dims_to_encode=3), 14)
+    x = np.arange(6, dtype=np.float32).reshape(2, 3)
+    assert np.abs(enc.fwd(_t(x)).cpu().numpy() - O.frequency_forward(x, 2, padded=14)).max() < 1e-4
+    # NeRF-style use: 3-D positions in [0, 1], 12 octaves, padded to the network width, bf16 for the MLP
+    enc = tnn_lib.create_encoding("Frequency", dict(otype="Frequency", n_frequencies=12, n_dims_to_encode=3), 128)
+    x = synth.uniform_inputs(4096 + 8, 3, 100, 0.0, 1.0)
+    ref = O.frequency_forward(x, 12, padded=128)
+    # arguments reach 2^11 pi: the device sine and the host sine agree to a few fp32 ulps of the argument
+    assert np.abs(enc.fwd(_t(x)).cpu().numpy() - ref).max() < 1e-4
+    out16 = enc.fwd(_t(x), out_dtype=torch.bfloat16).float().cpu().numpy()
+    assert np.abs(out16 - ref).max() < 1e-2
+    assert enc.bwd_with_encoding_grad(_t(ref), _t(x), False, False) == (None, None)
+
+
 def test_encoding_errors(tnn_lib):
     with pytest.raises(tnn_lib.TnnError, match="outside the scope"):
-        tnn_lib.create_encoding("Frequency", dict(otype="Frequency", n_frequencies=4, n_dims_to_encode=2))
+        tnn_lib.create_encoding("SphericalHarmonics", dict(otype="SphericalHarmonics", degree=4, n_dims_to_encode=3))
     with pytest.raises(tnn_lib.TnnError, match="simultaneously"):
         tnn_lib.create_encoding("HashGrid", dict(otype="HashGrid", n_levels=4, n_features=8))
     with pytest.raises(tnn_lib.TnnError, match="2 or 3"):

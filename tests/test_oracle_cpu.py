@@ -2,6 +2,8 @@
 import json
 import os
 
+import math
+
 import numpy as np
 import pytest
 
@@ -175,6 +177,23 @@ def test_reference_host_mlp_live_when_available():
     r2 = O.ref_mlp_sample(W, n_mat, "relu", "none", x, t, weights=None, init_mode=1)
     interm2 = O.mlp_forward(x[None, :], r2["weights"], n_mat, W, "relu", "none", bf16=False)
     assert O.within_tolerance(interm2[:, 0, :], r2["fwd"], 1e-5)[0]
+
+
+def test_frequency_encoding_closed_forms():
+    """The reference's expectations (test/doctest_encodings.cpp:486-560, test/python/test_encodings.py:611-633):
+    sin / cos of pi x 2^k per feature, padding columns 1, tolerance 1e-4."""
+    out = O.frequency_forward(np.array([[1.234]], np.float32), 1, padded=4)
+    assert np.allclose(out[0], [math.sin(math.pi * 1.234), math.cos(math.pi * 1.234), 1, 1], atol=1e-4)
+    x = np.arange(6, dtype=np.float32).reshape(2, 3)
+    out = O.frequency_forward(x, 2, padded=14)
+    exp = np.ones((2, 14))
+    for r in range(2):
+        for f in range(3):
+            for k in range(2):
+                exp[r, f * 4 + 2 * k] = math.sin(math.pi * (1 << k) * x[r, f])
+                exp[r, f * 4 + 2 * k + 1] = math.cos(math.pi * (1 << k) * x[r, f])
+    assert O.within_tolerance(out, exp.astype(np.float32), 1e-4)[0]
+    assert np.abs(out - exp).max() < 1e-4
 
 
 def test_identity_pads_with_ones():

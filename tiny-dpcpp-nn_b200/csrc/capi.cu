@@ -490,6 +490,7 @@ struct tnn_encoding {
     int n_out = 0;    // natural output width
     int padded = 0;   // padded output width
     float scale = 1.0f, offset = 0.0f; // identity
+    int n_frequencies = 0;             // > 0: frequency encoding
     tnn::GridParams gp{};
     size_t n_params = 0;
     float *table = nullptr;
@@ -566,8 +567,19 @@ int tnn_encoding_create(const char *json_config, int padded_output_width, tnn_en
         enc->n_params = (size_t)entries * F;
         enc->n_in = (int)g.n_dims;
         enc->n_out = (int)g.n_features;
-    } else if (name == "SphericalHarmonics" || name == "Frequency") {
-        return fail("encoding type " + name + " is outside the scope of this library (HashGrid and Identity only)");
+    } else if (name == "Frequency") {
+        // encoding_factory.h:88-107
+        if (!cfg.has("n_frequencies")) return fail("Config misses n_frequencies");
+        if (!cfg.has("n_dims_to_encode")) return fail("Config misses n_dims_to_encode");
+        const double nf = cfg.at("n_frequencies").num;
+        const double nd = cfg.at("n_dims_to_encode").num;
+        if (nf < 1.0 || nf > 32.0) return fail("n_frequencies must be in [1, 32]");
+        if (nd < 1.0 || nd * nf * 2.0 > 2147483647.0) return fail("n_frequencies * 2 * n_dims_to_encode out of range");
+        enc->n_frequencies = (int)nf;
+        enc->n_in = (int)nd;
+        enc->n_out = enc->n_in * enc->n_frequencies * 2;
+    } else if (name == "SphericalHarmonics") {
+        return fail("encoding type " + name + " is outside the scope of this library (HashGrid, Identity and Frequency only)");
     } else {
         return fail("Unknown encoding type: " + name);
     }
@@ -647,6 +659,8 @@ int tnn_encoding_forward(tnn_encoding *e, const float *x, void *out, int out_dty
     const int bf = out_dtype == TNN_DTYPE_BF16;
     if (e->is_grid)
         TNN_CUDA(tnn::launch_grid_fwd(e->gp, x, e->table, out, bf, batch, (cudaStream_t)stream));
+    else if (e->n_frequencies > 0)
+        TNN_CUDA(tnn::launch_frequency_fwd(x, out, bf, batch, e->n_in, e->n_frequencies, e->padded, (cudaStream_t)stream));
     else
         TNN_CUDA(tnn::launch_identity_fwd(x, out, bf, batch, e->n_in, e->padded, e->scale, e->offset, (cudaStream_t)stream));
     return 0;

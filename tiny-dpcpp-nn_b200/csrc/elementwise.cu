@@ -113,6 +113,44 @@ cudaError_t launch_identity_fwd(const float *x, void *out, int out_bf16, size_t 
     return cudaGetLastError();
 }
 
+// Frequency encoding (include/encodings/frequency.h:63-80): column j of input feature j / (2 F) holds
+// sin(x * 2^((j / 2) % F) * pi + (j % 2) * pi / 2), i.e. sin / cos pairs of F octaves; padding columns are 1.
+// The argument is formed in double precision and rounded to fp32 before the sine, as the reference's
+// expression does (its pi is a double constant).
+template <typename OutT>
+__global__ void frequency_fwd_kernel(const float *__restrict__ x, OutT *__restrict__ out, size_t batch, int n_in,
+                                     int n_freq, int padded) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= batch * (size_t)padded) return;
+    const size_t row = idx / padded;
+    const int col = (int)(idx % padded);
+    float v = 1.0f;
+    if (col < n_in * n_freq * 2) {
+        const int feature = col / (n_freq * 2);
+        const int log2_frequency = (col / 2) % n_freq;
+        const float phase_shift = (float)((col % 2) * (3.14159265358979323846 / 2.0));
+        const float scaled = x[row * n_in + feature] * (float)((size_t)1 << log2_frequency);
+        const float arg = (float)__dadd_rn(__dmul_rn((double)scaled, 3.14159265358979323846), (double)phase_shift);
+        v = sinf(arg);
+    }
+    if constexpr (sizeof(OutT) == 2)
+        out[idx] = __float2bfloat16_rn(v);
+    else
+        out[idx] = v;
+}
+
+cudaError_t launch_frequency_fwd(const float *x, void *out, int out_bf16, size_t batch, int n_in, int n_freq, int padded,
+                                 cudaStream_t stream) {
+    const size_t n = batch * (size_t)padded;
+    if (n == 0) return cudaSuccess;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (out_bf16)
+        frequency_fwd_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (__nv_bfloat16 *)out, batch, n_in, n_freq, padded);
+    else
+        frequency_fwd_kernel<float><<<blocks, 256, 0, stream>>>(x, (float *)out, batch, n_in, n_freq, padded);
+    return cudaGetLastError();
+}
+
 // L2 loss (include/losses/l2.h:19-41): value = (p - t)^2 / n, grad = scale * 2 (p - t) / n with
 // n = batch * stride.  Targets are [batch][n_targets]; prediction columns >= n_targets are padding and
 // compare against 0.  Per-block partial sums of the loss values go to `loss_partials` (fixed order).

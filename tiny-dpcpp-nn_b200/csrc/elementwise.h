@@ -13,6 +13,8 @@ cudaError_t launch_reduce_dw(const float *slabs, int n_slabs, int n_mat, int wid
                              float *out_f32, __nv_bfloat16 *out_bf16, cudaStream_t stream);
 cudaError_t launch_identity_fwd(const float *x, void *out, int out_bf16, size_t batch, int n_in, int padded,
                                 float scale, float offset, cudaStream_t stream);
+cudaError_t launch_frequency_fwd(const float *x, void *out, int out_bf16, size_t batch, int n_in, int n_freq, int padded,
+                                 cudaStream_t stream);
 cudaError_t launch_l2_loss(const __nv_bfloat16 *pred, const float *target, int n_targets, float *values,
                            __nv_bfloat16 *grads, size_t batch, int stride, float loss_scale, float *loss_partials,
                            int n_partials, float *loss_sum, cudaStream_t stream);
