@@ -14,10 +14,13 @@ class TorchMLP(torch.nn.Module):
     """Reference network: Linear layers without bias; the bias is the column of ones the input is padded with
     (test/python/src/mlp.py of the reference builds the same thing)."""
 
-    def __init__(self, width, n_hidden, act, out_act):
+    def __init__(self, width, n_hidden, act, out_act, round_weights=False):
         super().__init__()
         self.layers = torch.nn.ModuleList([torch.nn.Linear(width, width, bias=False) for _ in range(n_hidden + 1)])
         self.act, self.out_act = act, out_act
+        # the device computes with the bf16 rounding of its fp32 master weights; a model whose weights are being
+        # trained has to do the same to stay comparable (updates smaller than a bf16 step change nothing at first)
+        self.round_weights = round_weights
 
     @staticmethod
     def _a(name, x):
@@ -25,7 +28,8 @@ class TorchMLP(torch.nn.Module):
 
     def forward(self, x):
         for i, layer in enumerate(self.layers):
-            x = layer(x)
+            w = layer.weight.to(torch.bfloat16).to(torch.float32) if self.round_weights else layer.weight
+            x = torch.nn.functional.linear(x, w)
             x = self._a(self.out_act if i == len(self.layers) - 1 else self.act, x)
             x = x.to(torch.bfloat16).to(torch.float32)  # the fused kernels round every layer to bf16
         return x
@@ -129,3 +133,71 @@ def test_identity_encoding_feeds_network(tnn_lib):
     out = enc(x)
     assert out.shape == (64, 64)
     assert torch.equal(out[:, :2], x) and torch.all(out[:, 2:] == 1.0)
+
+
+def test_regression_with_sgd_tracks_torch(tnn_lib):
+    """test/python/test_training.py:57-182: the module and a torch MLP with the same weights are trained side by
+    side with plain SGD on a linear target; after every step outputs, loss, gradient mass and parameter mass agree."""
+    import tiny_dpcpp_nn as tnn
+
+    width, n_hidden, lr, steps = 32, 1, 5e-3, 30
+    cfg = {"n_neurons": width, "n_hidden_layers": n_hidden, "activation": "relu", "output_activation": "linear"}
+    net = tnn.Network(width, 1, cfg, dtype=torch.bfloat16, seed=3)
+    packed = net.params.detach().float().cpu().numpy().reshape(-1)
+    w = O.unpack_weights(packed, n_hidden + 1, width).reshape(n_hidden + 1, width, width)
+    ref = TorchMLP(width, n_hidden, "relu", "none", round_weights=True).cuda()
+    with torch.no_grad():
+        for l, layer in enumerate(ref.layers):
+            layer.weight.copy_(torch.from_numpy(w[l].T.copy()))
+    x = torch.ones((8, width), device="cuda")
+    labels = 0.5 * x[:, :1]
+    first_loss = None
+    for step in range(steps):
+        y = net(x).float()
+        loss = ((y - labels) ** 2).mean()
+        net.zero_grad()
+        loss.backward()
+        before = net.params.detach().clone()
+        with torch.no_grad():
+            net.params.copy_(net.params - lr * net.params.grad)
+        assert step > 0 or not torch.equal(before, net.params.detach())  # (later on the loss may reach exactly 0)
+
+        y_ref = ref(x)[:, :1]
+        loss_ref = ((y_ref - labels) ** 2).mean()
+        ref.zero_grad()
+        loss_ref.backward()
+        grad_mass_ref = sum(layer.weight.grad.abs().sum().item() for layer in ref.layers)
+        with torch.no_grad():
+            for layer in ref.layers:
+                layer.weight.copy_(layer.weight - lr * layer.weight.grad)
+
+        first_loss = loss.item() if first_loss is None else first_loss
+        assert torch.allclose(y.detach(), y_ref.detach(), rtol=5e-2, atol=5e-3), step
+        assert abs(loss.item() - loss_ref.item()) <= 5e-2 * abs(loss_ref.item()) + 1e-4, step
+        grad_mass = net.params.grad.float().abs().sum().item()
+        assert abs(grad_mass - grad_mass_ref) <= 5e-2 * grad_mass_ref + 1e-3, step
+    assert loss.item() < 0.5 * first_loss  # and the regression made progress
+    mass = net.params.detach().float().abs().sum().item()
+    mass_ref = sum(layer.weight.detach().abs().sum().item() for layer in ref.layers)
+    assert abs(mass - mass_ref) <= 1e-2 * mass_ref
+
+
+def test_set_params_roundtrip_through_the_module(tnn_lib):
+    """test/python/test_set_param.py:22-75: a constant parameter vector set through the module is what the module
+    reports afterwards, and the forward pass uses it (linear network, input 0.1: closed form)."""
+    import tiny_dpcpp_nn as tnn
+
+    width, n_hidden = 16, 3
+    cfg = {"n_neurons": width, "n_hidden_layers": n_hidden, "activation": "none", "output_activation": "none"}
+    net = tnn.Network(width, width, cfg, dtype=torch.bfloat16)
+    val = 0.123
+    vals = torch.full((width * width * (n_hidden + 1), 1), val, device="cuda", dtype=torch.bfloat16)
+    net.set_params(vals)
+    assert torch.allclose(net.params.detach().to(torch.bfloat16).reshape(-1, 1), vals)
+    y = net(torch.full((8, width), 0.1, device="cuda")).float()
+    # every layer multiplies by 16 x bf16(0.123), rounded to bf16 after each layer
+    expect = torch.tensor(0.1, dtype=torch.bfloat16).float()
+    wv = torch.tensor(val, dtype=torch.bfloat16).float()
+    for _ in range(n_hidden + 1):
+        expect = (expect * wv * width).to(torch.bfloat16).float()
+    assert torch.allclose(y, torch.full_like(y, expect.item()), rtol=2e-2)
