@@ -59,6 +59,8 @@ __global__ void __launch_bounds__(256) grid_bwd_atomic_kernel(const GridParams p
         red_add_entry<F>(gl + (size_t)e * F, gr);
         return;
     }
+    uint32_t ent[1 << D];
+    float wt[1 << D];
 #pragma unroll
     for (int c = 0; c < (1 << D); ++c) {
         float weight = 1.0f;
@@ -73,11 +75,34 @@ __global__ void __launch_bounds__(256) grid_bwd_atomic_kernel(const GridParams p
                 gc[d] = g[d] + 1u;
             }
         }
-        const uint32_t e = grid_index<D>(p.grid_type, p.hash_type, hsize, res, gc);
+        wt[c] = weight;
+        ent[c] = grid_index<D>(p.grid_type, p.hash_type, hsize, res, gc);
+    }
+#pragma unroll
+    for (int c = 0; c < (1 << D); ++c) {
+        const uint32_t e = ent[c];
         float contrib[F];
 #pragma unroll
-        for (int f = 0; f < F; ++f) contrib[f] = __fmul_rn(weight, gr[f]);
-        red_add_entry<F>(gl + (size_t)e * F, contrib);
+        for (int f = 0; f < F; ++f) contrib[f] = __fmul_rn(wt[c], gr[f]);
+        if constexpr (F == 2) {
+            // corners c and c + 1 (c even) are often the two entries of one aligned 16-byte pair: one reduction for both
+            if ((c & 1) == 0) {
+                const uint32_t e1 = ent[c + 1];
+                const float n0 = __fmul_rn(wt[c + 1], gr[0]), n1 = __fmul_rn(wt[c + 1], gr[1]);
+                if ((e ^ e1) == 1u) {
+                    const bool odd = e & 1u;
+                    const float both[4] = {odd ? n0 : contrib[0], odd ? n1 : contrib[1], odd ? contrib[0] : n0,
+                                           odd ? contrib[1] : n1};
+                    red_add_entry<4>(gl + (size_t)(e & ~1u) * 2, both);
+                } else {
+                    const float next[2] = {n0, n1};
+                    red_add_entry<2>(gl + (size_t)e * 2, contrib);
+                    red_add_entry<2>(gl + (size_t)e1 * 2, next);
+                }
+            }
+        } else {
+            red_add_entry<F>(gl + (size_t)e * F, contrib);
+        }
     }
 }
 
