@@ -139,7 +139,7 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ chain-GEMM issuer
-        if (lane == 0 && my_tiles > 0) {
+        if (my_tiles > 0) { // all lanes run the loop, one elected lane issues (see ptx::elect_one)
             constexpr uint32_t idesc_fwd = ptx::make_idesc_bf16(128, W, 0, 1); // B = W_l read MN-major
             constexpr uint32_t idesc_bwd = ptx::make_idesc_bf16(128, W, 0, 0); // B = W_l read K-major
             const uint64_t x_desc0 = T::kdesc_base(smem_base + S::X);
@@ -148,16 +148,15 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
             const uint64_t wk_desc0 = T::kdesc_base(smem_base + S::WBUF(n_mat));
             const uint64_t wmn_desc0 = T::mndesc_base(smem_base + S::WBUF(n_mat), T::WGT_ATOM_BYTES);
             bool ok = ptx::mbar_wait(&bars.w_full, 0, abort_flag);
-            if (!ok) atomicExch(status, KS_TIMEOUT_WEIGHTS);
+            if (!ok && lane == 0) atomicExch(status, KS_TIMEOUT_WEIGHTS);
             uint32_t sr_parity = 0;
             uint32_t ci_count = 0; // chain_issued signals sent
-            auto signal_chain_issued = [&]() {
+            auto signal_chain_issued = [&]() { // called by the elected lane
                 ptx::mbar_arrive(&bars.chain_issued[ci_count & 1u]);
-                ++ci_count;
             };
             auto wait_step = [&]() {
                 const long long t0 = TNN_TIC();
-                const bool r = ptx::mbar_wait_busy(&bars.step_ready, sr_parity, abort_flag);
+                const bool r = ptx::mbar_wait(&bars.step_ready, sr_parity, abort_flag);
                 sr_parity ^= 1u;
                 TNN_TOC(0, t0);
                 return r;
@@ -167,52 +166,64 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                 const int b = t & 1;
                 // the previous tile's last hand-over (delta_0) also says the accumulator is drained
                 if (t > 0 && !wait_step()) ok = false;
-                if (ok && !ptx::mbar_wait_busy(&bars.x_full[b], (t >> 1) & 1, abort_flag)) ok = false;
+                if (ok && !ptx::mbar_wait(&bars.x_full[b], (t >> 1) & 1, abort_flag)) ok = false;
                 if (!ok) {
-                    atomicExch(status, KS_TIMEOUT_MMA | 1);
+                    if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 1);
                     break;
                 }
                 ptx::tc_fence_after_sync();
-                T::template issue_chain<true>(acc_tmem, x_desc0 + (uint64_t)(b * T::ACT_UNITS), wmn_desc0, idesc_fwd);
-                ptx::mma_commit(&bars.acc_full);
-                ptx::mma_commit(&bars.x_empty[b]);
-                // the previous tile's last weight-gradient GEMM (layer 0) may queue behind this one
-                if (t > 0) signal_chain_issued();
+                if (ptx::elect_one()) {
+                    T::template issue_chain<true>(acc_tmem, x_desc0 + (uint64_t)(b * T::ACT_UNITS), wmn_desc0, idesc_fwd);
+                    ptx::mma_commit(&bars.acc_full);
+                    ptx::mma_commit(&bars.x_empty[b]);
+                    // the previous tile's last weight-gradient GEMM (layer 0) may queue behind this one
+                    if (t > 0) signal_chain_issued();
+                }
+                __syncwarp();
+                if (t > 0) ++ci_count;
                 for (int l = 1; l <= L; ++l) { // forward
                     if (!wait_step()) {
-                        atomicExch(status, KS_TIMEOUT_MMA | 2 | (l << 4));
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 2 | (l << 4));
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    T::template issue_chain<true>(acc_tmem, a_desc0 + (uint64_t)((l - 1) * T::ACT_UNITS),
-                                                  wmn_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc_fwd);
-                    ptx::mma_commit(&bars.acc_full);
+                    if (ptx::elect_one()) {
+                        T::template issue_chain<true>(acc_tmem, a_desc0 + (uint64_t)((l - 1) * T::ACT_UNITS),
+                                                      wmn_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc_fwd);
+                        ptx::mma_commit(&bars.acc_full);
+                    }
+                    __syncwarp();
                 }
                 for (int l = L; ok && l >= 1; --l) { // backward: delta_l sits in D[(L - l) & 1]
                     if (!wait_step()) {
-                        atomicExch(status, KS_TIMEOUT_MMA | 3 | (l << 4));
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 3 | (l << 4));
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    T::template issue_chain<false>(acc_tmem, d_desc0 + (uint64_t)(((L - l) & 1) * T::ACT_UNITS),
-                                                   wk_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc_bwd);
-                    ptx::mma_commit(&bars.acc_full);
-                    signal_chain_issued(); // the weight-gradient GEMM of layer l may follow
+                    if (ptx::elect_one()) {
+                        T::template issue_chain<false>(acc_tmem, d_desc0 + (uint64_t)(((L - l) & 1) * T::ACT_UNITS),
+                                                       wk_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc_bwd);
+                        ptx::mma_commit(&bars.acc_full);
+                        signal_chain_issued(); // the weight-gradient GEMM of layer l may follow
+                    }
+                    __syncwarp();
+                    ++ci_count;
                 }
             }
-            if (ok) signal_chain_issued(); // releases the very last layer-0 weight-gradient GEMM
+            if (ok && ptx::elect_one()) signal_chain_issued(); // releases the very last layer-0 weight-gradient GEMM
+            __syncwarp();
             TNN_TOC(1, t_all);
             if constexpr (PROF) {
-                if (blockIdx.x == 0 && prof)
+                if (blockIdx.x == 0 && prof && lane == 0)
                     printf("[train prof] chain issuer: tiles %d, waiting for the epilogue %lld, total %lld cycles\n",
                            my_tiles, prof_acc[0], prof_acc[1]);
             }
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------ weight-gradient issuer
-        if (lane == 0 && my_tiles > 0) {
+        if (my_tiles > 0) {
             constexpr int DW_M = (W == 128) ? 128 : 64;
             constexpr uint32_t idesc_dw = ptx::make_idesc_bf16(DW_M, W, 1, 1);
             const uint64_t x_desc0 = T::mndesc_base(smem_base + S::X, T::ACT_ATOM_BYTES);
@@ -226,13 +237,13 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                     const uint32_t kb = k & 1u, kp = (k >> 1) & 1u;
                     ++k;
                     if (!ptx::mbar_wait(&bars.dw_go[kb], kp, abort_flag)) {
-                        atomicExch(status, KS_TIMEOUT_MMA | 4 | (l << 4));
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 4 | (l << 4));
                         ok = false;
                         break;
                     }
                     // keep the chain GEMM that consumes the same delta tile ahead in the tensor pipe's queue
                     if (!ptx::mbar_wait(&bars.chain_issued[kb], kp, abort_flag)) {
-                        atomicExch(status, KS_TIMEOUT_MMA | 5 | (l << 4));
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 5 | (l << 4));
                         ok = false;
                         break;
                     }
@@ -240,16 +251,20 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                     const int p = (L - l) & 1;
                     const uint64_t act_desc = (l == 0) ? x_desc0 + (uint64_t)(b * T::ACT_UNITS)
                                                        : a_desc0 + (uint64_t)((l - 1) * T::ACT_UNITS);
-                    T::issue_outer(tmem_base + (uint32_t)(W + l * W), d_desc0 + (uint64_t)(p * T::ACT_UNITS), act_desc,
-                                   idesc_dw, t > 0 ? 1u : 0u);
-                    ptx::mma_commit(&bars.d_free[p]);
-                    if (l == 0)
-                        ptx::mma_commit(&bars.x_empty[b]);
-                    else
-                        ptx::mma_commit(&bars.a_free[l]);
+                    if (ptx::elect_one()) {
+                        T::issue_outer(tmem_base + (uint32_t)(W + l * W), d_desc0 + (uint64_t)(p * T::ACT_UNITS), act_desc,
+                                       idesc_dw, t > 0 ? 1u : 0u);
+                        ptx::mma_commit(&bars.d_free[p]);
+                        if (l == 0)
+                            ptx::mma_commit(&bars.x_empty[b]);
+                        else
+                            ptx::mma_commit(&bars.a_free[l]);
+                    }
+                    __syncwarp();
                 }
             }
-            ptx::mma_commit(&bars.all_done);
+            if (ptx::elect_one()) ptx::mma_commit(&bars.all_done);
+            __syncwarp();
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------ epilogue: four threads per row
