@@ -26,6 +26,9 @@
 namespace tnn {
 
 constexpr int kBwdMaxRing = 3;
+constexpr int kBwdEpiWarps = 8;                      // epilogue: two threads per tile row
+constexpr int kBwdEpiThreads = 32 * kBwdEpiWarps;
+constexpr int kBwdThreads = 64 + kBwdEpiThreads;     // producer warp, issuer warp, epilogue warps
 
 template <int W, bool BIG> struct BwdSmem {
     using T = Tile<W>;
@@ -54,7 +57,7 @@ struct BwdBarriers {
 };
 
 template <int W, bool B_MN_MAJOR, bool BIG>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_interm,
                const __grid_constant__ CUtensorMap tm_ibwd, const __grid_constant__ CUtensorMap tm_dx,
                const __nv_bfloat16 *__restrict__ wimg, float *__restrict__ dw_slabs, int n_tiles, int n_mat, int act,
@@ -85,9 +88,9 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
         }
         for (int r = 0; r < kBwdRing; ++r) {
             ptx::mbar_init(&bars.a_full[r], 1);
-            ptx::mbar_init(&bars.a_empty[r], 129); // 128 epilogue threads + MMA commit
+            ptx::mbar_init(&bars.a_empty[r], kBwdEpiWarps + 1); // epilogue warps + MMA commit
         }
-        ptx::mbar_init(&bars.d_ready, 128);
+        ptx::mbar_init(&bars.d_ready, kBwdEpiWarps);
         ptx::mbar_init(&bars.acc_full, 1);
         ptx::mbar_init(&bars.all_done, 1);
         bars.abort_flag = 0;
@@ -265,15 +268,30 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
             __syncwarp();
         }
     } else {
-        // ------------------------------------------------------------ epilogue group (4 warps)
-        const int quad = warp & 3;
+        // ------------------------------------------------------------ epilogue group: two threads per row
+        const int quad = warp & 3;            // TMEM lane quarter this warp may touch
+        const int half = (warp - 2) >> 2;     // which half of the columns this thread owns
         const int row = quad * 32 + lane;
         const bool leader = (warp == 2) && lane == 0;
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
         bool ok = true;
         int r = 0;  // forward-activation loads consumed
         int ac = 0; // acc_full completions consumed
-        constexpr int CW = (W >= 32) ? 32 : 16;
+        constexpr int CPT = W / 2;                 // columns per thread
+        constexpr int CW = CPT < 32 ? CPT : 32;    // columns per TMEM load
+        constexpr int NLD = CPT / CW;
+        const int col0 = half * CPT;
+        auto chunk_off = [&](int c) { // byte offset of the 16-byte chunk holding columns c..c+7 of this thread's row
+            return (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES + T::chunk_off(row, (c % T::ATOM_COLS) / 8);
+        };
+        auto load_cols = [&](uint32_t taddr, uint32_t (&v)[CW]) {
+            if constexpr (CW == 32)
+                ptx::tmem_ld32(taddr, v);
+            else if constexpr (CW == 16)
+                ptx::tmem_ld16(taddr, v);
+            else
+                ptx::tmem_ld8(taddr, v);
+        };
 
         for (int t = 0; ok && t < my_tiles; ++t) {
             const int tile = blockIdx.x + t * gridDim.x;
@@ -298,8 +316,8 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                 dispatch_act(out_act, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
 #pragma unroll
-                    for (int c = 0; c < W; c += 8) {
-                        const int off = (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES + T::chunk_off(row, (c % T::ATOM_COLS) / 8);
+                    for (int cc = 0; cc < CPT; cc += 8) {
+                        const int off = chunk_off(col0 + cc);
                         uint4 d = *reinterpret_cast<const uint4 *>(dybuf + off);
                         const uint4 y = *reinterpret_cast<const uint4 *>(ybuf + off);
                         d.x = act_bwd_pack_t<ACT>(ptx::bf16lo_to_f32(d.x), ptx::bf16hi_to_f32(d.x), y.x);
@@ -310,12 +328,15 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                     }
                 });
                 ptx::fence_proxy_async_smem();
-                ptx::mbar_arrive(&bars.d_ready);
-                ptx::mbar_arrive(&bars.a_empty[slot]);
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(&bars.d_ready);
+                    ptx::mbar_arrive(&bars.a_empty[slot]);
+                }
                 ++r;
             }
             if (store_bwd) {
-                ptx::named_bar_sync(1, 128);
+                ptx::named_bar_sync(1, kBwdEpiThreads);
                 if (leader) {
                     for (int at = 0; at < T::KATOMS; ++at)
                         ptx::tma_store_3d(&tm_ibwd, dybuf + at * T::ACT_ATOM_BYTES, at * T::ATOM_COLS, tile * T::TM, L);
@@ -352,18 +373,12 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                             else
                                 ptx::tma_wait_group_read<0>();
                         }
-                        ptx::named_bar_sync(1, 128);
+                        ptx::named_bar_sync(1, kBwdEpiThreads);
                     }
                     const uint8_t *abuf = smem + S::AR + slot * T::ACT_BYTES;
-                    constexpr int NLD = W / CW;
                     uint32_t v[NLD][CW];
 #pragma unroll
-                    for (int i = 0; i < NLD; ++i) {
-                        if constexpr (CW == 32)
-                            ptx::tmem_ld32(acc_tmem + lane_addr + i * CW, v[i]);
-                        else
-                            ptx::tmem_ld16(acc_tmem + lane_addr + i * CW, v[i]);
-                    }
+                    for (int i = 0; i < NLD; ++i) load_cols(acc_tmem + lane_addr + col0 + i * CW, v[i]);
                     ptx::tmem_ld_wait();
                     dispatch_act((l > 0) ? act : (int)ACT_NONE, [&](auto tag) {
                         constexpr int ACT = decltype(tag)::value;
@@ -371,9 +386,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                         for (int i = 0; i < NLD; ++i) {
 #pragma unroll
                             for (int ch = 0; ch < CW / 8; ++ch) {
-                                const int c = i * CW + ch * 8;
-                                const int off =
-                                    (c / T::ATOM_COLS) * T::ACT_ATOM_BYTES + T::chunk_off(row, (c % T::ATOM_COLS) / 8);
+                                const int off = chunk_off(col0 + i * CW + ch * 8);
                                 uint4 f = make_uint4(0, 0, 0, 0);
                                 if constexpr (ACT != ACT_NONE) f = *reinterpret_cast<const uint4 *>(abuf + off);
                                 uint4 o;
@@ -387,12 +400,14 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                     });
                     ptx::fence_proxy_async_smem();
                     ptx::tc_fence_before_sync();
-                    ptx::mbar_arrive(&bars.d_ready);
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&bars.d_ready);
                 }
-                ptx::mbar_arrive(&bars.a_empty[slot]);
+                __syncwarp(); // every lane has read its part of the activation tile
+                if (lane == 0) ptx::mbar_arrive(&bars.a_empty[slot]);
                 ++r;
                 if (produce && (store_bwd || l == 0)) {
-                    ptx::named_bar_sync(1, 128);
+                    ptx::named_bar_sync(1, kBwdEpiThreads);
                     if (leader) {
                         for (int at = 0; at < T::KATOMS; ++at) {
                             if (l > 0) {
@@ -431,12 +446,9 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                 const int o = (S::DW_M == 64) ? quad * 16 + lane : quad * 32 + lane;
                 const bool valid = (S::DW_M == 64) ? (lane < 16 && o < W) : true;
 #pragma unroll
-                for (int c0 = 0; c0 < W; c0 += CW) {
+                for (int c0 = col0; c0 < col0 + CPT; c0 += CW) {
                     uint32_t v[CW];
-                    if constexpr (CW == 32)
-                        ptx::tmem_ld32(dw_tmem(l) + lane_addr + c0, v);
-                    else
-                        ptx::tmem_ld16(dw_tmem(l) + lane_addr + c0, v);
+                    load_cols(dw_tmem(l) + lane_addr + c0, v);
                     ptx::tmem_ld_wait();
                     if (valid) {
                         float4 *dstp = reinterpret_cast<float4 *>(slab + ((size_t)l * W + o) * W + c0);
@@ -484,7 +496,7 @@ template <int W, bool B_MN, bool BIG> static cudaError_t launch_bwd_variant(BwdL
         while (tmem_cols < cols_needed) tmem_cols *= 2;
         const int first = lo == 0; // deltas and dL/dx are the same in every pass: store them once
         // K-major weights for the chain are rows = input feature; the MN-major variant reads the transposed image
-        kern<<<grid, 192, smem, p.stream>>>(p.tm_dy, p.tm_interm, p.tm_ibwd, p.tm_dx, B_MN ? p.wimg_t : p.wimg,
+        kern<<<grid, kBwdThreads, smem, p.stream>>>(p.tm_dy, p.tm_interm, p.tm_ibwd, p.tm_dx, B_MN ? p.wimg_t : p.wimg,
                                             p.dw_partials, n_tiles, p.n_mat, p.act, p.out_act, first ? p.store_bwd : 0,
                                             first ? p.want_dx : 0, tmem_cols, lo, hi, p.status);
         e = cudaGetLastError();
