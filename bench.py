@@ -219,6 +219,37 @@ def run_only(args):
     out = {"only": args.only, "log2_batch": args.log2_batch, "steps": args.steps}
     if args.only == "grid":
         out.update(grid_leg(L, torch, batch, args.steps, timed))
+    elif args.only == "c4":
+        # hash grid (3-D, 16 levels x 2 features, 2^19 entries per level) feeding a width-64 network with 2 hidden
+        # layers and 3 outputs, through the torch.nn.Module front end: forward, and forward + backward of an L2 loss
+        import tiny_dpcpp_nn as tnn
+
+        net_cfg = {"n_neurons": 64, "n_hidden_layers": 2, "activation": "relu", "output_activation": "none"}
+        model = tnn.NetworkWithInputEncoding(3, 3, net_cfg, GRID_CFG, seed=3)
+        gen = torch.Generator(device="cuda").manual_seed(7)
+        pos = torch.rand((batch, 3), device="cuda", generator=gen)
+        target = torch.rand((batch, 3), device="cuda", generator=gen)
+
+        def fwd():
+            with torch.no_grad():
+                return model(pos)
+
+        def fwd_bwd():
+            model.zero_grad(set_to_none=True)
+            loss = ((model(pos).float() - target) ** 2).mean()
+            loss.backward()
+            return loss
+
+        model.eval()
+        for _ in range(2):
+            fwd()
+        out["c4_inference_ms"] = timed(fwd, args.steps) / args.steps
+        model.train()
+        for _ in range(2):
+            fwd_bwd()
+        out["c4_forward_backward_ms"] = timed(fwd_bwd, args.steps) / args.steps
+        out["c4_inference_samples_per_s"] = batch / out["c4_inference_ms"] * 1e3
+        out["c4_training_samples_per_s"] = batch / out["c4_forward_backward_ms"] * 1e3
     elif args.only == "sweep":
         # the reference's sweep (benchmarks/benchmark_all.cpp): widths 16..128, 2 / 4 / 8 hidden layers
         peaks = load_peaks()
@@ -517,8 +548,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--log2-batch", type=int, default=LOG2_BATCH)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--only", choices=["train", "infer", "grid", "sweep"],
-                    help="run one kernel only (profiler captures), or the width / depth sweep")
+    ap.add_argument("--only", choices=["train", "infer", "grid", "sweep", "c4"],
+                    help="run one kernel only (profiler captures), the width / depth sweep, or the grid -> MLP model")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

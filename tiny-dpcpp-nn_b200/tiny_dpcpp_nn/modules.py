@@ -56,7 +56,10 @@ class _module_function(torch.autograd.Function):
     @staticmethod
     def forward(ctx, native_tnn_module, input, params, info, loss_scale):
         batch_size = input.shape[0]
-        if info["is_in_eval_mode"]:
+        if "encoding_out_dtype" in info:
+            # an encoding that feeds a network writes the network's dtype directly: no separate cast pass
+            output = native_tnn_module.fwd(input, out_dtype=info["encoding_out_dtype"])
+        elif info["is_in_eval_mode"]:
             output = native_tnn_module.inference(input)
         else:
             output = native_tnn_module.fwd(input)
@@ -86,7 +89,8 @@ class _module_function(torch.autograd.Function):
                 if batch_size == 0 or params.numel() <= 1:
                     grad = torch.zeros_like(params)
                 else:
-                    _, grad = ctx.native_tnn_module.bwd_with_encoding_grad(doutput.float(), input, False, False)
+                    dy = doutput if doutput.dtype == torch.bfloat16 else doutput.float()
+                    _, grad = ctx.native_tnn_module.bwd_with_encoding_grad(dy, input, False, False)
             else:
                 input_grad, grad = ctx.native_tnn_module.bwd_no_encoding_grad(
                     doutput.to(torch.bfloat16), True, True, grads_dtype=torch.float32)
@@ -124,6 +128,8 @@ class Module(torch.nn.Module):
             return
         packed = params is None and self.name != "encoding"  # encoding weights are never packed
         if params is None:
+            # (pushed before every forward like modules.py:236 of the reference: an optimiser that writes through
+            # `.data` leaves no trace on the tensor's version counter, so the push cannot be skipped safely)
             params = self.params
         assert isinstance(params, torch.Tensor), "Params is not a torch.Tensor"
         src = params.detach()
@@ -154,6 +160,8 @@ class Module(torch.nn.Module):
                          "output_dim": self.n_output_dims, "width": self.width})
         if hasattr(self, "encoding_config"):
             info.update({"encoding_config": self.encoding_config})
+            if getattr(self, "output_dtype", None) is not None:
+                info.update({"encoding_out_dtype": self.output_dtype})
         self.set_params()
         output = _module_function.apply(self.tnn_module, padded_tensor.contiguous(), self.params, info,
                                         self.loss_scale)
@@ -226,6 +234,8 @@ class NetworkWithInputEncoding(Module):
                                  store_params_as_full_precision=store_params_as_full_precision,
                                  n_output_dims=network_config["n_neurons"], seed=seed)
         assert self.encoding.n_output_dims == network_config["n_neurons"]
+        if dtype == torch.bfloat16:
+            self.encoding.output_dtype = dtype  # the reference casts in Python (modules.py:223); here the kernel does
         self.network = Network(self.encoding.n_output_dims, n_output_dims, network_config, device=device, dtype=dtype,
                                store_params_as_full_precision=store_params_as_full_precision, use_bias=use_bias,
                                seed=seed)
