@@ -146,8 +146,13 @@ int tnn_encoding_initialize_params(tnn_encoding *enc, uint64_t seed, void *strea
 /* EncodingModule::set_params / get_params - include/tnn_api.h:424-439: n_params fp32, never packed. */
 int tnn_encoding_set_params(tnn_encoding *enc, const float *params, void *stream);
 int tnn_encoding_get_params(const tnn_encoding *enc, float *params_out, void *stream);
-/* Device pointer of the fp32 table owned by the handle (for in-place optimiser steps). */
+/* Device pointer of the fp32 table the handle currently uses (for in-place optimiser steps). */
 float *tnn_encoding_params_ptr(tnn_encoding *enc);
+/* Makes the handle read its n_params fp32 parameters from caller-owned device memory (16-byte aligned) instead of
+ * its own table, so that a framework's parameter tensor is used in place; NULL returns to the owned table.  The
+ * memory must stay valid while it is bound.  No reference counterpart: the reference copies the parameter tensor
+ * into the module before every forward pass (dpcpp_bindings/tiny_dpcpp_nn/modules.py:236). */
+int tnn_encoding_bind_params(tnn_encoding *enc, float *params);
 /* EncodingModule::forward_pass - include/tnn_api.h:332-356 (kernel_grid, grid.h:37-135; identity,
  * identity.h:63-77).  x: batch x n_input_dims fp32.  out: batch x n_output_dims of out_dtype
  * (fp32 like the reference, or bf16 to feed a network directly). */

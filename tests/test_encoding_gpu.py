@@ -123,6 +123,25 @@ def test_grid_adjoint_property_at_full_size(tnn_lib):
     assert abs(lhs - rhs) <= 1e-5 * abs(lhs)
 
 
+def test_bound_parameter_storage_is_used_in_place(tnn_lib):
+    """tnn_encoding_bind_params: the kernels read the caller's tensor; in-place updates need no set_params."""
+    cfg = dict(otype="HashGrid", n_dims_to_encode=2, n_levels=4, n_features_per_level=2, log2_hashmap_size=10,
+               base_resolution=4, per_level_scale=2.0)
+    enc = tnn_lib.create_encoding("HashGrid", cfg, 8, seed=1)
+    x = _t(synth.uniform_inputs(256, 2, 5, 0.0, 1.0))
+    table = torch.rand(enc.n_params(), device="cuda") - 0.5
+    enc.set_params(table)
+    ref = enc.fwd(x).clone()
+    bound = table.clone()
+    enc.bind_params(bound)
+    assert torch.equal(enc.fwd(x), ref)
+    bound.mul_(2.0)  # an optimiser step would do this
+    assert torch.equal(enc.fwd(x), enc.fwd(x)) and torch.allclose(enc.fwd(x), 2.0 * ref)
+    assert torch.equal(enc.get_params().reshape(-1), bound)
+    enc.bind_params(None)  # back to the handle's own table, which still holds the first values
+    assert torch.equal(enc.fwd(x), ref)
+
+
 def test_identity_encoding(tnn_lib):
     """include/encodings/identity.h:63-77; test/doctest_encodings.cpp:156-195: pads with ones."""
     enc = tnn_lib.create_encoding("Identity", dict(otype="Identity", n_dims_to_encode=2, scale=1.0, offset=0.0), 64)

@@ -493,7 +493,9 @@ struct tnn_encoding {
     int n_frequencies = 0;             // > 0: frequency encoding
     tnn::GridParams gp{};
     size_t n_params = 0;
-    float *table = nullptr;
+    float *table = nullptr;    // owned storage
+    float *bound = nullptr;    // caller-owned storage used instead, when set (tnn_encoding_bind_params)
+    float *params() const { return bound ? bound : table; }
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
 };
@@ -608,7 +610,14 @@ int tnn_encoding_destroy(tnn_encoding *e) {
 size_t tnn_encoding_n_params(const tnn_encoding *e) { return e ? e->n_params : 0; }
 int tnn_encoding_n_output_dims(const tnn_encoding *e) { return e ? e->padded : 0; }
 int tnn_encoding_n_input_dims(const tnn_encoding *e) { return e ? e->n_in : 0; }
-float *tnn_encoding_params_ptr(tnn_encoding *e) { return e ? e->table : nullptr; }
+float *tnn_encoding_params_ptr(tnn_encoding *e) { return e ? e->params() : nullptr; }
+
+int tnn_encoding_bind_params(tnn_encoding *e, float *params) {
+    if (!e) return fail("encoding is null");
+    if (params && reinterpret_cast<uintptr_t>(params) % 16 != 0) return fail("parameter storage must be 16-byte aligned");
+    e->bound = params;
+    return 0;
+}
 
 int tnn_encoding_level_info(const tnn_encoding *e, int level, uint32_t *offset, uint32_t *size, float *scale,
                             uint32_t *resolution) {
@@ -629,7 +638,7 @@ int tnn_encoding_initialize_params(tnn_encoding *e, uint64_t seed, void *stream)
     std::uniform_real_distribution<float> dis(-1e-4f, 1e-4f);
     std::vector<float> h(e->n_params);
     for (auto &v : h) v = dis(gen);
-    TNN_CUDA(cudaMemcpyAsync(e->table, h.data(), h.size() * sizeof(float), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    TNN_CUDA(cudaMemcpyAsync(e->params(), h.data(), h.size() * sizeof(float), cudaMemcpyHostToDevice, (cudaStream_t)stream));
     TNN_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     return 0;
     TNN_GUARD_END
@@ -638,14 +647,15 @@ int tnn_encoding_initialize_params(tnn_encoding *e, uint64_t seed, void *stream)
 int tnn_encoding_set_params(tnn_encoding *e, const float *params, void *stream) {
     if (!e || !params) return fail("null argument");
     if (!e->n_params) return fail("no encoding params to set");
-    TNN_CUDA(cudaMemcpyAsync(e->table, params, e->n_params * sizeof(float), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    if (params == e->params()) return 0; // bound storage: nothing to copy
+    TNN_CUDA(cudaMemcpyAsync(e->params(), params, e->n_params * sizeof(float), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
     return 0;
 }
 
 int tnn_encoding_get_params(const tnn_encoding *e, float *out, void *stream) {
     if (!e || !out) return fail("null argument");
     if (!e->n_params) return 0;
-    TNN_CUDA(cudaMemcpyAsync(out, e->table, e->n_params * sizeof(float), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    TNN_CUDA(cudaMemcpyAsync(out, e->params(), e->n_params * sizeof(float), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
     return 0;
 }
 
@@ -658,7 +668,7 @@ int tnn_encoding_forward(tnn_encoding *e, const float *x, void *out, int out_dty
     if (batch > 0xFFFFFFFFull / 8) return fail("batch too large");
     const int bf = out_dtype == TNN_DTYPE_BF16;
     if (e->is_grid)
-        TNN_CUDA(tnn::launch_grid_fwd(e->gp, x, e->table, out, bf, batch, (cudaStream_t)stream));
+        TNN_CUDA(tnn::launch_grid_fwd(e->gp, x, e->params(), out, bf, batch, (cudaStream_t)stream));
     else if (e->n_frequencies > 0)
         TNN_CUDA(tnn::launch_frequency_fwd(x, out, bf, batch, e->n_in, e->n_frequencies, e->padded, (cudaStream_t)stream));
     else

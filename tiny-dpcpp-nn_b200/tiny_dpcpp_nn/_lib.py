@@ -53,6 +53,7 @@ _SIGNATURES = {
     "tnn_encoding_set_params": (_c.c_int, [_vp, _vp, _vp]),
     "tnn_encoding_get_params": (_c.c_int, [_vp, _vp, _vp]),
     "tnn_encoding_params_ptr": (_vp, [_vp]),
+    "tnn_encoding_bind_params": (ctypes.c_int, [_vp, _vp]),
     "tnn_encoding_forward": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _c.c_size_t, _vp]),
     "tnn_encoding_backward": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _vp, _c.c_size_t, _c.c_int, _vp]),
     "tnn_l2_loss": (_c.c_int, [_vp, _vp, _c.c_int, _vp, _vp, _c.c_size_t, _c.c_int, _c.c_float, _vp, _vp]),
@@ -348,6 +349,19 @@ class EncodingModule:
             raise TnnError("encoding params must be n_params float32 values")
         check(self._lib.tnn_encoding_set_params(self._h, dptr(params), stream_ptr()))
         params.record_stream(torch.cuda.current_stream())
+
+    def bind_params(self, params):
+        """Use `params` (n_params float32 values on the device) in place as the parameter table; the caller keeps
+        the tensor alive while it is bound.  None returns to the table owned by the handle."""
+        if params is None:
+            check(self._lib.tnn_encoding_bind_params(self._h, None))
+            self._bound = None
+            return
+        if params.dtype != torch.float32 or params.numel() != self.n_params() or not params.is_contiguous() \
+                or not params.is_cuda:
+            raise TnnError("bound encoding params must be n_params contiguous float32 values on the device")
+        check(self._lib.tnn_encoding_bind_params(self._h, dptr(params)))
+        self._bound = params  # keeps the storage alive
 
     def get_params(self):
         out = torch.empty((self.n_params(), 1) if self.n_params() else (0,), dtype=torch.float32, device="cuda")

@@ -133,6 +133,12 @@ class Module(torch.nn.Module):
             params = self.params
         assert isinstance(params, torch.Tensor), "Params is not a torch.Tensor"
         src = params.detach()
+        if self.name == "encoding" and params is self.params and src.dtype == torch.float32 and src.is_contiguous():
+            # the parameter tensor itself is the table the kernels read: no copy per forward pass
+            if getattr(self, "_bound_ptr", None) != src.data_ptr():
+                self.tnn_module.bind_params(src)
+                self._bound_ptr = src.data_ptr()
+            return
         if self.name == "encoding":
             src = src.to(torch.float32)
         elif src.dtype not in (torch.float32, torch.bfloat16):
