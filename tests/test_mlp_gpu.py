@@ -70,13 +70,14 @@ def test_forward_backward_matrix(tnn_lib, W, nh, act, oact):
         _check(dxg.float().cpu().numpy().reshape(batch, W), dx)
 
 
-@pytest.mark.parametrize("W,nh,variant", [(128, 2, 0), (128, 4, 0), (128, 8, 0), (64, 8, 0), (32, 8, 0), (16, 8, 0),
-                                          (64, 4, 256), (32, 2, 256)])
-def test_wide_and_deep_networks(tnn_lib, W, nh, variant):
+@pytest.mark.parametrize("W,nh,variant,act,oact", [
+    (128, 2, 0, "relu", "none"), (128, 4, 0, "relu", "none"), (128, 8, 0, "relu", "none"), (64, 8, 0, "relu", "none"),
+    (32, 8, 0, "relu", "none"), (16, 8, 0, "relu", "none"), (64, 4, 256, "relu", "none"), (32, 2, 256, "relu", "none"),
+    (128, 4, 0, "sigmoid", "sigmoid"), (64, 8, 0, "none", "relu"), (64, 2, 256, "sigmoid", "sigmoid")])
+def test_wide_and_deep_networks(tnn_lib, W, nh, variant, act, oact):
     """The reference's sweep (benchmarks/benchmark_all.cpp: widths 16..128, up to 8+ hidden layers): networks whose
     weights do not stay resident (streamed through per-slot rings; variant 256 forces that path) and whose weight
     gradients need more than one pass over the tensor-memory accumulators."""
-    act, oact = "relu", "none"
     for batch in (64, 128 * 150 + 8):
         w, x = synth.mlp_case(W, nh, batch, w_seed=3, x_seed=200 + batch)
         n_mat = nh + 1
