@@ -192,6 +192,16 @@ def grid_leg(L, torch, batch, steps, timed):
         for _ in range(2):
             fn()
         res[name] = timed(fn, steps) / steps
+    # Adam over the whole table (fp32 parameters, two moments, gradient: 28 bytes per parameter and step)
+    n = enc.n_params()
+    table = torch.zeros(n, device="cuda")
+    m, v = torch.zeros_like(table), torch.zeros_like(table)
+    g = torch.rand(n, device="cuda", generator=gen) - 0.5
+    adam = lambda: L.adam_step(table, m, v, g, 1)  # noqa: E731
+    for _ in range(2):
+        adam()
+    res["grid_adam"] = timed(adam, steps) / steps
+    res["grid_adam_gbs"] = 28.0 * n / (res["grid_adam"] * 1e-3) * 1e-9
     return res
 
 
@@ -440,11 +450,17 @@ def run_gpu_arm(args):
     grid_ms = grid_leg(L, torch, grid_batch, max(3, min(args.steps, 10)), timed_local) if rank == 0 else {}
     # per sample and level: 8 corners x 2 features (4 B each) read, position read once, 2 features written
     grid_fwd_bytes = 16 * (8 * 2 * 4) + 3 * 4 + 32 * 4
+    grid_adam_gbs = grid_ms.pop("grid_adam_gbs", None)
+    grid_adam_ms = grid_ms.pop("grid_adam", None)
     grid_rooflines = [{"kernel": k, "ms": v, "batch": grid_batch,
                        "gbs": grid_fwd_bytes * grid_batch / (v * 1e-3) * 1e-9,
                        "frac_hbm": grid_fwd_bytes * grid_batch / (v * 1e-3) * 1e-9 / peaks["hbm_gbs"],
                        "note": "16 levels x 8 corners x 2 fp32 features gathered (or scattered) per sample; "
                                "the fine levels' tables exceed L2"} for k, v in grid_ms.items()]
+    if grid_adam_ms is not None:
+        grid_rooflines.append({"kernel": "adam_kernel (grid table, 14.2 M parameters)", "ms": grid_adam_ms,
+                               "gbs": grid_adam_gbs, "frac_hbm": grid_adam_gbs / peaks["hbm_gbs"],
+                               "note": "28 bytes per parameter and step: parameter, two moments read and written, gradient read"})
     dom_r = rooflines[0]
     roofline = {"bound": "tensor", "kernel": "mlp_train_pipe_kernel", "achieved": dom_r["tflops"], "peak": peaks["tflops"],
                 "unit": "TFLOP/s", "frac": dom_r["frac_tensor"],

@@ -216,3 +216,14 @@ def test_l2_loss_and_adam(tnn_lib):
         opt.step()
     assert np.allclose(tp.cpu().numpy(), p, rtol=1e-5, atol=1e-7)
     assert np.allclose(tp.cpu().numpy(), ref.detach().numpy(), rtol=1e-5, atol=1e-7)
+    # table-sized vectors take the 16-byte path plus a scalar tail: same arithmetic
+    n = (1 << 17) + 3
+    p0 = rng.normal(size=n).astype(np.float32)
+    p, m, vv = p0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+    tp, tm, tv = _t(p0), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    for step in range(1, 4):
+        gr = (rng.normal(size=n) * 1e-3).astype(np.float32)
+        O.adam(p, m, vv, gr, step)
+        tnn_lib.adam_step(tp, tm, tv, _t(gr), step)
+    assert np.allclose(tp.cpu().numpy(), p, rtol=1e-5, atol=1e-7)
+    assert np.allclose(tm.cpu().numpy(), m, rtol=1e-5, atol=1e-9) and np.allclose(tv.cpu().numpy(), vv, rtol=1e-5, atol=1e-12)
