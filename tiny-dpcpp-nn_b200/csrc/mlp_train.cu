@@ -336,7 +336,7 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
             const bool row_valid = grow < batch;
             // this thread's slice of the target row: requested now, consumed after the forward pass
             float tg[CPT];
-            if (row_valid && n_targets == W) {
+            if (row_valid && n_targets == W && (reinterpret_cast<uintptr_t>(targets) & 15) == 0) { // 16-byte loads
 #pragma unroll
                 for (int q4 = 0; q4 < CPT / 4; ++q4) {
                     const float4 t4 = __ldg(reinterpret_cast<const float4 *>(targets + grow * W + col0) + q4);

@@ -26,7 +26,7 @@
 
 namespace tnn {
 
-constexpr int kPipeMaxMat = 6; // (L + 3) * W TMEM columns and L + 6 tiles of shared memory must fit
+constexpr int kPipeMaxMat = 12; // upper bound of the barrier array; what fits is decided by shared memory and TMEM columns
 
 // TGT: the fp32 targets of a tile (128 x W, twice the bytes of a bf16 tile) are staged by TMA into the delta_L
 // buffer plus one more tile right behind it; the loss step pulls its slice into registers before delta_L is written.
@@ -373,8 +373,10 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
         auto load_acc = [&](uint32_t (&v)[CPT]) {
             if constexpr (CPT == 32)
                 ptx::tmem_ld32(acc_addr, v);
-            else
+            else if constexpr (CPT == 16)
                 ptx::tmem_ld16(acc_addr, v);
+            else
+                ptx::tmem_ld8(acc_addr, v);
             ptx::tmem_ld_wait();
         };
         for (int t = 0; ok && t < my_tiles; ++t) {
@@ -452,7 +454,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     ok = false;
                     break;
                 }
-            } else if (row_valid && n_targets == W) {
+            } else if (row_valid && n_targets == W && (reinterpret_cast<uintptr_t>(targets) & 15) == 0) {
 #pragma unroll
                 for (int q4 = 0; q4 < CPT / 4; ++q4) {
                     const float4 t4 = __ldg(reinterpret_cast<const float4 *>(targets + grow * W + col0) + q4);
@@ -600,8 +602,10 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 const long long t_l = TNN_TIC();
                 if constexpr (CPT == 32)
                     ptx::tmem_ld32(acc_addr, v);
-                else
+                else if constexpr (CPT == 16)
                     ptx::tmem_ld16(acc_addr, v);
+                else
+                    ptx::tmem_ld8(acc_addr, v);
                 ptx::tmem_ld_wait();
                 TNN_TOC(2, t_l);
                 const long long t_p = TNN_TIC();
@@ -651,8 +655,10 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 const uint32_t addr = tmem_base + ((uint32_t)(quad * 32) << 16) + 2 * W + l * W + col0;
                 if constexpr (CPT == 32)
                     ptx::tmem_ld32(addr, v);
-                else
+                else if constexpr (CPT == 16)
                     ptx::tmem_ld16(addr, v);
+                else
+                    ptx::tmem_ld8(addr, v);
                 ptx::tmem_ld_wait();
                 if (valid) {
                     float4 *dstp = reinterpret_cast<float4 *>(slab + ((size_t)l * W + o) * W + col0);
@@ -717,6 +723,7 @@ template <int W, bool TGT> static cudaError_t launch_pipe_w(TrainLaunch &p) {
 cudaError_t launch_mlp_train_pipe(TrainLaunch &p) {
     // staged targets need one more tile of shared memory: without room for it the per-thread loads remain
     cudaError_t e = cudaErrorInvalidConfiguration;
+    if (p.width == 16) return launch_pipe_w<16, false>(p); // 64-byte target rows: read directly
     if (p.width != 64 && p.width != 32) return e;
     const bool w64 = p.width == 64;
     if (p.tgt_tma) e = w64 ? launch_pipe_w<64, true>(p) : launch_pipe_w<32, true>(p);
