@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_interm,
                const __grid_constant__ CUtensorMap tm_ibwd, const __grid_constant__ CUtensorMap tm_dx,
                const __nv_bfloat16 *__restrict__ wimg, float *__restrict__ dw_slabs, int n_tiles, int n_mat, int act,
-               int out_act, int store_bwd, int want_dx, int tmem_cols, int dw_lo, int dw_hi, int *status) {
+               int out_act, int store_bwd, int want_dx, int tmem_cols, int dw_lo, int dw_hi, int l_stop, int *status) {
     using T = Tile<W>;
     using S = BwdSmem<W, BIG>;
     constexpr int kBwdRing = S::RING;
@@ -76,7 +76,9 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
     const uint32_t smem_base = ptx::smem_u32(smem);
     volatile uint32_t *abort_flag = &bars.abort_flag;
     const bool has_oact = out_act != ACT_NONE;
-    const int loads_per_tile = n_mat + (has_oact ? 1 : 0); // a_L..a_0 (+ y for the output activation)
+    // A pass walks the chain from layer L down to l_stop only: 0 in the pass that stores deltas / dL/dx, the first
+    // layer of its weight-gradient group in the others (delta_l below that is of no use to it).
+    const int loads_per_tile = (L - l_stop + 1) + (has_oact ? 1 : 0); // a_L..a_{l_stop} (+ y for the output activation)
     const int my_tiles = (n_tiles > (int)blockIdx.x) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
     if (threadIdx.x == 0) {
@@ -161,7 +163,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
             const uint64_t w_desc0 = B_MN_MAJOR ? T::mndesc_base(smem_base + S::WBUF, T::WGT_ATOM_BYTES)
                                                 : T::kdesc_base(smem_base + S::WBUF);
             // BIG: chain GEMM number g reads ring stage g & 1; its weights are fetched while GEMM g - 1 is issued
-            const int last_chain = want_dx ? 0 : 1; // lowest layer with a chain GEMM
+            const int last_chain = (l_stop == 0 && want_dx) ? 0 : l_stop + 1; // lowest layer with a chain GEMM
             [[maybe_unused]] uint32_t wg = 0;
             [[maybe_unused]] auto fetch_weights = [&](int l, uint32_t g) {
                 uint64_t *bar = &bars.wring_full[g & 1u];
@@ -197,7 +199,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 1);
                     break;
                 }
-                for (int l = L; ok && l >= 0; --l) {
+                for (int l = L; ok && l >= l_stop; --l) {
                     // delta_l: dL/dy buffer for l == L, else ping-pong buffer (L - 1 - l) & 1
                     // (index into the four contiguous delta tiles DY[0], DY[1], DP[0], DP[1])
                     const int d_idx = (l == L) ? b : NDY + ((L - 1 - l) & 1);
@@ -209,7 +211,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                         }
                         ++dr;
                     }
-                    const bool chain = l > 0 || want_dx;
+                    const bool chain = l > l_stop || (l_stop == 0 && want_dx);
                     uint64_t w_desc = w_desc0 + (uint64_t)(l * T::WGT_UNITS);
                     if constexpr (BIG) {
                         if (chain) {
@@ -343,9 +345,9 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                     ptx::tma_commit_group();
                 }
             }
-            for (int l = L; l >= 0; --l) {
+            for (int l = L; l >= l_stop; --l) {
                 const int slot = r % kBwdRing;
-                const bool produce = (l > 0) || want_dx; // this step turns the accumulator into a bf16 tile
+                const bool produce = (l > l_stop) || (l_stop == 0 && want_dx); // the accumulator becomes a bf16 tile
                 // delta_{l-1} goes to ping-pong buffer (L - l) & 1; dL/dx (l == 0) uses the same rule
                 uint8_t *dst = smem + S::DP + ((L - l) & 1) * T::ACT_BYTES;
                 if (produce) {
@@ -498,7 +500,7 @@ template <int W, bool B_MN, bool BIG> static cudaError_t launch_bwd_variant(BwdL
         // K-major weights for the chain are rows = input feature; the MN-major variant reads the transposed image
         kern<<<grid, kBwdThreads, smem, p.stream>>>(p.tm_dy, p.tm_interm, p.tm_ibwd, p.tm_dx, B_MN ? p.wimg_t : p.wimg,
                                             p.dw_partials, n_tiles, p.n_mat, p.act, p.out_act, first ? p.store_bwd : 0,
-                                            first ? p.want_dx : 0, tmem_cols, lo, hi, p.status);
+                                            first ? p.want_dx : 0, tmem_cols, lo, hi, first ? 0 : lo, p.status);
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
