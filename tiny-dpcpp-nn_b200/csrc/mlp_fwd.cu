@@ -48,7 +48,7 @@ template <int W, int NSLOT, bool TMEM_A, bool STORE_ALL, bool STREAM_W = false> 
     __host__ __device__ static constexpr int weight_tiles(int n_mat) { return STREAM_W ? 2 * NSLOT : n_mat; }
 };
 
-constexpr int kMaxSlots = 4;
+constexpr int kMaxSlots = 6;
 
 struct FwdBarriers {
     uint64_t w_full;
@@ -389,6 +389,13 @@ template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
     }
     if (p.variant & 2) return launch_variant<W, 2, false, false, true>(p);
     cudaError_t e = cudaErrorInvalidConfiguration;
+    if constexpr (W <= 32) {
+        // narrow layers are pure latency chains (one or two MMAs per layer): six tiles in flight instead of four
+        if (!(p.variant & (1 | 4 | 8))) {
+            e = launch_variant<W, 6, false, W >= 32, false>(p);
+            if (e != cudaErrorInvalidConfiguration) return e;
+        }
+    }
     if constexpr (W >= 32) {
         if (!(p.variant & 1)) {
             if (p.variant & 8) e = launch_variant<W, 3, false, true, false>(p);
