@@ -398,7 +398,9 @@ template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
     }
     if constexpr (W >= 32) {
         if (!(p.variant & 1)) {
-            if (p.variant & 8) e = launch_variant<W, 3, false, true, false>(p);
+            // measured at W = 64, batch 2^22: four tiles in flight win up to 4 hidden layers (0.170 / 0.213 ms at 2 / 4),
+            // three from 6 on (0.261 vs 0.272 ms at 6, 0.337 vs 0.465 ms at 8 layers)
+            if ((p.variant & 8) || (!(p.variant & 4) && p.n_mat >= 7)) e = launch_variant<W, 3, false, true, false>(p);
             if (e == cudaErrorInvalidConfiguration && !(p.variant & 4)) e = launch_variant<W, 4, false, true, false>(p);
             if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, false, true, false>(p);
             if (e != cudaErrorInvalidConfiguration) return e;
