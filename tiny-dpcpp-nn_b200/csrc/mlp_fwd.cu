@@ -35,9 +35,13 @@ template <int W, int NSLOT, bool TMEM_A, bool STORE_ALL, bool STREAM_W = false> 
     // activation buffers per slot: two (ping-pong) when every layer is also streamed out by TMA,
     // one when the next layer's MMA is the only reader
     static constexpr int NABUF = STORE_ALL ? 2 : 1;
+    // With the hidden activations in TMEM the only shared-memory tile a slot writes is its output, once per tile.
+    // Streamed-weight configurations, which are short of shared memory, let all slots take turns on one such tile.
+    static constexpr bool SHARED_OUT = TMEM_A && !STORE_ALL && STREAM_W && NSLOT > 1;
+    static constexpr int ABUF_TILES = SHARED_OUT ? 1 : NSLOT * NABUF;
     static constexpr int XBUF = 0;                                   // NSLOT input tiles
     static constexpr int ABUF = XBUF + NSLOT * T::ACT_BYTES;         // NSLOT x NABUF activation tiles
-    static constexpr int WBUF = ABUF + NSLOT * NABUF * T::ACT_BYTES; // (L+1) weight tiles follow
+    static constexpr int WBUF = ABUF + ABUF_TILES * T::ACT_BYTES;    // (L+1) weight tiles follow
     static constexpr int tmem_cols_needed = NSLOT * (W + (TMEM_A ? W / 2 : 0));
     static constexpr int tmem_cols =
         tmem_cols_needed <= 32 ? 32 : tmem_cols_needed <= 64 ? 64 : tmem_cols_needed <= 128 ? 128
@@ -59,6 +63,7 @@ struct FwdBarriers {
     uint64_t wring_full[kMaxSlots][2]; // STREAM_W: weight ring stages of every slot
     uint32_t tmem_base;
     uint32_t abort_flag;
+    uint32_t out_lock; // SHARED_OUT: 1 while a slot owns the output tile
 };
 
 template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN_MAJOR, bool STREAM_W = false>
@@ -94,6 +99,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
             ptx::mbar_init(&bars.wring_full[s][1], 1);
         }
         bars.abort_flag = 0;
+        bars.out_lock = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tmap(&tm_x);
         ptx::prefetch_tmap(&tm_y);
@@ -261,7 +267,8 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                 ptx::tc_fence_after_sync();
                 const int a = (l == L) ? out_act : act;
                 const bool to_tmem = TMEM_A && l < L;
-                uint8_t *abuf = smem + S::ABUF + (s * S::NABUF + (l & (S::NABUF - 1))) * T::ACT_BYTES;
+                uint8_t *abuf = smem + S::ABUF +
+                                (S::SHARED_OUT ? 0 : (s * S::NABUF + (l & (S::NABUF - 1))) * T::ACT_BYTES);
                 constexpr int CW = (W >= 32) ? 32 : 16; // columns per TMEM load
                 constexpr int NLD = W / CW;
                 uint32_t v[NLD][CW];
@@ -272,7 +279,31 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                     else
                         ptx::tmem_ld16(acc_addr + i * CW, v[i]);
                 }
-                if (!to_tmem && (STORE_ALL || TMEM_A || l == 0)) {
+                if constexpr (S::SHARED_OUT) {
+                    if (l == L) {
+                        // take the shared output tile: the previous owner releases it once its store has read it
+                        if (leader) {
+                            bool got = false;
+                            for (uint32_t it = 0; it < (1u << 22); ++it) {
+                                if (atomicCAS(&bars.out_lock, 0u, 1u) == 0u) {
+                                    got = true;
+                                    break;
+                                }
+                                if ((it & 63u) == 63u && *abort_flag) break;
+                                __nanosleep(32);
+                            }
+                            if (!got) {
+                                *abort_flag = 1u;
+                                atomicExch(status, KS_TIMEOUT_EPILOGUE | 0x80 | s);
+                            }
+                        }
+                        // (one verdict for the whole group: nobody is left alone at a later barrier)
+                        if (ptx::named_bar_red_or(1 + s, 128, *abort_flag != 0)) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                } else if (!to_tmem && (STORE_ALL || TMEM_A || l == 0)) {
                     // the buffer about to be overwritten may still be read by an earlier TMA store: with
                     // per-layer stores the newest one reads the other ping-pong buffer, otherwise only the
                     // previous tile's output store can be pending
@@ -327,6 +358,11 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                                                   tile * T::TM);
                         }
                         ptx::tma_commit_group();
+                        if constexpr (S::SHARED_OUT) {
+                            ptx::tma_wait_group_read<0>(); // the store has read the tile: hand it to the next slot
+                            __threadfence_block();
+                            atomicExch(&bars.out_lock, 0u);
+                        }
                     }
                 }
             }

@@ -103,6 +103,19 @@ __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Named barrier that also ORs a predicate over its participants: every thread gets the same verdict.
+__device__ __forceinline__ bool named_bar_red_or(uint32_t id, uint32_t nthreads, bool pred) {
+    uint32_t r;
+    asm volatile("{\n\t.reg .pred P, Q;\n\t"
+                 "setp.ne.u32 P, %3, 0;\n\t"
+                 "barrier.red.or.pred Q, %1, %2, P;\n\t"
+                 "selp.b32 %0, 1, 0, Q;\n\t}"
+                 : "=r"(r)
+                 : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
+                 : "memory");
+    return r != 0;
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
