@@ -263,7 +263,10 @@ int tnn_network_get_params(const tnn_network *n, void *out, void *stream) {
     return 0;
 }
 
-static int run_forward(tnn_network *n, const void *x, void *y, void *interm, size_t batch, void *stream) {
+// copy_input: matrix 0 of the workspace becomes a copy of x, as callers of the C ABI expect; the training path of
+// this library reads x itself in its backward pass and skips the copy.
+static int run_forward(tnn_network *n, const void *x, void *y, void *interm, size_t batch, void *stream,
+                       bool copy_input = true) {
     TNN_GUARD_BEGIN
     if (!n) return fail("network is null");
     if (batch == 0) return 0;
@@ -294,7 +297,7 @@ static int run_forward(tnn_network *n, const void *x, void *y, void *interm, siz
     p.n_sm = n->n_sm;
     p.status = n->status;
     p.stream = (cudaStream_t)stream;
-    if (interm) // matrix 0 of the forward workspace is a copy of the input (kernel_esimd.h:601-605)
+    if (interm && copy_input) // matrix 0 of the forward workspace is a copy of the input (kernel_esimd.h:601-605)
         TNN_CUDA(cudaMemcpyAsync(interm, x, batch * n->width * sizeof(__nv_bfloat16), cudaMemcpyDeviceToDevice, p.stream));
     cudaError_t e = tnn::launch_mlp_fwd(p);
     if (e == cudaErrorInvalidConfiguration)
@@ -313,8 +316,9 @@ int tnn_network_forward(tnn_network *n, const void *x, void *y, void *interm_fwd
     return run_forward(n, x, y, interm_fwd, batch, stream);
 }
 
-int tnn_network_backward(tnn_network *n, const void *dy, const void *interm_fwd, void *grads, int grads_dtype,
-                         int pack_transpose, void *dx, void *interm_bwd, size_t batch, void *stream) {
+// x_override: where the network input lives when it is not matrix 0 of interm_fwd
+static int run_backward(tnn_network *n, const void *dy, const void *interm_fwd, const void *x_override, void *grads,
+                        int grads_dtype, int pack_transpose, void *dx, void *interm_bwd, size_t batch, void *stream) {
     TNN_GUARD_BEGIN
     if (!n) return fail("network is null");
     if (!grads) return fail("grads is null");
@@ -330,6 +334,7 @@ int tnn_network_backward(tnn_network *n, const void *dy, const void *interm_fwd,
     tnn::BwdLaunch p{};
     make_act_tmap(&p.tm_dy, dy, batch, n->width, 1);
     make_act_tmap(&p.tm_interm, interm_fwd, batch, n->width, n->n_mat + 1);
+    make_act_tmap(&p.tm_a0, x_override ? x_override : interm_fwd, batch, n->width, 1);
     if (interm_bwd)
         make_act_tmap(&p.tm_ibwd, interm_bwd, batch, n->width, n->n_mat);
     else
@@ -361,6 +366,11 @@ int tnn_network_backward(tnn_network *n, const void *dy, const void *interm_fwd,
                                    grads_dtype == TNN_DTYPE_BF16 ? (__nv_bfloat16 *)grads : nullptr, s));
     return 0;
     TNN_GUARD_END
+}
+
+int tnn_network_backward(tnn_network *n, const void *dy, const void *interm_fwd, void *grads, int grads_dtype,
+                         int pack_transpose, void *dx, void *interm_bwd, size_t batch, void *stream) {
+    return run_backward(n, dy, interm_fwd, nullptr, grads, grads_dtype, pack_transpose, dx, interm_bwd, batch, stream);
 }
 
 int tnn_network_train_step(tnn_network *n, const void *x, const float *targets, int n_targets, size_t batch,
@@ -423,12 +433,12 @@ int tnn_network_train_step(tnn_network *n, const void *x, const float *targets, 
         TNN_CUDA(cudaMalloc(&n->ws_dy, batch * n->width * sizeof(__nv_bfloat16)));
         n->ws_batch = batch;
     }
-    if (int rc = tnn_network_forward(n, x, nullptr, n->ws_interm, batch, stream)) return rc;
+    if (int rc = run_forward(n, x, nullptr, n->ws_interm, batch, stream, /*copy_input=*/false)) return rc;
     const __nv_bfloat16 *pred = n->ws_interm + (size_t)n->n_mat * batch * n->width;
     if (int rc = tnn_l2_loss(pred, targets, n_targets, nullptr, n->ws_dy, batch, n->width, loss_scale, loss_sum, stream))
         return rc;
-    return tnn_network_backward(n, n->ws_dy, n->ws_interm, grads, grads_dtype, pack_transpose, nullptr, nullptr, batch,
-                                stream);
+    return run_backward(n, n->ws_dy, n->ws_interm, x, grads, grads_dtype, pack_transpose, nullptr, nullptr, batch,
+                        stream);
     TNN_GUARD_END
 }
 

@@ -59,7 +59,8 @@ struct BwdBarriers {
 template <int W, bool B_MN_MAJOR, bool BIG>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_interm,
-               const __grid_constant__ CUtensorMap tm_ibwd, const __grid_constant__ CUtensorMap tm_dx,
+               const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_ibwd,
+               const __grid_constant__ CUtensorMap tm_dx,
                const __nv_bfloat16 *__restrict__ wimg, float *__restrict__ dw_slabs, int n_tiles, int n_mat, int act,
                int out_act, int store_bwd, int want_dx, int tmem_cols, int dw_lo, int dw_hi, int l_stop, int *status) {
     using T = Tile<W>;
@@ -99,6 +100,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
         ptx::fence_barrier_init();
         ptx::prefetch_tmap(&tm_dy);
         ptx::prefetch_tmap(&tm_interm);
+        ptx::prefetch_tmap(&tm_a0);
     }
     if (warp == 1) {
         ptx::tmem_alloc(&bars.tmem_base, (uint32_t)tmem_cols);
@@ -145,9 +147,13 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                         break;
                     }
                     ptx::mbar_arrive_expect_tx(&bars.a_full[slot], T::ACT_BYTES);
-                    for (int at = 0; at < T::KATOMS; ++at)
-                        ptx::tma_load_3d(smem + S::AR + slot * T::ACT_BYTES + at * T::ACT_ATOM_BYTES, &tm_interm,
-                                         at * T::ATOM_COLS, tile * T::TM, mat, &bars.a_full[slot]);
+                    for (int at = 0; at < T::KATOMS; ++at) {
+                        uint8_t *dst = smem + S::AR + slot * T::ACT_BYTES + at * T::ACT_ATOM_BYTES;
+                        if (mat == 0) // the network input may live outside the activation workspace
+                            ptx::tma_load_2d(dst, &tm_a0, at * T::ATOM_COLS, tile * T::TM, &bars.a_full[slot]);
+                        else
+                            ptx::tma_load_3d(dst, &tm_interm, at * T::ATOM_COLS, tile * T::TM, mat, &bars.a_full[slot]);
+                    }
                 }
             }
         }
@@ -498,7 +504,8 @@ template <int W, bool B_MN, bool BIG> static cudaError_t launch_bwd_variant(BwdL
         while (tmem_cols < cols_needed) tmem_cols *= 2;
         const int first = lo == 0; // deltas and dL/dx are the same in every pass: store them once
         // K-major weights for the chain are rows = input feature; the MN-major variant reads the transposed image
-        kern<<<grid, kBwdThreads, smem, p.stream>>>(p.tm_dy, p.tm_interm, p.tm_ibwd, p.tm_dx, B_MN ? p.wimg_t : p.wimg,
+        kern<<<grid, kBwdThreads, smem, p.stream>>>(p.tm_dy, p.tm_interm, p.tm_a0, p.tm_ibwd, p.tm_dx,
+                                                    B_MN ? p.wimg_t : p.wimg,
                                             p.dw_partials, n_tiles, p.n_mat, p.act, p.out_act, first ? p.store_bwd : 0,
                                             first ? p.want_dx : 0, tmem_cols, lo, hi, first ? 0 : lo, p.status);
         e = cudaGetLastError();

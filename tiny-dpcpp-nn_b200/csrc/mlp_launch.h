@@ -30,6 +30,7 @@ cudaError_t launch_mlp_fwd(const FwdLaunch &p);
 struct BwdLaunch {
     CUtensorMap tm_dy;      // [batch][W] bf16 dL/dy (after loss)
     CUtensorMap tm_interm;  // [L+2][batch][W] bf16 forward activations (matrix 0 = input)
+    CUtensorMap tm_a0;      // [batch][W] bf16 network input: matrix 0 of the workspace, or the caller's x itself
     CUtensorMap tm_ibwd;    // [L+1][batch][W] bf16 deltas (written when store_bwd)
     CUtensorMap tm_dx;      // [batch][W] bf16 dL/dx (written when want_dx)
     const __nv_bfloat16 *wimg;
