@@ -37,6 +37,7 @@ def _oracle_step(x, t, w, W, nh, act, oact):
     (32, 4, "relu", "none", 4096, 32),
     (32, 2, "sigmoid", "none", 4096, 5),
     (16, 2, "relu", "none", 4096, 16),
+    (64, 6, "relu", "none", 4096, 64),
     (64, 8, "relu", "none", 4096, 64),
     (32, 8, "relu", "none", 128 * 150 + 8, 32),
     (32, 10, "sigmoid", "none", 4096, 7),
