@@ -89,6 +89,7 @@ __global__ void __launch_bounds__(256) grid_fwd_kernel(const GridParams p, const
             // issue all 2^D gathers first, then combine in corner order 0..2^D-1 (grid.h:114-129)
             float vals[1 << D][F];
             float wt[1 << D];
+            uint32_t ent[1 << D];
 #pragma unroll
             for (int c = 0; c < (1 << D); ++c) {
                 float weight = 1.0f;
@@ -104,7 +105,12 @@ __global__ void __launch_bounds__(256) grid_fwd_kernel(const GridParams p, const
                     }
                 }
                 wt[c] = weight;
-                const uint32_t e = grid_index<D>(p.grid_type, p.hash_type, hsize, res, gl);
+                ent[c] = grid_index_raw<D>(p.grid_type, p.hash_type, hsize, res, gl);
+            }
+            grid_wrap<(1 << D)>(ent, hsize);
+#pragma unroll
+            for (int c = 0; c < (1 << D); ++c) {
+                const uint32_t e = ent[c];
                 if constexpr (F == 2) {
                     const float2 v = __ldg(reinterpret_cast<const float2 *>(tl) + e);
                     vals[c][0] = v.x;

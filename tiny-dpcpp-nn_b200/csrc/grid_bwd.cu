@@ -76,8 +76,9 @@ __global__ void __launch_bounds__(256) grid_bwd_atomic_kernel(const GridParams p
             }
         }
         wt[c] = weight;
-        ent[c] = grid_index<D>(p.grid_type, p.hash_type, hsize, res, gc);
+        ent[c] = grid_index_raw<D>(p.grid_type, p.hash_type, hsize, res, gc);
     }
+    grid_wrap<(1 << D)>(ent, hsize);
 #pragma unroll
     for (int c = 0; c < (1 << D); ++c) {
         const uint32_t e = ent[c];
