@@ -159,8 +159,9 @@ int tnn_encoding_bind_params(tnn_encoding *enc, float *params);
 int tnn_encoding_forward(tnn_encoding *enc, const float *x, void *out, int out_dtype, size_t batch,
                          void *stream);
 /* EncodingModule::backward_pass(grad_output, input_from_fwd, false, false) - include/tnn_api.h:368-416
- * (kernel_grid_backward, grid.h:137-245).  grads: n_params fp32, overwritten.  Deterministic
- * (no floating-point atomics) unless deterministic == 0. */
+ * (kernel_grid_backward, grid.h:137-245).  grads: n_params fp32, overwritten.  deterministic == 0: fp32
+ * reductions in memory like the reference (summation order not fixed); otherwise 64-bit fixed-point integer
+ * reductions, whose result does not depend on the order and repeats bit for bit. */
 int tnn_encoding_backward(tnn_encoding *enc, const float *x, const void *dy, int dy_dtype, float *grads,
                           size_t batch, int deterministic, void *stream);
 

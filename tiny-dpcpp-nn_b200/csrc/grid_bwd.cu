@@ -2,7 +2,8 @@
 //
 // Two implementations of the same sum  grad[l][index(g + c)][f] += w_c * dL/dy[i, l F + f]:
 //   * an atomic scatter with the reference's structure (fp32 atomics, summation order not fixed), and
-//   * a deterministic, atomic-free pipeline (see grid_bwd_det.cu) that the C ABI uses by default.
+//   * the same scatter with 64-bit fixed-point integer reductions (grid_bwd_fixed.cu): order-independent, so two runs
+//     give identical bits; chosen with `deterministic` in the C ABI.
 #include "grid.h"
 #include "grid_device.cuh"
 

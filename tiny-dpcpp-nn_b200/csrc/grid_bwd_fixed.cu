@@ -1,0 +1,172 @@
+// Deterministic hash-grid backward (parameter gradients): the reference's scatter with exact accumulation.
+//
+// The reference adds w_c * dL/dy into the gradient table with fp32 atomics (include/encodings/grid.h:137-245), so
+// the rounding of every sum depends on the order in which the additions happen to arrive.  Integer addition has no
+// such dependence: here every contribution is converted to 64-bit fixed point with one power-of-two scale for the
+// whole call and added with 64-bit integer reductions in memory; the finished sums are converted back to fp32.
+// Two runs on the same inputs therefore give identical bits, whatever the scheduling.
+//
+// The scale is chosen from the largest |dL/dy| of the call so that even a table entry hit by every contribution of
+// the batch cannot overflow: with a = max |dy| < 2^e and n = batch * 2^D <= 2^b contributions per level, the scale
+// 2^(61 - e - b) keeps every sum below 2^61.  An entry that receives k contributions of typical size loses at
+// most k / 2 units of 2^-(61 - e - b), i.e. a relative error far below fp32 rounding.
+#include "grid.h"
+#include "grid_device.cuh"
+
+#include <cuda_bf16.h>
+
+namespace tnn {
+
+namespace {
+
+struct FixedHeader {
+    uint32_t absmax_bits; // max |dy| over the real feature columns, as float bits (non-negative floats order like integers)
+    uint32_t pad[63];
+};
+
+template <typename DyT>
+__global__ void __launch_bounds__(256) grid_absmax_kernel(const DyT *__restrict__ dy, size_t batch, uint32_t n_features,
+                                                          uint32_t padded, FixedHeader *hdr) {
+    float m = 0.0f;
+    const size_t n = batch * (size_t)n_features;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / n_features;
+        const uint32_t c = (uint32_t)(i % n_features);
+        const float v = fabsf((float)dy[r * padded + c]);
+        if (v <= 3.0e38f) m = fmaxf(m, v); // non-finite values do not take part in choosing the scale
+    }
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0 && m > 0.0f) atomicMax(&hdr->absmax_bits, __float_as_uint(m));
+}
+
+// exponent E of the scale 2^E (see the file comment); clamped to what fp32 can represent
+__device__ __forceinline__ int fixed_exponent(uint32_t absmax_bits, size_t contributions) {
+    const float a = __uint_as_float(absmax_bits);
+    if (!(a > 0.0f)) return 0;
+    int e;
+    frexpf(a, &e); // a = f * 2^e with 0.5 <= f < 1
+    const int b = contributions > 1 ? 64 - __clzll((unsigned long long)(contributions - 1)) : 0;
+    int E = 61 - e - b;
+    return E > 126 ? 126 : (E < -126 ? -126 : E);
+}
+
+template <int D, int F, typename DyT>
+__global__ void __launch_bounds__(256) grid_bwd_fixed_kernel(const GridParams p, const float *__restrict__ x,
+                                                              const DyT *__restrict__ dy, const FixedHeader *hdr,
+                                                              unsigned long long *__restrict__ acc, size_t batch) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t NL = p.n_levels;
+    const size_t i = idx / NL;
+    const uint32_t level = (uint32_t)(idx % NL);
+    if (i >= batch) return;
+    const float max_level = (p.max_level * (float)p.n_features) / (float)F;
+    if ((float)level >= max_level + 1e-3f) return;
+    const float scale = ldexpf(1.0f, fixed_exponent(hdr->absmax_bits, batch << D));
+
+    unsigned long long *al = acc + (size_t)p.offsets[level] * F;
+    const uint32_t hsize = p.offsets[level + 1] - p.offsets[level];
+    const uint32_t res = p.resolution[level];
+    float w[D], xin[D];
+    uint32_t g[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) xin[d] = __ldg(x + i * D + d);
+    grid_pos<D>(xin, p.scale[level], p.interpolation, w, g);
+    float gr[F];
+#pragma unroll
+    for (int f = 0; f < F; ++f) gr[f] = (float)dy[i * p.padded_width + level * F + f];
+
+    auto add = [&](uint32_t e, float weight) {
+#pragma unroll
+        for (int f = 0; f < F; ++f) {
+            // the product is rounded to fp32 like the reference's, the scaling by a power of two is exact
+            const long long q = __float2ll_rn(__fmul_rn(__fmul_rn(weight, gr[f]), scale));
+            if (q != 0) atomicAdd(al + (size_t)e * F + f, (unsigned long long)q);
+        }
+    };
+    if (p.interpolation == INTERP_NEAREST) {
+        add(grid_index<D>(p.grid_type, p.hash_type, hsize, res, g), 1.0f);
+        return;
+    }
+    uint32_t ent[1 << D];
+    float wt[1 << D];
+#pragma unroll
+    for (int c = 0; c < (1 << D); ++c) {
+        float weight = 1.0f;
+        uint32_t gc[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            if ((c & (1 << d)) == 0) {
+                weight = __fmul_rn(weight, __fsub_rn(1.0f, w[d]));
+                gc[d] = g[d];
+            } else {
+                weight = __fmul_rn(weight, w[d]);
+                gc[d] = g[d] + 1u;
+            }
+        }
+        wt[c] = weight;
+        ent[c] = grid_index_raw<D>(p.grid_type, p.hash_type, hsize, res, gc);
+    }
+    grid_wrap<(1 << D)>(ent, hsize);
+#pragma unroll
+    for (int c = 0; c < (1 << D); ++c) add(ent[c], wt[c]);
+}
+
+__global__ void __launch_bounds__(256) grid_fixed_finalize_kernel(const unsigned long long *__restrict__ acc,
+                                                                   const FixedHeader *hdr, float *__restrict__ grads,
+                                                                   size_t n, size_t contributions) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const double inv_scale = ldexp(1.0, -fixed_exponent(hdr->absmax_bits, contributions));
+    grads[i] = (float)((double)(long long)acc[i] * inv_scale);
+}
+
+template <int D, int F>
+cudaError_t run_fixed(const GridParams &p, const float *x, const void *dy, int dy_bf16, float *grads, size_t batch,
+                      void *scratch, size_t scratch_bytes, cudaStream_t stream) {
+    const size_t n_params = (size_t)p.offsets[p.n_levels] * F;
+    if (scratch_bytes < sizeof(FixedHeader) + n_params * sizeof(unsigned long long)) return cudaErrorInvalidValue;
+    FixedHeader *hdr = reinterpret_cast<FixedHeader *>(scratch);
+    unsigned long long *acc = reinterpret_cast<unsigned long long *>(hdr + 1);
+    cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(FixedHeader) + n_params * sizeof(unsigned long long), stream);
+    if (e != cudaSuccess) return e;
+    const size_t n_dy = batch * (size_t)p.n_features;
+    const unsigned red_blocks = (unsigned)((n_dy + 256 * 8 - 1) / (256 * 8) < 148 * 8 ? (n_dy + 256 * 8 - 1) / (256 * 8) : 148 * 8);
+    const size_t n = batch * p.n_levels;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dy_bf16) {
+        grid_absmax_kernel<__nv_bfloat16><<<red_blocks ? red_blocks : 1, 256, 0, stream>>>(
+            (const __nv_bfloat16 *)dy, batch, p.n_features, p.padded_width, hdr);
+        grid_bwd_fixed_kernel<D, F, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p, x, (const __nv_bfloat16 *)dy, hdr, acc, batch);
+    } else {
+        grid_absmax_kernel<float><<<red_blocks ? red_blocks : 1, 256, 0, stream>>>((const float *)dy, batch, p.n_features,
+                                                                                   p.padded_width, hdr);
+        grid_bwd_fixed_kernel<D, F, float><<<blocks, 256, 0, stream>>>(p, x, (const float *)dy, hdr, acc, batch);
+    }
+    grid_fixed_finalize_kernel<<<(unsigned)((n_params + 255) / 256), 256, 0, stream>>>(acc, hdr, grads, n_params,
+                                                                                      batch << D);
+    return cudaGetLastError();
+}
+
+} // namespace
+
+size_t grid_bwd_scratch_bytes(const GridParams &p, size_t) {
+    return sizeof(FixedHeader) + (size_t)p.offsets[p.n_levels] * p.features_per_level * sizeof(unsigned long long);
+}
+
+cudaError_t launch_grid_bwd_det(const GridParams &p, const float *x, const void *dy, int dy_bf16, float *grads,
+                                size_t batch, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
+    const int key = (int)p.n_dims * 16 + (int)p.features_per_level;
+    switch (key) {
+    case 2 * 16 + 1: return run_fixed<2, 1>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
+    case 2 * 16 + 2: return run_fixed<2, 2>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
+    case 2 * 16 + 4: return run_fixed<2, 4>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
+    case 2 * 16 + 8: return run_fixed<2, 8>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
+    case 3 * 16 + 1: return run_fixed<3, 1>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
+    case 3 * 16 + 2: return run_fixed<3, 2>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
+    case 3 * 16 + 4: return run_fixed<3, 4>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
+    case 3 * 16 + 8: return run_fixed<3, 8>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+} // namespace tnn

@@ -311,8 +311,8 @@ class EncodingModule:
         raise TnnError("backward_pass needs input_from_fwd")
 
     #: default summation of the table gradient: False = floating-point reductions in memory like the reference's
-    #: kernel_grid_backward (grid.h:177-183, order not fixed, fastest); True = the atomic-free pipeline whose
-    #: result repeats bit for bit (about 7x slower at the benchmark grid)
+    #: kernel_grid_backward (grid.h:177-183, order not fixed, fastest); True = 64-bit fixed-point accumulation whose
+    #: result repeats bit for bit (about 3x slower at the benchmark grid)
     deterministic_backward = False
 
     def bwd_with_encoding_grad(self, grad_output, input_from_fwd, pack_gradient, get_dl_dinput, deterministic=None):
