@@ -8,7 +8,7 @@
  *   - All data pointers are DEVICE pointers owned by the caller unless stated otherwise.  Matrices
  *     are row-major, batch x width.  Network activations are bf16, encodings take fp32 inputs.
  *   - `stream` is a cudaStream_t passed as void*; calls only enqueue work on it and never
- *     synchronise, except where a function says so.
+ *     synchronise or allocate, except where a function says so (workspace growth, parameter initialisation).
  *   - Handles are not thread-safe; use one handle per host thread or lock around it.
  *   - There is no CPU fallback: without a CUDA device of compute capability 10.x the create
  *     functions fail.
@@ -27,6 +27,8 @@ extern "C" {
 
 typedef struct tnn_network tnn_network;
 typedef struct tnn_encoding tnn_encoding;
+typedef struct tnn_trainer tnn_trainer;
+typedef struct tnn_dp_comm tnn_dp_comm;
 
 /* Activation codes: same enumerator order as `enum class Activation`, include/common/common.h:28-38.
  * Only ReLU, Sigmoid and None are accepted, as in include/network/SwiftNetMLP.h:281-288. */
@@ -38,6 +40,9 @@ enum { TNN_DTYPE_BF16 = 0, TNN_DTYPE_FP16 = 1, TNN_DTYPE_FP32 = 2 };
 const char *tnn_last_error(void);
 /* Library version string. */
 const char *tnn_version(void);
+/* Number of kernels of this library that the process has launched so far, on all streams and devices (library
+ * routines such as memset, memcpy and NCCL collectives are not counted).  No reference counterpart. */
+unsigned long long tnn_launch_count(void);
 
 /* ------------------------------------------------------------------------------------------
  * Network: replaces tnn::NetworkModule<T, WIDTH> (include/tnn_api.h:491-697) and the
@@ -62,7 +67,8 @@ int tnn_network_n_hidden_layers(const tnn_network *net);
 
 /* Network::initialize_xavier_normal - include/network/Network.h:271-295: uniform(+-sqrt(6 / fan)),
  * fan of first and last matrix = pad16(input_width) + width.  The reference seeds from
- * std::random_device; here the seed is explicit (std::mt19937). */
+ * std::random_device; here the seed is explicit (std::mt19937).  Draws on the host, copies, and waits for
+ * `stream`. */
 int tnn_network_initialize_params(tnn_network *net, uint64_t seed, void *stream);
 /* Module::set_params(tensor, weights_are_packed) - include/tnn_api.h:637-641 and
  * Network::set_weights_matrices, include/network/Network.h:90-112.  `params` holds n_params values
@@ -99,21 +105,29 @@ int tnn_network_backward(tnn_network *net, const void *dy, const void *interm_fw
  * targets: batch x n_targets fp32 (output columns >= n_targets compare against 0); the loss is
  * normalised by batch * width.  grads as in tnn_network_backward; loss_sum (optional): one fp32.
  * Where width and depth allow (all activations of a 128-row tile resident on the SM) this is a single
- * kernel; otherwise the forward, loss and backward kernels run one after another on a workspace
- * owned by the handle. */
+ * kernel that needs no workspace; otherwise the forward, loss and backward kernels run one after another on a
+ * workspace of tnn_network_workspace_bytes(batch) bytes.  Unless the caller has lent one with
+ * tnn_network_set_workspace, the handle allocates it at the first such call and re-allocates it when a larger
+ * batch arrives; that (re-)allocation synchronises `stream` - the one place where this call is not purely
+ * asynchronous.  targets: 4-byte aligned; 16-byte aligned targets are staged by bulk copies (faster). */
 int tnn_network_train_step(tnn_network *net, const void *x, const float *targets, int n_targets,
                            size_t batch, float loss_scale, void *grads, int grads_dtype,
                            int pack_transpose, float *loss_sum, void *stream);
+/* Bytes of workspace tnn_network_train_step needs for `batch` rows when the network does not fit a fused
+ * kernel (n_hidden_layers + 3 matrices batch x width bf16).  No reference counterpart: the reference's modules
+ * grow their workspaces silently (include/tnn_api.h:649-684). */
+size_t tnn_network_workspace_bytes(const tnn_network *net, size_t batch);
+/* Lends the handle a caller-owned workspace (256-byte aligned device memory) so that no call allocates or
+ * synchronises; a call that needs more than `bytes` fails with a message instead of allocating.  NULL returns to
+ * the library-owned, growing workspace.  The memory must stay valid while it is lent. */
+int tnn_network_set_workspace(tnn_network *net, void *workspace, size_t bytes);
 /* Waits for `stream` and returns the kernels' status word in *status (0 = fine; non-zero = a
  * bounded device-side wait gave up, results are invalid).  No reference counterpart: the
  * reference kernels have no device-side waits. */
 int tnn_network_sync_status(tnn_network *net, int *status, void *stream);
-/* Selects a kernel variant for tuning experiments.  Default 0 (the fastest measured choice everywhere).
- *   1    inference keeps hidden activations in shared memory instead of tensor memory
- *   2    MN-major weight operand in the forward / backward kernels
- *   4    fewer tiles in flight in the forward kernel        8    three tiles in flight (inference)
+/* Forces a kernel path that the library would not pick by itself, so that tests can cover every path on
+ * small networks.  Default 0 (the fastest measured choice everywhere).
  *   16   training through the forward / loss / backward kernels instead of a fused kernel
- *   32   the pipelined training kernel prints event time stamps of one tile (tuning build)
  *   64   single-tile instead of pipelined fused training kernel
  *   256  stream the weights through per-slot rings even if they would fit on chip
  * No reference counterpart. */
@@ -161,9 +175,38 @@ int tnn_encoding_forward(tnn_encoding *enc, const float *x, void *out, int out_d
 /* EncodingModule::backward_pass(grad_output, input_from_fwd, false, false) - include/tnn_api.h:368-416
  * (kernel_grid_backward, grid.h:137-245).  grads: n_params fp32, overwritten.  deterministic == 0: fp32
  * reductions in memory like the reference (summation order not fixed); otherwise 64-bit fixed-point integer
- * reductions, whose result does not depend on the order and repeats bit for bit. */
+ * reductions, whose result does not depend on the order and repeats bit for bit (an inf or NaN in dy then makes
+ * every gradient of the call NaN).  grads must be 16-byte aligned.  The deterministic path keeps 8 bytes of
+ * scratch per parameter in the handle, allocated (with a synchronisation of `stream`) at its first use. */
 int tnn_encoding_backward(tnn_encoding *enc, const float *x, const void *dy, int dy_dtype, float *grads,
                           size_t batch, int deterministic, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Network with input encoding: replaces NetworkWithInputEncoding
+ * (dpcpp_bindings/tiny_dpcpp_nn/modules.py:357-421, a torch.nn.Sequential of the two modules) without the
+ * batch x width matrix between them where a kernel can produce the network's input tile itself.  The
+ * encoding's padded output width must equal the network width.  x: batch x n_input_dims fp32.
+ *   Identity (up to 16 inputs): folded into the first-layer load of the network kernels - the encoded matrix
+ *     never exists (include/encodings/identity.h:63-77 + include/network/kernel_esimd.h:565-640 in one kernel).
+ *   Other encodings: encoding kernel, then network kernels, through the network handle's workspace
+ *     (tnn_network_with_encoding_workspace_bytes; same allocation rule as tnn_network_train_step).
+ * ------------------------------------------------------------------------------------------ */
+size_t tnn_network_with_encoding_workspace_bytes(const tnn_network *net, size_t batch);
+/* Sequential(encoding, network) in eval mode: y = network(encoding(x)), batch x width bf16. */
+int tnn_network_with_encoding_inference(tnn_network *net, tnn_encoding *enc, const float *x, void *y,
+                                        size_t batch, void *stream);
+/* Sequential(encoding, network) forward in training mode: like tnn_network_forward; matrix 0 of interm_fwd
+ * receives the encoded input. */
+int tnn_network_with_encoding_forward(tnn_network *net, tnn_encoding *enc, const float *x, void *y,
+                                      void *interm_fwd, size_t batch, void *stream);
+/* One training pass of the pair: forward, L2 loss, backward, network weight gradients (as
+ * tnn_network_train_step) and - for an encoding with parameters, when encoding_grads is given - the
+ * encoding's parameter gradient (n_params fp32, as tnn_encoding_backward with `deterministic`). */
+int tnn_network_with_encoding_train_step(tnn_network *net, tnn_encoding *enc, const float *x,
+                                         const float *targets, int n_targets, size_t batch, float loss_scale,
+                                         void *grads, int grads_dtype, int pack_transpose,
+                                         float *encoding_grads, int deterministic, float *loss_sum,
+                                         void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Loss and optimiser
@@ -172,7 +215,10 @@ int tnn_encoding_backward(tnn_encoding *enc, const float *x, const void *dy, int
 /* L2Loss::evaluate - include/losses/l2.h:19-41, include/losses/loss.h:19-25.
  * pred: batch x stride bf16; target: batch x n_targets fp32 (columns >= n_targets compare with 0);
  * values (optional): batch x stride fp32; grads (optional): batch x stride bf16;
- * loss_sum (optional): one fp32 = sum of values. */
+ * loss_sum (optional): one fp32 = sum of values.  pred, values and grads must be 16-byte aligned, target 4-byte
+ * (16-byte when n_targets == stride).  The per-block partial sums behind loss_sum live in one buffer per device
+ * that the library allocates at the first call on that device and keeps: calls that overlap on one device (two
+ * streams) race on it. */
 int tnn_l2_loss(const void *pred, const float *target, int n_targets, float *values, void *grads,
                 size_t batch, int stride, float loss_scale, float *loss_sum, void *stream);
 /* No counterpart in the reference.  Same computation and arguments as tnn_l2_loss for callers that must
@@ -201,6 +247,64 @@ int tnn_adam_step(float *params, float *m, float *v, const float *grads, size_t 
 int tnn_network_adam_step(tnn_network *net, float *master, float *m, float *v, const float *grads,
                           float grad_scale, int step, float lr, float beta1, float beta2, float eps,
                           void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Data parallelism.  No reference counterpart: the reference's multi-GPU benchmarks are independent MPI replicas
+ * without any exchange (benchmarks/common_benchmarks.h:53-54).  One process per GPU; the only exchange of a
+ * training step is one ncclAllReduce(sum) of the (n_hidden_layers + 1) * width^2 fp32 weight-gradient buffer
+ * (plus reduce-scatter / all-gather of a trainable encoding's table).  NCCL is loaded with dlopen("libnccl.so.2")
+ * at the first of these calls - the copy the process already uses, if it has one.
+ * ------------------------------------------------------------------------------------------ */
+/* ncclGetUniqueId into 128 caller bytes (rank 0 calls this and sends the bytes to the other ranks). */
+int tnn_dp_get_unique_id(void *id128);
+/* ncclCommInitRank on the current device: collective over all `world` ranks. */
+int tnn_dp_comm_create(const void *id128, int rank, int world, tnn_dp_comm **out);
+/* Wraps a communicator the application already has (an ncclComm_t passed as void*); not destroyed by
+ * tnn_dp_comm_destroy. */
+int tnn_dp_init(void *nccl_comm, tnn_dp_comm **out);
+int tnn_dp_comm_destroy(tnn_dp_comm *comm);
+int tnn_dp_rank(const tnn_dp_comm *comm);
+int tnn_dp_world_size(const tnn_dp_comm *comm);
+/* In-place sum of n fp32 values over the ranks, enqueued on `stream` (comm == NULL: single process, no-op). */
+int tnn_dp_allreduce_sum(tnn_dp_comm *comm, float *buf, size_t n, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Trainer: replaces Trainer<T> (include/trainer.h:16-52) together with the loss and optimiser the reference's
+ * training loops wrap around it (L2Loss, include/losses/l2.h:19-41; torch.optim.Adam on the fp32 master copy of
+ * the packed parameters, dpcpp_bindings/tiny_dpcpp_nn/modules.py:169-175).  Owns master parameters, Adam moments,
+ * the fp32 gradient and the loss sum on the device.  With `enc` the input is batch x n_input_dims fp32 and the
+ * pair trains like NetworkWithInputEncoding; a trainable encoding (HashGrid) gets its own Adam state (sharded
+ * over the ranks when a communicator is set: reduce-scatter, Adam on this rank's slice, all-gather).
+ * ------------------------------------------------------------------------------------------ */
+int tnn_trainer_create(tnn_network *net, tnn_encoding *enc_or_null, float lr, float beta1, float beta2, float eps,
+                       float loss_scale, tnn_trainer **out);
+int tnn_trainer_destroy(tnn_trainer *trainer);
+/* Gradients are averaged over the ranks of `comm` (NULL: single GPU).  Set before the first step. */
+int tnn_trainer_set_dp(tnn_trainer *trainer, tnn_dp_comm *comm);
+/* Table gradient of a trainable encoding by order-independent fixed-point sums (see tnn_encoding_backward). */
+int tnn_trainer_set_deterministic_encoding(tnn_trainer *trainer, int deterministic);
+/* n_params fp32 in the packed layout -> master copy and the network's working weights. */
+int tnn_trainer_set_master_params(tnn_trainer *trainer, const float *packed_fp32, void *stream);
+/* Device pointers into the trainer's state (valid until tnn_trainer_destroy): master parameters and gradient
+ * (n_params fp32, packed layout), table gradient of a trainable encoding, loss sum of the last pass (one fp32). */
+float *tnn_trainer_master_params(tnn_trainer *trainer);
+float *tnn_trainer_grads(tnn_trainer *trainer);
+float *tnn_trainer_encoding_grads(tnn_trainer *trainer);
+float *tnn_trainer_loss(tnn_trainer *trainer);
+int tnn_trainer_step_count(const tnn_trainer *trainer);
+/* Trainer::training_step - include/trainer.h:23-46: forward_pass + backward_pass (with the L2 loss between them).
+ * x: batch x width bf16 (no encoding) or batch x n_input_dims fp32 (with encoding). */
+int tnn_trainer_forward_backward(tnn_trainer *trainer, const void *x, const float *targets, int n_targets,
+                                 size_t batch, void *stream);
+/* Finishes the sums of the last forward_backward into tnn_trainer_grads / tnn_trainer_loss without an optimiser
+ * step (tnn_trainer_optimizer_step does this itself). */
+int tnn_trainer_reduce(tnn_trainer *trainer, void *stream);
+/* optimizer.step() + Module.set_params(): gradient all-reduce when a communicator is set, Adam on the master
+ * copy, refresh of the bf16 weights the kernels read. */
+int tnn_trainer_optimizer_step(tnn_trainer *trainer, void *stream);
+/* forward_backward + optimizer_step: one call enqueues the whole loop body. */
+int tnn_trainer_training_step(tnn_trainer *trainer, const void *x, const float *targets, int n_targets,
+                              size_t batch, void *stream);
 
 #ifdef __cplusplus
 }

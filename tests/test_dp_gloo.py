@@ -64,8 +64,23 @@ def test_two_rank_gradient_average_equals_full_batch_gradient(tmp_path):
 def test_shard_rows_cover_the_batch():
     from tiny_dpcpp_nn.parallel import shard_rows
 
-    for n, world in ((1 << 22, 8), (1000 * 8, 3), (64, 4)):
+    for n, world in ((1 << 22, 8), (1000 * 24, 3), (64, 4)):
         edges = [shard_rows(n, r, world) for r in range(world)]
         assert edges[0][0] == 0 and edges[-1][1] == n
+        sizes = {b - a for a, b in edges}
+        assert len(sizes) == 1 and sizes.pop() % 8 == 0  # equal shards: equal weights in the gradient average
         for (a0, b0), (a1, b1) in zip(edges, edges[1:]):
-            assert b0 == a1 and (b0 - a0) % 8 == 0
+            assert b0 == a1
+
+
+def test_shard_rows_rejects_unequal_or_empty_shards():
+    """Unequal shards would not give the gradient of the global mean loss, an empty shard would leave one rank
+    raising alone while the others wait in the all-reduce: both are refused on every rank before any collective."""
+    import pytest
+
+    from tiny_dpcpp_nn.parallel import shard_rows
+
+    for n, world in ((8000, 3), (8, 2), (0, 2), (1 << 22, 7)):
+        for r in range(world):
+            with pytest.raises(ValueError):
+                shard_rows(n, r, world)

@@ -1,8 +1,7 @@
 """Builds libtnn_b200.so (sm_100a only) next to this file with plain nvcc.
 
-Usage: python build.py [--force] [-v] [--microbench]
+Usage: python build.py [--force] [-v]
 The library has no torch dependency: it exports the C ABI of include/tnn_b200.h.
---microbench also builds the stand-alone tcgen05 microbenchmark (csrc/umma_microbench.cu) next to the library.
 """
 import os
 import subprocess
@@ -12,7 +11,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libtnn_b200.so")
-SOURCES = ["capi.cu", "mlp_fwd.cu", "mlp_bwd.cu", "mlp_train.cu", "mlp_train_pipe.cu", "elementwise.cu", "l2_static.cu", "grid.cu", "grid_bwd.cu", "grid_bwd_fixed.cu"]
+SOURCES = ["capi.cu", "mlp_fwd.cu", "mlp_bwd.cu", "mlp_train.cu", "mlp_train_pipe.cu", "elementwise.cu", "l2_static.cu", "trainer.cu", "grid.cu", "grid_bwd.cu", "grid_bwd_fixed.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
@@ -55,24 +54,12 @@ def build(force=False, verbose=False):
 
     with ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as ex:
         objs = list(ex.map(compile_one, SOURCES))
-    cmd = [nvcc, "-shared", "-o", OUT, *objs, "-cudart", "shared"]
+    cmd = [nvcc, "-shared", "-o", OUT, *objs, "-cudart", "shared", "-ldl"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     return OUT
 
 
-def build_microbench():
-    out = os.path.join(HERE, "umma_microbench")
-    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", out,
-           os.path.join(CSRC, "umma_microbench.cu")]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"nvcc failed for umma_microbench.cu:\n{r.stdout}\n{r.stderr}")
-    return out
-
-
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
-    if "--microbench" in sys.argv:
-        print(build_microbench())

@@ -6,14 +6,17 @@
 
 #include "elementwise.h"
 #include "grid.h"
+#include "handles.h"
 #include "json_min.h"
 #include "mlp_common.cuh"
 #include "mlp_launch.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstring>
 #include <memory>
+#include <mutex>
 #include <random>
 #include <stdexcept>
 #include <string>
@@ -96,6 +99,17 @@ int device_checks() {
     return 0;
 }
 
+// The L2 kernel moves 16 bytes at a time: eight bf16 predictions / gradients, four fp32 values, and - when the
+// targets are as wide as the predictions - four fp32 targets.
+int check_l2_alignment(const void *pred, const float *target, int n_targets, const float *values, const void *grads,
+                       int stride) {
+    auto mis = [](const void *q, uintptr_t a) { return q && reinterpret_cast<uintptr_t>(q) % a != 0; };
+    if (mis(pred, 16) || mis(values, 16) || mis(grads, 16)) return fail("pred, values and grads must be 16-byte aligned");
+    if (mis(target, n_targets == stride ? 16 : 4))
+        return fail("target must be 16-byte aligned when n_targets == stride (4-byte aligned otherwise)");
+    return 0;
+}
+
 bool act_supported(int a) { return a == tnn::ACT_RELU || a == tnn::ACT_SIGMOID || a == tnn::ACT_NONE; }
 
 } // namespace
@@ -103,40 +117,17 @@ bool act_supported(int a) { return a == tnn::ACT_RELU || a == tnn::ACT_SIGMOID |
 namespace tnn {
 // error recording for translation units that implement further entry points
 int api_fail(const std::string &msg, int code) { return fail(msg, code); }
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 } // namespace tnn
 
 // ======================================================================== network
-struct tnn_network {
-    int input_width = 0, output_width = 0; // as requested (unpadded)
-    int width = 0, n_hidden = 0, n_mat = 0;
-    int act = 0, out_act = 0, use_bias = 1;
-    int variant = 0;
-    int n_sm = 0;
-    size_t n_params = 0;
-    __nv_bfloat16 *packed = nullptr; // packed-layout bf16 weights (what get_params returns)
-    __nv_bfloat16 *wimg = nullptr;   // swizzled operand images, rows = input feature
-    __nv_bfloat16 *wimg_t = nullptr; // swizzled operand images, rows = output feature
-    float *dw_slabs = nullptr;       // per-CTA weight-gradient partial sums
-    float *loss_partials = nullptr;  // per-CTA loss partial sums of the fused training kernel
-    int *status = nullptr;
-    // workspace of the unfused training path (grown on demand, like the reference's module workspaces)
-    __nv_bfloat16 *ws_interm = nullptr;
-    __nv_bfloat16 *ws_dy = nullptr;
-    size_t ws_batch = 0;
-
-    int one_padded_input() const {
-        // rows of the first matrix that can carry signal: the real inputs, plus (with bias) the
-        // ones-padding up to the next multiple of 16 (Network.h:188-200)
-        if (!use_bias) return input_width;
-        if (input_width % 16 == 0) return width;
-        return (input_width / 16 + 1) * 16;
-    }
-};
-
 extern "C" {
 
 const char *tnn_last_error(void) { return g_last_error.c_str(); }
-const char *tnn_version(void) { return "tnn_b200 0.1 (sm_100a)"; }
+const char *tnn_version(void) { return "tnn_b200 0.2 (sm_100a)"; }
+unsigned long long tnn_launch_count(void) { return tnn::g_launches.load(std::memory_order_relaxed); }
 
 int tnn_network_create(int input_width, int output_width, int n_hidden_layers, int activation, int output_activation,
                        int width, int dtype, int use_bias, tnn_network **out) {
@@ -200,8 +191,7 @@ int tnn_network_destroy(tnn_network *n) {
     cudaFree(n->wimg_t);
     cudaFree(n->dw_slabs);
     cudaFree(n->loss_partials);
-    cudaFree(n->ws_interm);
-    cudaFree(n->ws_dy);
+    if (n->ws_owned) cudaFree(n->ws);
     cudaFree(n->status);
     delete n;
     return 0;
@@ -265,25 +255,28 @@ int tnn_network_get_params(const tnn_network *n, void *out, void *stream) {
 
 // copy_input: matrix 0 of the workspace becomes a copy of x, as callers of the C ABI expect; the training path of
 // this library reads x itself in its backward pass and skips the copy.
+// enc: when set, the kernel produces its input tiles from fp32 coordinates (folded identity encoding) and x is unused
 static int run_forward(tnn_network *n, const void *x, void *y, void *interm, size_t batch, void *stream,
-                       bool copy_input = true) {
+                       bool copy_input = true, const tnn::EncodedInput *enc = nullptr) {
     TNN_GUARD_BEGIN
     if (!n) return fail("network is null");
     if (batch == 0) return 0;
-    if (!x) return fail("input is null");
+    if (!x && !enc) return fail("input is null");
     if (batch % 8 != 0) return fail("Batch size is not divisible by 8."); // SwiftNetMLP.h:293-302
     if (batch > (size_t)1 << 30) return fail("batch too large");
     if (!y && !interm) return fail("forward needs y or interm_fwd");
     tnn::FwdLaunch p{};
-    make_act_tmap(&p.tm_x, x, batch, n->width, 1);
-    if (y)
-        make_act_tmap(&p.tm_y, y, batch, n->width, 1);
+    if (y) make_act_tmap(&p.tm_y, y, batch, n->width, 1);
+    if (interm) make_act_tmap(&p.tm_interm, interm, batch, n->width, n->n_mat + 1);
+    if (enc)
+        p.enc = *enc;
     else
-        p.tm_y = p.tm_x;
-    if (interm)
-        make_act_tmap(&p.tm_interm, interm, batch, n->width, n->n_mat + 1);
-    else
-        p.tm_interm = p.tm_x;
+        make_act_tmap(&p.tm_x, x, batch, n->width, 1);
+    // (maps that a launch does not use are never dereferenced; give them a valid value all the same)
+    const CUtensorMap &any = y ? p.tm_y : p.tm_interm;
+    if (enc) p.tm_x = any;
+    if (!y) p.tm_y = any;
+    if (!interm) p.tm_interm = any;
     p.wimg = n->wimg;
     p.wimg_t = n->wimg_t;
     p.batch = batch;
@@ -297,7 +290,7 @@ static int run_forward(tnn_network *n, const void *x, void *y, void *interm, siz
     p.n_sm = n->n_sm;
     p.status = n->status;
     p.stream = (cudaStream_t)stream;
-    if (interm && copy_input) // matrix 0 of the forward workspace is a copy of the input (kernel_esimd.h:601-605)
+    if (interm && copy_input && !enc) // matrix 0 of the forward workspace is a copy of the input (kernel_esimd.h:601-605)
         TNN_CUDA(cudaMemcpyAsync(interm, x, batch * n->width * sizeof(__nv_bfloat16), cudaMemcpyDeviceToDevice, p.stream));
     cudaError_t e = tnn::launch_mlp_fwd(p);
     if (e == cudaErrorInvalidConfiguration)
@@ -317,11 +310,14 @@ int tnn_network_forward(tnn_network *n, const void *x, void *y, void *interm_fwd
 }
 
 // x_override: where the network input lives when it is not matrix 0 of interm_fwd
+// n_slabs_out: when set, the per-CTA weight-gradient slabs are left unreduced in n->dw_slabs and their number is
+// returned (the trainer sums them in its optimiser kernel); grads is then unused
 static int run_backward(tnn_network *n, const void *dy, const void *interm_fwd, const void *x_override, void *grads,
-                        int grads_dtype, int pack_transpose, void *dx, void *interm_bwd, size_t batch, void *stream) {
+                        int grads_dtype, int pack_transpose, void *dx, void *interm_bwd, size_t batch, void *stream,
+                        int *n_slabs_out = nullptr) {
     TNN_GUARD_BEGIN
     if (!n) return fail("network is null");
-    if (!grads) return fail("grads is null");
+    if (!grads && !n_slabs_out) return fail("grads is null");
     if (grads_dtype != TNN_DTYPE_BF16 && grads_dtype != TNN_DTYPE_FP32) return fail("grads must be bf16 or fp32");
     cudaStream_t s = (cudaStream_t)stream;
     if (batch == 0) {
@@ -361,6 +357,10 @@ static int run_backward(tnn_network *n, const void *dy, const void *interm_fwd, 
     if (e == cudaErrorInvalidConfiguration)
         return fail("this width / depth does not fit the on-chip staging of the backward kernel");
     TNN_CUDA(e);
+    if (n_slabs_out) {
+        *n_slabs_out = p.grid_out;
+        return 0;
+    }
     TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, p.grid_out, n->n_mat, n->width, pack_transpose, 1.0f,
                                    grads_dtype == TNN_DTYPE_FP32 ? (float *)grads : nullptr,
                                    grads_dtype == TNN_DTYPE_BF16 ? (__nv_bfloat16 *)grads : nullptr, s));
@@ -373,30 +373,62 @@ int tnn_network_backward(tnn_network *n, const void *dy, const void *interm_fwd,
     return run_backward(n, dy, interm_fwd, nullptr, grads, grads_dtype, pack_transpose, dx, interm_bwd, batch, stream);
 }
 
-int tnn_network_train_step(tnn_network *n, const void *x, const float *targets, int n_targets, size_t batch,
-                           float loss_scale, void *grads, int grads_dtype, int pack_transpose, float *loss_sum,
-                           void *stream) {
+// Bytes of the workspace the three-kernel training path (forward with stored activations, L2 loss, backward)
+// needs for `batch` rows: n_mat + 1 activation matrices and dL/dy.
+static size_t unfused_workspace_bytes(const tnn_network *n, size_t batch) {
+    return (size_t)(n->n_mat + 2) * batch * n->width * sizeof(__nv_bfloat16);
+}
+
+// Makes n->ws hold at least `need` bytes.  A workspace lent by the caller is never replaced; one owned by the
+// library grows (synchronising the stream first, since earlier launches may still use the old block).
+static int ensure_workspace(tnn_network *n, size_t need, cudaStream_t s) {
+    if (need <= n->ws_bytes) return 0;
+    if (n->ws && !n->ws_owned)
+        return fail("the workspace set with tnn_network_set_workspace is too small: " + std::to_string(n->ws_bytes) +
+                    " bytes, " + std::to_string(need) + " needed (see tnn_network_workspace_bytes)");
+    TNN_CUDA(cudaStreamSynchronize(s));
+    cudaFree(n->ws);
+    n->ws = nullptr;
+    n->ws_bytes = 0;
+    TNN_CUDA(cudaMalloc(&n->ws, need));
+    n->ws_bytes = need;
+    n->ws_owned = true;
+    return 0;
+}
+
+// One training pass.  Input: x (batch x width bf16) or, when enc is set, fp32 coordinates the kernels encode
+// themselves.  dx (optional): dL/dinput, batch x width bf16 - only the three-kernel path produces it.
+// raw (optional, two ints): leave the per-CTA slabs and loss partials unreduced in the network's buffers and return
+// their counts in raw[0] (slabs) and raw[1] (loss partials); grads and loss_sum are then unused.
+static int train_step_impl(tnn_network *n, const void *x, const tnn::EncodedInput *enc, const float *targets,
+                           int n_targets, size_t batch, float loss_scale, void *grads, int grads_dtype,
+                           int pack_transpose, void *dx, float *loss_sum, void *stream, int *raw = nullptr) {
     TNN_GUARD_BEGIN
     if (!n) return fail("network is null");
-    if (!grads) return fail("grads is null");
+    if (!grads && !raw) return fail("grads is null");
     if (grads_dtype != TNN_DTYPE_BF16 && grads_dtype != TNN_DTYPE_FP32) return fail("grads must be bf16 or fp32");
     if (batch == 0) return fail("batch_size == 0");
-    if (!x || !targets) return fail("x and targets are required");
+    if ((!x && !enc) || !targets) return fail("x and targets are required");
     if (batch % 8 != 0) return fail("Batch size is not divisible by 8.");
     if (n_targets <= 0 || n_targets > n->width) return fail("n_targets must be in [1, width]");
     if (loss_scale == 0.0f) return fail("loss_scale must not be 0");
+    if (reinterpret_cast<uintptr_t>(targets) % 4 != 0) return fail("targets must be 4-byte aligned");
     cudaStream_t s = (cudaStream_t)stream;
     float *gf = grads_dtype == TNN_DTYPE_FP32 ? (float *)grads : nullptr;
     __nv_bfloat16 *gb = grads_dtype == TNN_DTYPE_BF16 ? (__nv_bfloat16 *)grads : nullptr;
 
-    if (!(n->variant & 16)) { // fused single-kernel path
+    if (!(n->variant & 16) && !dx) { // fused single-kernel path
         tnn::TrainLaunch p{};
-        make_act_tmap(&p.tm_x, x, batch, n->width, 1);
+        if (enc)
+            p.enc = *enc;
+        else
+            make_act_tmap(&p.tm_x, x, batch, n->width, 1);
         p.wimg = n->wimg;
         p.targets = targets;
         p.n_targets = n_targets;
-        p.tgt_tma = (n_targets == n->width && n->width >= 32 && reinterpret_cast<uintptr_t>(targets) % 16 == 0) ? 1 : 0;
-        if (p.tgt_tma) make_tgt_tmap(&p.tm_tgt, targets, batch, n->width);
+        const bool aligned = reinterpret_cast<uintptr_t>(targets) % 16 == 0;
+        p.tgt_mode = (!aligned || n->width < 32) ? 0 : (n_targets == n->width ? 1 : 2);
+        if (p.tgt_mode == 1) make_tgt_tmap(&p.tm_tgt, targets, batch, n->width);
         p.dw_partials = n->dw_slabs;
         p.loss_partials = n->loss_partials;
         p.batch = batch;
@@ -408,12 +440,15 @@ int tnn_network_train_step(tnn_network *n, const void *x, const float *targets, 
         p.n_sm = n->n_sm;
         p.status = n->status;
         p.stream = s;
-        p.prof = (n->variant & 32) ? reinterpret_cast<long long *>(n->loss_partials) : nullptr; // non-null = print cycle accounting
         // widest-overlap kernel first; the single-tile kernel covers deeper networks
         cudaError_t e = (n->variant & 64) ? cudaErrorInvalidConfiguration : tnn::launch_mlp_train_pipe(p);
         if (e == cudaErrorInvalidConfiguration) {
             cudaGetLastError();
             e = tnn::launch_mlp_train(p);
+        }
+        if (e == cudaSuccess && raw) {
+            raw[0] = raw[1] = p.grid_out;
+            return 0;
         }
         if (e == cudaSuccess) {
             if (loss_sum) TNN_CUDA(tnn::launch_sum_partials(n->loss_partials, p.grid_out, loss_sum, s));
@@ -423,23 +458,42 @@ int tnn_network_train_step(tnn_network *n, const void *x, const float *targets, 
         if (e != cudaErrorInvalidConfiguration) TNN_CUDA(e);
         cudaGetLastError(); // the fused kernel does not cover this width / depth: use the three-kernel path
     }
-    if (batch > n->ws_batch) {
-        TNN_CUDA(cudaStreamSynchronize(s));
-        cudaFree(n->ws_interm);
-        cudaFree(n->ws_dy);
-        n->ws_interm = n->ws_dy = nullptr;
-        n->ws_batch = 0;
-        TNN_CUDA(cudaMalloc(&n->ws_interm, (size_t)(n->n_mat + 1) * batch * n->width * sizeof(__nv_bfloat16)));
-        TNN_CUDA(cudaMalloc(&n->ws_dy, batch * n->width * sizeof(__nv_bfloat16)));
-        n->ws_batch = batch;
-    }
-    if (int rc = run_forward(n, x, nullptr, n->ws_interm, batch, stream, /*copy_input=*/false)) return rc;
-    const __nv_bfloat16 *pred = n->ws_interm + (size_t)n->n_mat * batch * n->width;
-    if (int rc = tnn_l2_loss(pred, targets, n_targets, nullptr, n->ws_dy, batch, n->width, loss_scale, loss_sum, stream))
-        return rc;
-    return run_backward(n, n->ws_dy, n->ws_interm, x, grads, grads_dtype, pack_transpose, nullptr, nullptr, batch,
-                        stream);
+    if (int rc = ensure_workspace(n, unfused_workspace_bytes(n, batch), s)) return rc;
+    __nv_bfloat16 *interm = reinterpret_cast<__nv_bfloat16 *>(n->ws);
+    __nv_bfloat16 *ws_dy = interm + (size_t)(n->n_mat + 1) * batch * n->width;
+    // (with an encoded input the forward kernel stores the encoded tile as matrix 0, which the backward pass reads)
+    if (int rc = run_forward(n, x, nullptr, interm, batch, stream, /*copy_input=*/false, enc)) return rc;
+    const __nv_bfloat16 *pred = interm + (size_t)n->n_mat * batch * n->width;
+    TNN_CUDA(tnn::launch_l2_loss(pred, targets, n_targets, nullptr, ws_dy, batch, n->width, loss_scale,
+                                 (loss_sum || raw) ? n->loss_partials : nullptr, 1024, raw ? nullptr : loss_sum, s));
+    if (raw) raw[1] = 1024;
+    return run_backward(n, ws_dy, interm, enc ? nullptr : x, grads, grads_dtype, pack_transpose, dx, nullptr, batch, stream,
+                        raw ? &raw[0] : nullptr);
     TNN_GUARD_END
+}
+
+int tnn_network_train_step(tnn_network *n, const void *x, const float *targets, int n_targets, size_t batch,
+                           float loss_scale, void *grads, int grads_dtype, int pack_transpose, float *loss_sum,
+                           void *stream) {
+    if (!x) return fail("x and targets are required");
+    return train_step_impl(n, x, nullptr, targets, n_targets, batch, loss_scale, grads, grads_dtype, pack_transpose,
+                           nullptr, loss_sum, stream);
+}
+
+size_t tnn_network_workspace_bytes(const tnn_network *n, size_t batch) { return n ? unfused_workspace_bytes(n, batch) : 0; }
+
+int tnn_network_set_workspace(tnn_network *n, void *workspace, size_t bytes) {
+    if (!n) return fail("network is null");
+    if (workspace && reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return fail("workspace must be 256-byte aligned");
+    if (n->ws_owned) {
+        // a launch may still be using the library's own block
+        TNN_CUDA(cudaDeviceSynchronize());
+        cudaFree(n->ws);
+    }
+    n->ws = workspace;
+    n->ws_bytes = workspace ? bytes : 0;
+    n->ws_owned = false;
+    return 0;
 }
 
 int tnn_network_sync_status(tnn_network *n, int *status, void *stream) {
@@ -471,13 +525,24 @@ int tnn_l2_loss(const void *pred, const float *target, int n_targets, float *val
     if (n_targets <= 0 || n_targets > stride) return fail("n_targets must be in [1, stride]");
     if (loss_scale == 0.0f) return fail("loss_scale must not be 0");
     if (stride % 16 != 0) return fail("stride must be a multiple of 16 (network widths are)");
-    // per-block partial sums of the loss; the buffer is owned by the library (one per process)
-    static float *partials = nullptr;
+    if (int rc = check_l2_alignment(pred, target, n_targets, values, grads, stride)) return rc;
+    // Per-block partial sums of the loss: one buffer per device, allocated at the first call on that device that
+    // asks for the sum and kept until the process exits.  Calls on one device share it, like tnn_l2_loss_static.
     constexpr int kPartials = 1024;
-    if (loss_sum && !partials) TNN_CUDA(cudaMalloc(&partials, kPartials * sizeof(float)));
+    constexpr int kMaxDevices = 64;
+    static float *partials[kMaxDevices] = {};
+    static std::mutex mu;
+    float *buf = nullptr;
+    if (loss_sum) {
+        int dev = 0;
+        TNN_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= kMaxDevices) return fail("device ordinal out of range");
+        std::lock_guard<std::mutex> lock(mu);
+        if (!partials[dev]) TNN_CUDA(cudaMalloc(&partials[dev], kPartials * sizeof(float)));
+        buf = partials[dev];
+    }
     TNN_CUDA(tnn::launch_l2_loss((const __nv_bfloat16 *)pred, target, n_targets, values, (__nv_bfloat16 *)grads, batch,
-                                 stride, loss_scale, loss_sum ? partials : nullptr, kPartials, loss_sum,
-                                 (cudaStream_t)stream));
+                                 stride, loss_scale, buf, kPartials, loss_sum, (cudaStream_t)stream));
     return 0;
     TNN_GUARD_END
 }
@@ -494,22 +559,6 @@ int tnn_adam_step(float *params, float *m, float *v, const float *grads, size_t 
 } // extern "C"
 
 // ======================================================================== encoding
-struct tnn_encoding {
-    bool is_grid = false;
-    int n_in = 0;
-    int n_out = 0;    // natural output width
-    int padded = 0;   // padded output width
-    float scale = 1.0f, offset = 0.0f; // identity
-    int n_frequencies = 0;             // > 0: frequency encoding
-    tnn::GridParams gp{};
-    size_t n_params = 0;
-    float *table = nullptr;    // owned storage
-    float *bound = nullptr;    // caller-owned storage used instead, when set (tnn_encoding_bind_params)
-    float *params() const { return bound ? bound : table; }
-    void *scratch = nullptr;
-    size_t scratch_bytes = 0;
-};
-
 namespace {
 
 int enum_value(const tnn::JsonObject &cfg, const char *key, const std::vector<const char *> &names, int dflt) {
@@ -698,6 +747,7 @@ int tnn_encoding_backward(tnn_encoding *e, const float *x, const void *dy, int d
     if (!x || !dy) return fail("null argument");
     if (dy_dtype != TNN_DTYPE_FP32 && dy_dtype != TNN_DTYPE_BF16) return fail("dy must be fp32 or bf16");
     if (batch > 0xFFFFFFFFull / 8) return fail("batch too large");
+    if (reinterpret_cast<uintptr_t>(grads) % 16 != 0) return fail("grads must be 16-byte aligned (vector reductions)");
     size_t need = deterministic ? tnn::grid_bwd_scratch_bytes(e->gp, batch) : 0;
     if (need > e->scratch_bytes) {
         TNN_CUDA(cudaStreamSynchronize(s));
@@ -714,3 +764,122 @@ int tnn_encoding_backward(tnn_encoding *e, const float *x, const void *dy, int d
 }
 
 } // extern "C"
+
+// ======================================================================== network with input encoding
+namespace {
+
+// The identity encoding can be folded into the network kernels' first-layer load.
+bool foldable(const tnn_encoding *e) {
+    return !e->is_grid && e->n_frequencies == 0 && e->n_in <= tnn::kMaxFoldedInputs;
+}
+
+int nwe_checks(const tnn_network *n, const tnn_encoding *e, const float *x, size_t batch) {
+    if (!n || !e) return fail("null handle");
+    if (e->padded != n->width)
+        return fail("the encoding's padded output width (" + std::to_string(e->padded) + ") must equal the network width (" +
+                    std::to_string(n->width) + ")");
+    if (batch && !x) return fail("input is null");
+    if (batch % 8 != 0) return fail("Batch size is not divisible by 8.");
+    if (reinterpret_cast<uintptr_t>(x) % 4 != 0) return fail("input must be 4-byte aligned");
+    return 0;
+}
+
+size_t nwe_workspace_bytes(const tnn_network *n, size_t batch) {
+    // encoded input, the three-kernel training workspace, dL/d(encoded input)
+    return (size_t)(n->n_mat + 4) * batch * n->width * sizeof(__nv_bfloat16);
+}
+
+} // namespace
+
+extern "C" {
+
+size_t tnn_network_with_encoding_workspace_bytes(const tnn_network *n, size_t batch) {
+    return n ? nwe_workspace_bytes(n, batch) : 0;
+}
+
+int tnn_network_with_encoding_forward(tnn_network *n, tnn_encoding *e, const float *x, void *y, void *interm_fwd,
+                                      size_t batch, void *stream) {
+    TNN_GUARD_BEGIN
+    if (int rc = nwe_checks(n, e, x, batch)) return rc;
+    if (batch == 0) return 0;
+    if (!y && !interm_fwd) return fail("forward needs y or interm_fwd");
+    if (foldable(e)) {
+        const tnn::EncodedInput enc{x, e->n_in, e->scale, e->offset};
+        return run_forward(n, nullptr, y, interm_fwd, batch, stream, false, &enc);
+    }
+    // other encodings: the encoded rows go through matrix 0 of interm_fwd when the caller provides it (that is where
+    // the backward pass expects the network input), else through the handle's workspace
+    void *encoded = interm_fwd;
+    if (!encoded) {
+        if (int rc = ensure_workspace(n, batch * n->width * sizeof(__nv_bfloat16), (cudaStream_t)stream)) return rc;
+        encoded = n->ws;
+    }
+    if (int rc = tnn_encoding_forward(e, x, encoded, TNN_DTYPE_BF16, batch, stream)) return rc;
+    return run_forward(n, encoded, y, interm_fwd, batch, stream, /*copy_input=*/false);
+    TNN_GUARD_END
+}
+
+int tnn_network_with_encoding_inference(tnn_network *n, tnn_encoding *e, const float *x, void *y, size_t batch,
+                                        void *stream) {
+    if (!y && batch) return fail("output is null");
+    return tnn_network_with_encoding_forward(n, e, x, y, nullptr, batch, stream);
+}
+
+static int nwe_train_step_impl(tnn_network *n, tnn_encoding *e, const float *x, const float *targets, int n_targets,
+                               size_t batch, float loss_scale, void *grads, int grads_dtype, int pack_transpose,
+                               float *encoding_grads, int deterministic, float *loss_sum, void *stream, int *raw) {
+    TNN_GUARD_BEGIN
+    if (int rc = nwe_checks(n, e, x, batch)) return rc;
+    if (foldable(e)) {
+        const tnn::EncodedInput enc{x, e->n_in, e->scale, e->offset};
+        return train_step_impl(n, nullptr, &enc, targets, n_targets, batch, loss_scale, grads, grads_dtype, pack_transpose,
+                               nullptr, loss_sum, stream, raw);
+    }
+    if (batch == 0) return fail("batch_size == 0");
+    const bool want_enc_grads = encoding_grads && e->n_params;
+    if (int rc = ensure_workspace(n, nwe_workspace_bytes(n, batch), (cudaStream_t)stream)) return rc;
+    // layout: [three-kernel workspace][encoded input][dL/d(encoded input)]
+    uint8_t *base = reinterpret_cast<uint8_t *>(n->ws);
+    const size_t mat = batch * n->width * sizeof(__nv_bfloat16);
+    void *encoded = base + (size_t)(n->n_mat + 2) * mat;
+    void *dx = want_enc_grads ? base + (size_t)(n->n_mat + 3) * mat : nullptr;
+    if (int rc = tnn_encoding_forward(e, x, encoded, TNN_DTYPE_BF16, batch, stream)) return rc;
+    if (int rc = train_step_impl(n, encoded, nullptr, targets, n_targets, batch, loss_scale, grads, grads_dtype,
+                                 pack_transpose, dx, loss_sum, stream, raw))
+        return rc;
+    if (want_enc_grads)
+        return tnn_encoding_backward(e, x, dx, TNN_DTYPE_BF16, encoding_grads, batch, deterministic, stream);
+    return 0;
+    TNN_GUARD_END
+}
+
+int tnn_network_with_encoding_train_step(tnn_network *n, tnn_encoding *e, const float *x, const float *targets,
+                                         int n_targets, size_t batch, float loss_scale, void *grads, int grads_dtype,
+                                         int pack_transpose, float *encoding_grads, int deterministic, float *loss_sum,
+                                         void *stream) {
+    return nwe_train_step_impl(n, e, x, targets, n_targets, batch, loss_scale, grads, grads_dtype, pack_transpose,
+                               encoding_grads, deterministic, loss_sum, stream, nullptr);
+}
+
+} // extern "C"
+
+namespace tnn {
+// The training pass as the trainer wants it: per-CTA slabs and loss partials left in the network's buffers.
+int train_step_raw(tnn_network *n, tnn_encoding *e, const void *x, const float *targets, int n_targets, size_t batch,
+                   float loss_scale, float *encoding_grads, int deterministic, int *n_slabs, int *n_loss_partials,
+                   void *stream) {
+    int raw[2] = {0, 0};
+    int rc;
+    if (e)
+        rc = nwe_train_step_impl(n, e, (const float *)x, targets, n_targets, batch, loss_scale, nullptr, TNN_DTYPE_FP32, 1,
+                                 encoding_grads, deterministic, nullptr, stream, raw);
+    else if (!x)
+        rc = fail("x and targets are required");
+    else
+        rc = train_step_impl(n, x, nullptr, targets, n_targets, batch, loss_scale, nullptr, TNN_DTYPE_FP32, 1, nullptr,
+                             nullptr, stream, raw);
+    *n_slabs = raw[0];
+    *n_loss_partials = raw[1];
+    return rc;
+}
+} // namespace tnn

@@ -44,6 +44,7 @@ cudaError_t launch_set_params(int width, const void *src, int src_fp32, int src_
                               __nv_bfloat16 *wimg_t, cudaStream_t stream) {
     const int n = n_mat * width * width;
     const int blocks = (n + 255) / 256;
+    count_launch();
 #define TNN_CASE(WW)                                                                                                    \
     case WW:                                                                                                            \
         set_params_kernel<WW><<<blocks, 256, 0, stream>>>(src, src_fp32, src_packed, n_mat, one_padded_in, unpadded_out, \
@@ -80,6 +81,7 @@ __global__ void reduce_dw_kernel(const float *__restrict__ slabs, int n_slabs, i
 cudaError_t launch_reduce_dw(const float *slabs, int n_slabs, int n_mat, int width, int pack_transpose, float scale,
                              float *out_f32, __nv_bfloat16 *out_bf16, cudaStream_t stream) {
     const int n = n_mat * width * width;
+    count_launch();
     reduce_dw_kernel<<<(n + 127) / 128, 128, 0, stream>>>(slabs, n_slabs, n_mat, width, pack_transpose, scale, out_f32,
                                                          out_bf16);
     return cudaGetLastError();
@@ -126,6 +128,7 @@ cudaError_t launch_identity_fwd(const float *x, void *out, int out_bf16, size_t 
                                 float scale, float offset, cudaStream_t stream) {
     const size_t n = batch * (size_t)padded;
     if (n == 0) return cudaSuccess;
+    count_launch();
     if (out_bf16 && padded % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0) {
         const size_t n8 = n / 8;
         identity_fwd_bf16x8_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(x, (uint4 *)out, batch, n_in, padded,
@@ -171,6 +174,7 @@ cudaError_t launch_frequency_fwd(const float *x, void *out, int out_bf16, size_t
                                  cudaStream_t stream) {
     const size_t n = batch * (size_t)padded;
     if (n == 0) return cudaSuccess;
+    count_launch();
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (out_bf16)
         frequency_fwd_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (__nv_bfloat16 *)out, batch, n_in, n_freq, padded);
@@ -249,6 +253,7 @@ __global__ void sum_partials_kernel(const float *__restrict__ partials, int n, f
 }
 
 cudaError_t launch_sum_partials(const float *partials, int n, float *out, cudaStream_t stream) {
+    count_launch();
     sum_partials_kernel<<<1, 256, 0, stream>>>(partials, n, out);
     return cudaGetLastError();
 }
@@ -257,6 +262,7 @@ cudaError_t launch_l2_loss(const __nv_bfloat16 *pred, const float *target, int n
                            __nv_bfloat16 *grads, size_t batch, int stride, float loss_scale, float *loss_partials,
                            int n_partials, float *loss_sum, cudaStream_t stream) {
     if (batch == 0) return cudaSuccess;
+    count_launch(loss_sum && loss_partials ? 2 : 1);
     l2_loss_kernel<<<n_partials, 256, 0, stream>>>(pred, target, n_targets, values, grads, batch, stride, loss_scale,
                                                    loss_partials);
     if (loss_sum && loss_partials) sum_partials_kernel<<<1, 256, 0, stream>>>(loss_partials, n_partials, loss_sum);
@@ -318,15 +324,18 @@ cudaError_t launch_adam(float *p, float *m, float *v, const float *g, size_t n, 
     size_t done = 0;
     if (!p_bf16 && n >= (1u << 16) && aligned16(p) && aligned16(m) && aligned16(v) && aligned16(g)) {
         const size_t n4 = n / 4;
+        count_launch();
         adam_vec4_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, stream>>>(
             reinterpret_cast<float4 *>(p), reinterpret_cast<float4 *>(m), reinterpret_cast<float4 *>(v),
             reinterpret_cast<const float4 *>(g), n4, grad_scale, lr, b1, b2, eps, bc1, bc2_sqrt);
         done = n4 * 4;
     }
-    if (done < n)
+    if (done < n) {
+        count_launch();
         adam_kernel<<<(unsigned)((n - done + 255) / 256), 256, 0, stream>>>(p + done, m + done, v + done, g + done, n - done,
                                                                         grad_scale, lr, b1, b2, eps, bc1, bc2_sqrt,
                                                                         p_bf16 ? p_bf16 + done : nullptr);
+    }
     return cudaGetLastError();
 }
 
@@ -335,10 +344,12 @@ template <typename A, typename B> __global__ void convert_kernel(const A *__rest
     if (i < n) b[i] = (B)(float)a[i];
 }
 cudaError_t launch_f32_to_bf16(const float *a, __nv_bfloat16 *b, size_t n, cudaStream_t s) {
+    count_launch(n ? 1 : 0);
     if (n) convert_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, b, n);
     return cudaGetLastError();
 }
 cudaError_t launch_bf16_to_f32(const __nv_bfloat16 *a, float *b, size_t n, cudaStream_t s) {
+    count_launch(n ? 1 : 0);
     if (n) convert_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, b, n);
     return cudaGetLastError();
 }

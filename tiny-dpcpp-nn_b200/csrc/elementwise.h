@@ -6,6 +6,9 @@
 
 namespace tnn {
 
+// Counts kernel launches of this library (tnn_launch_count): every launcher reports the kernels it enqueued.
+void count_launch(int n = 1);
+
 cudaError_t launch_set_params(int width, const void *src, int src_fp32, int src_packed, int n_mat, int one_padded_in,
                               int unpadded_out, __nv_bfloat16 *packed_out, float *master_out, __nv_bfloat16 *wimg,
                               __nv_bfloat16 *wimg_t, cudaStream_t stream);

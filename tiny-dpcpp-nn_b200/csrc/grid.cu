@@ -11,6 +11,7 @@
 // so the F features of all levels of one sample are written as one contiguous segment and
 // the only uncoalesced traffic is the unavoidable random gather from the tables.
 #include "grid.h"
+#include "elementwise.h"
 #include "grid_device.cuh"
 
 #include <cmath>
@@ -129,10 +130,14 @@ __global__ void __launch_bounds__(256) grid_fwd_kernel(const GridParams p, const
                 for (int f = 0; f < F; ++f) res_v[f] = fmaf(wt[c], vals[c][f], res_v[f]);
         }
     }
-    if constexpr (sizeof(OutT) == 2 && F == 2) {
-        *reinterpret_cast<__nv_bfloat162 *>(orow + level * F) = __floats2bfloat162_rn(res_v[0], res_v[1]);
-    } else if constexpr (sizeof(OutT) == 4 && F == 2) {
-        *reinterpret_cast<float2 *>(orow + level * F) = make_float2(res_v[0], res_v[1]);
+    // A level's two features go out as one vector store when every row starts on a vector boundary: an even padded
+    // width and a base pointer aligned to two elements (uniform over the launch).  Odd widths use scalar stores.
+    const bool vec2 = F == 2 && (p.padded_width & 1u) == 0u && (reinterpret_cast<uintptr_t>(out) % (2 * sizeof(OutT))) == 0;
+    if (vec2) {
+        if constexpr (sizeof(OutT) == 2)
+            *reinterpret_cast<__nv_bfloat162 *>(orow + level * F) = __floats2bfloat162_rn(res_v[0], res_v[1]);
+        else
+            *reinterpret_cast<float2 *>(orow + level * F) = make_float2(res_v[0], res_v[F > 1 ? 1 : 0]);
     } else {
 #pragma unroll
         for (int f = 0; f < F; ++f) orow[level * F + f] = (OutT)res_v[f];
@@ -144,6 +149,7 @@ static cudaError_t launch_fwd_df(const GridParams &p, const float *x, const floa
                                  size_t batch, cudaStream_t stream) {
     const size_t n = batch * p.n_levels;
     const unsigned blocks = (unsigned)((n + 255) / 256);
+    count_launch();
     if (out_bf16)
         grid_fwd_kernel<D, F, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p, x, table, (__nv_bfloat16 *)out, batch);
     else

@@ -5,6 +5,7 @@
 //   * the same scatter with 64-bit fixed-point integer reductions (grid_bwd_fixed.cu): order-independent, so two runs
 //     give identical bits; chosen with `deterministic` in the C ABI.
 #include "grid.h"
+#include "elementwise.h"
 #include "grid_device.cuh"
 
 #include <cuda_bf16.h>
@@ -116,6 +117,7 @@ static cudaError_t launch_bwd_atomic_df(const GridParams &p, const float *x, con
     if (e != cudaSuccess) return e;
     const size_t n = batch * p.n_levels;
     const unsigned blocks = (unsigned)((n + 255) / 256);
+    count_launch();
     if (dy_bf16)
         grid_bwd_atomic_kernel<D, F, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p, x, (const __nv_bfloat16 *)dy, grads, batch);
     else

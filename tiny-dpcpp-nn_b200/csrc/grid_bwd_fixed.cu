@@ -11,6 +11,7 @@
 // 2^(61 - e - b) keeps every sum below 2^61.  An entry that receives k contributions of typical size loses at
 // most k / 2 units of 2^-(61 - e - b), i.e. a relative error far below fp32 rounding.
 #include "grid.h"
+#include "elementwise.h"
 #include "grid_device.cuh"
 
 #include <cuda_bf16.h>
@@ -21,20 +22,29 @@ namespace {
 
 struct FixedHeader {
     uint32_t absmax_bits; // max |dy| over the real feature columns, as float bits (non-negative floats order like integers)
-    uint32_t pad[63];
+    uint32_t non_finite;  // set when dy holds an inf or a NaN: every gradient of the call is then reported as NaN
+    uint32_t pad[62];
 };
 
 template <typename DyT>
 __global__ void __launch_bounds__(256) grid_absmax_kernel(const DyT *__restrict__ dy, size_t batch, uint32_t n_features,
                                                           uint32_t padded, FixedHeader *hdr) {
     float m = 0.0f;
+    bool bad = false;
     const size_t n = batch * (size_t)n_features;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / n_features;
         const uint32_t c = (uint32_t)(i % n_features);
         const float v = fabsf((float)dy[r * padded + c]);
-        if (v <= 3.0e38f) m = fmaxf(m, v); // non-finite values do not take part in choosing the scale
+        if (v <= 3.0e38f)
+            m = fmaxf(m, v); // non-finite values do not take part in choosing the scale
+        else
+            bad = true;
     }
+    // The reference's float atomics (and the default path here) propagate inf / NaN into the gradient; integer
+    // accumulation cannot represent them, so the call is flagged and the finalize kernel reports NaN instead of
+    // finite garbage (a loss-scale overflow check on the gradients then still fires).
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(&hdr->non_finite, 1u);
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if ((threadIdx.x & 31) == 0 && m > 0.0f) atomicMax(&hdr->absmax_bits, __float_as_uint(m));
 }
@@ -79,7 +89,8 @@ __global__ void __launch_bounds__(256) grid_bwd_fixed_kernel(const GridParams p,
 #pragma unroll
         for (int f = 0; f < F; ++f) {
             // the product is rounded to fp32 like the reference's, the scaling by a power of two is exact
-            const long long q = __float2ll_rn(__fmul_rn(__fmul_rn(weight, gr[f]), scale));
+            const float prod = __fmul_rn(__fmul_rn(weight, gr[f]), scale);
+            const long long q = fabsf(prod) <= 3.0e38f ? __float2ll_rn(prod) : 0ll; // flagged by grid_absmax_kernel
             if (q != 0) atomicAdd(al + (size_t)e * F + f, (unsigned long long)q);
         }
     };
@@ -117,7 +128,7 @@ __global__ void __launch_bounds__(256) grid_fixed_finalize_kernel(const unsigned
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const double inv_scale = ldexp(1.0, -fixed_exponent(hdr->absmax_bits, contributions));
-    grads[i] = (float)((double)(long long)acc[i] * inv_scale);
+    grads[i] = hdr->non_finite ? __int_as_float(0x7FC00000) : (float)((double)(long long)acc[i] * inv_scale);
 }
 
 template <int D, int F>
@@ -133,6 +144,7 @@ cudaError_t run_fixed(const GridParams &p, const float *x, const void *dy, int d
     const unsigned red_blocks = (unsigned)((n_dy + 256 * 8 - 1) / (256 * 8) < 148 * 8 ? (n_dy + 256 * 8 - 1) / (256 * 8) : 148 * 8);
     const size_t n = batch * p.n_levels;
     const unsigned blocks = (unsigned)((n + 255) / 256);
+    count_launch(3);
     if (dy_bf16) {
         grid_absmax_kernel<__nv_bfloat16><<<red_blocks ? red_blocks : 1, 256, 0, stream>>>(
             (const __nv_bfloat16 *)dy, batch, p.n_features, p.padded_width, hdr);

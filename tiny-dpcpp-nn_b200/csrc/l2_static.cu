@@ -40,6 +40,13 @@ extern "C" int tnn_l2_loss_static(const void *pred, const float *target, int n_t
     if (n_targets <= 0 || n_targets > stride) return tnn::api_fail("n_targets must be in [1, stride]", 1);
     if (loss_scale == 0.0f) return tnn::api_fail("loss_scale must not be 0", 1);
     if (stride % 16 != 0) return tnn::api_fail("stride must be a multiple of 16 (network widths are)", 1);
+    {
+        auto mis = [](const void *q, uintptr_t a) { return q && reinterpret_cast<uintptr_t>(q) % a != 0; };
+        if (mis(pred, 16) || mis(values, 16) || mis(grads, 16))
+            return tnn::api_fail("pred, values and grads must be 16-byte aligned", 1);
+        if (mis(target, n_targets == stride ? 16 : 4))
+            return tnn::api_fail("target must be 16-byte aligned when n_targets == stride (4-byte aligned otherwise)", 1);
+    }
     const size_t n_el = batch * (size_t)stride;
     if (n_el > kMaxElements)
         return tnn::api_fail("tnn_l2_loss_static: batch * stride = " + std::to_string(n_el) +

@@ -21,6 +21,7 @@
 // weights that do not fit beside the tiles) the weights are not resident: the issuer streams W_l through a ring
 // of two tiles, fetching the next one when it issues a chain GEMM, and fewer tiles are kept in flight.
 #include "mlp_common.cuh"
+#include "elementwise.h"
 #include "mlp_launch.h"
 
 namespace tnn {
@@ -504,6 +505,7 @@ template <int W, bool B_MN, bool BIG> static cudaError_t launch_bwd_variant(BwdL
         while (tmem_cols < cols_needed) tmem_cols *= 2;
         const int first = lo == 0; // deltas and dL/dx are the same in every pass: store them once
         // K-major weights for the chain are rows = input feature; the MN-major variant reads the transposed image
+        count_launch();
         kern<<<grid, kBwdThreads, smem, p.stream>>>(p.tm_dy, p.tm_interm, p.tm_a0, p.tm_ibwd, p.tm_dx,
                                                     B_MN ? p.wimg_t : p.wimg,
                                             p.dw_partials, n_tiles, p.n_mat, p.act, p.out_act, first ? p.store_bwd : 0,
@@ -515,8 +517,7 @@ template <int W, bool B_MN, bool BIG> static cudaError_t launch_bwd_variant(BwdL
 }
 
 template <int W> static cudaError_t launch_bwd_w(BwdLaunch &p) {
-    const bool mn = (p.variant & 2) != 0;
-    if (mn) return launch_bwd_variant<W, true, false>(p);
+    // variant bit 256 (tests): stream the weights even if they would fit on chip
     cudaError_t e = (p.variant & 256) ? cudaErrorInvalidConfiguration : launch_bwd_variant<W, false, false>(p);
     if (e == cudaErrorInvalidConfiguration) e = launch_bwd_variant<W, false, true>(p); // streamed weights
     return e;

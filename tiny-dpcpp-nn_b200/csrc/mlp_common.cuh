@@ -1,6 +1,7 @@
 // Shared definitions of the fused-MLP kernels: tile geometry, the swizzled shared-memory
 // layout that both TMA and the tcgen05 descriptors agree on, and activation helpers.
 #pragma once
+#include "mlp_launch.h"
 #include "umma.cuh"
 
 namespace tnn {
@@ -106,6 +107,41 @@ template <int W> struct Tile {
                         (k > 0) ? 1u : accumulate);
     }
 };
+
+// Network input produced inside the kernel from fp32 coordinates: the identity encoding
+// (include/encodings/identity.h:63-77: out[i, j] = j < n_in ? x * scale + offset : 1) folded into the first-layer
+// load, so the batch x W bf16 matrix the reference materialises between the two modules never exists.
+// (struct EncodedInput: mlp_launch.h)
+
+// Whole warp: fill `n_tiles` consecutive input tiles with bf16 ones (the padding value of the encoding).
+template <int W> __device__ __forceinline__ void fill_tiles_with_ones(uint8_t *tiles, int n_tiles, int lane) {
+    const uint4 ones = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
+    for (int i = lane; i < n_tiles * (Tile<W>::ACT_BYTES / 16); i += 32) reinterpret_cast<uint4 *>(tiles)[i] = ones;
+}
+// Whole warp: write the encoded columns (the first one or two 16-byte chunks of every row; the rest of the tile keeps
+// its ones) of the tile whose first row is `row0`.  Rows past the end of the batch become zeros.
+template <int W>
+__device__ __forceinline__ void encode_identity_tile(uint8_t *xtile, const EncodedInput &e, size_t row0, size_t batch,
+                                                     int lane) {
+    using T = Tile<W>;
+    const int n_chunks = (e.n_in + 7) >> 3;
+    for (int r = lane; r < T::TM; r += 32) {
+        const size_t grow = row0 + r;
+        const bool valid = grow < batch;
+        for (int c = 0; c < n_chunks; ++c) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int col = c * 8 + j;
+                v[j] = col < e.n_in ? (valid ? __fadd_rn(__fmul_rn(__ldg(e.x + grow * e.n_in + col), e.scale), e.offset) : 0.0f)
+                                    : 1.0f;
+            }
+            *reinterpret_cast<uint4 *>(xtile + T::chunk_off(r, c)) =
+                make_uint4(ptx::pack_bf16x2(v[0], v[1]), ptx::pack_bf16x2(v[2], v[3]), ptx::pack_bf16x2(v[4], v[5]),
+                           ptx::pack_bf16x2(v[6], v[7]));
+        }
+    }
+}
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
 

@@ -26,6 +26,7 @@
 // running the chains of several slots side by side: every slot has its own issuer warp and its
 // own epilogue group, and nothing but the tensor pipe and shared memory is shared between them.
 #include "mlp_common.cuh"
+#include "elementwise.h"
 #include "mlp_launch.h"
 
 namespace tnn {
@@ -70,7 +71,7 @@ template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN_MAJOR, bool S
 __global__ void __launch_bounds__(FwdSmem<W, NSLOT, TMEM_A, STORE_ALL>::THREADS, 1)
 mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                const __grid_constant__ CUtensorMap tm_interm, const __nv_bfloat16 *__restrict__ wimg,
-               int n_tiles, int n_mat, int act, int out_act, int write_y, int *status) {
+               int n_tiles, int n_mat, int act, int out_act, int write_y, size_t batch, const EncodedInput enc, int *status) {
     using T = Tile<W>;
     using S = FwdSmem<W, NSLOT, TMEM_A, STORE_ALL, STREAM_W>;
     static_assert(NSLOT <= kMaxSlots, "too many slots");
@@ -101,7 +102,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         bars.abort_flag = 0;
         bars.out_lock = 0;
         ptx::fence_barrier_init();
-        ptx::prefetch_tmap(&tm_x);
+        if (!enc.x) ptx::prefetch_tmap(&tm_x);
         ptx::prefetch_tmap(&tm_y);
         if (STORE_ALL) ptx::prefetch_tmap(&tm_interm);
     }
@@ -116,26 +117,53 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
-        if (lane == 0 && my_tiles > 0) {
+        // input tiles by TMA (lane 0) or, with a folded identity encoding, written by the whole warp from fp32
+        // coordinates (with STORE_ALL the encoded tile is also stored as matrix 0 of the activations)
+        if (my_tiles > 0) {
             if constexpr (!STREAM_W) {
-                ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
-                for (int l = 0; l < n_mat; ++l)
-                    ptx::bulk_load(smem + S::WBUF + l * T::WGT_BYTES,
-                                   reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
-                                   &bars.w_full);
+                if (lane == 0) {
+                    ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
+                    for (int l = 0; l < n_mat; ++l)
+                        ptx::bulk_load(smem + S::WBUF + l * T::WGT_BYTES,
+                                       reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
+                                       &bars.w_full);
+                }
+            }
+            if (enc.x) {
+                fill_tiles_with_ones<W>(smem + S::XBUF, NSLOT, lane);
+                __syncwarp();
             }
             for (int j = 0; j < my_tiles; ++j) {
                 const int s = j % NSLOT, t = j / NSLOT;
                 const int tile = blockIdx.x + j * gridDim.x;
-                if (t >= 1 && !ptx::mbar_wait(&bars.x_empty[s], (t - 1) & 1, abort_flag)) {
-                    atomicExch(status, KS_TIMEOUT_PRODUCER | s);
+                if (t >= 1 && !__all_sync(0xffffffffu, lane != 0 || ptx::mbar_wait(&bars.x_empty[s], (t - 1) & 1, abort_flag))) {
+                    if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | s);
                     break;
                 }
-                ptx::mbar_arrive_expect_tx(&bars.x_full[s], T::ACT_BYTES);
-                for (int a = 0; a < T::KATOMS; ++a)
-                    ptx::tma_load_2d(smem + S::XBUF + s * T::ACT_BYTES + a * T::ACT_ATOM_BYTES, &tm_x,
-                                     a * T::ATOM_COLS, tile * T::TM, &bars.x_full[s]);
+                uint8_t *xt = smem + S::XBUF + s * T::ACT_BYTES;
+                if (enc.x) {
+                    if (STORE_ALL && j >= NSLOT) { // the store of this slot's previous tile has read the buffer
+                        if (lane == 0) ptx::tma_wait_group_read<NSLOT - 1>();
+                        __syncwarp();
+                    }
+                    encode_identity_tile<W>(xt, enc, (size_t)tile * T::TM, batch, lane);
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::mbar_arrive(&bars.x_full[s]);
+                        if (STORE_ALL) {
+                            for (int a = 0; a < T::KATOMS; ++a)
+                                ptx::tma_store_3d(&tm_interm, xt + a * T::ACT_ATOM_BYTES, a * T::ATOM_COLS, tile * T::TM, 0);
+                            ptx::tma_commit_group();
+                        }
+                    }
+                } else if (lane == 0) {
+                    ptx::mbar_arrive_expect_tx(&bars.x_full[s], T::ACT_BYTES);
+                    for (int a = 0; a < T::KATOMS; ++a)
+                        ptx::tma_load_2d(xt + a * T::ACT_ATOM_BYTES, &tm_x, a * T::ATOM_COLS, tile * T::TM, &bars.x_full[s]);
+                }
             }
+            if (enc.x && STORE_ALL && lane == 0) ptx::tma_wait_group<0>();
         }
     } else if (warp <= NSLOT) {
         // ------------------------------------------------------------ MMA issuer of slot s
@@ -397,20 +425,19 @@ static cudaError_t launch_variant(const FwdLaunch &p) {
     const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
     const int grid = n_tiles < p.n_sm ? n_tiles : p.n_sm;
     if (grid == 0) return cudaSuccess;
+    count_launch();
     kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, p.tm_y, p.tm_interm, B_MN ? p.wimg : p.wimg_t, n_tiles, p.n_mat,
-                                               p.act, p.out_act, p.write_y, p.status);
+                                               p.act, p.out_act, p.write_y, p.batch, p.enc, p.status);
     return cudaGetLastError();
 }
 
 template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
-    // variant bits (tuning): 1 = hidden activations through shared memory instead of TMEM (inference),
-    // 2 = MN-major weight operand, 4 = two instead of four tiles in flight, 8 = three tiles in flight
-    // bit 256 = stream the weights even if they would fit
+    // variant bit 256 (tests): stream the weights through the per-slot rings even if they would fit on chip
     const bool force_stream = (p.variant & 256) != 0;
+    cudaError_t e = cudaErrorInvalidConfiguration;
     if (p.store_all) {
-        cudaError_t e = cudaErrorInvalidConfiguration;
         if (!force_stream) {
-            if (!(p.variant & 4)) e = launch_variant<W, 3, true, false, false>(p);
+            e = launch_variant<W, 3, true, false, false>(p);
             if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, true, false, false>(p);
         }
         // weights do not fit beside the tiles: per-slot weight rings
@@ -418,35 +445,21 @@ template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
         if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 1, true, false, false, true>(p);
         return e;
     }
-    if (force_stream) {
-        cudaError_t e = launch_variant<W, 2, false, W >= 32, false, true>(p);
-        if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 1, false, W >= 32, false, true>(p);
-        return e;
-    }
-    if (p.variant & 2) return launch_variant<W, 2, false, false, true>(p);
-    cudaError_t e = cudaErrorInvalidConfiguration;
-    if constexpr (W <= 32) {
-        // narrow layers are pure latency chains (one or two MMAs per layer): six tiles in flight instead of four
-        if (!(p.variant & (1 | 4 | 8))) {
-            e = launch_variant<W, 6, false, W >= 32, false>(p);
-            if (e != cudaErrorInvalidConfiguration) return e;
+    // inference: hidden activations in tensor memory where the A operand can live there (W >= 32)
+    constexpr bool TA = W >= 32;
+    if (!force_stream) {
+        if constexpr (W <= 32) {
+            // narrow layers are pure latency chains (one or two MMAs per layer): six tiles in flight
+            e = launch_variant<W, 6, false, TA, false>(p);
         }
+        // measured at W = 64, batch 2^22: four tiles in flight win up to 4 hidden layers (0.170 / 0.213 ms at 2 / 4),
+        // three from 6 on (0.261 vs 0.272 ms at 6, 0.337 vs 0.465 ms at 8 layers)
+        if (e == cudaErrorInvalidConfiguration && p.n_mat >= 7) e = launch_variant<W, 3, false, TA, false>(p);
+        if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 4, false, TA, false>(p);
+        if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, false, TA, false>(p);
     }
-    if constexpr (W >= 32) {
-        if (!(p.variant & 1)) {
-            // measured at W = 64, batch 2^22: four tiles in flight win up to 4 hidden layers (0.170 / 0.213 ms at 2 / 4),
-            // three from 6 on (0.261 vs 0.272 ms at 6, 0.337 vs 0.465 ms at 8 layers)
-            if ((p.variant & 8) || (!(p.variant & 4) && p.n_mat >= 7)) e = launch_variant<W, 3, false, true, false>(p);
-            if (e == cudaErrorInvalidConfiguration && !(p.variant & 4)) e = launch_variant<W, 4, false, true, false>(p);
-            if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, false, true, false>(p);
-            if (e != cudaErrorInvalidConfiguration) return e;
-        }
-    }
-    if (p.variant & 8) return launch_variant<W, 3, false, false, false>(p);
-    if (!(p.variant & 4)) e = launch_variant<W, 4, false, false, false>(p);
-    if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, false, false, false>(p);
-    if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, false, W >= 32, false, true>(p);
-    if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 1, false, W >= 32, false, true>(p);
+    if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, false, TA, false, true>(p);
+    if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 1, false, TA, false, true>(p);
     return e;
 }
 

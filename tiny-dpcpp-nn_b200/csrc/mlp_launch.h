@@ -8,6 +8,14 @@
 
 namespace tnn {
 
+// Identity encoding folded into a kernel's first-layer load (include/encodings/identity.h:63-77).
+struct EncodedInput {
+    const float *x; // [batch][n_in] fp32; nullptr = the input is a bf16 matrix fetched by TMA
+    int n_in;       // 1..kMaxFoldedInputs
+    float scale, offset;
+};
+constexpr int kMaxFoldedInputs = 16;
+
 struct FwdLaunch {
     CUtensorMap tm_x;      // [batch][W] bf16 input, box 128 x min(W, 64)
     CUtensorMap tm_y;      // [batch][W] bf16 output
@@ -20,6 +28,7 @@ struct FwdLaunch {
     int act, out_act;
     int store_all;
     int write_y;
+    EncodedInput enc; // enc.x != nullptr: the input tile is produced in the kernel from fp32 coordinates
     int variant;
     int n_sm;
     int *status;
@@ -55,8 +64,12 @@ struct TrainLaunch {
     const __nv_bfloat16 *wimg;
     const float *targets;   // [batch][n_targets] fp32
     int n_targets;
-    CUtensorMap tm_tgt;     // the same targets as a tiled map, box 128 x 32 fp32 (valid when tgt_tma)
-    int tgt_tma;            // targets are as wide as the network and 16-byte aligned: stage them with TMA
+    CUtensorMap tm_tgt;     // the same targets as a tiled map, box 128 x 32 fp32 (valid when tgt_mode == 1)
+    // how the pipelined kernel fetches targets: 0 = per-thread loads, 1 = TMA boxes (n_targets == width),
+    // 2 = one bulk copy of the tile's 128 * n_targets contiguous floats (n_targets < width); 1 and 2 need
+    // 16-byte aligned targets
+    int tgt_mode;
+    EncodedInput enc;       // enc.x != nullptr: the input tile is produced in the kernel from fp32 coordinates
     float *dw_partials;     // [grid][L+1][W][W] fp32, layout (out, in)
     float *loss_partials;   // [grid] fp32
     size_t batch;
@@ -68,7 +81,6 @@ struct TrainLaunch {
     int *status;
     cudaStream_t stream;
     int grid_out;
-    long long *prof; // cycle-accounting buffer of tuning builds, normally nullptr
 };
 // cudaErrorInvalidConfiguration when the network does not fit the on-chip budget of the fused kernel.
 cudaError_t launch_mlp_train(TrainLaunch &p);

@@ -20,9 +20,8 @@
 // Each weight tile is staged once and used in both directions without a transposed copy: as the
 // MN-major B operand of the forward GEMM and as the K-major B operand of the backward GEMM.
 #include "mlp_common.cuh"
+#include "elementwise.h"
 #include "mlp_launch.h"
-
-#include <cstdio>
 
 namespace tnn {
 
@@ -61,20 +60,14 @@ struct TrainBarriers {
     float loss_red[16];
 };
 
-// Cycle accounting for tuning (PROF instantiations only): CTA 0 adds the cycles its chain issuer and its
-// first epilogue thread spend in each region to prof[0..15].
-#define TNN_TIC() ([&]() { if constexpr (PROF) return (long long)clock64(); else return 0ll; }())
-#define TNN_TOC(slot, t0) do { if constexpr (PROF) prof_acc[slot] += (long long)clock64() - (t0); } while (0)
-
-template <int W, bool PROF = false>
+template <int W>
 __global__ void __launch_bounds__(TrainSmem<W>::THREADS, 1)
 mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *__restrict__ wimg,
                  const float *__restrict__ targets, int n_targets, float *__restrict__ dw_slabs,
                  float *__restrict__ loss_partials, size_t batch, int n_tiles, int n_mat, int act, int out_act,
-                 float loss_scale, float inv_n, int tmem_cols, int *status, long long *prof = nullptr) {
+                 float loss_scale, float inv_n, int tmem_cols, const EncodedInput enc, int *status) {
     using T = Tile<W>;
     using S = TrainSmem<W>;
-    [[maybe_unused]] long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ TrainBarriers bars;
@@ -104,7 +97,7 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
         ptx::mbar_init(&bars.all_done, 1);
         bars.abort_flag = 0;
         ptx::fence_barrier_init();
-        ptx::prefetch_tmap(&tm_x);
+        if (!enc.x) ptx::prefetch_tmap(&tm_x);
     }
     if (warp == 1) {
         ptx::tmem_alloc(&bars.tmem_base, (uint32_t)tmem_cols);
@@ -118,23 +111,37 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
-        if (lane == 0 && my_tiles > 0) {
-            ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
-            for (int l = 0; l < n_mat; ++l)
-                ptx::bulk_load(smem + S::WBUF(n_mat) + l * T::WGT_BYTES,
-                               reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
-                               &bars.w_full);
+        // input tiles by TMA (lane 0) or, with a folded identity encoding, written by the whole warp from fp32 coordinates
+        if (my_tiles > 0) {
+            if (lane == 0) {
+                ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
+                for (int l = 0; l < n_mat; ++l)
+                    ptx::bulk_load(smem + S::WBUF(n_mat) + l * T::WGT_BYTES,
+                                   reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
+                                   &bars.w_full);
+            }
+            if (enc.x) {
+                fill_tiles_with_ones<W>(smem + S::X, 2, lane);
+                __syncwarp();
+            }
             for (int t = 0; t < my_tiles; ++t) {
                 const int tile = blockIdx.x + t * gridDim.x;
                 const int b = t & 1;
-                if (t >= 2 && !ptx::mbar_wait(&bars.x_empty[b], ((t >> 1) - 1) & 1, abort_flag)) {
-                    atomicExch(status, KS_TIMEOUT_PRODUCER | 1);
+                if (t >= 2 && !__all_sync(0xffffffffu, lane != 0 || ptx::mbar_wait(&bars.x_empty[b], ((t >> 1) - 1) & 1, abort_flag))) {
+                    if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | 1);
                     break;
                 }
-                ptx::mbar_arrive_expect_tx(&bars.x_full[b], T::ACT_BYTES);
-                for (int at = 0; at < T::KATOMS; ++at)
-                    ptx::tma_load_2d(smem + S::X + b * T::ACT_BYTES + at * T::ACT_ATOM_BYTES, &tm_x, at * T::ATOM_COLS,
-                                     tile * T::TM, &bars.x_full[b]);
+                if (enc.x) {
+                    encode_identity_tile<W>(smem + S::X + b * T::ACT_BYTES, enc, (size_t)tile * T::TM, batch, lane);
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&bars.x_full[b]);
+                } else if (lane == 0) {
+                    ptx::mbar_arrive_expect_tx(&bars.x_full[b], T::ACT_BYTES);
+                    for (int at = 0; at < T::KATOMS; ++at)
+                        ptx::tma_load_2d(smem + S::X + b * T::ACT_BYTES + at * T::ACT_ATOM_BYTES, &tm_x, at * T::ATOM_COLS,
+                                         tile * T::TM, &bars.x_full[b]);
+                }
             }
         }
     } else if (warp == 1) {
@@ -155,13 +162,10 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                 ptx::mbar_arrive(&bars.chain_issued[ci_count & 1u]);
             };
             auto wait_step = [&]() {
-                const long long t0 = TNN_TIC();
                 const bool r = ptx::mbar_wait(&bars.step_ready, sr_parity, abort_flag);
                 sr_parity ^= 1u;
-                TNN_TOC(0, t0);
                 return r;
             };
-            const long long t_all = TNN_TIC();
             for (int t = 0; ok && t < my_tiles; ++t) {
                 const int b = t & 1;
                 // the previous tile's last hand-over (delta_0) also says the accumulator is drained
@@ -214,12 +218,6 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
             }
             if (ok && ptx::elect_one()) signal_chain_issued(); // releases the very last layer-0 weight-gradient GEMM
             __syncwarp();
-            TNN_TOC(1, t_all);
-            if constexpr (PROF) {
-                if (blockIdx.x == 0 && prof && lane == 0)
-                    printf("[train prof] chain issuer: tiles %d, waiting for the epilogue %lld, total %lld cycles\n",
-                           my_tiles, prof_acc[0], prof_acc[1]);
-            }
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------ weight-gradient issuer
@@ -281,23 +279,18 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
         float loss_local = 0.0f;
         bool ok = true;
 
-        const long long t_all = TNN_TIC();
         auto wait_acc = [&](int code) {
-            const long long t0 = TNN_TIC();
             const bool r = __all_sync(0xffffffffu, ptx::mbar_wait(&bars.acc_full, af_parity, abort_flag));
             af_parity ^= 1u;
-            TNN_TOC(2, t0);
             if (!r && lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | code);
             return r;
         };
         auto load_acc = [&](uint32_t (&v)[CPT]) {
-            const long long t0 = TNN_TIC();
             if constexpr (CPT == 16)
                 ptx::tmem_ld16(acc_addr, v);
             else
                 ptx::tmem_ld8(acc_addr, v);
             ptx::tmem_ld_wait();
-            TNN_TOC(3, t0);
         };
         // byte offset of this thread's 16-byte chunk `ch` (0 .. CPT/8-1) inside an activation tile
         auto chunk_at = [&](int ch) {
@@ -320,12 +313,10 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
         // every write to a delta buffer but its first waits for the weight-gradient GEMM that read it
         auto acquire_dbuf = [&](int p) {
             bool r = true;
-            const long long t0 = TNN_TIC();
             if (dfree_writes[p] > 0) {
                 r = __all_sync(0xffffffffu, ptx::mbar_wait(&bars.d_free[p], dfree_parity[p], abort_flag));
                 dfree_parity[p] ^= 1u;
             }
-            TNN_TOC(4, t0);
             ++dfree_writes[p];
             return r;
         };
@@ -343,9 +334,14 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                     tg[q4 * 4 + 0] = t4.x, tg[q4 * 4 + 1] = t4.y, tg[q4 * 4 + 2] = t4.z, tg[q4 * 4 + 3] = t4.w;
                 }
             } else {
+                // narrow targets: only the threads whose column slice holds targets load anything
 #pragma unroll
-                for (int q = 0; q < CPT; ++q)
-                    tg[q] = (row_valid && col0 + q < n_targets) ? __ldg(targets + grow * n_targets + col0 + q) : 0.0f;
+                for (int q = 0; q < CPT; ++q) tg[q] = 0.0f;
+                if (row_valid && col0 < n_targets) {
+#pragma unroll
+                    for (int q = 0; q < CPT; ++q)
+                        if (col0 + q < n_targets) tg[q] = __ldg(targets + grow * n_targets + col0 + q);
+                }
             }
             // ---------------- forward, hidden layers
             for (int l = 0; l < L && ok; ++l) {
@@ -357,15 +353,12 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                 uint32_t v[CPT];
                 load_acc(v);
                 // a_{l+1} of the previous tile must have been consumed by its weight-gradient GEMM
-                const long long t_af = TNN_TIC();
                 if (t > 0 &&
                     !__all_sync(0xffffffffu, ptx::mbar_wait(&bars.a_free[l + 1], (t - 1) & 1, abort_flag))) {
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | 2 | (l << 4));
                     ok = false;
                     break;
                 }
-                TNN_TOC(4, t_af);
-                const long long t_ps = TNN_TIC();
                 uint8_t *dst = smem + S::A(l + 1);
                 dispatch_act(act, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
@@ -379,7 +372,6 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                         *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) = o;
                     }
                 });
-                TNN_TOC(5, t_ps);
                 hand_over(false);
             }
             if (!ok) break;
@@ -397,7 +389,6 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                     ok = false;
                     break;
                 }
-                const long long t_loss = TNN_TIC();
                 uint8_t *dst = smem + S::D(n_mat, 0);
                 dispatch_act(out_act, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
@@ -422,7 +413,6 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                         *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) = make_uint4(o[0], o[1], o[2], o[3]);
                     }
                 });
-                TNN_TOC(6, t_loss);
                 hand_over(true);
             }
             // ---------------- backward: step l turns (delta_l W_l^T) into delta_{l-1} in D[(L - l + 1) & 1]
@@ -440,7 +430,6 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                     ok = false;
                     break;
                 }
-                const long long t_ps = TNN_TIC();
                 const uint8_t *abuf = smem + S::A(l);
                 uint8_t *dst = smem + S::D(n_mat, p);
                 dispatch_act(act, [&](auto tag) {
@@ -458,18 +447,10 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                         *reinterpret_cast<uint4 *>(dst + off) = o;
                     }
                 });
-                TNN_TOC(5, t_ps);
                 hand_over(true);
             }
         }
 
-        TNN_TOC(7, t_all);
-        if constexpr (PROF) {
-            if (blockIdx.x == 0 && prof && threadIdx.x == 128)
-                printf("[train prof] epilogue thread: wait acc %lld, tmem load %lld, wait d/a_free %lld, pack+store %lld, "
-                       "loss+targets %lld, total %lld cycles\n",
-                       prof_acc[2], prof_acc[3], prof_acc[4], prof_acc[5], prof_acc[6], prof_acc[7]);
-        }
         // ---------------- loss partial of this CTA (fixed summation order)
         for (int o = 16; o > 0; o >>= 1) loss_local += __shfl_xor_sync(0xffffffffu, loss_local, o);
         if (lane == 0) bars.loss_red[ew] = loss_local;
@@ -540,15 +521,13 @@ template <int W> static cudaError_t launch_train_w(TrainLaunch &p) {
     auto go = [&](auto kern) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
+        count_launch();
         kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, p.wimg, p.targets, p.n_targets, p.dw_partials,
                                                    p.loss_partials, p.batch, n_tiles, p.n_mat, p.act, p.out_act,
-                                                   p.loss_scale, inv_n, tmem_cols, p.status, p.prof);
+                                                   p.loss_scale, inv_n, tmem_cols, p.enc, p.status);
         return cudaGetLastError();
     };
-    if constexpr (W == 64) {
-        if (p.prof) return go(mlp_train_kernel<W, true>);
-    }
-    return go(mlp_train_kernel<W, false>);
+    return go(mlp_train_kernel<W>);
 }
 
 cudaError_t launch_mlp_train(TrainLaunch &p) {

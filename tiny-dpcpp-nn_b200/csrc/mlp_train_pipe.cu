@@ -20,9 +20,8 @@
 //   warps 4-11  forward-stage epilogue, two threads per row: activation, bf16, next A operand; L2 loss
 //   warps 12-19 backward-stage epilogue, two threads per row: activation backward, next delta tile
 #include "mlp_common.cuh"
+#include "elementwise.h"
 #include "mlp_launch.h"
-
-#include <cstdio>
 
 namespace tnn {
 
@@ -66,45 +65,22 @@ struct PipeBarriers {
     float loss_red[8];
 };
 
-// Cycle accounting for tuning (PROF instantiations only): CTA 0 prints how many cycles one thread of every
-// role spent in each region.
-// (region sums and event stamps disturb each other: TNN_PROF_ACC selects which of the two a PROF build records)
-#ifndef TNN_PROF_ACC
-#define TNN_PROF_ACC 0
-#endif
-#define TNN_TIC() ([&]() { if constexpr (PROF && TNN_PROF_ACC) return (long long)clock64(); else return 0ll; }())
-#define TNN_TOC(slot, t0) do { if constexpr (PROF && TNN_PROF_ACC) prof_acc[slot] += (long long)clock64() - (t0); } while (0)
-// Time stamp of one event of the tile kProfTile of CTA 0 (all roles share the SM's clock).
-constexpr int kProfTile = 10;
-// PROF only: the issuer waits for the completion of the GEMM it just issued and stamps it.
-#define TNN_DONE(t, which, cnt, id) do { if constexpr (PROF && TNN_PROF_ACC) { if (blockIdx.x == 0) { ptx::mma_commit(&prof_bar[which]); \
-    ptx::mbar_wait_busy(&prof_bar[which], (cnt) & 1u, abort_flag); ++(cnt); TNN_EV(t, id); } } } while (0)
-#define TNN_EV(t, id) do { if constexpr (PROF) { if ((t) == kProfTile && blockIdx.x == 0) prof_ev[id] = (long long)clock64(); } } while (0)
-
 // (The chain GEMMs read both operands from shared memory.  Feeding their A operand from tensor memory, as the
 // inference kernel does, was measured slower here: the activations must be in shared memory anyway for the
 // weight-gradient GEMMs and the activation backward, and the extra tcgen05.st in every epilogue step costs more
 // than the shorter GEMMs save.)
-template <int W, bool TGT, bool PROF = false>
+template <int W, bool TGT>
 __global__ void __launch_bounds__(PipeSmem<W, TGT>::THREADS, 1)
 mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_tgt,
                       const __nv_bfloat16 *__restrict__ wimg,
                       const float *__restrict__ targets, int n_targets, float *__restrict__ dw_slabs,
                       float *__restrict__ loss_partials, size_t batch, int n_tiles, int n_mat, int act, int out_act,
-                      float loss_scale, float inv_n, int *status) {
+                      float loss_scale, float inv_n, const EncodedInput enc, int narrow_targets, int *status) {
     using T = Tile<W>;
     using S = PipeSmem<W, TGT>;
-    [[maybe_unused]] long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    [[maybe_unused]] const long long prof_t_all = TNN_TIC();
-    [[maybe_unused]] uint32_t prof_cnt = 0;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ PipeBarriers bars;
-    __shared__ long long prof_ev[PROF ? 96 : 1];
-    __shared__ uint64_t prof_bar[3];
-    if constexpr (PROF) {
-        if (threadIdx.x < 96) prof_ev[threadIdx.x] = 0;
-    }
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -139,12 +115,9 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
         ptx::mbar_init(&bars.all_done, 1);
         ptx::mbar_init(&bars.tgt_full, 1);
         ptx::mbar_init(&bars.tgt_read, S::GROUP_WARPS);
-        if constexpr (PROF) {
-            for (int i = 0; i < 3; ++i) ptx::mbar_init(&prof_bar[i], 1);
-        }
         bars.abort_flag = 0;
         ptx::fence_barrier_init();
-        ptx::prefetch_tmap(&tm_x);
+        if (!enc.x) ptx::prefetch_tmap(&tm_x);
         if constexpr (TGT) ptx::prefetch_tmap(&tm_tgt);
     }
     if (warp == 1) {
@@ -160,33 +133,60 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
-        if (lane == 0 && my_tiles > 0) {
-            ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
-            for (int l = 0; l < n_mat; ++l)
-                ptx::bulk_load(smem + S::WBUF(n_mat) + l * T::WGT_BYTES,
-                               reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
-                               &bars.w_full);
+        // Input tiles arrive by TMA (lane 0), or - with a folded identity encoding - are written by the whole warp
+        // from the fp32 coordinates.  Targets are staged by lane 0: full-width rows as swizzled TMA boxes, narrower
+        // rows (n_targets < W: 128 * n_targets contiguous floats per tile) by one plain bulk copy.
+        if (my_tiles > 0) {
+            if (lane == 0) {
+                ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
+                for (int l = 0; l < n_mat; ++l)
+                    ptx::bulk_load(smem + S::WBUF(n_mat) + l * T::WGT_BYTES,
+                                   reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
+                                   &bars.w_full);
+            }
+            if (enc.x) {
+                fill_tiles_with_ones<W>(smem + S::X(0), 2, lane);
+                __syncwarp();
+            }
             for (int t = 0; t < my_tiles; ++t) {
                 const int tile = blockIdx.x + t * gridDim.x;
                 const int b = t & 1;
-                if (t >= 2 && !ptx::mbar_wait(&bars.x_empty[b], ((t >> 1) - 1) & 1, abort_flag)) {
-                    atomicExch(status, KS_TIMEOUT_PRODUCER | 1);
+                // (lane 0 polls; the vote hands its verdict - and the ordering it implies - to the other lanes)
+                if (t >= 2 && !__all_sync(0xffffffffu, lane != 0 || ptx::mbar_wait(&bars.x_empty[b], ((t >> 1) - 1) & 1, abort_flag))) {
+                    if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | 1);
                     break;
                 }
-                ptx::mbar_arrive_expect_tx(&bars.x_full[b], T::ACT_BYTES);
-                for (int at = 0; at < T::KATOMS; ++at)
-                    ptx::tma_load_2d(smem + S::X(b) + at * T::ACT_ATOM_BYTES, &tm_x, at * T::ATOM_COLS, tile * T::TM,
-                                     &bars.x_full[b]);
+                if (enc.x) {
+                    encode_identity_tile<W>(smem + S::X(b), enc, (size_t)tile * T::TM, batch, lane);
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&bars.x_full[b]);
+                } else if (lane == 0) {
+                    ptx::mbar_arrive_expect_tx(&bars.x_full[b], T::ACT_BYTES);
+                    for (int at = 0; at < T::KATOMS; ++at)
+                        ptx::tma_load_2d(smem + S::X(b) + at * T::ACT_ATOM_BYTES, &tm_x, at * T::ATOM_COLS, tile * T::TM,
+                                         &bars.x_full[b]);
+                }
                 if constexpr (TGT) {
                     // the staging area overlaps delta_L: both GEMMs that read delta_L of the previous tile are complete
-                    if (t > 0 && !ptx::mbar_wait(&bars.dl_free, (t - 1) & 1, abort_flag)) {
-                        atomicExch(status, KS_TIMEOUT_PRODUCER | 2);
+                    if (t > 0 && !__all_sync(0xffffffffu, lane != 0 || ptx::mbar_wait(&bars.dl_free, (t - 1) & 1, abort_flag))) {
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | 2);
                         break;
                     }
-                    ptx::mbar_arrive_expect_tx(&bars.tgt_full, (uint32_t)(S::TGT_BOXES * S::TGT_BOX_BYTES));
-                    for (int bx = 0; bx < S::TGT_BOXES; ++bx)
-                        ptx::tma_load_2d(smem + S::DL + bx * S::TGT_BOX_BYTES, &tm_tgt, bx * 32, tile * T::TM,
-                                         &bars.tgt_full);
+                    if (lane == 0) {
+                        if (narrow_targets) {
+                            const size_t row0 = (size_t)tile * T::TM;
+                            const uint32_t rows = (uint32_t)(batch - row0 < (size_t)T::TM ? batch - row0 : (size_t)T::TM);
+                            const uint32_t bytes = rows * (uint32_t)n_targets * 4u; // rows % 8 == 0: a multiple of 16
+                            ptx::mbar_arrive_expect_tx(&bars.tgt_full, bytes);
+                            ptx::bulk_load(smem + S::DL, targets + row0 * n_targets, bytes, &bars.tgt_full);
+                        } else {
+                            ptx::mbar_arrive_expect_tx(&bars.tgt_full, (uint32_t)(S::TGT_BOXES * S::TGT_BOX_BYTES));
+                            for (int bx = 0; bx < S::TGT_BOXES; ++bx)
+                                ptx::tma_load_2d(smem + S::DL + bx * S::TGT_BOX_BYTES, &tm_tgt, bx * 32, tile * T::TM,
+                                                 &bars.tgt_full);
+                        }
+                    }
                 }
             }
         }
@@ -202,12 +202,10 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
             uint32_t fr_parity = 0;
             for (int t = 0; ok && t < my_tiles; ++t) {
                 const int b = t & 1;
-                const long long t_w0 = TNN_TIC();
                 if (t > 0) { // the loss step of the previous tile has drained the accumulator
                     ok = ptx::mbar_wait(&bars.f_ready, fr_parity, abort_flag);
                     fr_parity ^= 1u;
                 }
-                TNN_TOC(0, t_w0);
                 if (ok) ok = ptx::mbar_wait(&bars.x_full[b], (t >> 1) & 1, abort_flag);
                 if (!ok) {
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 1);
@@ -215,39 +213,26 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 }
                 ptx::tc_fence_after_sync();
                 if (ptx::elect_one()) {
-                    TNN_EV(t, 40);
                     T::template issue_chain<true>(accf_tmem, x_desc0 + (uint64_t)(b * T::ACT_UNITS), w_desc0, idesc);
                     ptx::mma_commit(&bars.accf_full);
                     ptx::mma_commit(&bars.x_empty[b]);
-                    TNN_EV(t, 45);
-                    TNN_DONE(t, 0, prof_cnt, 80);
                 }
                 __syncwarp();
                 for (int l = 1; l <= L; ++l) {
-                    const long long t_w = TNN_TIC();
                     if (!ptx::mbar_wait(&bars.f_ready, fr_parity, abort_flag)) {
                         if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 2 | (l << 4));
                         ok = false;
                         break;
                     }
-                    TNN_TOC(0, t_w);
                     fr_parity ^= 1u;
                     ptx::tc_fence_after_sync();
                     if (ptx::elect_one()) {
-                        TNN_EV(t, 40 + l);
                         T::template issue_chain<true>(accf_tmem, ab_desc0 + (uint64_t)(ab_index(t, l) * T::ACT_UNITS),
                                                       w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
                         ptx::mma_commit(&bars.accf_full);
-                        TNN_EV(t, 45 + l);
-                        TNN_DONE(t, 0, prof_cnt, 80 + l);
                     }
                     __syncwarp();
                 }
-            }
-            if constexpr (PROF) {
-                if (blockIdx.x == 0 && lane == 0)
-                    printf("[pipe prof] fwd issuer: tiles %d, waiting %lld of %lld cycles\n", my_tiles, prof_acc[0],
-                           (long long)clock64() - prof_t_all);
             }
         }
     } else if (warp == 2) {
@@ -281,13 +266,10 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     ptx::tc_fence_after_sync();
                     const uint64_t d_desc = (l == L) ? dl_desc : dp_desc0 + (uint64_t)(((L - 1 - l) & 1) * T::ACT_UNITS);
                     if (ptx::elect_one()) {
-                        TNN_EV(t, 50 + L - l);
                         T::template issue_chain<false>(accb_tmem, d_desc, w_desc0 + (uint64_t)(l * T::WGT_UNITS), idesc);
                         ptx::mma_commit(&bars.accb_full);
                         if (l == L) ptx::mma_commit(&bars.dl_free);
                         ptx::mbar_arrive(&bars.chain_issued[ci_count & 1u]); // the weight-gradient GEMM of layer l may follow
-                        TNN_EV(t, 55 + L - l);
-                        TNN_DONE(t, 1, prof_cnt, 85 + L - l);
                     }
                     __syncwarp();
                     ++ci_count;
@@ -330,7 +312,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     const uint64_t a_desc = (l >= 1) ? ab_desc0 + (uint64_t)(ai * T::ACT_UNITS)
                                                      : x_desc0 + (uint64_t)(b * T::ACT_UNITS);
                     if (ptx::elect_one()) {
-                        TNN_EV(t, 60 + L - l);
                         T::issue_outer(tmem_base + (uint32_t)(2 * W + l * W), d_desc, a_desc, idesc, t > 0 ? 1u : 0u);
                         if (l == L)
                             ptx::mma_commit(&bars.dl_free);
@@ -340,8 +321,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                             ptx::mma_commit(&bars.ab_free[ai]);
                         else
                             ptx::mma_commit(&bars.x_empty[b]);
-                        TNN_EV(t, 66 + L - l);
-                        TNN_DONE(t, 2, prof_cnt, 90 + L - l);
                     }
                     __syncwarp();
                 }
@@ -389,27 +368,18 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 // then hides under the GEMM this step waits for anyway.
                 const int bi = ab_index(t, l + 1);
                 const int uses = ab_prior_uses(t, bi);
-                const long long t_f = TNN_TIC();
                 if (uses > 0 && !wait_u(&bars.ab_free[bi], (uses - 1) & 1, 2 | (l << 4))) {
                     ok = false;
                     break;
                 }
-                TNN_TOC(3, t_f);
-                if (threadIdx.x == 128) TNN_EV(t, l * 4 + 1);
-                const long long t_a = TNN_TIC();
                 if (!wait_u(&bars.accf_full, af_parity, 1 | (l << 4))) {
                     ok = false;
                     break;
                 }
-                TNN_TOC(1, t_a);
-                if (threadIdx.x == 128) TNN_EV(t, l * 4);
                 af_parity ^= 1u;
                 ptx::tc_fence_after_sync();
                 uint32_t v[CPT];
-                const long long t_l = TNN_TIC();
                 load_acc(v);
-                TNN_TOC(2, t_l);
-                const long long t_p = TNN_TIC();
                 uint8_t *dst = smem + S::AB(bi);
                 dispatch_act(act, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
@@ -422,17 +392,12 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                         *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) =
                             make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
                 });
-                TNN_TOC(4, t_p);
-                const long long t_h = TNN_TIC();
                 ptx::fence_proxy_async_smem();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&bars.f_ready);
-                TNN_TOC(5, t_h);
-                if (threadIdx.x == 128) TNN_EV(t, l * 4 + 2);
             }
             if (!ok) break;
-            const long long t_loss = TNN_TIC();
             // ---- output layer + L2 loss.  The target slice is requested before the wait for the last GEMM.
             float tg[CPT];
             if constexpr (TGT) {
@@ -440,12 +405,24 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     ok = false;
                     break;
                 }
-                const uint8_t *src = smem + S::DL + (col0 / 32) * S::TGT_BOX_BYTES + row * 128;
+                if (narrow_targets) {
+                    // row-major rows of n_targets floats; columns past them (and rows past the batch) compare with 0
+                    const float *src = reinterpret_cast<const float *>(smem + S::DL) + row * n_targets;
 #pragma unroll
-                for (int q4 = 0; q4 < CPT / 4; ++q4) {
-                    const int chunk = (col0 % 32) / 4 + q4;
-                    const float4 t4 = *reinterpret_cast<const float4 *>(src + ((chunk ^ (row & 7)) << 4));
-                    tg[q4 * 4 + 0] = t4.x, tg[q4 * 4 + 1] = t4.y, tg[q4 * 4 + 2] = t4.z, tg[q4 * 4 + 3] = t4.w;
+                    for (int q = 0; q < CPT; ++q) tg[q] = 0.0f;
+                    if (col0 < n_targets && row_valid) {
+#pragma unroll
+                        for (int q = 0; q < CPT; ++q)
+                            if (col0 + q < n_targets) tg[q] = src[col0 + q];
+                    }
+                } else {
+                    const uint8_t *src = smem + S::DL + (col0 / 32) * S::TGT_BOX_BYTES + row * 128;
+#pragma unroll
+                    for (int q4 = 0; q4 < CPT / 4; ++q4) {
+                        const int chunk = (col0 % 32) / 4 + q4;
+                        const float4 t4 = *reinterpret_cast<const float4 *>(src + ((chunk ^ (row & 7)) << 4));
+                        tg[q4 * 4 + 0] = t4.x, tg[q4 * 4 + 1] = t4.y, tg[q4 * 4 + 2] = t4.z, tg[q4 * 4 + 3] = t4.w;
+                    }
                 }
                 // every thread of the stage holds its targets before the first one overwrites the area with delta_L
                 __syncwarp();
@@ -470,7 +447,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 break;
             }
             af_parity ^= 1u;
-            if (threadIdx.x == 128) TNN_EV(t, 16);
             ptx::tc_fence_after_sync();
             uint32_t v[CPT];
             load_acc(v);
@@ -484,7 +460,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     break;
                 }
             }
-            if (threadIdx.x == 128) TNN_EV(t, 17);
             uint8_t *dst = smem + S::DL;
             // rows past the end of the batch contribute neither loss nor gradient
             const float gscale = row_valid ? loss_scale * 2.0f * inv_n : 0.0f;
@@ -519,15 +494,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 ptx::mbar_arrive(&bars.dl_ready); // backward chain may start
                 ptx::mbar_arrive(&bars.dwgo_f);   // weight gradient of the output layer may start
             }
-            TNN_TOC(6, t_loss);
-            if (threadIdx.x == 128) TNN_EV(t, 18);
-        }
-        if constexpr (PROF) {
-            if (blockIdx.x == 0 && threadIdx.x == 128)
-                printf("[pipe prof] fwd epilogue: wait acc %lld, tmem ld %lld, wait buffer %lld, pack+store %lld, "
-                       "hand-over %lld, loss step (incl. its wait) %lld, total %lld cycles\n",
-                       prof_acc[1], prof_acc[2], prof_acc[3], prof_acc[4], prof_acc[5], prof_acc[6],
-                       (long long)clock64() - prof_t_all);
         }
         // loss partial of this CTA (fixed summation order)
         for (int o = 16; o > 0; o >>= 1) loss_local += __shfl_xor_sync(0xffffffffu, loss_local, o);
@@ -571,7 +537,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 // this step completes: wait for the former and fetch the latter first, so that both
                 // shared-memory round trips hide under the GEMM (see the forward stage).
                 const int p = (L - l) & 1; // delta_{l-1} goes to ping-pong buffer (L - l) & 1
-                const long long t_f = TNN_TIC();
                 if ((dp_written >> p) & 1u) { // all but the first write wait for the GEMM that read the buffer
                     if (!wait_u(&bars.dp_free[p], (dp_parity >> p) & 1u, 6 | (l << 4))) {
                         ok = false;
@@ -580,8 +545,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     dp_parity ^= 1u << p;
                 }
                 dp_written |= 1u << p;
-                TNN_TOC(3, t_f);
-                if (gw == 0 && lane == 0) TNN_EV(t, 20 + (L - l) * 4 + 1);
                 const int ai = ab_index(t, l);
                 const uint8_t *abuf = smem + S::AB(ai);
                 uint8_t *dst = smem + S::DP(p);
@@ -589,17 +552,13 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
 #pragma unroll
                 for (int ch = 0; ch < CPT / 8; ++ch)
                     fa[ch] = (act != ACT_NONE) ? *reinterpret_cast<const uint4 *>(abuf + chunk_at(ch)) : make_uint4(0, 0, 0, 0);
-                const long long t_a = TNN_TIC();
                 if (!wait_u(&bars.accb_full, ab_parity, 5 | (l << 4))) {
                     ok = false;
                     break;
                 }
-                TNN_TOC(1, t_a);
-                if (gw == 0 && lane == 0) TNN_EV(t, 20 + (L - l) * 4);
                 ab_parity ^= 1u;
                 ptx::tc_fence_after_sync();
                 uint32_t v[CPT];
-                const long long t_l = TNN_TIC();
                 if constexpr (CPT == 32)
                     ptx::tmem_ld32(acc_addr, v);
                 else if constexpr (CPT == 16)
@@ -607,8 +566,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 else
                     ptx::tmem_ld8(acc_addr, v);
                 ptx::tmem_ld_wait();
-                TNN_TOC(2, t_l);
-                const long long t_p = TNN_TIC();
                 dispatch_act(act, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
                     uint32_t pk[CPT / 2];
@@ -625,7 +582,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                         *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) =
                             make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
                 });
-                TNN_TOC(4, t_p);
                 ptx::fence_proxy_async_smem();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
@@ -634,14 +590,8 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     ptx::mbar_arrive(&bars.dwgo_b[go_count & 1u]);
                     ptx::mbar_arrive(&bars.ab_free[ai]); // this stage is done with a_l
                 }
-                if (gw == 0 && lane == 0) TNN_EV(t, 20 + (L - l) * 4 + 2);
                 ++go_count;
             }
-        }
-        if constexpr (PROF) {
-            if (blockIdx.x == 0 && threadIdx.x == 128 + S::GROUP_THREADS)
-                printf("[pipe prof] bwd epilogue: wait acc %lld, tmem ld %lld, wait delta buffer %lld, mask+pack+store %lld, total %lld "
-                       "cycles\n", prof_acc[1], prof_acc[2], prof_acc[3], prof_acc[4], (long long)clock64() - prof_t_all);
         }
         // ---- drain the weight-gradient accumulators into this CTA's slab
         if (ok && my_tiles > 0 && !wait_u(&bars.all_done, 0, 7)) ok = false;
@@ -676,15 +626,6 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if constexpr (PROF) {
-        if (blockIdx.x == 0 && threadIdx.x == 0) {
-            long long t0 = 0;
-            for (int i = 0; i < 96; ++i)
-                if (prof_ev[i] && (!t0 || prof_ev[i] < t0)) t0 = prof_ev[i];
-            for (int i = 0; i < 96; ++i)
-                if (prof_ev[i]) printf("[pipe ev] %d %lld\n", i, prof_ev[i] - t0);
-        }
-    }
     if (warp == 1) {
         __syncwarp();
         ptx::tc_fence_after_sync();
@@ -702,11 +643,7 @@ template <int W, bool TGT> static cudaError_t launch_pipe_w(TrainLaunch &p) {
     const size_t smem = (size_t)S::WBUF(p.n_mat) + (size_t)p.n_mat * T::WGT_BYTES + 1024;
     const int cols_needed = 2 * W + p.n_mat * W;
     if (smem > kPipeSmemLimit || cols_needed > 512 || p.n_mat > kPipeMaxMat) return cudaErrorInvalidConfiguration;
-    void (*kern)(const CUtensorMap, const CUtensorMap, const __nv_bfloat16 *, const float *, int, float *, float *, size_t,
-                 int, int, int, int, float, float, int *) = mlp_train_pipe_kernel<W, TGT, false>;
-    if constexpr (W == 64 && TGT) {
-        if (p.prof) kern = mlp_train_pipe_kernel<W, TGT, true>;
-    }
+    auto kern = mlp_train_pipe_kernel<W, TGT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
@@ -714,19 +651,21 @@ template <int W, bool TGT> static cudaError_t launch_pipe_w(TrainLaunch &p) {
     p.grid_out = grid;
     if (grid == 0) return cudaSuccess;
     const float inv_n = 1.0f / ((float)p.batch * (float)W);
+    count_launch();
     kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, TGT ? p.tm_tgt : p.tm_x, p.wimg, p.targets, p.n_targets, p.dw_partials, p.loss_partials,
                                                p.batch, n_tiles, p.n_mat, p.act, p.out_act, p.loss_scale, inv_n,
-                                               p.status);
+                                               p.enc, TGT && p.tgt_mode == 2 ? 1 : 0, p.status);
     return cudaGetLastError();
 }
 
 cudaError_t launch_mlp_train_pipe(TrainLaunch &p) {
-    // staged targets need one more tile of shared memory: without room for it the per-thread loads remain
+    // staged targets (tgt_mode 1: TMA boxes, 2: one bulk copy of narrow rows) need one more tile of shared memory:
+    // without room for it the per-thread loads remain
     cudaError_t e = cudaErrorInvalidConfiguration;
     if (p.width == 16) return launch_pipe_w<16, false>(p); // 64-byte target rows: read directly
     if (p.width != 64 && p.width != 32) return e;
     const bool w64 = p.width == 64;
-    if (p.tgt_tma) e = w64 ? launch_pipe_w<64, true>(p) : launch_pipe_w<32, true>(p);
+    if (p.tgt_mode) e = w64 ? launch_pipe_w<64, true>(p) : launch_pipe_w<32, true>(p);
     if (e == cudaErrorInvalidConfiguration) e = w64 ? launch_pipe_w<64, false>(p) : launch_pipe_w<32, false>(p);
     return e;
 }

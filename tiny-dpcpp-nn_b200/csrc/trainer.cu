@@ -1,0 +1,459 @@
+// Trainer and data parallelism behind the C ABI.
+//
+// The reference's Trainer<T>::training_step (include/trainer.h:23-46) runs forward_pass and backward_pass; its
+// training loops add torch's loss and torch.optim.Adam around the module, with one host round trip per piece.
+// Here the whole loop body is device work enqueued by ONE call:
+//
+//   single GPU     fused forward + L2 + backward kernel -> ONE kernel that sums the per-CTA weight-gradient slabs
+//                  and loss partials, applies Adam to the fp32 master parameters and rewrites the bf16 operand
+//                  images the kernels read
+//   data parallel  fused kernel -> slab / loss reduction -> ncclAllReduce(sum) of the (L+1) W^2 fp32 gradient
+//                  buffer -> Adam + operand refresh
+//
+// The reference has no data-parallel training (its MPI benchmarks run independent replicas,
+// benchmarks/common_benchmarks.h:53-54); the exchange is what a data-parallel use of its modules needs: one
+// all-reduce of the small weight-gradient buffer per step.  A trainable encoding (hash grid) shards its optimiser:
+// reduce-scatter of the table gradient, Adam on this rank's slice of the table, all-gather of the table.
+//
+// NCCL is reached through dlopen, so the library itself links neither NCCL nor MPI: a process that already loaded
+// NCCL (PyTorch does) shares that copy.
+#include "../../include/tnn_b200.h"
+
+#include "elementwise.h"
+#include "handles.h"
+#include "mlp_common.cuh"
+
+#include <cmath>
+#include <cstring>
+#include <dlfcn.h>
+#include <mutex>
+#include <string>
+
+// ------------------------------------------------------------------------------------ NCCL by dlopen
+namespace {
+
+// The few NCCL entry points used, with the types of nccl.h (ncclComm_t is an opaque pointer, ncclUniqueId a
+// 128-byte struct passed by value, enums are ints: ncclFloat32 = 7, ncclSum = 0).
+struct NcclUniqueId { char internal[128]; };
+struct NcclApi {
+    int (*GetUniqueId)(NcclUniqueId *) = nullptr;
+    int (*CommInitRank)(void **, int, NcclUniqueId, int) = nullptr;
+    int (*CommDestroy)(void *) = nullptr;
+    int (*CommCount)(void *, int *) = nullptr;
+    int (*CommUserRank)(void *, int *) = nullptr;
+    int (*AllReduce)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
+    int (*ReduceScatter)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
+    int (*AllGather)(const void *, void *, size_t, int, void *, cudaStream_t) = nullptr;
+    const char *(*GetErrorString)(int) = nullptr;
+    bool ok = false;
+    std::string why;
+};
+constexpr int kNcclFloat32 = 7, kNcclSum = 0;
+
+NcclApi &nccl() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD); // the copy the process already uses, if any
+        if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) {
+            api.why = "libnccl.so.2 could not be loaded";
+            return;
+        }
+        auto sym = [&](const char *name) { return dlsym(h, name); };
+        api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
+        api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+        api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
+        api.CommCount = reinterpret_cast<decltype(api.CommCount)>(sym("ncclCommCount"));
+        api.CommUserRank = reinterpret_cast<decltype(api.CommUserRank)>(sym("ncclCommUserRank"));
+        api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(sym("ncclAllReduce"));
+        api.ReduceScatter = reinterpret_cast<decltype(api.ReduceScatter)>(sym("ncclReduceScatter"));
+        api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
+        api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
+        api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.CommCount && api.CommUserRank &&
+                 api.AllReduce && api.ReduceScatter && api.AllGather && api.GetErrorString;
+        if (!api.ok) api.why = "libnccl.so.2 lacks an expected symbol";
+    });
+    return api;
+}
+
+int nccl_fail(const char *what, int rc) {
+    return tnn::api_fail(std::string(what) + ": " + (nccl().GetErrorString ? nccl().GetErrorString(rc) : "NCCL error"), 3);
+}
+
+#define TNN_CUDA(expr)                                                                                                 \
+    do {                                                                                                               \
+        cudaError_t e_ = (expr);                                                                                       \
+        if (e_ != cudaSuccess) return tnn::api_fail(std::string(#expr) + ": " + cudaGetErrorString(e_), 2);            \
+    } while (0)
+
+} // namespace
+
+struct tnn_dp_comm {
+    void *comm = nullptr; // ncclComm_t
+    int rank = 0, world = 1;
+    bool owned = false;
+};
+
+// ------------------------------------------------------------------------------------ kernels
+namespace tnn {
+
+__host__ __device__ inline int packed_coord_(int i, int j, int cols) {
+    return (i & 1) == 0 ? i * cols + 2 * j : (i - 1) * cols + 2 * j + 1;
+}
+
+// Adam (torch.optim.Adam arithmetic, see adam_kernel) on the fp32 master parameters of a network, followed by the
+// refresh of everything the kernels read: packed bf16 weights and both swizzled operand images, with the padding
+// rows / columns forced to zero (Network.h:171-233).  One thread per weight.
+// FROM_SLABS: the gradient is summed here from the per-CTA slabs of the training kernel (fixed order), and block 0
+// also sums the loss partials; otherwise it is read from `grads` (already reduced, e.g. across ranks).
+template <int W, bool FROM_SLABS>
+__global__ void __launch_bounds__(128)
+adam_refresh_kernel(float *__restrict__ master, float *__restrict__ m, float *__restrict__ v, float *__restrict__ grads,
+                    const float *__restrict__ slabs, int n_slabs, const float *__restrict__ loss_partials, int n_loss,
+                    float *__restrict__ loss_out, int n_mat, int one_padded_in, int unpadded_out, float grad_scale,
+                    float lr, float b1, float b2, float eps, float bc1, float bc2_sqrt,
+                    __nv_bfloat16 *__restrict__ packed_out, __nv_bfloat16 *__restrict__ wimg,
+                    __nv_bfloat16 *__restrict__ wimg_t) {
+    using T = Tile<W>;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x; // slab order: (matrix, output feature, input feature)
+    const int per = n_mat * W * W;
+    if (FROM_SLABS && blockIdx.x == 0 && loss_out) {
+        __shared__ float red[128];
+        float local = 0.0f;
+        for (int i = threadIdx.x; i < n_loss; i += 128) local += loss_partials[i];
+        red[threadIdx.x] = local;
+        __syncthreads();
+        for (int s = 64; s > 0; s >>= 1) {
+            if ((int)threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) *loss_out = red[0];
+    }
+    if (idx >= per) return;
+    const int l = idx / (W * W);
+    const int o = (idx / W) % W; // output feature
+    const int i = idx % W;       // input feature
+    const int pk = l * W * W + packed_coord_(i, o, W);
+    float g;
+    if constexpr (FROM_SLABS) {
+        g = 0.0f;
+        for (int s = 0; s < n_slabs; ++s) g += slabs[(size_t)s * per + idx];
+        grads[pk] = g;
+    } else {
+        g = grads[pk];
+    }
+    g *= grad_scale;
+    const float mi = b1 * m[pk] + (1.0f - b1) * g;
+    const float vi = b2 * v[pk] + (1.0f - b2) * g * g;
+    m[pk] = mi;
+    v[pk] = vi;
+    const float denom = sqrtf(vi) / bc2_sqrt + eps;
+    float p = master[pk] - (lr / bc1) * (mi / denom);
+    master[pk] = p;
+    if (l == 0 && i >= one_padded_in) p = 0.0f;
+    if (l == n_mat - 1 && o >= unpadded_out) p = 0.0f;
+    const __nv_bfloat16 b = __float2bfloat16_rn(p);
+    packed_out[pk] = b;
+    uint8_t *wi = reinterpret_cast<uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES;
+    uint8_t *wt = reinterpret_cast<uint8_t *>(wimg_t) + (size_t)l * T::WGT_BYTES;
+    *reinterpret_cast<__nv_bfloat16 *>(wi + T::elem_off(i, o, T::WGT_ATOM_BYTES)) = b;
+    *reinterpret_cast<__nv_bfloat16 *>(wt + T::elem_off(o, i, T::WGT_ATOM_BYTES)) = b;
+}
+
+template <bool FROM_SLABS>
+static cudaError_t launch_adam_refresh(int width, float *master, float *m, float *v, float *grads, const float *slabs,
+                                       int n_slabs, const float *loss_partials, int n_loss, float *loss_out, int n_mat,
+                                       int one_padded_in, int unpadded_out, float grad_scale, int step, float lr, float b1,
+                                       float b2, float eps, __nv_bfloat16 *packed, __nv_bfloat16 *wimg,
+                                       __nv_bfloat16 *wimg_t, cudaStream_t s) {
+    const int n = n_mat * width * width;
+    const int blocks = (n + 127) / 128;
+    const float bc1 = 1.0f - powf(b1, (float)step);
+    const float bc2_sqrt = sqrtf(1.0f - powf(b2, (float)step));
+    count_launch();
+#define TNN_CASE(WW)                                                                                                    \
+    case WW:                                                                                                            \
+        adam_refresh_kernel<WW, FROM_SLABS><<<blocks, 128, 0, s>>>(master, m, v, grads, slabs, n_slabs, loss_partials,  \
+                                                                   n_loss, loss_out, n_mat, one_padded_in, unpadded_out, \
+                                                                   grad_scale, lr, b1, b2, eps, bc1, bc2_sqrt, packed,  \
+                                                                   wimg, wimg_t);                                       \
+        break;
+    switch (width) {
+        TNN_CASE(16) TNN_CASE(32) TNN_CASE(64) TNN_CASE(128)
+    default: return cudaErrorInvalidValue;
+    }
+#undef TNN_CASE
+    return cudaGetLastError();
+}
+
+} // namespace tnn
+
+// entry points of capi.cu that hand the raw per-CTA results to the trainer instead of reducing them
+namespace tnn {
+int train_step_raw(tnn_network *n, tnn_encoding *e, const void *x, const float *targets, int n_targets, size_t batch,
+                   float loss_scale, float *encoding_grads, int deterministic, int *n_slabs, int *n_loss_partials,
+                   void *stream);
+}
+
+// ------------------------------------------------------------------------------------ trainer
+struct tnn_trainer {
+    tnn_network *net = nullptr;
+    tnn_encoding *enc = nullptr;
+    float lr = 1e-3f, b1 = 0.9f, b2 = 0.99f, eps = 1e-15f, loss_scale = 1.0f;
+    int step = 0;
+    float *master = nullptr, *m = nullptr, *v = nullptr, *grads = nullptr; // network: n_params fp32 each (one block)
+    float *loss = nullptr;                                                  // one fp32: loss sum of the last step
+    // trainable encoding: gradient of the whole table; moments for this rank's slice of it
+    float *enc_grads = nullptr, *enc_m = nullptr, *enc_v = nullptr;
+    size_t enc_shard = 0;      // table elements whose moments this rank keeps
+    bool enc_sharded = false;  // reduce-scatter / sharded Adam / all-gather instead of all-reduce + replicated Adam
+    int deterministic_encoding = 0;
+    tnn_dp_comm *dp = nullptr;
+    int n_slabs = 0, n_loss = 0; // what the last forward_backward left in the network's slab buffers
+    bool reduced = false;        // grads / loss already hold the reduced values of the last forward_backward
+};
+
+namespace {
+
+int world_of(const tnn_trainer *t) { return t->dp ? t->dp->world : 1; }
+int rank_of(const tnn_trainer *t) { return t->dp ? t->dp->rank : 0; }
+
+int alloc_encoding_state(tnn_trainer *t) {
+    cudaFree(t->enc_grads);
+    cudaFree(t->enc_m);
+    cudaFree(t->enc_v);
+    t->enc_grads = t->enc_m = t->enc_v = nullptr;
+    if (!t->enc || !t->enc->n_params) return 0;
+    const size_t n = t->enc->n_params;
+    const size_t world = (size_t)world_of(t);
+    // the optimiser state is sharded when the table splits into equal 16-byte aligned slices; otherwise every rank
+    // keeps the whole state and the gradient is all-reduced
+    t->enc_sharded = world > 1 && n % (4 * world) == 0;
+    t->enc_shard = t->enc_sharded ? n / world : n;
+    TNN_CUDA(cudaMalloc(&t->enc_grads, n * sizeof(float)));
+    TNN_CUDA(cudaMemset(t->enc_grads, 0, n * sizeof(float)));
+    TNN_CUDA(cudaMalloc(&t->enc_m, t->enc_shard * sizeof(float)));
+    TNN_CUDA(cudaMalloc(&t->enc_v, t->enc_shard * sizeof(float)));
+    TNN_CUDA(cudaMemset(t->enc_m, 0, t->enc_shard * sizeof(float)));
+    TNN_CUDA(cudaMemset(t->enc_v, 0, t->enc_shard * sizeof(float)));
+    return 0;
+}
+
+} // namespace
+
+extern "C" {
+
+// ---- data parallelism
+int tnn_dp_get_unique_id(void *id128) {
+    if (!id128) return tnn::api_fail("null argument");
+    if (!nccl().ok) return tnn::api_fail("NCCL is not available: " + nccl().why, 3);
+    NcclUniqueId id;
+    if (int rc = nccl().GetUniqueId(&id)) return nccl_fail("ncclGetUniqueId", rc);
+    memcpy(id128, &id, sizeof(id));
+    return 0;
+}
+
+int tnn_dp_comm_create(const void *id128, int rank, int world, tnn_dp_comm **out) {
+    if (!id128 || !out) return tnn::api_fail("null argument");
+    *out = nullptr;
+    if (world < 1 || rank < 0 || rank >= world) return tnn::api_fail("rank must be in [0, world)");
+    if (!nccl().ok) return tnn::api_fail("NCCL is not available: " + nccl().why, 3);
+    NcclUniqueId id;
+    memcpy(&id, id128, sizeof(id));
+    void *comm = nullptr;
+    if (int rc = nccl().CommInitRank(&comm, world, id, rank)) return nccl_fail("ncclCommInitRank", rc);
+    auto *c = new tnn_dp_comm();
+    c->comm = comm;
+    c->rank = rank;
+    c->world = world;
+    c->owned = true;
+    *out = c;
+    return 0;
+}
+
+int tnn_dp_init(void *nccl_comm, tnn_dp_comm **out) {
+    if (!nccl_comm || !out) return tnn::api_fail("null argument");
+    *out = nullptr;
+    if (!nccl().ok) return tnn::api_fail("NCCL is not available: " + nccl().why, 3);
+    int world = 0, rank = 0;
+    if (int rc = nccl().CommCount(nccl_comm, &world)) return nccl_fail("ncclCommCount", rc);
+    if (int rc = nccl().CommUserRank(nccl_comm, &rank)) return nccl_fail("ncclCommUserRank", rc);
+    auto *c = new tnn_dp_comm();
+    c->comm = nccl_comm;
+    c->rank = rank;
+    c->world = world;
+    c->owned = false;
+    *out = c;
+    return 0;
+}
+
+int tnn_dp_comm_destroy(tnn_dp_comm *c) {
+    if (!c) return 0;
+    if (c->owned && c->comm && nccl().ok) nccl().CommDestroy(c->comm);
+    delete c;
+    return 0;
+}
+
+int tnn_dp_rank(const tnn_dp_comm *c) { return c ? c->rank : 0; }
+int tnn_dp_world_size(const tnn_dp_comm *c) { return c ? c->world : 1; }
+
+int tnn_dp_allreduce_sum(tnn_dp_comm *c, float *buf, size_t n, void *stream) {
+    if (!buf) return tnn::api_fail("null argument");
+    if (!c || c->world == 1 || n == 0) return 0;
+    if (int rc = nccl().AllReduce(buf, buf, n, kNcclFloat32, kNcclSum, c->comm, (cudaStream_t)stream))
+        return nccl_fail("ncclAllReduce", rc);
+    return 0;
+}
+
+// ---- trainer
+int tnn_trainer_create(tnn_network *net, tnn_encoding *enc, float lr, float beta1, float beta2, float eps,
+                       float loss_scale, tnn_trainer **out) {
+    if (!net || !out) return tnn::api_fail("null argument");
+    *out = nullptr;
+    if (loss_scale == 0.0f) return tnn::api_fail("loss_scale must not be 0");
+    if (enc && enc->padded != net->width)
+        return tnn::api_fail("the encoding's padded output width must equal the network width");
+    auto *t = new tnn_trainer();
+    t->net = net;
+    t->enc = enc;
+    t->lr = lr, t->b1 = beta1, t->b2 = beta2, t->eps = eps, t->loss_scale = loss_scale;
+    const size_t n = net->n_params;
+    cudaError_t e = cudaMalloc(&t->master, (4 * n + 4) * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemset(t->master, 0, (4 * n + 4) * sizeof(float));
+    if (e != cudaSuccess) {
+        delete t;
+        return tnn::api_fail(std::string("device allocation failed: ") + cudaGetErrorString(e), 2);
+    }
+    t->m = t->master + n;
+    t->v = t->m + n;
+    t->grads = t->v + n;
+    t->loss = t->grads + n;
+    // master copy = the network's current (bf16) weights; tnn_trainer_set_master_params replaces it with the fp32 draw
+    e = tnn::launch_bf16_to_f32(net->packed, t->master, n, nullptr);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(nullptr);
+    if (e != cudaSuccess) {
+        tnn_trainer_destroy(t);
+        return tnn::api_fail(std::string("master copy: ") + cudaGetErrorString(e), 2);
+    }
+    if (int rc = alloc_encoding_state(t)) {
+        tnn_trainer_destroy(t);
+        return rc;
+    }
+    *out = t;
+    return 0;
+}
+
+int tnn_trainer_destroy(tnn_trainer *t) {
+    if (!t) return 0;
+    cudaFree(t->master);
+    cudaFree(t->enc_grads);
+    cudaFree(t->enc_m);
+    cudaFree(t->enc_v);
+    delete t;
+    return 0;
+}
+
+int tnn_trainer_set_dp(tnn_trainer *t, tnn_dp_comm *comm) {
+    if (!t) return tnn::api_fail("trainer is null");
+    if (t->step != 0 && t->enc && t->enc->n_params)
+        return tnn::api_fail("the communicator of a trainer with a trainable encoding must be set before the first step");
+    t->dp = comm;
+    return alloc_encoding_state(t); // the encoding's optimiser state is sharded over the ranks
+}
+
+int tnn_trainer_set_deterministic_encoding(tnn_trainer *t, int deterministic) {
+    if (!t) return tnn::api_fail("trainer is null");
+    t->deterministic_encoding = deterministic ? 1 : 0;
+    return 0;
+}
+
+int tnn_trainer_set_master_params(tnn_trainer *t, const float *packed_fp32, void *stream) {
+    if (!t || !packed_fp32) return tnn::api_fail("null argument");
+    TNN_CUDA(cudaMemcpyAsync(t->master, packed_fp32, t->net->n_params * sizeof(float), cudaMemcpyDeviceToDevice,
+                             (cudaStream_t)stream));
+    return tnn_network_set_params(t->net, t->master, TNN_DTYPE_FP32, 1, stream);
+}
+
+float *tnn_trainer_master_params(tnn_trainer *t) { return t ? t->master : nullptr; }
+float *tnn_trainer_grads(tnn_trainer *t) { return t ? t->grads : nullptr; }
+float *tnn_trainer_encoding_grads(tnn_trainer *t) { return t ? t->enc_grads : nullptr; }
+float *tnn_trainer_loss(tnn_trainer *t) { return t ? t->loss : nullptr; }
+int tnn_trainer_step_count(const tnn_trainer *t) { return t ? t->step : 0; }
+
+int tnn_trainer_forward_backward(tnn_trainer *t, const void *x, const float *targets, int n_targets, size_t batch,
+                                 void *stream) {
+    if (!t) return tnn::api_fail("trainer is null");
+    t->reduced = false;
+    if (int rc = tnn::train_step_raw(t->net, t->enc, x, targets, n_targets, batch, t->loss_scale,
+                                     (t->enc && t->enc->n_params) ? t->enc_grads : nullptr, t->deterministic_encoding,
+                                     &t->n_slabs, &t->n_loss, stream))
+        return rc;
+    return 0;
+}
+
+// Sums the slabs and loss partials the last forward_backward left behind into grads / loss (no optimiser step).
+int tnn_trainer_reduce(tnn_trainer *t, void *stream) {
+    if (!t) return tnn::api_fail("trainer is null");
+    if (t->reduced) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    tnn_network *n = t->net;
+    TNN_CUDA(tnn::launch_sum_partials(n->loss_partials, t->n_loss, t->loss, s));
+    TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, t->n_slabs, n->n_mat, n->width, 1, 1.0f, t->grads, nullptr, s));
+    t->reduced = true;
+    return 0;
+}
+
+int tnn_trainer_optimizer_step(tnn_trainer *t, void *stream) {
+    if (!t) return tnn::api_fail("trainer is null");
+    cudaStream_t s = (cudaStream_t)stream;
+    tnn_network *n = t->net;
+    const int world = world_of(t);
+    const float grad_scale = 1.0f / (t->loss_scale * (float)world);
+    t->step += 1;
+    if (world > 1) {
+        if (int rc = tnn_trainer_reduce(t, stream)) return rc;
+        if (int rc = tnn_dp_allreduce_sum(t->dp, t->grads, n->n_params, stream)) return rc;
+    }
+    if (world > 1 || t->reduced) {
+        TNN_CUDA(tnn::launch_adam_refresh<false>(n->width, t->master, t->m, t->v, t->grads, nullptr, 0, nullptr, 0, nullptr,
+                                                 n->n_mat, n->one_padded_input(), n->output_width, grad_scale, t->step,
+                                                 t->lr, t->b1, t->b2, t->eps, n->packed, n->wimg, n->wimg_t, s));
+    } else {
+        TNN_CUDA(tnn::launch_adam_refresh<true>(n->width, t->master, t->m, t->v, t->grads, n->dw_slabs, t->n_slabs,
+                                                n->loss_partials, t->n_loss, t->loss, n->n_mat, n->one_padded_input(),
+                                                n->output_width, grad_scale, t->step, t->lr, t->b1, t->b2, t->eps,
+                                                n->packed, n->wimg, n->wimg_t, s));
+        t->reduced = true;
+    }
+    if (t->enc && t->enc->n_params) {
+        tnn_encoding *e = t->enc;
+        float *table = e->params();
+        if (!t->enc_sharded) {
+            if (world > 1)
+                if (int rc = tnn_dp_allreduce_sum(t->dp, t->enc_grads, e->n_params, stream)) return rc;
+            TNN_CUDA(tnn::launch_adam(table, t->enc_m, t->enc_v, t->enc_grads, e->n_params, grad_scale, t->step, t->lr,
+                                      t->b1, t->b2, t->eps, nullptr, s));
+        } else {
+            // sharded optimiser: each rank owns enc_shard consecutive table entries
+            const size_t off = (size_t)rank_of(t) * t->enc_shard;
+            if (int rc = nccl().ReduceScatter(t->enc_grads, t->enc_grads + off, t->enc_shard, kNcclFloat32, kNcclSum,
+                                              t->dp->comm, s))
+                return nccl_fail("ncclReduceScatter", rc);
+            TNN_CUDA(tnn::launch_adam(table + off, t->enc_m, t->enc_v, t->enc_grads + off, t->enc_shard, grad_scale,
+                                      t->step, t->lr, t->b1, t->b2, t->eps, nullptr, s));
+            if (int rc = nccl().AllGather(table + off, table, t->enc_shard, kNcclFloat32, t->dp->comm, s))
+                return nccl_fail("ncclAllGather", rc);
+        }
+    }
+    return 0;
+}
+
+int tnn_trainer_training_step(tnn_trainer *t, const void *x, const float *targets, int n_targets, size_t batch,
+                              void *stream) {
+    if (int rc = tnn_trainer_forward_backward(t, x, targets, n_targets, batch, stream)) return rc;
+    return tnn_trainer_optimizer_step(t, stream);
+}
+
+} // extern "C"

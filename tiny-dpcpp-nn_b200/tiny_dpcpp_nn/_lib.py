@@ -26,6 +26,7 @@ _vp = ctypes.c_void_p
 _SIGNATURES = {
     "tnn_last_error": (_c.c_char_p, []),
     "tnn_version": (_c.c_char_p, []),
+    "tnn_launch_count": (_c.c_ulonglong, []),
     "tnn_network_create": (_c.c_int, [_c.c_int] * 8 + [_c.POINTER(_vp)]),
     "tnn_network_destroy": (_c.c_int, [_vp]),
     "tnn_network_n_params": (_c.c_size_t, [_vp]),
@@ -40,6 +41,13 @@ _SIGNATURES = {
     "tnn_network_backward": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _vp, _vp, _c.c_size_t, _vp]),
     "tnn_network_train_step": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _c.c_size_t, _c.c_float, _vp, _c.c_int, _c.c_int,
                                           _vp, _vp]),
+    "tnn_network_workspace_bytes": (_c.c_size_t, [_vp, _c.c_size_t]),
+    "tnn_network_set_workspace": (_c.c_int, [_vp, _vp, _c.c_size_t]),
+    "tnn_network_with_encoding_workspace_bytes": (_c.c_size_t, [_vp, _c.c_size_t]),
+    "tnn_network_with_encoding_inference": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_size_t, _vp]),
+    "tnn_network_with_encoding_forward": (_c.c_int, [_vp, _vp, _vp, _vp, _vp, _c.c_size_t, _vp]),
+    "tnn_network_with_encoding_train_step": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_int, _c.c_size_t, _c.c_float, _vp,
+                                                        _c.c_int, _c.c_int, _vp, _c.c_int, _vp, _vp]),
     "tnn_network_sync_status": (_c.c_int, [_vp, _c.POINTER(_c.c_int), _vp]),
     "tnn_network_set_variant": (_c.c_int, [_vp, _c.c_int]),
     "tnn_encoding_create": (_c.c_int, [_c.c_char_p, _c.c_int, _c.POINTER(_vp)]),
@@ -62,6 +70,28 @@ _SIGNATURES = {
                                  _c.c_float, _c.c_float, _vp]),
     "tnn_network_adam_step": (_c.c_int, [_vp, _vp, _vp, _vp, _vp, _c.c_float, _c.c_int, _c.c_float, _c.c_float,
                                          _c.c_float, _c.c_float, _vp]),
+    "tnn_dp_get_unique_id": (_c.c_int, [_vp]),
+    "tnn_dp_comm_create": (_c.c_int, [_vp, _c.c_int, _c.c_int, _c.POINTER(_vp)]),
+    "tnn_dp_init": (_c.c_int, [_vp, _c.POINTER(_vp)]),
+    "tnn_dp_comm_destroy": (_c.c_int, [_vp]),
+    "tnn_dp_rank": (_c.c_int, [_vp]),
+    "tnn_dp_world_size": (_c.c_int, [_vp]),
+    "tnn_dp_allreduce_sum": (_c.c_int, [_vp, _vp, _c.c_size_t, _vp]),
+    "tnn_trainer_create": (_c.c_int, [_vp, _vp, _c.c_float, _c.c_float, _c.c_float, _c.c_float, _c.c_float,
+                                      _c.POINTER(_vp)]),
+    "tnn_trainer_destroy": (_c.c_int, [_vp]),
+    "tnn_trainer_set_dp": (_c.c_int, [_vp, _vp]),
+    "tnn_trainer_set_deterministic_encoding": (_c.c_int, [_vp, _c.c_int]),
+    "tnn_trainer_set_master_params": (_c.c_int, [_vp, _vp, _vp]),
+    "tnn_trainer_master_params": (_vp, [_vp]),
+    "tnn_trainer_grads": (_vp, [_vp]),
+    "tnn_trainer_encoding_grads": (_vp, [_vp]),
+    "tnn_trainer_loss": (_vp, [_vp]),
+    "tnn_trainer_step_count": (_c.c_int, [_vp]),
+    "tnn_trainer_forward_backward": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _c.c_size_t, _vp]),
+    "tnn_trainer_reduce": (_c.c_int, [_vp, _vp]),
+    "tnn_trainer_optimizer_step": (_c.c_int, [_vp, _vp]),
+    "tnn_trainer_training_step": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _c.c_size_t, _vp]),
 }
 
 _lib = None
@@ -401,6 +431,30 @@ def l2_loss_static(pred, target, loss_sum, grads, values=None, loss_scale=1.0):
     batch, stride = pred.shape
     check(lib.tnn_l2_loss_static(dptr(pred), dptr(target), target.shape[1], dptr(values), dptr(grads), batch, stride,
                                  float(loss_scale), dptr(loss_sum), stream_ptr()))
+
+
+def nwe_inference(net, enc, x, out=None):
+    """tnn_network_with_encoding_inference: y = network(encoding(x)) without the encoded matrix in between where the
+    kernels can fold the encoding (identity).  x: batch x n_input_dims float32; returns batch x width bfloat16."""
+    lib = load()
+    if x.dtype != torch.float32 or x.dim() != 2 or x.shape[1] != enc.n_input_dims():
+        raise TnnError("encoding input must be (batch, n_input_dims) float32")
+    y = out if out is not None else torch.empty((x.shape[0], net.width), dtype=torch.bfloat16, device=x.device)
+    check(lib.tnn_network_with_encoding_inference(net._h, enc._h, dptr(x), dptr(y), x.shape[0], stream_ptr()))
+    return y
+
+
+def nwe_forward(net, enc, x):
+    """tnn_network_with_encoding_forward in training mode: stores the activations in the network module (matrix 0 =
+    the encoded input) for a following bwd_no_encoding_grad, returns the output rows."""
+    lib = load()
+    batch = x.shape[0]
+    if net._interm_fwd is None or net._interm_fwd.shape[1] != batch:
+        net._interm_fwd = torch.empty((net.n_mat + 1, batch, net.width), dtype=torch.bfloat16, device=x.device)
+    net._batch = batch
+    check(lib.tnn_network_with_encoding_forward(net._h, enc._h, dptr(x), None, dptr(net._interm_fwd), batch,
+                                                stream_ptr()))
+    return net._interm_fwd[net.n_mat].clone()
 
 
 def adam_step(params, m, v, grads, step, lr=1e-3, beta1=0.9, beta2=0.99, eps=1e-15, grad_scale=1.0):

@@ -1,58 +1,109 @@
-"""Training step for a Network: forward -> L2 loss -> backward -> (gradient all-reduce) -> Adam.
+"""Training step for a Network (optionally behind an input encoding): forward -> L2 loss -> backward ->
+(gradient all-reduce) -> Adam, as one call into the library.
 
 The reference's Trainer<T>::training_step (include/trainer.h:23-46) runs forward_pass and
 backward_pass only ("no optimisation as we run benchmarking", trainer.h:39); its Python training
-loops add torch's loss and torch.optim.Adam around the module.  This class is the device-resident
-equivalent of that whole loop body: nothing leaves the GPU between the kernels, the parameter
-vector keeps the packed layout the reference exposes to optimisers (modules.py:169-175), and in
-data-parallel runs the only communication is one all-reduce of the fp32 weight-gradient buffer.
+loops add torch's loss and torch.optim.Adam around the module.  This class is a thin front end of the
+library's tnn_trainer, the device-resident equivalent of that whole loop body: nothing leaves the GPU
+between the kernels, the parameter vector keeps the packed layout the reference exposes to optimisers
+(modules.py:169-175), and in data-parallel runs the only communication is one all-reduce of the fp32
+weight-gradient buffer (plus reduce-scatter / all-gather of a trainable encoding's table).
 """
+import ctypes
+
 import torch
 
 from . import _lib
-from .parallel import allreduce_sum_
+from .parallel import create_dp_comm
+
+
+class _DevArray:
+    """A device buffer owned by the library, exposed through the CUDA array interface."""
+
+    def __init__(self, ptr, n):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (int(ptr), False), "version": 2}
+
+
+def _wrap(ptr, n):
+    return torch.as_tensor(_DevArray(ptr, n), device="cuda")
 
 
 class Trainer:
     def __init__(self, network, lr=1e-3, betas=(0.9, 0.99), eps=1e-15, loss_scale=1.0, process_group=None,
-                 world_size=1):
-        """network: a _lib.NetworkModule.  process_group: torch.distributed group for data parallelism
-        (None = single GPU); gradients are averaged over world_size ranks."""
+                 world_size=1, encoding=None):
+        """network: a _lib.NetworkModule; encoding: an optional _lib.EncodingModule in front of it (inputs are
+        then float32 coordinates).  process_group: torch.distributed group for data parallelism (None = single
+        GPU); gradients are averaged over its ranks through a NCCL communicator the library creates."""
+        lib = _lib.load()
+        self._lib = lib
         self.net = network
+        self.encoding = encoding
         self.lr, self.betas, self.eps = lr, betas, eps
         self.loss_scale = loss_scale
-        self.pg = process_group
         self.world_size = world_size
+        h = ctypes.c_void_p()
+        _lib.check(lib.tnn_trainer_create(network._h, encoding._h if encoding is not None else None, lr, betas[0],
+                                          betas[1], eps, loss_scale, ctypes.byref(h)))
+        self._h = h
+        self._comm = None
+        if process_group is not None and world_size > 1:
+            self._comm = create_dp_comm(process_group)
+            _lib.check(lib.tnn_trainer_set_dp(self._h, self._comm))
         n = network.n_params()
-        self.master = network.get_params().float().reshape(-1).contiguous()  # fp32 master copy, packed layout
-        self.m = torch.zeros(n, dtype=torch.float32, device="cuda")
-        self.v = torch.zeros(n, dtype=torch.float32, device="cuda")
-        self.grads = torch.zeros(n, dtype=torch.float32, device="cuda")
-        self.step = 0
-        self._loss = torch.zeros(1, dtype=torch.float32, device="cuda")
+        # views of the trainer's device state (fp32, packed layout)
+        self.master = _wrap(lib.tnn_trainer_master_params(self._h), n)
+        self.grads = _wrap(lib.tnn_trainer_grads(self._h), n)
+        self._loss = _wrap(lib.tnn_trainer_loss(self._h), 1)
+        self.encoding_grads = None
+        if encoding is not None and encoding.n_params():
+            self.encoding_grads = _wrap(lib.tnn_trainer_encoding_grads(self._h), encoding.n_params())
+
+    def __del__(self):
+        try:
+            import sys
+            if getattr(self, "_h", None) and not sys.is_finalizing():
+                self._lib.tnn_trainer_destroy(self._h)
+                self._h = None
+                if self._comm:
+                    self._lib.tnn_dp_comm_destroy(self._comm)
+        except Exception:
+            pass
+
+    @property
+    def step(self):
+        return int(self._lib.tnn_trainer_step_count(self._h))
+
+    def set_deterministic_encoding(self, on=True):
+        _lib.check(self._lib.tnn_trainer_set_deterministic_encoding(self._h, int(bool(on))))
 
     def set_master_params(self, packed_fp32):
-        self.master.copy_(packed_fp32.reshape(-1))
-        self.net.set_params(self.master, True)
+        src = packed_fp32.reshape(-1).to(torch.float32).contiguous()
+        _lib.check(self._lib.tnn_trainer_set_master_params(self._h, _lib.dptr(src), _lib.stream_ptr()))
+        src.record_stream(torch.cuda.current_stream())
+
+    def _check(self, x, targets):
+        want = torch.float32 if self.encoding is not None else torch.bfloat16
+        if x.dtype != want or targets.dtype != torch.float32 or x.dim() != 2 or targets.dim() != 2 \
+                or targets.shape[0] != x.shape[0]:
+            raise _lib.TnnError(f"training inputs must be (batch, n) {want} and targets (batch, n_targets) float32")
 
     def forward_backward(self, x, targets):
-        """x: batch x width bf16, targets: batch x n_targets fp32.  Leaves the loss sum in self._loss
-        and the (packed, transposed) fp32 gradient of the mean loss in self.grads.  One call into the
-        library: forward, L2 loss, backward and the weight-gradient reduction are fused."""
-        net, lib = self.net, _lib.load()
-        _lib.check(lib.tnn_network_train_step(net._h, _lib.dptr(x), _lib.dptr(targets), targets.shape[1], x.shape[0],
-                                              float(self.loss_scale), _lib.dptr(self.grads), _lib.DTYPE_FP32, 1,
-                                              _lib.dptr(self._loss), _lib.stream_ptr()))
+        """x: batch x width bf16 (with an encoding: batch x n_input_dims fp32), targets: batch x n_targets fp32.
+        Leaves the loss sum in self._loss and the (packed, transposed) fp32 gradient of the mean loss in self.grads."""
+        self._check(x, targets)
+        s = _lib.stream_ptr()
+        _lib.check(self._lib.tnn_trainer_forward_backward(self._h, _lib.dptr(x), _lib.dptr(targets), targets.shape[1],
+                                                          x.shape[0], s))
+        _lib.check(self._lib.tnn_trainer_reduce(self._h, s))
         return self._loss
 
     def optimizer_step(self):
-        if self.world_size > 1:
-            allreduce_sum_(self.grads, self.pg)
-        self.step += 1
-        self.net.adam_step(self.master, self.m, self.v, self.grads, self.step, self.lr, self.betas[0], self.betas[1],
-                           self.eps, grad_scale=1.0 / (self.loss_scale * self.world_size))
+        _lib.check(self._lib.tnn_trainer_optimizer_step(self._h, _lib.stream_ptr()))
 
     def training_step(self, x, targets):
-        loss = self.forward_backward(x, targets)
-        self.optimizer_step()
-        return loss
+        """One call: fused forward / loss / backward kernel, then one kernel that finishes the gradient sums,
+        applies Adam and refreshes the weights (data parallel: with the all-reduce between two kernels)."""
+        self._check(x, targets)
+        _lib.check(self._lib.tnn_trainer_training_step(self._h, _lib.dptr(x), _lib.dptr(targets), targets.shape[1],
+                                                       x.shape[0], _lib.stream_ptr()))
+        return self._loss
