@@ -6,7 +6,8 @@
  *     failure on the calling thread is available from tnn_last_error().  Nothing throws across
  *     this boundary.
  *   - All data pointers are DEVICE pointers owned by the caller unless stated otherwise.  Matrices
- *     are row-major, batch x width.  Network activations are bf16, encodings take fp32 inputs.
+ *     are row-major, batch x width.  Network activations have the network's 16-bit type (bf16 or fp16; "bf16"
+ *     in the comments below stands for either), encodings take fp32 inputs.
  *   - `stream` is a cudaStream_t passed as void*; calls only enqueue work on it and never
  *     synchronise or allocate, except where a function says so (workspace growth, parameter initialisation).
  *   - Handles are not thread-safe; use one handle per host thread or lock around it.
@@ -51,8 +52,9 @@ unsigned long long tnn_launch_count(void);
 
 /* create_network(input_width, output_width, n_hidden_layers, activation, output_activation, width,
  * dtype, use_bias) - pybind_module.cpp:90-139; checks of include/network/Network.h:129-167.
- * width in {16, 32, 64, 128}; input/output widths are padded up to `width`.  dtype must be
- * TNN_DTYPE_BF16.  Weights start as zeros; call tnn_network_initialize_params or
+ * width in {16, 32, 64, 128}; input/output widths are padded up to `width`.  dtype: TNN_DTYPE_BF16 or
+ * TNN_DTYPE_FP16 (the reference's sycl::half instantiations, include/network/kernel_esimd.h:643-721) - the type of
+ * weights, activations and of every "16-bit" buffer of this network below.  Weights start as zeros; call tnn_network_initialize_params or
  * tnn_network_set_params. */
 int tnn_network_create(int input_width, int output_width, int n_hidden_layers, int activation,
                        int output_activation, int width, int dtype, int use_bias, tnn_network **out);
@@ -72,12 +74,12 @@ int tnn_network_n_hidden_layers(const tnn_network *net);
 int tnn_network_initialize_params(tnn_network *net, uint64_t seed, void *stream);
 /* Module::set_params(tensor, weights_are_packed) - include/tnn_api.h:637-641 and
  * Network::set_weights_matrices, include/network/Network.h:90-112.  `params` holds n_params values
- * of `dtype` (bf16 or fp32) on the device, either in the packed layout of
+ * of `dtype` (bf16, fp16 or fp32) on the device, either in the packed layout of
  * source/common/common.cpp:33-42 or unpacked (matrix l = in x out, row-major).  Padding rows /
  * columns are zeroed as in Network.h:171-233.  Device-to-device; no host round trip. */
 int tnn_network_set_params(tnn_network *net, const void *params, int dtype, int weights_are_packed,
                            void *stream);
-/* Module::get_params - include/tnn_api.h:622-624: n_params bf16 values in the packed layout. */
+/* Module::get_params - include/tnn_api.h:622-624: n_params values of the network's 16-bit type, packed layout. */
 int tnn_network_get_params(const tnn_network *net, void *params_out_bf16, void *stream);
 
 /* Module::inference - include/tnn_api.h:512-530 (EsimdKernels::inference_impl,
@@ -92,7 +94,7 @@ int tnn_network_forward(tnn_network *net, const void *x, void *y, void *interm_f
 /* Module::backward_pass(grad_output, pack_transpose_gradient, get_dl_dinput) -
  * include/tnn_api.h:561-620 (backward_impl + gemm_batch, kernel_esimd.h:160-240).
  * dy: batch x width bf16 = dL/d(output); interm_fwd: what tnn_network_forward stored.
- * grads: n_params values of grads_dtype (bf16 like the reference, or fp32), matrix l as (out x in)
+ * grads: n_params values of grads_dtype (bf16 / fp16 like the reference's T, or fp32), matrix l as (out x in)
  * row-major, or transposed and packed like the weights when pack_transpose != 0.
  * dx (optional): batch x width bf16 = dL/d(input).  interm_bwd (optional): n_hidden_layers + 1
  * matrices batch x width bf16, matrix l = dL/d(pre-activation of layer l). */
@@ -139,7 +141,7 @@ int tnn_network_set_variant(tnn_network *net, int variant);
  * ------------------------------------------------------------------------------------------ */
 
 /* `json_config`: flat JSON object with the reference's keys (include/encodings/encoding.h:28-52):
- * otype ("HashGrid" | "Identity"), n_dims_to_encode, type, n_levels | n_features,
+ * otype ("HashGrid" | "Identity" | "Frequency" | "SphericalHarmonics"), n_dims_to_encode, n_frequencies, degree, type, n_levels | n_features,
  * n_features_per_level, log2_hashmap_size, base_resolution, per_level_scale, hash, interpolation,
  * scale, offset.  Defaults as in include/encodings/grid.h:1010-1047.  Enum values may be strings
  * or integers.  padded_output_width 0 = natural width. */
@@ -169,7 +171,7 @@ float *tnn_encoding_params_ptr(tnn_encoding *enc);
 int tnn_encoding_bind_params(tnn_encoding *enc, float *params);
 /* EncodingModule::forward_pass - include/tnn_api.h:332-356 (kernel_grid, grid.h:37-135; identity,
  * identity.h:63-77).  x: batch x n_input_dims fp32.  out: batch x n_output_dims of out_dtype
- * (fp32 like the reference, or bf16 to feed a network directly). */
+ * (fp32 like the reference, or bf16 / fp16 to feed a network directly). */
 int tnn_encoding_forward(tnn_encoding *enc, const float *x, void *out, int out_dtype, size_t batch,
                          void *stream);
 /* EncodingModule::backward_pass(grad_output, input_from_fwd, false, false) - include/tnn_api.h:368-416
@@ -180,6 +182,16 @@ int tnn_encoding_forward(tnn_encoding *enc, const float *x, void *out, int out_d
  * scratch per parameter in the handle, allocated (with a synchronisation of `stream`) at its first use. */
 int tnn_encoding_backward(tnn_encoding *enc, const float *x, const void *dy, int dy_dtype, float *grads,
                           size_t batch, int deterministic, void *stream);
+
+/* dL/dinput of an encoding - the `dL_dinput` output of Encoding::backward_impl (include/encodings/encoding.h:120-135):
+ * dx: batch x n_input_dims fp32, overwritten.  Identity: dL/dy * scale (identity.h:91-97); Frequency:
+ * include/encodings/frequency.h:91-131; HashGrid: the product of kernel_grid_backward_input
+ * (include/encodings/grid.h:247-268) with the derivative taken directly from the interpolation formula (the reference's
+ * forward pass never fills the dy/dx context that kernel reads, grid.h:669-670); SphericalHarmonics: fails with the
+ * reference's message (spherical_harmonics.h:66-71).  The reference's Python layer never asks for it
+ * (include/tnn_api.h:380-382). */
+int tnn_encoding_backward_input(tnn_encoding *enc, const float *x, const void *dy, int dy_dtype, float *dx,
+                                size_t batch, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Network with input encoding: replaces NetworkWithInputEncoding
@@ -221,6 +233,10 @@ int tnn_network_with_encoding_train_step(tnn_network *net, tnn_encoding *enc, co
  * streams) race on it. */
 int tnn_l2_loss(const void *pred, const float *target, int n_targets, float *values, void *grads,
                 size_t batch, int stride, float loss_scale, float *loss_sum, void *stream);
+/* The same loss for predictions of either 16-bit type: dtype = TNN_DTYPE_BF16 or TNN_DTYPE_FP16 (pred and grads
+ * share it) - Loss<T> with T = sycl::half, include/losses/loss.h:19-25. */
+int tnn_l2_loss_dtype(const void *pred, int dtype, const float *target, int n_targets, float *values, void *grads,
+                      size_t batch, int stride, float loss_scale, float *loss_sum, void *stream);
 /* No counterpart in the reference.  Same computation and arguments as tnn_l2_loss for callers that must
  * not allocate device memory - e.g. a plug-in inside a host application whose allocator already owns all
  * free device memory, or a latency-critical loop that cannot afford the device-wide synchronisation an

@@ -42,6 +42,15 @@ inline float bf16_round(float v) {
     return r;
 }
 
+inline float fp16_round(float v) {
+    // round-to-nearest-even to IEEE half precision (11 significant bits, subnormals below 2^-14, overflow to inf),
+    // like static_cast<sycl::half>(float)
+    return (float)(_Float16)v;
+}
+
+// storage rounding of the device type T: mode 0 = none, 1 = bf16, 2 = fp16
+inline float round16(float v, int mode) { return mode == 2 ? fp16_round(v) : mode == 1 ? bf16_round(v) : v; }
+
 inline void set_threads(int n) {
 #ifdef _OPENMP
     if (n > 0) omp_set_num_threads(n);
@@ -63,6 +72,7 @@ int oracle_max_threads() {
 }
 
 float oracle_bf16_round(float v) { return bf16_round(v); }
+float oracle_fp16_round(float v) { return fp16_round(v); }
 
 // ---------------------------------------------------------------------------------------------
 // Weight packing: source/common/common.cpp:33-66 (to/fromPackedLayoutCoord) and
@@ -89,7 +99,7 @@ void oracle_pack_weights(const float *unpacked, int n_mat, int width, float *pac
 // Fused MLP forward: include/network/kernel_esimd.h:565-640 (forward_impl_general) with the
 // activation rules of 443-458.  x: batch x W.  w: n_mat matrices (in x out, row-major, unpacked).
 // interm: (n_mat + 1) matrices batch x W; matrix 0 = x, matrix l + 1 = activation of layer l.
-// bf16 != 0: every stored activation is rounded to bf16 like the device type T; accumulation is
+// bf16 != 0: every stored activation is rounded like the device type T (1 = bf16, 2 = fp16); accumulation is
 // done in double, the device's fp32 accumulation differs from it by less than one bf16 ulp.
 // bf16 == 0: plain double-precision network, the arithmetic of test/mlp.h:234-282.
 // ---------------------------------------------------------------------------------------------
@@ -115,7 +125,7 @@ void oracle_mlp_forward(const float *x, const float *w, int n_mat, int W, int ac
             for (int n = 0; n < W; ++n) {
                 double v = nxt[n];
                 if (a_ == ACT_SIGMOID) v = 1.0 / (1.0 + std::exp(-v));
-                if (bf16) v = bf16_round((float)v);
+                if (bf16) v = round16((float)v, bf16);
                 if (a_ == ACT_RELU) v = std::max(v, 0.0);
                 dst[n] = (float)v;
                 cur[n] = v;
@@ -161,7 +171,7 @@ void oracle_mlp_backward(const float *dy, const float *interm, const float *w, i
                 } else if (out_act == ACT_SIGMOID) {
                     d *= (double)y[n] * (1.0 - (double)y[n]);
                 }
-                if (bf16) d = bf16_round((float)d);
+                if (bf16) d = round16((float)d, bf16);
                 delta[n] = d;
             }
             for (int l = L; l >= 0; --l) {
@@ -188,7 +198,7 @@ void oracle_mlp_backward(const float *dy, const float *interm, const float *w, i
                             s *= (double)al[k] * (1.0 - (double)al[k]);
                         }
                     }
-                    if (bf16) s = bf16_round((float)s);
+                    if (bf16) s = round16((float)s, bf16);
                     prev[k] = s;
                 }
                 if (l == 0) {
@@ -216,7 +226,7 @@ void oracle_l2_loss(const float *pred, const float *target, int n_targets, size_
             if (values) values[b * stride + c] = diff * diff * inv_n;
             if (grads) {
                 const float g = loss_scale * 2 * diff * inv_n;
-                grads[b * stride + c] = bf16_grads ? bf16_round(g) : g;
+                grads[b * stride + c] = round16(g, bf16_grads);
             }
         }
 }
@@ -262,6 +272,75 @@ void oracle_frequency_forward(const float *x, size_t batch, int n_in, int n_freq
             const float arg = (float)((double)(x[b * n_in + feature] * (float)((size_t)1 << log2_frequency)) * M_PI + phase_shift);
             out[b * padded + j] = std::sin(arg);
         }
+}
+
+// dL/dinput of the frequency encoding: include/encodings/frequency.h:72-73 (dy/dx = 2^f pi cos(arg)) and 91-131
+// (dL/dx_j = sum over the 2 F outputs of feature j of dL/dy * dy/dx).  Accumulated in double.
+void oracle_frequency_backward_input(const float *x, const float *dy, size_t batch, int n_in, int n_freq, int padded,
+                                     float *dx) {
+    for (size_t b = 0; b < batch; ++b)
+        for (int f = 0; f < n_in; ++f) {
+            double acc = 0.0;
+            for (int k = 0; k < 2 * n_freq; ++k) {
+                const int j = f * 2 * n_freq + k;
+                const int log2_frequency = (j / 2) % n_freq;
+                const float phase_shift = (float)((j % 2) * (M_PI / 2.0));
+                const float scale = (float)((size_t)1 << log2_frequency);
+                const float arg = (float)((double)(x[b * n_in + f] * scale) * M_PI + phase_shift);
+                acc += (double)dy[b * padded + j] * (double)scale * M_PI * std::cos((double)arg);
+            }
+            dx[b * n_in + f] = (float)acc;
+        }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Spherical harmonics: include/encodings/spherical_harmonics.h:28-64 encodes the direction 2 x - 1 with the
+// degree^2 real spherical harmonics (order l (l + 1) + m), padded with ones.  The reference evaluates generated
+// polynomials (include/common/common_device.h:33-206, "generated ... based on the recurrence relations in appendix A1
+// of Sloan, Stupid Spherical Harmonics Tricks"); this restatement evaluates the same functions from that published
+// definition in double precision:
+//   Y_l^m = sqrt(2) K_l^m (-1)^m Q_l^m(z) Re (x + i y)^m,  Y_l^-m = ... Im (x + i y)^m,  Y_l^0 = K_l^0 Q_l^0(z),
+//   K_l^m = sqrt((2 l + 1) (l - m)! / (4 pi (l + m)!)),  Q_l^m = d^m P_l / dz^m.
+// ---------------------------------------------------------------------------------------------
+void oracle_spherical_harmonics_forward(const float *in, size_t batch, int degree, int padded, float *out) {
+    for (size_t b = 0; b < batch; ++b) {
+        // the inputs are mapped in fp32 like the device code (x * 2.f - 1.f)
+        const double x = (double)(in[b * 3 + 0] * 2.0f - 1.0f), y = (double)(in[b * 3 + 1] * 2.0f - 1.0f),
+                     z = (double)(in[b * 3 + 2] * 2.0f - 1.0f);
+        float *o = out + b * padded;
+        for (int j = degree * degree; j < padded; ++j) o[j] = 1.0f;
+        double c = 1.0, s = 0.0, qmm = 1.0;
+        for (int m = 0; m < degree; ++m) {
+            if (m > 0) {
+                const double cn = c * x - s * y;
+                s = c * y + s * x;
+                c = cn;
+                qmm *= (double)(2 * m - 1);
+            }
+            double q2 = 0.0, q1 = 0.0;
+            for (int l = m; l < degree; ++l) {
+                double q;
+                if (l == m)
+                    q = qmm;
+                else if (l == m + 1)
+                    q = (2 * m + 1) * z * q1;
+                else
+                    q = ((2 * l - 1) * z * q1 - (l + m - 1) * q2) / (double)(l - m);
+                q2 = q1;
+                q1 = q;
+                double ratio = 1.0;
+                for (int i = l - m + 1; i <= l + m; ++i) ratio /= (double)i;
+                double k = std::sqrt((2.0 * l + 1.0) / (4.0 * M_PI) * ratio);
+                if (m > 0) k *= std::sqrt(2.0) * ((m & 1) ? -1.0 : 1.0);
+                if (m == 0) {
+                    o[l * (l + 1)] = (float)(k * q);
+                } else {
+                    o[l * (l + 1) + m] = (float)(k * q * c);
+                    o[l * (l + 1) - m] = (float)(k * q * s);
+                }
+            }
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -390,6 +469,50 @@ void oracle_grid_forward(const OracleGrid *g, const float *x, const float *table
             }
             for (uint32_t f = 0; f < F; ++f) orow[level * F + f] = result[f];
         }
+    }
+}
+
+// dL/dinput of the grid: the derivative of the interpolation formula above with respect to x (the quantity
+// kernel_grid_backward_input, grid.h:247-268, forms from a stored dy/dx), accumulated in double:
+//   dL/dx_d = sum_l scale_l sum_c (+-1)_(c_d) [smoothstep: 6 p (1 - p)] prod_(e != d) w_e(c) <dL/dy_l, table_l[index(g + c)]>
+void oracle_grid_backward_input(const OracleGrid *g, const float *x, const float *table, const float *dy, size_t batch,
+                                int padded, float *dx, int n_threads) {
+    set_threads(n_threads);
+    const uint32_t F = g->F, D = g->D;
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < (long long)batch; ++i) {
+        double acc[3] = {0, 0, 0};
+        for (uint32_t level = 0; level < g->n_levels && g->interpolation != 0; ++level) {
+            const float *grid = table + (size_t)g->offsets[level] * F;
+            const uint32_t hashmap_size = g->offsets[level + 1] - g->offsets[level];
+            const float scale = grid_scale(level, g->log2_per_level_scale, g->base_resolution);
+            const uint32_t resolution = grid_resolution(scale);
+            double w[3], dw[3];
+            uint32_t pos_grid[3];
+            for (uint32_t d = 0; d < D; ++d) {
+                float p = std::fma(scale, x[(size_t)i * D + d], 0.5f);
+                const float fl = std::floor(p);
+                pos_grid[d] = (uint32_t)(int)fl;
+                p -= fl;
+                dw[d] = g->interpolation == 2 ? 6.0 * p * (1.0 - p) : 1.0;
+                w[d] = g->interpolation == 2 ? (double)p * p * (3.0 - 2.0 * p) : (double)p;
+            }
+            for (uint32_t c = 0; c < (1u << D); ++c) {
+                uint32_t local[3];
+                for (uint32_t d = 0; d < D; ++d) local[d] = pos_grid[d] + ((c >> d) & 1u);
+                const uint32_t idx = grid_index(g, hashmap_size, resolution, local);
+                double v = 0.0;
+                for (uint32_t f = 0; f < F; ++f)
+                    v += (double)dy[(size_t)i * padded + level * F + f] * (double)grid[(size_t)idx * F + f];
+                for (uint32_t d = 0; d < D; ++d) {
+                    double wd = ((c >> d) & 1u) ? dw[d] : -dw[d];
+                    for (uint32_t e = 0; e < D; ++e)
+                        if (e != d) wd *= ((c >> e) & 1u) ? w[e] : 1.0 - w[e];
+                    acc[d] += (double)scale * wd * v;
+                }
+            }
+        }
+        for (uint32_t d = 0; d < D; ++d) dx[(size_t)i * D + d] = (float)acc[d];
     }
 }
 

@@ -92,14 +92,31 @@ def unpack_weights(packed, n_mat, width):
     return p[:, idx].reshape(-1)
 
 
+def _mode(bf16):
+    """Storage rounding of the device type: False / 0 none, True / 1 / "bf16" bfloat16, 2 / "fp16" half."""
+    if bf16 in ("fp16", "float16", 2):
+        return 2
+    return 1 if bf16 else 0
+
+
+def fp16_round(a):
+    """Round-to-nearest-even to IEEE half, returned as float32."""
+    return np.ascontiguousarray(a, dtype=np.float32).astype(np.float16).astype(np.float32)
+
+
+def round16(a, dtype):
+    return fp16_round(a) if _mode(dtype) == 2 else bf16_round(a)
+
+
 def mlp_forward(x, w, n_mat, width, act, out_act, bf16=True, n_threads=0):
-    """Returns interm_fwd as array (n_mat + 1, batch, width); [0] = input, [-1] = output."""
+    """Returns interm_fwd as array (n_mat + 1, batch, width); [0] = input, [-1] = output.
+    bf16: True / "bf16" or "fp16" = the device type whose rounding every stored activation gets; False = none."""
     x = _f32(x)
     w = _f32(w).reshape(-1)
     batch = x.shape[0]
     interm = np.empty((n_mat + 1, batch, width), dtype=np.float32)
     lib().oracle_mlp_forward(_ptr(x), _ptr(w), ctypes.c_int(n_mat), ctypes.c_int(width), ctypes.c_int(ACT[act]),
-                             ctypes.c_int(ACT[out_act]), ctypes.c_size_t(batch), ctypes.c_int(1 if bf16 else 0),
+                             ctypes.c_int(ACT[out_act]), ctypes.c_size_t(batch), ctypes.c_int(_mode(bf16)),
                              _ptr(interm), ctypes.c_int(n_threads))
     return interm
 
@@ -115,7 +132,7 @@ def mlp_backward(dy, interm, w, n_mat, width, act, out_act, bf16=True, want_dx=T
     dx = np.empty((batch, width), dtype=np.float32) if want_dx else None
     lib().oracle_mlp_backward(_ptr(dy), _ptr(interm), _ptr(w), ctypes.c_int(n_mat), ctypes.c_int(width),
                               ctypes.c_int(ACT[act]), ctypes.c_int(ACT[out_act]), ctypes.c_size_t(batch),
-                              ctypes.c_int(1 if bf16 else 0), _ptr(ibwd), _ptr(grads, ctypes.c_double),
+                              ctypes.c_int(_mode(bf16)), _ptr(ibwd), _ptr(grads, ctypes.c_double),
                               _ptr(dx) if want_dx else None, ctypes.c_int(n_threads))
     return ibwd, grads, dx
 
@@ -128,7 +145,7 @@ def l2_loss(pred, target, loss_scale=1.0, bf16_grads=False):
     grads = np.empty_like(pred)
     lib().oracle_l2_loss(_ptr(pred), _ptr(target), ctypes.c_int(target.shape[1]), ctypes.c_size_t(batch),
                          ctypes.c_int(stride), ctypes.c_float(loss_scale), _ptr(values), _ptr(grads),
-                         ctypes.c_int(1 if bf16_grads else 0))
+                         ctypes.c_int(_mode(bf16_grads)))
     return values, grads
 
 
@@ -156,6 +173,26 @@ def frequency_forward(x, n_frequencies, padded=None):
     out = np.empty((x.shape[0], padded), dtype=np.float32)
     lib().oracle_frequency_forward(_ptr(x), ctypes.c_size_t(x.shape[0]), ctypes.c_int(x.shape[1]),
                                    ctypes.c_int(n_frequencies), ctypes.c_int(padded), _ptr(out))
+    return out
+
+
+def frequency_backward_input(x, dy, n_frequencies):
+    """include/encodings/frequency.h:91-131: dL/dinput (batch x n_in) from dL/dy (batch x padded)."""
+    x, dy = _f32(x), _f32(dy)
+    dx = np.empty_like(x)
+    lib().oracle_frequency_backward_input(_ptr(x), _ptr(dy), ctypes.c_size_t(x.shape[0]), ctypes.c_int(x.shape[1]),
+                                          ctypes.c_int(n_frequencies), ctypes.c_int(dy.shape[1]), _ptr(dx))
+    return dx
+
+
+def spherical_harmonics_forward(x, degree, padded=None):
+    """include/encodings/spherical_harmonics.h:28-64: degree^2 real spherical harmonics of 2 x - 1, padded with 1."""
+    x = _f32(x)
+    assert x.shape[1] == 3 and 1 <= degree <= 8
+    padded = padded or degree * degree
+    out = np.empty((x.shape[0], padded), dtype=np.float32)
+    lib().oracle_spherical_harmonics_forward(_ptr(x), ctypes.c_size_t(x.shape[0]), ctypes.c_int(degree),
+                                             ctypes.c_int(padded), _ptr(out))
     return out
 
 
@@ -194,6 +231,15 @@ class Grid:
         lib().oracle_grid_forward(ctypes.byref(self.s), _ptr(x), _ptr(table), ctypes.c_size_t(x.shape[0]),
                                   ctypes.c_int(padded), _ptr(out), ctypes.c_int(n_threads))
         return out
+
+    def backward_input(self, x, table, dy, n_threads=0):
+        """dL/dinput (batch x D) from dL/dy (batch x padded): derivative of the interpolation with respect to x."""
+        x, dy = _f32(x), _f32(dy)
+        table = _f32(table).reshape(-1)
+        dx = np.empty_like(x)
+        lib().oracle_grid_backward_input(ctypes.byref(self.s), _ptr(x), _ptr(table), _ptr(dy), ctypes.c_size_t(x.shape[0]),
+                                         ctypes.c_int(dy.shape[1]), _ptr(dx), ctypes.c_int(n_threads))
+        return dx
 
     def backward(self, x, dy, n_threads=0):
         x = _f32(x)

@@ -54,9 +54,18 @@ def test_argument_errors_need_no_device(tnn_lib):
                      (b'{"otype": "Frequency", "n_dims_to_encode": 0, "n_frequencies": 1}', 0),
                      (b'{"otype": "Frequency", "n_dims_to_encode": 1, "n_frequencies": 1}', 1)):
         assert lib.tnn_encoding_create(cfg, pad, ctypes.byref(e)) != 0, cfg
-    assert lib.tnn_encoding_create(b'{"otype": "SphericalHarmonics", "n_dims_to_encode": 3, "degree": 4}', 0,
-                                   ctypes.byref(e)) != 0
-    assert b"outside the scope" in lib.tnn_last_error()
+    # spherical harmonics (spherical_harmonics.h:18-26, encoding_factory.h:55-72): 3-D only, degree in [1, 8]
+    for cfg, msg in ((b'{"otype": "SphericalHarmonics", "n_dims_to_encode": 2, "degree": 4}', b"3D directions"),
+                     (b'{"otype": "SphericalHarmonics", "n_dims_to_encode": 3, "degree": 9}', b"degree > 0 and <= 8"),
+                     (b'{"otype": "SphericalHarmonics", "n_dims_to_encode": 3, "degree": 0}', b"degree > 0 and <= 8"),
+                     (b'{"otype": "SphericalHarmonics", "n_dims_to_encode": 3}', b"misses degree")):
+        assert lib.tnn_encoding_create(cfg, 0, ctypes.byref(e)) != 0
+        assert msg in lib.tnn_last_error(), (cfg, lib.tnn_last_error())
+    # fp16 networks are accepted (argument checks come first either way)
+    assert lib.tnn_network_create(64, 64, 4, 0, 8, 48, 1, 1, ctypes.byref(h)) != 0
+    assert b"power of 2" in lib.tnn_last_error()
+    assert lib.tnn_network_create(64, 64, 4, 0, 8, 64, 2, 1, ctypes.byref(h)) != 0
+    assert b"Only fp16 and bf16" in lib.tnn_last_error()
 
 
 def test_no_device_means_loud_failure(tnn_lib):

@@ -82,6 +82,52 @@ def test_grid_forward_bit_exact_and_backward(tnn_lib, cfg):
         assert torch.equal(g1, g2)
 
 
+@pytest.mark.parametrize("deterministic", [False, True])
+@pytest.mark.parametrize("dy_dtype", [torch.float32, torch.bfloat16])
+def test_grid_backward_hand_checked_fixture(tnn_lib, deterministic, dy_dtype):
+    """The hand-derived gradient of tests/golden/grid_backward_handcheck.json (see make_grid_backward_fixture.py) on
+    the device, through both backward paths: every weight and upstream value is a binary fraction, so the sums are
+    exact in fp32 (and in bf16 for the upstream values) whatever the order."""
+    k = json.load(open(os.path.join(GOLDEN, "grid_backward_handcheck.json")))
+    enc = tnn_lib.create_encoding("HashGrid", dict(otype="HashGrid", **k["config"]), None, seed=1)
+    assert enc.n_params() == k["n_params"]
+    x, dy = _t(k["x"]), _t(k["dy"]).to(dy_dtype)
+    _, g = enc.bwd_with_encoding_grad(dy, x, False, False, deterministic=deterministic)
+    assert np.array_equal(g.cpu().numpy().reshape(-1), np.array(k["expected_grad"], dtype=np.float32))
+
+
+def test_grid_odd_padded_width(tnn_lib):
+    """A padded output width that is odd leaves every second row unaligned for two-feature vector stores: the kernel
+    must fall back to scalar stores (any padded width >= the natural one is valid, grid.h:683-694)."""
+    cfg = dict(n_dims_to_encode=3, n_levels=16, n_features_per_level=2, log2_hashmap_size=12, base_resolution=4)
+    g = O.Grid(**cfg)
+    enc = tnn_lib.create_encoding("HashGrid", dict(otype="HashGrid", **cfg), 33, seed=1)
+    table = synth.grid_table(g.n_params)
+    enc.set_params(_t(table))
+    p = np.random.default_rng(4).uniform(0, 1, (257, 3)).astype(np.float32)
+    ref = g.forward(p, table, padded=33)
+    assert np.array_equal(enc.fwd(_t(p)).cpu().numpy(), ref)
+    out16 = enc.fwd(_t(p), out_dtype=torch.bfloat16).float().cpu().numpy()
+    assert np.array_equal(out16, O.bf16_round(ref))
+
+
+def test_grid_deterministic_backward_reports_non_finite_upstream(tnn_lib):
+    """An inf or NaN in dL/dy must not disappear in the integer accumulation: every gradient of the call is NaN, so a
+    loss-scale overflow check on the gradients still fires (the fp32 path propagates it into the entries it touches)."""
+    cfg = dict(n_dims_to_encode=2, n_levels=4, n_features_per_level=2, log2_hashmap_size=10, base_resolution=4)
+    enc = tnn_lib.create_encoding("HashGrid", dict(otype="HashGrid", **cfg), None, seed=1)
+    x = torch.rand((64, 2), device="cuda")
+    dy = torch.rand((64, 8), device="cuda")
+    dy[5, 3] = float("nan")
+    _, g = enc.bwd_with_encoding_grad(dy, x, False, False, deterministic=True)
+    assert torch.isnan(g).all()
+    _, g = enc.bwd_with_encoding_grad(dy, x, False, False, deterministic=False)
+    assert torch.isnan(g).any()
+    dy[5, 3] = 0.25
+    _, g = enc.bwd_with_encoding_grad(dy, x, False, False, deterministic=True)
+    assert torch.isfinite(g).all()
+
+
 def test_grid_backward_zero_upstream(tnn_lib):
     """test/doctest_encodings.cpp:286-341: zero upstream gradient => zero gradients, parameters untouched."""
     enc = tnn_lib.create_encoding("HashGrid", BENCH_GRID, 32, seed=1)
@@ -171,6 +217,87 @@ def test_frequency_encoding(tnn_lib):
     out16 = enc.fwd(_t(x), out_dtype=torch.bfloat16).float().cpu().numpy()
     assert np.abs(out16 - ref).max() < 1e-2
     assert enc.bwd_with_encoding_grad(_t(ref), _t(x), False, False) == (None, None)
+
+
+def test_frequency_backward_input(tnn_lib):
+    """include/encodings/frequency.h:91-131 on the device, fp32 and bf16 upstream gradients."""
+    enc = tnn_lib.create_encoding("Frequency", dict(n_dims_to_encode=3, n_frequencies=4), 32)
+    rng = np.random.default_rng(2)
+    x = rng.uniform(-1, 1, (1000, 3)).astype(np.float32)
+    dy = rng.uniform(-1, 1, (1000, 32)).astype(np.float32)
+    ref = O.frequency_backward_input(x, dy, 4)
+    got = enc.bwd_input(_t(dy), _t(x)).cpu().numpy()
+    assert np.allclose(got, ref, rtol=1e-4, atol=1e-4 * np.abs(ref).max())
+    dyb = O.bf16_round(dy)
+    got = enc.bwd_input(_t(dyb).to(torch.bfloat16), _t(x)).cpu().numpy()
+    assert np.allclose(got, O.frequency_backward_input(x, dyb, 4), rtol=1e-4, atol=1e-4 * np.abs(ref).max())
+
+
+def test_identity_backward_input(tnn_lib):
+    enc = tnn_lib.create_encoding("Identity", dict(n_dims_to_encode=3, scale=2.0, offset=0.5), 16)
+    dy = torch.rand((64, 16), device="cuda")
+    x = torch.rand((64, 3), device="cuda")
+    assert torch.equal(enc.bwd_input(dy, x), dy[:, :3] * 2.0)
+
+
+@pytest.mark.parametrize("cfg", [dict(n_dims_to_encode=3), dict(n_dims_to_encode=2, interpolation="Smoothstep"),
+                                 dict(n_dims_to_encode=3, n_levels=4, n_features_per_level=4, log2_hashmap_size=12)])
+def test_grid_backward_input(tnn_lib, cfg):
+    """dL/dinput of the hash grid (the product kernel_grid_backward_input forms, grid.h:247-268) against the oracle's
+    double-precision derivative of the interpolation."""
+    g = O.Grid(**cfg)
+    enc = tnn_lib.create_encoding("HashGrid", dict(otype="HashGrid", **cfg), None, seed=1)
+    table = np.random.default_rng(5).uniform(-1, 1, g.n_params).astype(np.float32)
+    enc.set_params(_t(table))
+    rng = np.random.default_rng(6)
+    x = rng.uniform(0, 1, (2000, g.D)).astype(np.float32)
+    dy = rng.uniform(-1, 1, (2000, g.n_levels * g.F)).astype(np.float32)
+    ref = g.backward_input(x, table, dy)
+    got = enc.bwd_input(_t(dy), _t(x)).cpu().numpy()
+    ok, rel = O.within_tolerance(got, ref, 1e-4)
+    assert ok, rel
+
+
+def test_spherical_harmonics_encoding(tnn_lib):
+    """include/encodings/spherical_harmonics.h:28-64: known answers of the reference's tests (degree 4 at ones,
+    degree 1 padded) and the oracle on random inputs for every degree, fp32 and bf16 output."""
+    enc = tnn_lib.create_encoding("SphericalHarmonics", dict(n_dims_to_encode=3, degree=4), None)
+    kat = [0.2821, -0.4886, 0.4886, -0.4886, 1.0925, -1.0925, 0.6308, -1.0925, 0.0, -1.1801, 2.8906, -1.8282, 0.7464,
+           -1.8282, 0.0, 1.1801]
+    out = enc.fwd(torch.ones((10, 3), device="cuda")).cpu().numpy()
+    assert out.shape == (10, 16) and np.allclose(out, np.array(kat, np.float32)[None, :], atol=1e-3)
+    enc1 = tnn_lib.create_encoding("SphericalHarmonics", dict(n_dims_to_encode=3, degree=1), 3)
+    out = enc1.fwd(_t(np.arange(6).reshape(2, 3))).cpu().numpy()
+    assert np.allclose(out, [[0.2821, 1.0, 1.0]] * 2, atol=1e-3)
+    x = np.random.default_rng(8).uniform(0, 1, (999, 3)).astype(np.float32)
+    for degree in range(1, 9):
+        enc = tnn_lib.create_encoding("SphericalHarmonics", dict(n_dims_to_encode=3, degree=degree), 64)
+        ref = O.spherical_harmonics_forward(x, degree, padded=64)
+        got = enc.fwd(_t(x)).cpu().numpy()
+        assert np.abs(got - ref).max() <= 2e-5 * max(1.0, np.abs(ref).max()), degree
+        got16 = enc.fwd(_t(x), out_dtype=torch.bfloat16).float().cpu().numpy()
+        assert np.abs(got16 - ref).max() <= 1e-2 * np.abs(ref).max()
+    with pytest.raises(tnn_lib.TnnError, match="not yet implemented"):
+        enc.bwd_input(torch.zeros((8, 64), device="cuda"), torch.zeros((8, 3), device="cuda"))
+    for bad in (dict(n_dims_to_encode=2, degree=4), dict(n_dims_to_encode=3, degree=9), dict(n_dims_to_encode=3, degree=0),
+                dict(n_dims_to_encode=3)):
+        with pytest.raises(tnn_lib.TnnError):
+            tnn_lib.create_encoding("SphericalHarmonics", bad, None)
+
+
+def test_grid_forward_fp16_output_and_wide_padding(tnn_lib):
+    """fp16 output rows (for fp16 networks) and a padded width too wide for the tiled kernel's staging buffer."""
+    cfg = dict(n_dims_to_encode=3, n_levels=8, n_features_per_level=2, log2_hashmap_size=12, base_resolution=4)
+    g = O.Grid(**cfg)
+    table = synth.grid_table(g.n_params) * 1e3
+    p = np.random.default_rng(4).uniform(0, 1, (700, 3)).astype(np.float32)
+    for padded in (16, 64, 400):
+        enc = tnn_lib.create_encoding("HashGrid", dict(otype="HashGrid", **cfg), padded, seed=1)
+        enc.set_params(_t(table))
+        ref = g.forward(p, table, padded=padded)
+        assert np.array_equal(enc.fwd(_t(p)).cpu().numpy(), ref)
+        assert np.array_equal(enc.fwd(_t(p), out_dtype=torch.float16).float().cpu().numpy(), O.fp16_round(ref))
+        assert np.array_equal(enc.fwd(_t(p), out_dtype=torch.bfloat16).float().cpu().numpy(), O.bf16_round(ref))
 
 
 def test_encoding_errors(tnn_lib):

@@ -201,3 +201,31 @@ def test_set_params_roundtrip_through_the_module(tnn_lib):
     for _ in range(n_hidden + 1):
         expect = (expect * wv * width).to(torch.bfloat16).float()
     assert torch.allclose(y, torch.full_like(y, expect.item()), rtol=2e-2)
+
+
+def test_network_with_identity_encoding_runs_folded_and_equals_the_sequential_path(tnn_lib):
+    """NetworkWithInputEncoding (modules.py:357-421 of the reference) with an Identity encoding: the single-kernel
+    path (encoding folded into the first-layer load) returns the bits of the two-module Sequential path, in eval and
+    in training mode, and the same parameter gradient; ragged batches are padded to 8 rows."""
+    import tiny_dpcpp_nn as tnn
+
+    net_cfg = {"n_neurons": 64, "n_hidden_layers": 4, "activation": "relu", "output_activation": "none"}
+    enc_cfg = {"otype": "Identity", "scale": 1.0, "offset": 0.0}
+    model = tnn.NetworkWithInputEncoding(2, 3, net_cfg, enc_cfg, seed=11)
+    assert model._foldable()
+    x = torch.rand((1000 + 3, 2), device="cuda")
+    tgt = torch.rand((1000 + 3, 3), device="cuda")
+    model.eval()
+    with torch.no_grad():
+        y_folded = model(x)
+        y_seq = model.network_with_encoding(x)
+    assert y_folded.shape == (1003, 3) and torch.equal(y_folded, y_seq)
+    model.train()
+    grads = []
+    for fn in (model, model.network_with_encoding):
+        model.zero_grad(set_to_none=True)
+        out = fn(x)
+        ((out.float() - tgt) ** 2).mean().backward()
+        grads.append(model.params.grad.clone())
+        assert torch.equal(out, y_seq)
+    assert torch.equal(grads[0], grads[1]) and grads[0].abs().sum() > 0

@@ -57,6 +57,23 @@ def test_grid_backward_is_adjoint_of_forward():
     assert abs(lhs - rhs) <= 1e-5 * max(abs(lhs), 1.0)
 
 
+def test_grid_backward_hand_checked_fixture():
+    """tests/golden/grid_backward_handcheck.json: the parameter gradient of five samples on a 2-level 2-D dense grid,
+    derived by explicit corner enumeration in tests/golden/make_grid_backward_fixture.py (independent of the oracle;
+    two entries worked by hand in that file).  Pins the oracle's backward, which the reference's own tests cannot
+    (their backward fixtures are CSV files that are not in the reference repository)."""
+    k = json.load(open(os.path.join(GOLDEN, "grid_backward_handcheck.json")))
+    c = k["config"]
+    g = O.Grid(n_dims_to_encode=c["n_dims_to_encode"], n_levels=c["n_levels"],
+               n_features_per_level=c["n_features_per_level"], log2_hashmap_size=c["log2_hashmap_size"],
+               base_resolution=c["base_resolution"], per_level_scale=c["per_level_scale"], type=c["type"])
+    assert g.n_params == k["n_params"] and list(g.offsets) == [0, 16, 80]
+    grads = g.backward(np.array(k["x"], np.float32), np.array(k["dy"], np.float32))
+    assert np.array_equal(grads, np.array(k["expected_grad"]))  # binary fractions: exact
+    # the two entries worked by hand in the generator's docstring
+    assert grads[10 * 2] == 1.0 + 0.0625 + 0.5 * 0.0625 and grads[52 * 2] == 3.0 and grads[52 * 2 + 1] == 4.0
+
+
 @pytest.mark.parametrize("dims,interp,gtype", [(2, "Linear", "Hash"), (3, "Smoothstep", "Hash"),
                                                (2, "Nearest", "Dense"), (3, "Linear", "Tiled")])
 def test_grid_variants_run(dims, interp, gtype):
@@ -201,3 +218,79 @@ def test_identity_pads_with_ones():
     x = np.array([[0.25, 0.5]], dtype=np.float32)
     out = O.identity_forward(x, 8, scale=2.0, offset=1.0)
     assert np.allclose(out[0], [1.5, 2.0, 1, 1, 1, 1, 1, 1])
+
+
+def test_spherical_harmonics_known_answer_and_definition():
+    """test/python/test_encodings.py:377-573 (degree 4, input ones -> direction (1, 1, 1)) and
+    test/doctest_encodings.cpp:197-231 (degree 1, padded with ones); beyond degree 4 the reference has no vectors, so
+    the restatement is checked against an independent evaluation of the defining formula (scipy's complex spherical
+    harmonics, which carry the same Condon-Shortley phase) on the unit sphere, and against orthonormality."""
+    kat = [0.2821, -0.4886, 0.4886, -0.4886, 1.0925, -1.0925, 0.6308, -1.0925, 0.0, -1.1801, 2.8906, -1.8282, 0.7464,
+           -1.8282, 0.0, 1.1801]
+    out = O.spherical_harmonics_forward(np.ones((10, 3), np.float32), 4)
+    assert np.allclose(out, np.array(kat, np.float32)[None, :], atol=1e-3)
+    x = np.arange(6, dtype=np.float32).reshape(2, 3)
+    assert np.allclose(O.spherical_harmonics_forward(x, 1, padded=3), [[0.2821, 1.0, 1.0]] * 2, atol=1e-3)
+    from scipy.special import sph_harm_y
+
+    rng = np.random.default_rng(0)
+    v = rng.normal(size=(500, 3))
+    v /= np.linalg.norm(v, axis=1, keepdims=True)
+    inp = ((v + 1) / 2).astype(np.float32)
+    out = O.spherical_harmonics_forward(inp, 8)
+    d = inp.astype(np.float64) * 2 - 1
+    az, pol = np.arctan2(d[:, 1], d[:, 0]), np.arccos(np.clip(d[:, 2] / np.linalg.norm(d, axis=1), -1, 1))
+    for l in range(8):
+        for m in range(-l, l + 1):
+            y = sph_harm_y(l, abs(m), pol, az)
+            ref = np.sqrt(2) * y.real if m > 0 else (np.sqrt(2) * y.imag if m < 0 else y.real)
+            assert np.abs(out[:, l * (l + 1) + m] - ref).max() < 2e-5, (l, m)
+    # orthonormality over the sphere (Monte-Carlo, 200k directions): the Gram matrix is the identity
+    v = rng.normal(size=(200000, 3))
+    v /= np.linalg.norm(v, axis=1, keepdims=True)
+    y = O.spherical_harmonics_forward(((v + 1) / 2).astype(np.float32), 8).astype(np.float64)
+    gram = 4 * np.pi * (y.T @ y) / len(v)
+    assert np.abs(gram - np.eye(64)).max() < 0.05
+
+
+def test_frequency_backward_input_is_the_derivative_of_the_forward():
+    """include/encodings/frequency.h:72-73, 91-131: dL/dx = sum_k dL/dy_k 2^f pi cos(arg_k); checked against central
+    differences of the pinned forward."""
+    rng = np.random.default_rng(3)
+    x = rng.uniform(-1, 1, (7, 2)).astype(np.float32)
+    dy = rng.uniform(-1, 1, (7, 2 * 3 * 2 + 4)).astype(np.float32)  # padded output: the padding carries no gradient
+    dx = O.frequency_backward_input(x, dy, 3)
+    eps = 1e-3
+    for j in range(2):
+        xp, xm = x.copy(), x.copy()
+        xp[:, j] += eps
+        xm[:, j] -= eps
+        fp = O.frequency_forward(xp, 3, padded=16).astype(np.float64)
+        fm = O.frequency_forward(xm, 3, padded=16).astype(np.float64)
+        num = ((fp - fm) * dy).sum(1) / (xp[:, j].astype(np.float64) - xm[:, j])
+        assert np.allclose(num, dx[:, j], rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("interp", ["Linear", "Smoothstep"])
+def test_grid_backward_input_is_the_derivative_of_the_forward(interp):
+    """dL/dinput of the grid against central differences of the pinned forward (2-D and 3-D)."""
+    for dims in (2, 3):
+        g = O.Grid(n_dims_to_encode=dims, n_levels=4, log2_hashmap_size=12, base_resolution=4, interpolation=interp)
+        rng = np.random.default_rng(dims)
+        x = rng.uniform(0.05, 0.95, (32, dims)).astype(np.float32)
+        t = rng.uniform(-1, 1, g.n_params).astype(np.float32)
+        dy = rng.uniform(-1, 1, (32, 8)).astype(np.float32)
+        dx = g.backward_input(x, t, dy)
+        eps = 1e-4
+        for d in range(dims):
+            xp, xm = x.copy(), x.copy()
+            xp[:, d] += eps
+            xm[:, d] -= eps
+            num = ((g.forward(xp, t).astype(np.float64) - g.forward(xm, t).astype(np.float64)) * dy).sum(1) \
+                / (xp[:, d].astype(np.float64) - xm[:, d])
+            # (a sample within eps of a cell boundary sees a kink: allow a few outliers)
+            close = np.isclose(num, dx[:, d], rtol=5e-3, atol=5e-3 * np.abs(dx).max())
+            assert close.mean() >= 0.9, (dims, d, close.mean())
+    assert not O.Grid(n_dims_to_encode=2, n_levels=2, interpolation="Nearest").backward_input(
+        x[:, :2], np.zeros(O.Grid(n_dims_to_encode=2, n_levels=2, interpolation="Nearest").n_params, np.float32),
+        dy[:, :4]).any()

@@ -134,8 +134,7 @@ int tnn_network_create(int input_width, int output_width, int n_hidden_layers, i
     TNN_GUARD_BEGIN
     if (!out) return fail("out is null");
     *out = nullptr;
-    if (dtype == TNN_DTYPE_FP16) return fail("fp16 networks are not implemented; use bf16");
-    if (dtype != TNN_DTYPE_BF16) return fail("Unsupported dtype. Only bf16 is supported");
+    if (dtype != TNN_DTYPE_BF16 && dtype != TNN_DTYPE_FP16) return fail("Unsupported dtype. Only fp16 and bf16 are supported");
     if (width != 16 && width != 32 && width != 64 && width != 128)
         return fail("Network width has to be a power of 2 between 16 and 128.");
     if (input_width <= 0) return fail("Input width of " + std::to_string(input_width) + " is not supported. Value must be larger than 0.");
@@ -156,6 +155,7 @@ int tnn_network_create(int input_width, int output_width, int n_hidden_layers, i
     n->act = activation;
     n->out_act = output_activation;
     n->use_bias = use_bias ? 1 : 0;
+    n->fp16 = dtype == TNN_DTYPE_FP16 ? 1 : 0;
     n->n_params = (size_t)n->n_mat * width * width;
     if (n->one_padded_input() > width) {
         delete n;
@@ -211,9 +211,10 @@ int tnn_network_set_variant(tnn_network *n, int variant) {
 int tnn_network_set_params(tnn_network *n, const void *params, int dtype, int packed, void *stream) {
     TNN_GUARD_BEGIN
     if (!n || !params) return fail("null argument");
-    if (dtype != TNN_DTYPE_BF16 && dtype != TNN_DTYPE_FP32) return fail("params must be bf16 or fp32");
-    TNN_CUDA(tnn::launch_set_params(n->width, params, dtype == TNN_DTYPE_FP32, packed, n->n_mat, n->one_padded_input(),
-                                    n->output_width, n->packed, nullptr, n->wimg, n->wimg_t, (cudaStream_t)stream));
+    if (dtype != TNN_DTYPE_BF16 && dtype != TNN_DTYPE_FP16 && dtype != TNN_DTYPE_FP32)
+        return fail("params must be bf16, fp16 or fp32");
+    TNN_CUDA(tnn::launch_set_params(n->width, params, dtype, packed, n->n_mat, n->one_padded_input(), n->output_width,
+                                    n->fp16, n->packed, nullptr, n->wimg, n->wimg_t, (cudaStream_t)stream));
     return 0;
     TNN_GUARD_END
 }
@@ -237,8 +238,8 @@ int tnn_network_initialize_params(tnn_network *n, uint64_t seed, void *stream) {
     cudaError_t e = cudaMemcpyAsync(tmp, w.data(), w.size() * sizeof(float), cudaMemcpyHostToDevice, (cudaStream_t)stream);
     // the reference fills the matrices in their stored (packed) order
     if (e == cudaSuccess)
-        e = tnn::launch_set_params(W, tmp, 1, 1, n->n_mat, n->one_padded_input(), n->output_width, n->packed, nullptr,
-                                   n->wimg, n->wimg_t, (cudaStream_t)stream);
+        e = tnn::launch_set_params(W, tmp, TNN_DTYPE_FP32, 1, n->n_mat, n->one_padded_input(), n->output_width, n->fp16,
+                                   n->packed, nullptr, n->wimg, n->wimg_t, (cudaStream_t)stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
     cudaFree(tmp);
     TNN_CUDA(e);
@@ -256,25 +257,32 @@ int tnn_network_get_params(const tnn_network *n, void *out, void *stream) {
 // copy_input: matrix 0 of the workspace becomes a copy of x, as callers of the C ABI expect; the training path of
 // this library reads x itself in its backward pass and skips the copy.
 // enc: when set, the kernel produces its input tiles from fp32 coordinates (folded identity encoding) and x is unused
+// grid / grid_x: when set, extra warps of the kernel gather the hash-grid encoding of the fp32 positions grid_x
 static int run_forward(tnn_network *n, const void *x, void *y, void *interm, size_t batch, void *stream,
-                       bool copy_input = true, const tnn::EncodedInput *enc = nullptr) {
+                       bool copy_input = true, const tnn::EncodedInput *enc = nullptr, const tnn_encoding *grid = nullptr,
+                       const float *grid_x = nullptr) {
     TNN_GUARD_BEGIN
     if (!n) return fail("network is null");
     if (batch == 0) return 0;
-    if (!x && !enc) return fail("input is null");
+    if (!x && !enc && !grid) return fail("input is null");
     if (batch % 8 != 0) return fail("Batch size is not divisible by 8."); // SwiftNetMLP.h:293-302
     if (batch > (size_t)1 << 30) return fail("batch too large");
     if (!y && !interm) return fail("forward needs y or interm_fwd");
     tnn::FwdLaunch p{};
     if (y) make_act_tmap(&p.tm_y, y, batch, n->width, 1);
     if (interm) make_act_tmap(&p.tm_interm, interm, batch, n->width, n->n_mat + 1);
-    if (enc)
+    if (grid) {
+        p.grid_params = grid->gp_dev;
+        p.grid_table = grid->params();
+        p.grid_x = grid_x;
+    } else if (enc) {
         p.enc = *enc;
-    else
+    } else {
         make_act_tmap(&p.tm_x, x, batch, n->width, 1);
+    }
     // (maps that a launch does not use are never dereferenced; give them a valid value all the same)
     const CUtensorMap &any = y ? p.tm_y : p.tm_interm;
-    if (enc) p.tm_x = any;
+    if (enc || grid) p.tm_x = any;
     if (!y) p.tm_y = any;
     if (!interm) p.tm_interm = any;
     p.wimg = n->wimg;
@@ -284,15 +292,20 @@ static int run_forward(tnn_network *n, const void *x, void *y, void *interm, siz
     p.n_mat = n->n_mat;
     p.act = n->act;
     p.out_act = n->out_act;
+    p.fp16 = n->fp16;
     p.store_all = interm ? 1 : 0;
     p.write_y = y ? 1 : 0;
     p.variant = n->variant;
     p.n_sm = n->n_sm;
     p.status = n->status;
     p.stream = (cudaStream_t)stream;
-    if (interm && copy_input && !enc) // matrix 0 of the forward workspace is a copy of the input (kernel_esimd.h:601-605)
+    if (interm && copy_input && !enc && !grid) // matrix 0 of the forward workspace is a copy of the input (kernel_esimd.h:601-605)
         TNN_CUDA(cudaMemcpyAsync(interm, x, batch * n->width * sizeof(__nv_bfloat16), cudaMemcpyDeviceToDevice, p.stream));
     cudaError_t e = tnn::launch_mlp_fwd(p);
+    if (e == cudaErrorInvalidConfiguration && grid) {
+        cudaGetLastError();
+        return -1; // the caller falls back to the two-kernel path
+    }
     if (e == cudaErrorInvalidConfiguration)
         return fail("this width / depth does not fit the on-chip weight staging of the forward kernel");
     TNN_CUDA(e);
@@ -318,7 +331,8 @@ static int run_backward(tnn_network *n, const void *dy, const void *interm_fwd, 
     TNN_GUARD_BEGIN
     if (!n) return fail("network is null");
     if (!grads && !n_slabs_out) return fail("grads is null");
-    if (grads_dtype != TNN_DTYPE_BF16 && grads_dtype != TNN_DTYPE_FP32) return fail("grads must be bf16 or fp32");
+    if (grads_dtype != TNN_DTYPE_BF16 && grads_dtype != TNN_DTYPE_FP16 && grads_dtype != TNN_DTYPE_FP32)
+        return fail("grads must be bf16, fp16 or fp32");
     cudaStream_t s = (cudaStream_t)stream;
     if (batch == 0) {
         const size_t esz = grads_dtype == TNN_DTYPE_FP32 ? 4 : 2;
@@ -347,6 +361,7 @@ static int run_backward(tnn_network *n, const void *dy, const void *interm_fwd, 
     p.n_mat = n->n_mat;
     p.act = n->act;
     p.out_act = n->out_act;
+    p.fp16 = n->fp16;
     p.store_bwd = interm_bwd ? 1 : 0;
     p.want_dx = dx ? 1 : 0;
     p.variant = n->variant;
@@ -363,7 +378,8 @@ static int run_backward(tnn_network *n, const void *dy, const void *interm_fwd, 
     }
     TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, p.grid_out, n->n_mat, n->width, pack_transpose, 1.0f,
                                    grads_dtype == TNN_DTYPE_FP32 ? (float *)grads : nullptr,
-                                   grads_dtype == TNN_DTYPE_BF16 ? (__nv_bfloat16 *)grads : nullptr, s));
+                                   grads_dtype != TNN_DTYPE_FP32 ? (__nv_bfloat16 *)grads : nullptr,
+                                   grads_dtype == TNN_DTYPE_FP16, s));
     return 0;
     TNN_GUARD_END
 }
@@ -406,7 +422,8 @@ static int train_step_impl(tnn_network *n, const void *x, const tnn::EncodedInpu
     TNN_GUARD_BEGIN
     if (!n) return fail("network is null");
     if (!grads && !raw) return fail("grads is null");
-    if (grads_dtype != TNN_DTYPE_BF16 && grads_dtype != TNN_DTYPE_FP32) return fail("grads must be bf16 or fp32");
+    if (grads_dtype != TNN_DTYPE_BF16 && grads_dtype != TNN_DTYPE_FP16 && grads_dtype != TNN_DTYPE_FP32)
+        return fail("grads must be bf16, fp16 or fp32");
     if (batch == 0) return fail("batch_size == 0");
     if ((!x && !enc) || !targets) return fail("x and targets are required");
     if (batch % 8 != 0) return fail("Batch size is not divisible by 8.");
@@ -415,7 +432,7 @@ static int train_step_impl(tnn_network *n, const void *x, const tnn::EncodedInpu
     if (reinterpret_cast<uintptr_t>(targets) % 4 != 0) return fail("targets must be 4-byte aligned");
     cudaStream_t s = (cudaStream_t)stream;
     float *gf = grads_dtype == TNN_DTYPE_FP32 ? (float *)grads : nullptr;
-    __nv_bfloat16 *gb = grads_dtype == TNN_DTYPE_BF16 ? (__nv_bfloat16 *)grads : nullptr;
+    __nv_bfloat16 *gb = grads_dtype != TNN_DTYPE_FP32 ? (__nv_bfloat16 *)grads : nullptr;
 
     if (!(n->variant & 16) && !dx) { // fused single-kernel path
         tnn::TrainLaunch p{};
@@ -436,6 +453,8 @@ static int train_step_impl(tnn_network *n, const void *x, const tnn::EncodedInpu
         p.n_mat = n->n_mat;
         p.act = n->act;
         p.out_act = n->out_act;
+        p.fp16 = n->fp16;
+    p.fp16 = n->fp16;
         p.loss_scale = loss_scale;
         p.n_sm = n->n_sm;
         p.status = n->status;
@@ -452,7 +471,8 @@ static int train_step_impl(tnn_network *n, const void *x, const tnn::EncodedInpu
         }
         if (e == cudaSuccess) {
             if (loss_sum) TNN_CUDA(tnn::launch_sum_partials(n->loss_partials, p.grid_out, loss_sum, s));
-            TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, p.grid_out, n->n_mat, n->width, pack_transpose, 1.0f, gf, gb, s));
+            TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, p.grid_out, n->n_mat, n->width, pack_transpose, 1.0f, gf, gb,
+                                           grads_dtype == TNN_DTYPE_FP16, s));
             return 0;
         }
         if (e != cudaErrorInvalidConfiguration) TNN_CUDA(e);
@@ -464,7 +484,7 @@ static int train_step_impl(tnn_network *n, const void *x, const tnn::EncodedInpu
     // (with an encoded input the forward kernel stores the encoded tile as matrix 0, which the backward pass reads)
     if (int rc = run_forward(n, x, nullptr, interm, batch, stream, /*copy_input=*/false, enc)) return rc;
     const __nv_bfloat16 *pred = interm + (size_t)n->n_mat * batch * n->width;
-    TNN_CUDA(tnn::launch_l2_loss(pred, targets, n_targets, nullptr, ws_dy, batch, n->width, loss_scale,
+    TNN_CUDA(tnn::launch_l2_loss(pred, n->fp16, targets, n_targets, nullptr, ws_dy, batch, n->width, loss_scale,
                                  (loss_sum || raw) ? n->loss_partials : nullptr, 1024, raw ? nullptr : loss_sum, s));
     if (raw) raw[1] = 1024;
     return run_backward(n, ws_dy, interm, enc ? nullptr : x, grads, grads_dtype, pack_transpose, dx, nullptr, batch, stream,
@@ -511,15 +531,22 @@ int tnn_network_adam_step(tnn_network *n, float *master, float *m, float *v, con
     if (step < 1) return fail("step counts from 1");
     cudaStream_t s = (cudaStream_t)stream;
     TNN_CUDA(tnn::launch_adam(master, m, v, grads, n->n_params, grad_scale, step, lr, beta1, beta2, eps, nullptr, s));
-    TNN_CUDA(tnn::launch_set_params(n->width, master, 1, 1, n->n_mat, n->one_padded_input(), n->output_width, n->packed,
-                                    nullptr, n->wimg, n->wimg_t, s));
+    TNN_CUDA(tnn::launch_set_params(n->width, master, TNN_DTYPE_FP32, 1, n->n_mat, n->one_padded_input(), n->output_width,
+                                    n->fp16, n->packed, nullptr, n->wimg, n->wimg_t, s));
     return 0;
     TNN_GUARD_END
 }
 
 int tnn_l2_loss(const void *pred, const float *target, int n_targets, float *values, void *grads, size_t batch,
                 int stride, float loss_scale, float *loss_sum, void *stream) {
+    return tnn_l2_loss_dtype(pred, TNN_DTYPE_BF16, target, n_targets, values, grads, batch, stride, loss_scale, loss_sum,
+                             stream);
+}
+
+int tnn_l2_loss_dtype(const void *pred, int dtype, const float *target, int n_targets, float *values, void *grads,
+                      size_t batch, int stride, float loss_scale, float *loss_sum, void *stream) {
     TNN_GUARD_BEGIN
+    if (dtype != TNN_DTYPE_BF16 && dtype != TNN_DTYPE_FP16) return fail("pred must be bf16 or fp16");
     if (batch == 0) return 0;
     if (!pred || !target) return fail("null argument");
     if (n_targets <= 0 || n_targets > stride) return fail("n_targets must be in [1, stride]");
@@ -541,8 +568,9 @@ int tnn_l2_loss(const void *pred, const float *target, int n_targets, float *val
         if (!partials[dev]) TNN_CUDA(cudaMalloc(&partials[dev], kPartials * sizeof(float)));
         buf = partials[dev];
     }
-    TNN_CUDA(tnn::launch_l2_loss((const __nv_bfloat16 *)pred, target, n_targets, values, (__nv_bfloat16 *)grads, batch,
-                                 stride, loss_scale, buf, kPartials, loss_sum, (cudaStream_t)stream));
+    TNN_CUDA(tnn::launch_l2_loss((const __nv_bfloat16 *)pred, dtype == TNN_DTYPE_FP16, target, n_targets, values,
+                                 (__nv_bfloat16 *)grads, batch, stride, loss_scale, buf, kPartials, loss_sum,
+                                 (cudaStream_t)stream));
     return 0;
     TNN_GUARD_END
 }
@@ -640,7 +668,15 @@ int tnn_encoding_create(const char *json_config, int padded_output_width, tnn_en
         enc->n_in = (int)nd;
         enc->n_out = enc->n_in * enc->n_frequencies * 2;
     } else if (name == "SphericalHarmonics") {
-        return fail("encoding type " + name + " is outside the scope of this library (HashGrid, Identity and Frequency only)");
+        // encoding_factory.h:55-72, spherical_harmonics.h:18-26
+        if (!cfg.has("degree")) return fail("Config misses degree");
+        if (!cfg.has("n_dims_to_encode")) return fail("Config misses n_dims_to_encode");
+        const double degree = cfg.at("degree").num;
+        if ((int)cfg.at("n_dims_to_encode").num != 3) return fail("Can only encode 3D directions in spherical harmonics.");
+        if (degree < 1.0 || degree > 8.0) return fail("Spherical harmonics degree > 0 and <= 8.");
+        enc->sh_degree = (int)degree;
+        enc->n_in = 3;
+        enc->n_out = enc->sh_degree * enc->sh_degree;
     } else {
         return fail("Unknown encoding type: " + name);
     }
@@ -652,6 +688,8 @@ int tnn_encoding_create(const char *json_config, int padded_output_width, tnn_en
         enc->gp.padded_width = (uint32_t)enc->padded;
         TNN_CUDA(cudaMalloc(&enc->table, enc->n_params * sizeof(float)));
         TNN_CUDA(cudaMemset(enc->table, 0, enc->n_params * sizeof(float)));
+        TNN_CUDA(cudaMalloc(&enc->gp_dev, sizeof(tnn::GridParams)));
+        TNN_CUDA(cudaMemcpy(enc->gp_dev, &enc->gp, sizeof(tnn::GridParams), cudaMemcpyHostToDevice));
     }
     *out = enc.release();
     return 0;
@@ -661,6 +699,7 @@ int tnn_encoding_create(const char *json_config, int padded_output_width, tnn_en
 int tnn_encoding_destroy(tnn_encoding *e) {
     if (!e) return 0;
     cudaFree(e->table);
+    cudaFree(e->gp_dev);
     cudaFree(e->scratch);
     delete e;
     return 0;
@@ -723,15 +762,19 @@ int tnn_encoding_forward(tnn_encoding *e, const float *x, void *out, int out_dty
     if (!e) return fail("encoding is null");
     if (batch == 0) return 0;
     if (!x || !out) return fail("null argument");
-    if (out_dtype != TNN_DTYPE_FP32 && out_dtype != TNN_DTYPE_BF16) return fail("output must be fp32 or bf16");
+    if (out_dtype != TNN_DTYPE_FP32 && out_dtype != TNN_DTYPE_BF16 && out_dtype != TNN_DTYPE_FP16)
+        return fail("output must be fp32, bf16 or fp16");
     if (batch > 0xFFFFFFFFull / 8) return fail("batch too large");
-    const int bf = out_dtype == TNN_DTYPE_BF16;
     if (e->is_grid)
-        TNN_CUDA(tnn::launch_grid_fwd(e->gp, x, e->params(), out, bf, batch, (cudaStream_t)stream));
+        TNN_CUDA(tnn::launch_grid_fwd(e->gp, x, e->params(), out, out_dtype, batch, (cudaStream_t)stream));
     else if (e->n_frequencies > 0)
-        TNN_CUDA(tnn::launch_frequency_fwd(x, out, bf, batch, e->n_in, e->n_frequencies, e->padded, (cudaStream_t)stream));
+        TNN_CUDA(tnn::launch_frequency_fwd(x, out, out_dtype, batch, e->n_in, e->n_frequencies, e->padded,
+                                           (cudaStream_t)stream));
+    else if (e->sh_degree > 0)
+        TNN_CUDA(tnn::launch_spherical_harmonics_fwd(x, out, out_dtype, batch, e->sh_degree, e->padded, (cudaStream_t)stream));
     else
-        TNN_CUDA(tnn::launch_identity_fwd(x, out, bf, batch, e->n_in, e->padded, e->scale, e->offset, (cudaStream_t)stream));
+        TNN_CUDA(tnn::launch_identity_fwd(x, out, out_dtype, batch, e->n_in, e->padded, e->scale, e->offset,
+                                          (cudaStream_t)stream));
     return 0;
     TNN_GUARD_END
 }
@@ -745,7 +788,8 @@ int tnn_encoding_backward(tnn_encoding *e, const float *x, const void *dy, int d
     cudaStream_t s = (cudaStream_t)stream;
     if (batch == 0) return fail("batch_size == 0"); // grid.h:744
     if (!x || !dy) return fail("null argument");
-    if (dy_dtype != TNN_DTYPE_FP32 && dy_dtype != TNN_DTYPE_BF16) return fail("dy must be fp32 or bf16");
+    if (dy_dtype != TNN_DTYPE_FP32 && dy_dtype != TNN_DTYPE_BF16 && dy_dtype != TNN_DTYPE_FP16)
+        return fail("dy must be fp32, bf16 or fp16");
     if (batch > 0xFFFFFFFFull / 8) return fail("batch too large");
     if (reinterpret_cast<uintptr_t>(grads) % 16 != 0) return fail("grads must be 16-byte aligned (vector reductions)");
     size_t need = deterministic ? tnn::grid_bwd_scratch_bytes(e->gp, batch) : 0;
@@ -757,7 +801,7 @@ int tnn_encoding_backward(tnn_encoding *e, const float *x, const void *dy, int d
         TNN_CUDA(cudaMalloc(&e->scratch, need));
         e->scratch_bytes = need;
     }
-    TNN_CUDA(tnn::launch_grid_bwd(e->gp, x, dy, dy_dtype == TNN_DTYPE_BF16, grads, batch,
+    TNN_CUDA(tnn::launch_grid_bwd(e->gp, x, dy, dy_dtype, grads, batch,
                                   deterministic ? e->scratch : nullptr, e->scratch_bytes, s));
     return 0;
     TNN_GUARD_END
@@ -765,12 +809,39 @@ int tnn_encoding_backward(tnn_encoding *e, const float *x, const void *dy, int d
 
 } // extern "C"
 
+extern "C" int tnn_encoding_backward_input(tnn_encoding *e, const float *x, const void *dy, int dy_dtype, float *dx,
+                                          size_t batch, void *stream) {
+    TNN_GUARD_BEGIN
+    if (!e) return fail("encoding is null");
+    if (batch == 0) return fail("batch_size == 0");
+    if (!x || !dy || !dx) return fail("null argument");
+    if (dy_dtype != TNN_DTYPE_FP32 && dy_dtype != TNN_DTYPE_BF16 && dy_dtype != TNN_DTYPE_FP16)
+        return fail("dy must be fp32, bf16 or fp16");
+    if (batch > 0xFFFFFFFFull / 8) return fail("batch too large");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (e->sh_degree > 0) return fail("Spherical backward not yet implemented."); // spherical_harmonics.h:66-71
+    if (e->is_grid)
+        TNN_CUDA(tnn::launch_grid_bwd_input(e->gp, x, e->params(), dy, dy_dtype, dx, batch, s));
+    else if (e->n_frequencies > 0)
+        TNN_CUDA(tnn::launch_frequency_bwd_input(x, dy, dy_dtype, dx, batch, e->n_in, e->n_frequencies, e->padded, s));
+    else
+        TNN_CUDA(tnn::launch_identity_bwd_input(dy, dy_dtype, dx, batch, e->n_in, e->padded, e->scale, s));
+    return 0;
+    TNN_GUARD_END
+}
+
 // ======================================================================== network with input encoding
 namespace {
 
 // The identity encoding can be folded into the network kernels' first-layer load.
 bool foldable(const tnn_encoding *e) {
-    return !e->is_grid && e->n_frequencies == 0 && e->n_in <= tnn::kMaxFoldedInputs;
+    return !e->is_grid && e->n_frequencies == 0 && e->sh_degree == 0 && e->n_in <= tnn::kMaxFoldedInputs;
+}
+
+// The fused kernel covers the common grids: 2-D / 3-D, two features per level, all features inside the network width.
+bool grid_fusable(const tnn_network *n, const tnn_encoding *e) {
+    return e->is_grid && e->gp_dev && (e->gp.n_dims == 2 || e->gp.n_dims == 3) && e->gp.features_per_level == 2 &&
+           (int)e->gp.n_features <= n->width && e->padded == n->width;
 }
 
 int nwe_checks(const tnn_network *n, const tnn_encoding *e, const float *x, size_t batch) {
@@ -807,6 +878,11 @@ int tnn_network_with_encoding_forward(tnn_network *n, tnn_encoding *e, const flo
         const tnn::EncodedInput enc{x, e->n_in, e->scale, e->offset};
         return run_forward(n, nullptr, y, interm_fwd, batch, stream, false, &enc);
     }
+    if (grid_fusable(n, e) && !(n->variant & 16)) {
+        // hash grid: gathered by extra warps of the network kernel straight into its input tile
+        const int rc = run_forward(n, nullptr, y, interm_fwd, batch, stream, false, nullptr, e, x);
+        if (rc >= 0) return rc;
+    }
     // other encodings: the encoded rows go through matrix 0 of interm_fwd when the caller provides it (that is where
     // the backward pass expects the network input), else through the handle's workspace
     void *encoded = interm_fwd;
@@ -814,7 +890,7 @@ int tnn_network_with_encoding_forward(tnn_network *n, tnn_encoding *e, const flo
         if (int rc = ensure_workspace(n, batch * n->width * sizeof(__nv_bfloat16), (cudaStream_t)stream)) return rc;
         encoded = n->ws;
     }
-    if (int rc = tnn_encoding_forward(e, x, encoded, TNN_DTYPE_BF16, batch, stream)) return rc;
+    if (int rc = tnn_encoding_forward(e, x, encoded, n->fp16 ? TNN_DTYPE_FP16 : TNN_DTYPE_BF16, batch, stream)) return rc;
     return run_forward(n, encoded, y, interm_fwd, batch, stream, /*copy_input=*/false);
     TNN_GUARD_END
 }
@@ -843,12 +919,13 @@ static int nwe_train_step_impl(tnn_network *n, tnn_encoding *e, const float *x, 
     const size_t mat = batch * n->width * sizeof(__nv_bfloat16);
     void *encoded = base + (size_t)(n->n_mat + 2) * mat;
     void *dx = want_enc_grads ? base + (size_t)(n->n_mat + 3) * mat : nullptr;
-    if (int rc = tnn_encoding_forward(e, x, encoded, TNN_DTYPE_BF16, batch, stream)) return rc;
+    const int net_dtype = n->fp16 ? TNN_DTYPE_FP16 : TNN_DTYPE_BF16;
+    if (int rc = tnn_encoding_forward(e, x, encoded, net_dtype, batch, stream)) return rc;
     if (int rc = train_step_impl(n, encoded, nullptr, targets, n_targets, batch, loss_scale, grads, grads_dtype,
                                  pack_transpose, dx, loss_sum, stream, raw))
         return rc;
     if (want_enc_grads)
-        return tnn_encoding_backward(e, x, dx, TNN_DTYPE_BF16, encoding_grads, batch, deterministic, stream);
+        return tnn_encoding_backward(e, x, dx, net_dtype, encoding_grads, batch, deterministic, stream);
     return 0;
     TNN_GUARD_END
 }

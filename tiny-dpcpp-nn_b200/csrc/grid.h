@@ -34,12 +34,17 @@ struct GridParams {
 // common_device.h:767-775).  Returns the total number of table entries.
 uint32_t grid_build_level_table(GridParams &p, uint32_t log2_hashmap_size);
 
-cudaError_t launch_grid_fwd(const GridParams &p, const float *x, const float *table, void *out, int out_bf16,
+// out_dtype / dy_dtype: 0 = bf16, 1 = fp16, 2 = fp32 (the TNN_DTYPE_* codes)
+cudaError_t launch_grid_fwd(const GridParams &p, const float *x, const float *table, void *out, int out_dtype,
                             size_t batch, cudaStream_t stream);
+
+// dL/dinput: dx[batch][n_dims] fp32 from dy[batch][padded_width] of dy_dtype
+cudaError_t launch_grid_bwd_input(const GridParams &p, const float *x, const float *table, const void *dy, int dy_dtype,
+                                  float *dx, size_t batch, cudaStream_t stream);
 
 // Scratch (bytes) the deterministic backward needs for `batch` samples.
 size_t grid_bwd_scratch_bytes(const GridParams &p, size_t batch);
-cudaError_t launch_grid_bwd(const GridParams &p, const float *x, const void *dy, int dy_bf16, float *grads,
+cudaError_t launch_grid_bwd(const GridParams &p, const float *x, const void *dy, int dy_dtype, float *grads,
                             size_t batch, void *scratch, size_t scratch_bytes, cudaStream_t stream);
 
 } // namespace tnn

@@ -9,6 +9,7 @@
 #include "grid_device.cuh"
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 namespace tnn {
 
@@ -110,7 +111,7 @@ __global__ void __launch_bounds__(256) grid_bwd_atomic_kernel(const GridParams p
 }
 
 template <int D, int F>
-static cudaError_t launch_bwd_atomic_df(const GridParams &p, const float *x, const void *dy, int dy_bf16, float *grads,
+static cudaError_t launch_bwd_atomic_df(const GridParams &p, const float *x, const void *dy, int dy_dtype, float *grads,
                                         size_t batch, cudaStream_t stream) {
     const size_t n_params = (size_t)p.offsets[p.n_levels] * F;
     cudaError_t e = cudaMemsetAsync(grads, 0, n_params * sizeof(float), stream); // grid.h:758-762
@@ -118,29 +119,31 @@ static cudaError_t launch_bwd_atomic_df(const GridParams &p, const float *x, con
     const size_t n = batch * p.n_levels;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     count_launch();
-    if (dy_bf16)
+    if (dy_dtype == 0)
         grid_bwd_atomic_kernel<D, F, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p, x, (const __nv_bfloat16 *)dy, grads, batch);
+    else if (dy_dtype == 1)
+        grid_bwd_atomic_kernel<D, F, __half><<<blocks, 256, 0, stream>>>(p, x, (const __half *)dy, grads, batch);
     else
         grid_bwd_atomic_kernel<D, F, float><<<blocks, 256, 0, stream>>>(p, x, (const float *)dy, grads, batch);
     return cudaGetLastError();
 }
 
-cudaError_t launch_grid_bwd_det(const GridParams &p, const float *x, const void *dy, int dy_bf16, float *grads,
+cudaError_t launch_grid_bwd_det(const GridParams &p, const float *x, const void *dy, int dy_dtype, float *grads,
                                 size_t batch, void *scratch, size_t scratch_bytes, cudaStream_t stream);
 
-cudaError_t launch_grid_bwd(const GridParams &p, const float *x, const void *dy, int dy_bf16, float *grads,
+cudaError_t launch_grid_bwd(const GridParams &p, const float *x, const void *dy, int dy_dtype, float *grads,
                             size_t batch, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
-    if (scratch) return launch_grid_bwd_det(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
+    if (scratch) return launch_grid_bwd_det(p, x, dy, dy_dtype, grads, batch, scratch, scratch_bytes, stream);
     const int key = (int)p.n_dims * 16 + (int)p.features_per_level;
     switch (key) {
-    case 2 * 16 + 1: return launch_bwd_atomic_df<2, 1>(p, x, dy, dy_bf16, grads, batch, stream);
-    case 2 * 16 + 2: return launch_bwd_atomic_df<2, 2>(p, x, dy, dy_bf16, grads, batch, stream);
-    case 2 * 16 + 4: return launch_bwd_atomic_df<2, 4>(p, x, dy, dy_bf16, grads, batch, stream);
-    case 2 * 16 + 8: return launch_bwd_atomic_df<2, 8>(p, x, dy, dy_bf16, grads, batch, stream);
-    case 3 * 16 + 1: return launch_bwd_atomic_df<3, 1>(p, x, dy, dy_bf16, grads, batch, stream);
-    case 3 * 16 + 2: return launch_bwd_atomic_df<3, 2>(p, x, dy, dy_bf16, grads, batch, stream);
-    case 3 * 16 + 4: return launch_bwd_atomic_df<3, 4>(p, x, dy, dy_bf16, grads, batch, stream);
-    case 3 * 16 + 8: return launch_bwd_atomic_df<3, 8>(p, x, dy, dy_bf16, grads, batch, stream);
+    case 2 * 16 + 1: return launch_bwd_atomic_df<2, 1>(p, x, dy, dy_dtype, grads, batch, stream);
+    case 2 * 16 + 2: return launch_bwd_atomic_df<2, 2>(p, x, dy, dy_dtype, grads, batch, stream);
+    case 2 * 16 + 4: return launch_bwd_atomic_df<2, 4>(p, x, dy, dy_dtype, grads, batch, stream);
+    case 2 * 16 + 8: return launch_bwd_atomic_df<2, 8>(p, x, dy, dy_dtype, grads, batch, stream);
+    case 3 * 16 + 1: return launch_bwd_atomic_df<3, 1>(p, x, dy, dy_dtype, grads, batch, stream);
+    case 3 * 16 + 2: return launch_bwd_atomic_df<3, 2>(p, x, dy, dy_dtype, grads, batch, stream);
+    case 3 * 16 + 4: return launch_bwd_atomic_df<3, 4>(p, x, dy, dy_dtype, grads, batch, stream);
+    case 3 * 16 + 8: return launch_bwd_atomic_df<3, 8>(p, x, dy, dy_dtype, grads, batch, stream);
     default: return cudaErrorInvalidValue;
     }
 }

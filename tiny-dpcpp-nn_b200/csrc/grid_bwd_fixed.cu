@@ -15,6 +15,7 @@
 #include "grid_device.cuh"
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 namespace tnn {
 
@@ -132,7 +133,7 @@ __global__ void __launch_bounds__(256) grid_fixed_finalize_kernel(const unsigned
 }
 
 template <int D, int F>
-cudaError_t run_fixed(const GridParams &p, const float *x, const void *dy, int dy_bf16, float *grads, size_t batch,
+cudaError_t run_fixed(const GridParams &p, const float *x, const void *dy, int dy_dtype, float *grads, size_t batch,
                       void *scratch, size_t scratch_bytes, cudaStream_t stream) {
     const size_t n_params = (size_t)p.offsets[p.n_levels] * F;
     if (scratch_bytes < sizeof(FixedHeader) + n_params * sizeof(unsigned long long)) return cudaErrorInvalidValue;
@@ -145,10 +146,14 @@ cudaError_t run_fixed(const GridParams &p, const float *x, const void *dy, int d
     const size_t n = batch * p.n_levels;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     count_launch(3);
-    if (dy_bf16) {
+    if (dy_dtype == 0) {
         grid_absmax_kernel<__nv_bfloat16><<<red_blocks ? red_blocks : 1, 256, 0, stream>>>(
             (const __nv_bfloat16 *)dy, batch, p.n_features, p.padded_width, hdr);
         grid_bwd_fixed_kernel<D, F, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p, x, (const __nv_bfloat16 *)dy, hdr, acc, batch);
+    } else if (dy_dtype == 1) {
+        grid_absmax_kernel<__half><<<red_blocks ? red_blocks : 1, 256, 0, stream>>>((const __half *)dy, batch, p.n_features,
+                                                                                    p.padded_width, hdr);
+        grid_bwd_fixed_kernel<D, F, __half><<<blocks, 256, 0, stream>>>(p, x, (const __half *)dy, hdr, acc, batch);
     } else {
         grid_absmax_kernel<float><<<red_blocks ? red_blocks : 1, 256, 0, stream>>>((const float *)dy, batch, p.n_features,
                                                                                    p.padded_width, hdr);
@@ -165,18 +170,18 @@ size_t grid_bwd_scratch_bytes(const GridParams &p, size_t) {
     return sizeof(FixedHeader) + (size_t)p.offsets[p.n_levels] * p.features_per_level * sizeof(unsigned long long);
 }
 
-cudaError_t launch_grid_bwd_det(const GridParams &p, const float *x, const void *dy, int dy_bf16, float *grads,
+cudaError_t launch_grid_bwd_det(const GridParams &p, const float *x, const void *dy, int dy_dtype, float *grads,
                                 size_t batch, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
     const int key = (int)p.n_dims * 16 + (int)p.features_per_level;
     switch (key) {
-    case 2 * 16 + 1: return run_fixed<2, 1>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
-    case 2 * 16 + 2: return run_fixed<2, 2>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
-    case 2 * 16 + 4: return run_fixed<2, 4>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
-    case 2 * 16 + 8: return run_fixed<2, 8>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
-    case 3 * 16 + 1: return run_fixed<3, 1>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
-    case 3 * 16 + 2: return run_fixed<3, 2>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
-    case 3 * 16 + 4: return run_fixed<3, 4>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
-    case 3 * 16 + 8: return run_fixed<3, 8>(p, x, dy, dy_bf16, grads, batch, scratch, scratch_bytes, stream);
+    case 2 * 16 + 1: return run_fixed<2, 1>(p, x, dy, dy_dtype, grads, batch, scratch, scratch_bytes, stream);
+    case 2 * 16 + 2: return run_fixed<2, 2>(p, x, dy, dy_dtype, grads, batch, scratch, scratch_bytes, stream);
+    case 2 * 16 + 4: return run_fixed<2, 4>(p, x, dy, dy_dtype, grads, batch, scratch, scratch_bytes, stream);
+    case 2 * 16 + 8: return run_fixed<2, 8>(p, x, dy, dy_dtype, grads, batch, scratch, scratch_bytes, stream);
+    case 3 * 16 + 1: return run_fixed<3, 1>(p, x, dy, dy_dtype, grads, batch, scratch, scratch_bytes, stream);
+    case 3 * 16 + 2: return run_fixed<3, 2>(p, x, dy, dy_dtype, grads, batch, scratch, scratch_bytes, stream);
+    case 3 * 16 + 4: return run_fixed<3, 4>(p, x, dy, dy_dtype, grads, batch, scratch, scratch_bytes, stream);
+    case 3 * 16 + 8: return run_fixed<3, 8>(p, x, dy, dy_dtype, grads, batch, scratch, scratch_bytes, stream);
     default: return cudaErrorInvalidValue;
     }
 }

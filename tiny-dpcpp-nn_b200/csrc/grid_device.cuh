@@ -83,4 +83,91 @@ __device__ __forceinline__ void grid_pos(const float *__restrict__ x, float scal
 }
 
 
+// What a kernel needs to know about one level, and about the grid as a whole.
+struct GridLevelInfo {
+    uint32_t offset; // first table entry
+    uint32_t hsize;  // entries
+    uint32_t res;
+    float scale;
+};
+struct GridCommon {
+    int interpolation, grid_type, hash_type;
+    float max_level_f; // levels >= this produce zeros (grid.h:56-63)
+};
+__host__ __device__ inline GridLevelInfo grid_level_info(const GridParams &p, uint32_t level) {
+    return GridLevelInfo{p.offsets[level], p.offsets[level + 1] - p.offsets[level], p.resolution[level], p.scale[level]};
+}
+__host__ __device__ inline GridCommon grid_common(const GridParams &p) {
+    return GridCommon{p.interpolation, p.grid_type, p.hash_type,
+                      (p.max_level * (float)p.n_features) / (float)p.features_per_level + 1e-3f};
+}
+
+// The F interpolated features of one sample at one level (reference kernel_grid, include/encodings/grid.h:64-133):
+// fp32 throughout, all 2^D gathers issued first, then combined with fma in corner order 0..2^D-1.  `level` should be
+// uniform over the warp: its table parameters are then read with one address per warp (a per-lane level serialises
+// those reads in the constant bank, which was the busiest pipe of an earlier forward kernel).
+template <int D, int F>
+__device__ __forceinline__ void grid_level_features(const GridCommon &gc, const GridLevelInfo &lv, uint32_t level,
+                                                    const float *__restrict__ table, const float (&xin)[D],
+                                                    float (&res_v)[F]) {
+#pragma unroll
+    for (int f = 0; f < F; ++f) res_v[f] = 0.0f;
+    if ((float)level >= gc.max_level_f) return;
+    const float *tl = table + (size_t)lv.offset * F;
+    const uint32_t hsize = lv.hsize;
+    const uint32_t res = lv.res;
+    struct {
+        int interpolation, grid_type, hash_type;
+    } p{gc.interpolation, gc.grid_type, gc.hash_type};
+    float w[D];
+    uint32_t g[D];
+    grid_pos<D>(xin, lv.scale, p.interpolation, w, g);
+    if (p.interpolation == INTERP_NEAREST) {
+        const uint32_t e = grid_index<D>(p.grid_type, p.hash_type, hsize, res, g);
+#pragma unroll
+        for (int f = 0; f < F; ++f) res_v[f] = __ldg(tl + (size_t)e * F + f);
+        return;
+    }
+    float vals[1 << D][F];
+    float wt[1 << D];
+    uint32_t ent[1 << D];
+#pragma unroll
+    for (int c = 0; c < (1 << D); ++c) {
+        float weight = 1.0f;
+        uint32_t gl[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            if ((c & (1 << d)) == 0) {
+                weight = __fmul_rn(weight, __fsub_rn(1.0f, w[d]));
+                gl[d] = g[d];
+            } else {
+                weight = __fmul_rn(weight, w[d]);
+                gl[d] = g[d] + 1u;
+            }
+        }
+        wt[c] = weight;
+        ent[c] = grid_index_raw<D>(p.grid_type, p.hash_type, hsize, res, gl);
+    }
+    grid_wrap<(1 << D)>(ent, hsize);
+#pragma unroll
+    for (int c = 0; c < (1 << D); ++c) {
+        const uint32_t e = ent[c];
+        if constexpr (F == 2) {
+            const float2 v = __ldg(reinterpret_cast<const float2 *>(tl) + e);
+            vals[c][0] = v.x;
+            vals[c][1] = v.y;
+        } else if constexpr (F == 4) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(tl) + e);
+            vals[c][0] = v.x, vals[c][1] = v.y, vals[c][2] = v.z, vals[c][3] = v.w;
+        } else {
+#pragma unroll
+            for (int f = 0; f < F; ++f) vals[c][f] = __ldg(tl + (size_t)e * F + f);
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < (1 << D); ++c)
+#pragma unroll
+        for (int f = 0; f < F; ++f) res_v[f] = fmaf(wt[c], vals[c][f], res_v[f]);
+}
+
 } // namespace tnn

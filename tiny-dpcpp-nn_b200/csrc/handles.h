@@ -17,10 +17,12 @@ struct tnn_network {
     int input_width = 0, output_width = 0; // as requested (unpadded)
     int width = 0, n_hidden = 0, n_mat = 0;
     int act = 0, out_act = 0, use_bias = 1;
+    int fp16 = 0; // element type of operands and activations: bf16 (0) or fp16 (1)
     int variant = 0;
     int n_sm = 0;
     size_t n_params = 0;
-    __nv_bfloat16 *packed = nullptr; // packed-layout bf16 weights (what get_params returns)
+    // (16-bit buffers are typed __nv_bfloat16 whatever the element type; see fp16)
+    __nv_bfloat16 *packed = nullptr; // packed-layout 16-bit weights (what get_params returns)
     __nv_bfloat16 *wimg = nullptr;   // swizzled operand images, rows = input feature
     __nv_bfloat16 *wimg_t = nullptr; // swizzled operand images, rows = output feature
     float *dw_slabs = nullptr;       // per-CTA weight-gradient partial sums
@@ -49,7 +51,9 @@ struct tnn_encoding {
     int padded = 0;   // padded output width
     float scale = 1.0f, offset = 0.0f; // identity
     int n_frequencies = 0;             // > 0: frequency encoding
+    int sh_degree = 0;                 // > 0: spherical-harmonics encoding
     tnn::GridParams gp{};
+    tnn::GridParams *gp_dev = nullptr; // device copy, read by kernels that keep the level table in shared memory
     size_t n_params = 0;
     float *table = nullptr;    // owned storage
     float *bound = nullptr;    // caller-owned storage used instead, when set (tnn_encoding_bind_params)

@@ -68,7 +68,7 @@ extern "C" int tnn_l2_loss_static(const void *pred, const float *target, int n_t
     const int n_partials = (int)((n_el + kElemsPerPartial - 1) / kElemsPerPartial);
     // every one of the n_partials slots is overwritten by its block and only those slots are summed, so
     // nothing left over from an earlier call can leak into this one and nothing needs clearing
-    e = tnn::launch_l2_loss((const __nv_bfloat16 *)pred, target, n_targets, values, (__nv_bfloat16 *)grads, batch, stride,
+    e = tnn::launch_l2_loss((const __nv_bfloat16 *)pred, /*fp16=*/0, target, n_targets, values, (__nv_bfloat16 *)grads, batch, stride,
                             loss_scale, loss_sum ? g_partials_addr[dev] : nullptr, n_partials, loss_sum,
                             (cudaStream_t)stream);
     if (e != cudaSuccess) return tnn::api_fail(std::string("l2 loss launch: ") + cudaGetErrorString(e), 2);

@@ -57,7 +57,7 @@ struct BwdBarriers {
     uint32_t abort_flag;
 };
 
-template <int W, bool B_MN_MAJOR, bool BIG>
+template <int W, bool B_MN_MAJOR, bool BIG, bool HF_>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_interm,
                const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_ibwd,
@@ -66,6 +66,7 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                int out_act, int store_bwd, int want_dx, int tmem_cols, int dw_lo, int dw_hi, int l_stop, int *status) {
     using T = Tile<W>;
     using S = BwdSmem<W, BIG>;
+    constexpr int fp16 = HF_ ? 1 : 0; // element type of operands and activations: bf16 or fp16
     constexpr int kBwdRing = S::RING;
     constexpr int NDY = S::NDY;
     extern __shared__ uint8_t smem_raw[];
@@ -161,8 +162,8 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (my_tiles > 0) { // all lanes run the loop, one elected lane issues (see ptx::elect_one)
-            constexpr uint32_t idesc_chain = ptx::make_idesc_bf16(128, W, 0, B_MN_MAJOR ? 1 : 0);
-            constexpr uint32_t idesc_dw = ptx::make_idesc_bf16(S::DW_M, W, 1, 1);
+            const uint32_t idesc_chain = ptx::make_idesc_16(128, W, 0, B_MN_MAJOR ? 1 : 0, fp16);
+            const uint32_t idesc_dw = ptx::make_idesc_16(S::DW_M, W, 1, 1, fp16);
             // base descriptors; buffers and k-steps are reached with constant adds
             const uint64_t dk_desc0 = T::kdesc_base(smem_base + S::DY);                        // delta tiles, K-major
             const uint64_t dmn_desc0 = T::mndesc_base(smem_base + S::DY, T::ACT_ATOM_BYTES);   // delta tiles, MN-major
@@ -322,17 +323,18 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                     break;
                 }
                 const uint8_t *ybuf = smem + S::AR + slot * T::ACT_BYTES;
-                dispatch_act(out_act, [&](auto tag) {
+                dispatch_act_t<HF_>(out_act, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
+                    constexpr bool HF = decltype(tag)::half;
 #pragma unroll
                     for (int cc = 0; cc < CPT; cc += 8) {
                         const int off = chunk_off(col0 + cc);
                         uint4 d = *reinterpret_cast<const uint4 *>(dybuf + off);
                         const uint4 y = *reinterpret_cast<const uint4 *>(ybuf + off);
-                        d.x = act_bwd_pack_t<ACT>(ptx::bf16lo_to_f32(d.x), ptx::bf16hi_to_f32(d.x), y.x);
-                        d.y = act_bwd_pack_t<ACT>(ptx::bf16lo_to_f32(d.y), ptx::bf16hi_to_f32(d.y), y.y);
-                        d.z = act_bwd_pack_t<ACT>(ptx::bf16lo_to_f32(d.z), ptx::bf16hi_to_f32(d.z), y.z);
-                        d.w = act_bwd_pack_t<ACT>(ptx::bf16lo_to_f32(d.w), ptx::bf16hi_to_f32(d.w), y.w);
+                        d.x = act_bwd_pack_t<ACT, HF>(ptx::lo_f32<HF>(d.x), ptx::hi_f32<HF>(d.x), y.x);
+                        d.y = act_bwd_pack_t<ACT, HF>(ptx::lo_f32<HF>(d.y), ptx::hi_f32<HF>(d.y), y.y);
+                        d.z = act_bwd_pack_t<ACT, HF>(ptx::lo_f32<HF>(d.z), ptx::hi_f32<HF>(d.z), y.z);
+                        d.w = act_bwd_pack_t<ACT, HF>(ptx::lo_f32<HF>(d.w), ptx::hi_f32<HF>(d.w), y.w);
                         *reinterpret_cast<uint4 *>(dybuf + off) = d;
                     }
                 });
@@ -389,8 +391,9 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < NLD; ++i) load_cols(acc_tmem + lane_addr + col0 + i * CW, v[i]);
                     ptx::tmem_ld_wait();
-                    dispatch_act((l > 0) ? act : (int)ACT_NONE, [&](auto tag) {
+                    dispatch_act_t<HF_>((l > 0) ? act : (int)ACT_NONE, [&](auto tag) {
                         constexpr int ACT = decltype(tag)::value;
+                    constexpr bool HF = decltype(tag)::half;
 #pragma unroll
                         for (int i = 0; i < NLD; ++i) {
 #pragma unroll
@@ -399,10 +402,10 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
                                 uint4 f = make_uint4(0, 0, 0, 0);
                                 if constexpr (ACT != ACT_NONE) f = *reinterpret_cast<const uint4 *>(abuf + off);
                                 uint4 o;
-                                o.x = act_bwd_pack_t<ACT>(__uint_as_float(v[i][ch * 8 + 0]), __uint_as_float(v[i][ch * 8 + 1]), f.x);
-                                o.y = act_bwd_pack_t<ACT>(__uint_as_float(v[i][ch * 8 + 2]), __uint_as_float(v[i][ch * 8 + 3]), f.y);
-                                o.z = act_bwd_pack_t<ACT>(__uint_as_float(v[i][ch * 8 + 4]), __uint_as_float(v[i][ch * 8 + 5]), f.z);
-                                o.w = act_bwd_pack_t<ACT>(__uint_as_float(v[i][ch * 8 + 6]), __uint_as_float(v[i][ch * 8 + 7]), f.w);
+                                o.x = act_bwd_pack_t<ACT, HF>(__uint_as_float(v[i][ch * 8 + 0]), __uint_as_float(v[i][ch * 8 + 1]), f.x);
+                                o.y = act_bwd_pack_t<ACT, HF>(__uint_as_float(v[i][ch * 8 + 2]), __uint_as_float(v[i][ch * 8 + 3]), f.y);
+                                o.z = act_bwd_pack_t<ACT, HF>(__uint_as_float(v[i][ch * 8 + 4]), __uint_as_float(v[i][ch * 8 + 5]), f.z);
+                                o.w = act_bwd_pack_t<ACT, HF>(__uint_as_float(v[i][ch * 8 + 6]), __uint_as_float(v[i][ch * 8 + 7]), f.w);
                                 *reinterpret_cast<uint4 *>(dst + off) = o;
                             }
                         }
@@ -484,12 +487,12 @@ mlp_bwd_kernel(const __grid_constant__ CUtensorMap tm_dy, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------- host side
-template <int W, bool B_MN, bool BIG> static cudaError_t launch_bwd_variant(BwdLaunch &p) {
+template <int W, bool B_MN, bool BIG, bool HF_> static cudaError_t launch_bwd_t(BwdLaunch &p) {
     using T = Tile<W>;
     using S = BwdSmem<W, BIG>;
     const size_t smem = (size_t)S::WBUF + (size_t)S::weight_tiles(p.n_mat) * T::WGT_BYTES + 1024;
     if (smem > 227 * 1024 - 512) return cudaErrorInvalidConfiguration;
-    auto kern = mlp_bwd_kernel<W, B_MN, BIG>;
+    auto kern = mlp_bwd_kernel<W, B_MN, BIG, HF_>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
@@ -514,6 +517,10 @@ template <int W, bool B_MN, bool BIG> static cudaError_t launch_bwd_variant(BwdL
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;
+}
+
+template <int W, bool B_MN, bool BIG> static cudaError_t launch_bwd_variant(BwdLaunch &p) {
+    return p.fp16 ? launch_bwd_t<W, B_MN, BIG, true>(p) : launch_bwd_t<W, B_MN, BIG, false>(p);
 }
 
 template <int W> static cudaError_t launch_bwd_w(BwdLaunch &p) {

@@ -114,67 +114,135 @@ template <int W> struct Tile {
 // (struct EncodedInput: mlp_launch.h)
 
 // Whole warp: fill `n_tiles` consecutive input tiles with bf16 ones (the padding value of the encoding).
-template <int W> __device__ __forceinline__ void fill_tiles_with_ones(uint8_t *tiles, int n_tiles, int lane) {
-    const uint4 ones = make_uint4(0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
+template <int W> __device__ __forceinline__ void fill_tiles_with_ones(uint8_t *tiles, int n_tiles, int lane, int fp16) {
+    const uint32_t one2 = fp16 ? 0x3C003C00u : 0x3F803F80u; // two 1.0 in fp16 / bf16
+    const uint4 ones = make_uint4(one2, one2, one2, one2);
     for (int i = lane; i < n_tiles * (Tile<W>::ACT_BYTES / 16); i += 32) reinterpret_cast<uint4 *>(tiles)[i] = ones;
 }
-// Whole warp: write the encoded columns (the first one or two 16-byte chunks of every row; the rest of the tile keeps
-// its ones) of the tile whose first row is `row0`.  Rows past the end of the batch become zeros.
-template <int W>
-__device__ __forceinline__ void encode_identity_tile(uint8_t *xtile, const EncodedInput &e, size_t row0, size_t batch,
-                                                     int lane) {
+// Whole warp: produces the encoded columns (the first one or two 16-byte chunks of every row; the rest of the tile
+// keeps its ones) of one input tile.  fetch() starts the global loads of a tile's coordinates into registers - issued
+// a tile ahead, so that their latency hides under the tile being consumed - and store() converts and writes them.
+// Rows past the end of the batch become zeros.  Lane i owns rows i, i + 32, i + 64, i + 96.
+template <int W> struct IdentityTileEncoder {
     using T = Tile<W>;
-    const int n_chunks = (e.n_in + 7) >> 3;
-    for (int r = lane; r < T::TM; r += 32) {
-        const size_t grow = row0 + r;
-        const bool valid = grow < batch;
-        for (int c = 0; c < n_chunks; ++c) {
-            float v[8];
+    static constexpr int kRegInputs = 4; // coordinates per row kept in registers between fetch and store
+    const EncodedInput e;
+    const size_t batch;
+    const int lane;
+    int fp16 = 0;
+    size_t row0 = 0;
+    float v[4][kRegInputs];
+    __device__ IdentityTileEncoder(const EncodedInput &enc, size_t batch_, int lane_, int fp16_ = 0)
+        : e(enc), batch(batch_), lane(lane_), fp16(fp16_) {}
+    __device__ __forceinline__ void fetch(size_t first_row) {
+        row0 = first_row;
+        if (e.n_in > kRegInputs) return; // wide inputs are read in store()
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int col = c * 8 + j;
-                v[j] = col < e.n_in ? (valid ? __fadd_rn(__fmul_rn(__ldg(e.x + grow * e.n_in + col), e.scale), e.offset) : 0.0f)
-                                    : 1.0f;
-            }
-            *reinterpret_cast<uint4 *>(xtile + T::chunk_off(r, c)) =
-                make_uint4(ptx::pack_bf16x2(v[0], v[1]), ptx::pack_bf16x2(v[2], v[3]), ptx::pack_bf16x2(v[4], v[5]),
-                           ptx::pack_bf16x2(v[6], v[7]));
+        for (int i = 0; i < 4; ++i) {
+            const size_t grow = row0 + lane + 32 * i;
+#pragma unroll
+            for (int j = 0; j < kRegInputs; ++j)
+                v[i][j] = (j < e.n_in && grow < batch) ? __ldg(e.x + grow * e.n_in + j) : 0.0f;
         }
     }
-}
+    __device__ __forceinline__ uint4 pack8(const float (&o)[8]) const {
+        return fp16 ? make_uint4(ptx::pack_f16x2(o[0], o[1]), ptx::pack_f16x2(o[2], o[3]), ptx::pack_f16x2(o[4], o[5]),
+                                 ptx::pack_f16x2(o[6], o[7]))
+                    : make_uint4(ptx::pack_bf16x2(o[0], o[1]), ptx::pack_bf16x2(o[2], o[3]), ptx::pack_bf16x2(o[4], o[5]),
+                                 ptx::pack_bf16x2(o[6], o[7]));
+    }
+    __device__ __forceinline__ void store(uint8_t *xtile) {
+        if (e.n_in <= kRegInputs) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = lane + 32 * i;
+                const bool valid = row0 + r < batch;
+                float o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    o[j] = (j < kRegInputs && j < e.n_in) ? (valid ? __fadd_rn(__fmul_rn(v[i][j < kRegInputs ? j : 0], e.scale), e.offset) : 0.0f)
+                                                        : 1.0f;
+                *reinterpret_cast<uint4 *>(xtile + T::chunk_off(r, 0)) = pack8(o);
+            }
+            return;
+        }
+        const int n_chunks = (e.n_in + 7) >> 3;
+        for (int r = lane; r < T::TM; r += 32) {
+            const size_t grow = row0 + r;
+            const bool valid = grow < batch;
+            for (int c = 0; c < n_chunks; ++c) {
+                float o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int col = c * 8 + j;
+                    o[j] = col < e.n_in ? (valid ? __fadd_rn(__fmul_rn(__ldg(e.x + grow * e.n_in + col), e.scale), e.offset) : 0.0f)
+                                        : 1.0f;
+                }
+                *reinterpret_cast<uint4 *>(xtile + T::chunk_off(r, c)) = pack8(o);
+            }
+        }
+    }
+};
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
 
-// Compile-time activation tags.  The epilogues select the activation ONCE per tile step with a
-// uniform branch and then run a straight-line body specialised for it: a run-time `act` inside the
-// per-element code makes the compiler evaluate every activation (including the exp and the division
-// of the sigmoid) for every element and select afterwards, which multiplied the epilogue's length.
-template <int A> struct ActTag { static constexpr int value = A; };
-template <class F> __device__ __forceinline__ void dispatch_act(int act, F &&f) {
+// Compile-time activation / element-type tags.  The epilogues select the activation (and whether the network
+// computes in bf16 or fp16) ONCE per tile step with a uniform branch and then run a straight-line body specialised
+// for it: a run-time `act` inside the per-element code makes the compiler evaluate every activation (including the
+// exp and the division of the sigmoid) for every element and select afterwards, which multiplied the epilogue's length.
+template <int A, bool H = false> struct ActTag {
+    static constexpr int value = A;
+    static constexpr bool half = H;
+};
+template <class F> __device__ __forceinline__ void dispatch_act(int act, int fp16, F &&f) {
+    if (!fp16) {
+        if (act == ACT_RELU)
+            f(ActTag<ACT_RELU, false>{});
+        else if (act == ACT_SIGMOID)
+            f(ActTag<ACT_SIGMOID, false>{});
+        else
+            f(ActTag<ACT_NONE, false>{});
+    } else {
+        if (act == ACT_RELU)
+            f(ActTag<ACT_RELU, true>{});
+        else if (act == ACT_SIGMOID)
+            f(ActTag<ACT_SIGMOID, true>{});
+        else
+            f(ActTag<ACT_NONE, true>{});
+    }
+}
+// Element type fixed at compile time (the kernels are instantiated per type): dispatch over the activation only.
+template <bool H, class F> __device__ __forceinline__ void dispatch_act_t(int act, F &&f) {
     if (act == ACT_RELU)
-        f(ActTag<ACT_RELU>{});
+        f(ActTag<ACT_RELU, H>{});
     else if (act == ACT_SIGMOID)
-        f(ActTag<ACT_SIGMOID>{});
+        f(ActTag<ACT_SIGMOID, H>{});
     else
-        f(ActTag<ACT_NONE>{});
+        f(ActTag<ACT_NONE, H>{});
 }
-template <int A> __device__ __forceinline__ uint32_t act_pack_t(float lo, float hi) {
-    if constexpr (A == ACT_RELU) return ptx::pack_bf16x2_relu(lo, hi);
-    if constexpr (A == ACT_SIGMOID) return ptx::pack_bf16x2(1.0f / (1.0f + __expf(-lo)), 1.0f / (1.0f + __expf(-hi)));
-    return ptx::pack_bf16x2(lo, hi);
+template <int A, bool H = false> __device__ __forceinline__ uint32_t act_pack_t(float lo, float hi) {
+    if constexpr (A == ACT_RELU) return ptx::pack2_relu<H>(lo, hi);
+    if constexpr (A == ACT_SIGMOID) return ptx::pack2<H>(1.0f / (1.0f + __expf(-lo)), 1.0f / (1.0f + __expf(-hi)));
+    return ptx::pack2<H>(lo, hi);
 }
-template <int A> __device__ __forceinline__ uint32_t act_bwd_pack_t(float lo, float hi, uint32_t fwd) {
+template <int A, bool H = false> __device__ __forceinline__ uint32_t act_bwd_pack_t(float lo, float hi, uint32_t fwd) {
     if constexpr (A == ACT_RELU) {
         // keep the gradient where the stored activation is > 0: one packed compare gives 0xffff per kept half
-        __nv_bfloat162 f2;
-        memcpy(&f2, &fwd, sizeof(f2));
-        return ptx::pack_bf16x2(lo, hi) & __hgt2_mask(f2, __floats2bfloat162_rn(0.0f, 0.0f));
+        if constexpr (H) {
+            __half2 f2;
+            memcpy(&f2, &fwd, sizeof(f2));
+            return ptx::pack2<H>(lo, hi) & __hgt2_mask(f2, __floats2half2_rn(0.0f, 0.0f));
+        } else {
+            __nv_bfloat162 f2;
+            memcpy(&f2, &fwd, sizeof(f2));
+            return ptx::pack2<H>(lo, hi) & __hgt2_mask(f2, __floats2bfloat162_rn(0.0f, 0.0f));
+        }
     } else if constexpr (A == ACT_SIGMOID) {
-        const float sl = ptx::bf16lo_to_f32(fwd), sh = ptx::bf16hi_to_f32(fwd);
+        const float sl = ptx::lo_f32<H>(fwd), sh = ptx::hi_f32<H>(fwd);
         lo *= sl * (1.0f - sl);
         hi *= sh * (1.0f - sh);
     }
-    return ptx::pack_bf16x2(lo, hi);
+    return ptx::pack2<H>(lo, hi);
 }
 
 // Forward activation on two fp32 accumulators, rounded to a bf16 pair.  The reference rounds

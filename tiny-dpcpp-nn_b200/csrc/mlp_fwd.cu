@@ -27,6 +27,7 @@
 // own epilogue group, and nothing but the tensor pipe and shared memory is shared between them.
 #include "mlp_common.cuh"
 #include "elementwise.h"
+#include "grid_device.cuh"
 #include "mlp_launch.h"
 
 namespace tnn {
@@ -67,18 +68,48 @@ struct FwdBarriers {
     uint32_t out_lock; // SHARED_OUT: 1 while a slot owns the output tile
 };
 
-template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN_MAJOR, bool STREAM_W = false>
-__global__ void __launch_bounds__(FwdSmem<W, NSLOT, TMEM_A, STORE_ALL>::THREADS, 1)
+// NENC > 0: the network input is the hash-grid encoding of fp32 positions, produced on the SM by NENC extra warps
+// (NetworkWithInputEncoding of the reference, dpcpp_bindings/tiny_dpcpp_nn/modules.py:357-421, without the
+// batch x W matrix between the two modules).  Each encoder warp owns 32 rows of the tile at one level at a time -
+// level parameters are warp-uniform and sit in shared memory - gathers the 2^D corners, interpolates
+// (include/encodings/grid.h:64-133, same arithmetic as the stand-alone encoding kernel) and writes the rounded
+// features straight into the swizzled input tile that layer 0's MMA reads; columns past the features stay zero.
+constexpr int kGridEncWarps = 8;
+
+template <int D>
+__device__ __forceinline__ void encode_grid_rows(uint8_t *xt, int row, int level0, const GridCommon &gc,
+                                                 const GridLevelInfo *levels, int n_levels, const float *__restrict__ table,
+                                                 const float (&xin)[D], bool valid, int fp16, int atom_cols,
+                                                 int atom_bytes, int row_bytes, int chunks) {
+#pragma unroll 2
+    for (int level = level0; level < n_levels; level += 2) {
+        float r[2];
+        grid_level_features<D, 2>(gc, levels[level], (uint32_t)level, table, xin, r);
+        if (!valid) r[0] = r[1] = 0.0f;
+        const uint32_t packed = fp16 ? ptx::pack_f16x2(r[0], r[1]) : ptx::pack_bf16x2(r[0], r[1]);
+        const int col = level * 2;
+        const int chunk = (col % atom_cols) / 8;
+        const int off = (col / atom_cols) * atom_bytes + row * row_bytes +
+                        ((chunk ^ (((row * row_bytes) >> 7) & (chunks - 1))) << 4) + (col % 8) * 2;
+        *reinterpret_cast<uint32_t *>(xt + off) = packed;
+    }
+}
+
+template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN_MAJOR, bool STREAM_W, int NENC, bool HF_>
+__global__ void __launch_bounds__(FwdSmem<W, NSLOT, TMEM_A, STORE_ALL>::THREADS + 32 * NENC, 1)
 mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                const __grid_constant__ CUtensorMap tm_interm, const __nv_bfloat16 *__restrict__ wimg,
+               const GridParams *__restrict__ gp, const float *__restrict__ table, const float *__restrict__ coords,
                int n_tiles, int n_mat, int act, int out_act, int write_y, size_t batch, const EncodedInput enc, int *status) {
     using T = Tile<W>;
     using S = FwdSmem<W, NSLOT, TMEM_A, STORE_ALL, STREAM_W>;
+    constexpr int fp16 = HF_ ? 1 : 0; // element type of operands and activations: bf16 or fp16
     static_assert(NSLOT <= kMaxSlots, "too many slots");
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment (swizzle span)
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ FwdBarriers bars;
+    __shared__ GridLevelInfo enc_levels[NENC ? kMaxGridLevels : 1];
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -92,7 +123,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     if (threadIdx.x == 0) {
         ptx::mbar_init(&bars.w_full, 1);
         for (int s = 0; s < NSLOT; ++s) {
-            ptx::mbar_init(&bars.x_full[s], 1);
+            ptx::mbar_init(&bars.x_full[s], NENC ? NENC : 1); // one arrival per encoder warp, or the producer's
             ptx::mbar_init(&bars.x_empty[s], 1);
             ptx::mbar_init(&bars.a_ready[s], 4); // one arrival per epilogue warp
             ptx::mbar_init(&bars.acc_full[s], 1);
@@ -102,7 +133,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         bars.abort_flag = 0;
         bars.out_lock = 0;
         ptx::fence_barrier_init();
-        if (!enc.x) ptx::prefetch_tmap(&tm_x);
+        if (!enc.x && !NENC) ptx::prefetch_tmap(&tm_x);
         ptx::prefetch_tmap(&tm_y);
         if (STORE_ALL) ptx::prefetch_tmap(&tm_interm);
     }
@@ -117,22 +148,40 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
-        // input tiles by TMA (lane 0) or, with a folded identity encoding, written by the whole warp from fp32
-        // coordinates (with STORE_ALL the encoded tile is also stored as matrix 0 of the activations)
-        if (my_tiles > 0) {
-            if constexpr (!STREAM_W) {
-                if (lane == 0) {
-                    ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
-                    for (int l = 0; l < n_mat; ++l)
-                        ptx::bulk_load(smem + S::WBUF + l * T::WGT_BYTES,
-                                       reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
-                                       &bars.w_full);
+        // weights once (unless streamed); then input tiles by TMA (lane 0) or, with a folded identity encoding, written
+        // by the whole warp from fp32 coordinates (with STORE_ALL the encoded tile is also stored as matrix 0 of the
+        // activations)
+        if constexpr (!STREAM_W) {
+            if (lane == 0 && my_tiles > 0) {
+                ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
+                for (int l = 0; l < n_mat; ++l)
+                    ptx::bulk_load(smem + S::WBUF + l * T::WGT_BYTES,
+                                   reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
+                                   &bars.w_full);
+            }
+        }
+        if constexpr (NENC > 0) {
+            // the encoder warps produce the input tiles
+        } else if (!enc.x) {
+            if (lane == 0) {
+                for (int j = 0; j < my_tiles; ++j) {
+                    const int s = j % NSLOT, t = j / NSLOT;
+                    const int tile = blockIdx.x + j * gridDim.x;
+                    if (t >= 1 && !ptx::mbar_wait(&bars.x_empty[s], (t - 1) & 1, abort_flag)) {
+                        atomicExch(status, KS_TIMEOUT_PRODUCER | s);
+                        break;
+                    }
+                    ptx::mbar_arrive_expect_tx(&bars.x_full[s], T::ACT_BYTES);
+                    for (int a = 0; a < T::KATOMS; ++a)
+                        ptx::tma_load_2d(smem + S::XBUF + s * T::ACT_BYTES + a * T::ACT_ATOM_BYTES, &tm_x,
+                                         a * T::ATOM_COLS, tile * T::TM, &bars.x_full[s]);
                 }
             }
-            if (enc.x) {
-                fill_tiles_with_ones<W>(smem + S::XBUF, NSLOT, lane);
-                __syncwarp();
-            }
+        } else if (my_tiles > 0) {
+            fill_tiles_with_ones<W>(smem + S::XBUF, NSLOT, lane, fp16);
+            __syncwarp();
+            IdentityTileEncoder<W> encoder(enc, batch, lane, fp16);
+            encoder.fetch((size_t)blockIdx.x * T::TM);
             for (int j = 0; j < my_tiles; ++j) {
                 const int s = j % NSLOT, t = j / NSLOT;
                 const int tile = blockIdx.x + j * gridDim.x;
@@ -141,35 +190,31 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                     break;
                 }
                 uint8_t *xt = smem + S::XBUF + s * T::ACT_BYTES;
-                if (enc.x) {
-                    if (STORE_ALL && j >= NSLOT) { // the store of this slot's previous tile has read the buffer
-                        if (lane == 0) ptx::tma_wait_group_read<NSLOT - 1>();
-                        __syncwarp();
-                    }
-                    encode_identity_tile<W>(xt, enc, (size_t)tile * T::TM, batch, lane);
-                    ptx::fence_proxy_async_smem();
+                if (STORE_ALL && j >= NSLOT) { // the store of this slot's previous tile has read the buffer
+                    if (lane == 0) ptx::tma_wait_group_read<NSLOT - 1>();
                     __syncwarp();
-                    if (lane == 0) {
-                        ptx::mbar_arrive(&bars.x_full[s]);
-                        if (STORE_ALL) {
-                            for (int a = 0; a < T::KATOMS; ++a)
-                                ptx::tma_store_3d(&tm_interm, xt + a * T::ACT_ATOM_BYTES, a * T::ATOM_COLS, tile * T::TM, 0);
-                            ptx::tma_commit_group();
-                        }
-                    }
-                } else if (lane == 0) {
-                    ptx::mbar_arrive_expect_tx(&bars.x_full[s], T::ACT_BYTES);
-                    for (int a = 0; a < T::KATOMS; ++a)
-                        ptx::tma_load_2d(xt + a * T::ACT_ATOM_BYTES, &tm_x, a * T::ATOM_COLS, tile * T::TM, &bars.x_full[s]);
                 }
+                encoder.store(xt);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(&bars.x_full[s]);
+                    if (STORE_ALL) {
+                        for (int a = 0; a < T::KATOMS; ++a)
+                            ptx::tma_store_3d(&tm_interm, xt + a * T::ACT_ATOM_BYTES, a * T::ATOM_COLS, tile * T::TM, 0);
+                        ptx::tma_commit_group();
+                    }
+                }
+                // coordinates of the next tile travel while this one is consumed
+                if (j + 1 < my_tiles) encoder.fetch((size_t)(tile + gridDim.x) * T::TM);
             }
-            if (enc.x && STORE_ALL && lane == 0) ptx::tma_wait_group<0>();
+            if (STORE_ALL && lane == 0) ptx::tma_wait_group<0>();
         }
     } else if (warp <= NSLOT) {
         // ------------------------------------------------------------ MMA issuer of slot s
         const int s = warp - 1;
         if (my_tiles > s) { // all lanes run the loop, one elected lane issues (see ptx::elect_one)
-            constexpr uint32_t idesc = ptx::make_idesc_bf16(128, W, 0, B_MN_MAJOR ? 1 : 0);
+            const uint32_t idesc = ptx::make_idesc_16(128, W, 0, B_MN_MAJOR ? 1 : 0, fp16);
             // every descriptor this thread will ever need, as bases that are stepped by constants
             const uint64_t x_desc = T::kdesc_base(smem_base + S::XBUF + s * T::ACT_BYTES);
             const uint64_t a_desc0 = T::kdesc_base(smem_base + S::ABUF + s * S::NABUF * T::ACT_BYTES);
@@ -269,7 +314,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                 }
             }
         }
-    } else {
+    } else if (warp < 1 + NSLOT + 4 * NSLOT) {
         // ------------------------------------------------------------ epilogue group of slot s
         const int ew = warp - (1 + NSLOT);  // epilogue warp index
         const int s = ew >> 2;              // slot owned by this group
@@ -344,15 +389,16 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                     ptx::named_bar_sync(1 + s, 128);
                 }
                 ptx::tmem_ld_wait();
-                dispatch_act(a, [&](auto tag) {
+                dispatch_act_t<HF_>(a, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
+                    constexpr bool HF = decltype(tag)::half;
 #pragma unroll
                     for (int i = 0; i < NLD; ++i) {
                         const int c0 = i * CW;
                         uint32_t p[CW / 2];
 #pragma unroll
                         for (int q = 0; q < CW / 2; ++q)
-                            p[q] = act_pack_t<ACT>(__uint_as_float(v[i][2 * q]), __uint_as_float(v[i][2 * q + 1]));
+                            p[q] = act_pack_t<ACT, HF>(__uint_as_float(v[i][2 * q]), __uint_as_float(v[i][2 * q + 1]));
                         if (to_tmem) {
                             if constexpr (CW == 32) ptx::tmem_st16(a_tmem + c0 / 2, p);
                         } else {
@@ -396,6 +442,62 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
             }
         }
         if (leader) ptx::tma_wait_group<0>();
+    } else if constexpr (NENC > 0) {
+        // ------------------------------------------------------------ hash-grid encoder warps
+        const int ew = warp - (1 + NSLOT + 4 * NSLOT); // 0 .. NENC-1
+        const int row = (ew & 3) * 32 + lane;          // tile row owned by this thread
+        const int level0 = ew >> 2;                     // this warp takes levels level0, level0 + 2, ...
+        const int etid = ew * 32 + lane;
+        const GridParams &g = *gp;
+        const int n_levels = (int)g.n_levels;
+        const int n_dims = (int)g.n_dims;
+        for (int l = etid; l < n_levels; l += 32 * NENC) enc_levels[l] = grid_level_info(g, (uint32_t)l);
+        const GridCommon gc = grid_common(g);
+        // all NSLOT input tiles start as zeros: the padding columns are never written again
+        for (int i = etid; i < NSLOT * (T::ACT_BYTES / 16); i += 32 * NENC)
+            reinterpret_cast<uint4 *>(smem + S::XBUF)[i] = make_uint4(0, 0, 0, 0);
+        ptx::named_bar_sync(8, 32 * NENC);
+        float xin[3] = {0.0f, 0.0f, 0.0f};
+        auto fetch = [&](int tile) {
+            const size_t grow = (size_t)tile * T::TM + row;
+            for (int d = 0; d < 3; ++d) xin[d] = (d < n_dims && grow < batch) ? __ldg(coords + grow * n_dims + d) : 0.0f;
+        };
+        if (my_tiles > 0) fetch(blockIdx.x);
+        for (int j = 0; j < my_tiles; ++j) {
+            const int s = j % NSLOT, t = j / NSLOT;
+            const int tile = blockIdx.x + j * gridDim.x;
+            if (t >= 1 && !__all_sync(0xffffffffu, lane != 0 || ptx::mbar_wait(&bars.x_empty[s], (t - 1) & 1, abort_flag))) {
+                if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | 0x40 | s);
+                break;
+            }
+            uint8_t *xt = smem + S::XBUF + s * T::ACT_BYTES;
+            if (STORE_ALL && j >= NSLOT) { // the store of this slot's previous tile has read the buffer
+                if (etid == 0) ptx::tma_wait_group_read<NSLOT - 1>();
+                ptx::named_bar_sync(8, 32 * NENC);
+            }
+            const bool valid = (size_t)tile * T::TM + row < batch;
+            if (n_dims == 3) {
+                encode_grid_rows<3>(xt, row, level0, gc, enc_levels, n_levels, table, xin, valid, fp16, T::ATOM_COLS,
+                                    T::ACT_ATOM_BYTES, T::ROW_BYTES, T::CHUNKS);
+            } else {
+                const float x2[2] = {xin[0], xin[1]};
+                encode_grid_rows<2>(xt, row, level0, gc, enc_levels, n_levels, table, x2, valid, fp16, T::ATOM_COLS,
+                                    T::ACT_ATOM_BYTES, T::ROW_BYTES, T::CHUNKS);
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&bars.x_full[s]);
+            if (STORE_ALL) { // the encoded tile is matrix 0 of the stored activations
+                ptx::named_bar_sync(8, 32 * NENC);
+                if (etid == 0) {
+                    for (int a = 0; a < T::KATOMS; ++a)
+                        ptx::tma_store_3d(&tm_interm, xt + a * T::ACT_ATOM_BYTES, a * T::ATOM_COLS, tile * T::TM, 0);
+                    ptx::tma_commit_group();
+                }
+            }
+            if (j + 1 < my_tiles) fetch(tile + gridDim.x);
+        }
+        if (STORE_ALL && etid == 0) ptx::tma_wait_group<0>();
     }
 
     // ---------------------------------------------------------------- teardown
@@ -413,25 +515,39 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
 }
 
 // ---------------------------------------------------------------------- host side
-template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN, bool STREAM_W = false>
-static cudaError_t launch_variant(const FwdLaunch &p) {
+template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN, bool STREAM_W, int NENC, bool HF_>
+static cudaError_t launch_variant_t(const FwdLaunch &p) {
     using T = Tile<W>;
     using S = FwdSmem<W, NSLOT, TMEM_A, STORE_ALL, STREAM_W>;
     const size_t smem = (size_t)S::WBUF + (size_t)S::weight_tiles(p.n_mat) * T::WGT_BYTES + 1024;
     if (smem > 227 * 1024 - 1024 || !S::fits_tmem) return cudaErrorInvalidConfiguration;
-    auto kern = mlp_fwd_kernel<W, NSLOT, STORE_ALL, TMEM_A, B_MN, STREAM_W>;
+    auto kern = mlp_fwd_kernel<W, NSLOT, STORE_ALL, TMEM_A, B_MN, STREAM_W, NENC, HF_>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
     const int grid = n_tiles < p.n_sm ? n_tiles : p.n_sm;
     if (grid == 0) return cudaSuccess;
     count_launch();
-    kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, p.tm_y, p.tm_interm, B_MN ? p.wimg : p.wimg_t, n_tiles, p.n_mat,
+    kern<<<grid, S::THREADS + 32 * NENC, smem, p.stream>>>(p.tm_x, p.tm_y, p.tm_interm, B_MN ? p.wimg : p.wimg_t, p.grid_params,
+                                                           p.grid_table, p.grid_x, n_tiles, p.n_mat,
                                                p.act, p.out_act, p.write_y, p.batch, p.enc, p.status);
     return cudaGetLastError();
 }
 
+template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN, bool STREAM_W = false, int NENC = 0>
+static cudaError_t launch_variant(const FwdLaunch &p) {
+    return p.fp16 ? launch_variant_t<W, NSLOT, STORE_ALL, TMEM_A, B_MN, STREAM_W, NENC, true>(p)
+                  : launch_variant_t<W, NSLOT, STORE_ALL, TMEM_A, B_MN, STREAM_W, NENC, false>(p);
+}
+
+// fused hash-grid encoding: two tiles in flight (the gathers, not the GEMMs, set the pace), weights resident
+template <int W> static cudaError_t launch_grid_w(const FwdLaunch &p) {
+    if (p.store_all) return launch_variant<W, 2, true, false, false, false, kGridEncWarps>(p);
+    return launch_variant<W, 2, false, (W >= 32), false, false, kGridEncWarps>(p);
+}
+
 template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
+    if (p.grid_params) return launch_grid_w<W>(p);
     // variant bit 256 (tests): stream the weights through the per-slot rings even if they would fit on chip
     const bool force_stream = (p.variant & 256) != 0;
     cudaError_t e = cudaErrorInvalidConfiguration;

@@ -26,9 +26,15 @@ struct FwdLaunch {
     int width;
     int n_mat; // number of weight matrices = n_hidden_layers + 1
     int act, out_act;
+    int fp16; // operands and activations are fp16 instead of bf16
     int store_all;
     int write_y;
     EncodedInput enc; // enc.x != nullptr: the input tile is produced in the kernel from fp32 coordinates
+    // grid_params != nullptr: the input tile is the hash-grid encoding (2-D or 3-D, 2 features per level, at most
+    // `width` features) of the fp32 positions grid_x, gathered from grid_table by extra warps of the kernel
+    const struct GridParams *grid_params; // device copy
+    const float *grid_table;
+    const float *grid_x;
     int variant;
     int n_sm;
     int *status;
@@ -49,6 +55,7 @@ struct BwdLaunch {
     int width;
     int n_mat;
     int act, out_act;
+    int fp16; // operands and activations are fp16 instead of bf16
     int store_bwd;
     int want_dx;
     int variant;
@@ -76,6 +83,7 @@ struct TrainLaunch {
     int width;
     int n_mat;
     int act, out_act;
+    int fp16; // operands and activations are fp16 instead of bf16
     float loss_scale;
     int n_sm;
     int *status;

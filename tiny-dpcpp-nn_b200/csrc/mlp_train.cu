@@ -60,7 +60,7 @@ struct TrainBarriers {
     float loss_red[16];
 };
 
-template <int W>
+template <int W, bool HF_>
 __global__ void __launch_bounds__(TrainSmem<W>::THREADS, 1)
 mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *__restrict__ wimg,
                  const float *__restrict__ targets, int n_targets, float *__restrict__ dw_slabs,
@@ -68,6 +68,7 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                  float loss_scale, float inv_n, int tmem_cols, const EncodedInput enc, int *status) {
     using T = Tile<W>;
     using S = TrainSmem<W>;
+    constexpr int fp16 = HF_ ? 1 : 0; // element type of operands and activations: bf16 or fp16
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ TrainBarriers bars;
@@ -111,19 +112,35 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
-        // input tiles by TMA (lane 0) or, with a folded identity encoding, written by the whole warp from fp32 coordinates
-        if (my_tiles > 0) {
+        // weights once; then input tiles by TMA (lane 0) or, with a folded identity encoding, written by the whole
+        // warp from fp32 coordinates
+        if (lane == 0 && my_tiles > 0) {
+            ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
+            for (int l = 0; l < n_mat; ++l)
+                ptx::bulk_load(smem + S::WBUF(n_mat) + l * T::WGT_BYTES,
+                               reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
+                               &bars.w_full);
+        }
+        if (!enc.x) {
             if (lane == 0) {
-                ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
-                for (int l = 0; l < n_mat; ++l)
-                    ptx::bulk_load(smem + S::WBUF(n_mat) + l * T::WGT_BYTES,
-                                   reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
-                                   &bars.w_full);
+                for (int t = 0; t < my_tiles; ++t) {
+                    const int tile = blockIdx.x + t * gridDim.x;
+                    const int b = t & 1;
+                    if (t >= 2 && !ptx::mbar_wait(&bars.x_empty[b], ((t >> 1) - 1) & 1, abort_flag)) {
+                        atomicExch(status, KS_TIMEOUT_PRODUCER | 1);
+                        break;
+                    }
+                    ptx::mbar_arrive_expect_tx(&bars.x_full[b], T::ACT_BYTES);
+                    for (int at = 0; at < T::KATOMS; ++at)
+                        ptx::tma_load_2d(smem + S::X + b * T::ACT_BYTES + at * T::ACT_ATOM_BYTES, &tm_x, at * T::ATOM_COLS,
+                                         tile * T::TM, &bars.x_full[b]);
+                }
             }
-            if (enc.x) {
-                fill_tiles_with_ones<W>(smem + S::X, 2, lane);
-                __syncwarp();
-            }
+        } else if (my_tiles > 0) {
+            fill_tiles_with_ones<W>(smem + S::X, 2, lane, fp16);
+            __syncwarp();
+            IdentityTileEncoder<W> encoder(enc, batch, lane, fp16);
+            encoder.fetch((size_t)blockIdx.x * T::TM);
             for (int t = 0; t < my_tiles; ++t) {
                 const int tile = blockIdx.x + t * gridDim.x;
                 const int b = t & 1;
@@ -131,24 +148,18 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | 1);
                     break;
                 }
-                if (enc.x) {
-                    encode_identity_tile<W>(smem + S::X + b * T::ACT_BYTES, enc, (size_t)tile * T::TM, batch, lane);
-                    ptx::fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&bars.x_full[b]);
-                } else if (lane == 0) {
-                    ptx::mbar_arrive_expect_tx(&bars.x_full[b], T::ACT_BYTES);
-                    for (int at = 0; at < T::KATOMS; ++at)
-                        ptx::tma_load_2d(smem + S::X + b * T::ACT_BYTES + at * T::ACT_ATOM_BYTES, &tm_x, at * T::ATOM_COLS,
-                                         tile * T::TM, &bars.x_full[b]);
-                }
+                encoder.store(smem + S::X + b * T::ACT_BYTES);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&bars.x_full[b]);
+                if (t + 1 < my_tiles) encoder.fetch((size_t)(tile + gridDim.x) * T::TM);
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ chain-GEMM issuer
         if (my_tiles > 0) { // all lanes run the loop, one elected lane issues (see ptx::elect_one)
-            constexpr uint32_t idesc_fwd = ptx::make_idesc_bf16(128, W, 0, 1); // B = W_l read MN-major
-            constexpr uint32_t idesc_bwd = ptx::make_idesc_bf16(128, W, 0, 0); // B = W_l read K-major
+            const uint32_t idesc_fwd = ptx::make_idesc_16(128, W, 0, 1, fp16); // B = W_l read MN-major
+            const uint32_t idesc_bwd = ptx::make_idesc_16(128, W, 0, 0, fp16); // B = W_l read K-major
             const uint64_t x_desc0 = T::kdesc_base(smem_base + S::X);
             const uint64_t a_desc0 = T::kdesc_base(smem_base + S::A(1));
             const uint64_t d_desc0 = T::kdesc_base(smem_base + S::D(n_mat, 0));
@@ -223,7 +234,7 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
         // ------------------------------------------------------------ weight-gradient issuer
         if (my_tiles > 0) {
             constexpr int DW_M = (W == 128) ? 128 : 64;
-            constexpr uint32_t idesc_dw = ptx::make_idesc_bf16(DW_M, W, 1, 1);
+            const uint32_t idesc_dw = ptx::make_idesc_16(DW_M, W, 1, 1, fp16);
             const uint64_t x_desc0 = T::mndesc_base(smem_base + S::X, T::ACT_ATOM_BYTES);
             const uint64_t a_desc0 = T::mndesc_base(smem_base + S::A(1), T::ACT_ATOM_BYTES);
             const uint64_t d_desc0 = T::mndesc_base(smem_base + S::D(n_mat, 0), T::ACT_ATOM_BYTES);
@@ -360,15 +371,16 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                     break;
                 }
                 uint8_t *dst = smem + S::A(l + 1);
-                dispatch_act(act, [&](auto tag) {
+                dispatch_act_t<HF_>(act, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
+                    constexpr bool HF = decltype(tag)::half;
 #pragma unroll
                     for (int ch = 0; ch < CPT / 8; ++ch) {
                         uint4 o;
-                        o.x = act_pack_t<ACT>(__uint_as_float(v[ch * 8 + 0]), __uint_as_float(v[ch * 8 + 1]));
-                        o.y = act_pack_t<ACT>(__uint_as_float(v[ch * 8 + 2]), __uint_as_float(v[ch * 8 + 3]));
-                        o.z = act_pack_t<ACT>(__uint_as_float(v[ch * 8 + 4]), __uint_as_float(v[ch * 8 + 5]));
-                        o.w = act_pack_t<ACT>(__uint_as_float(v[ch * 8 + 6]), __uint_as_float(v[ch * 8 + 7]));
+                        o.x = act_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 0]), __uint_as_float(v[ch * 8 + 1]));
+                        o.y = act_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 2]), __uint_as_float(v[ch * 8 + 3]));
+                        o.z = act_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 4]), __uint_as_float(v[ch * 8 + 5]));
+                        o.w = act_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 6]), __uint_as_float(v[ch * 8 + 7]));
                         *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) = o;
                     }
                 });
@@ -390,25 +402,26 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                     break;
                 }
                 uint8_t *dst = smem + S::D(n_mat, 0);
-                dispatch_act(out_act, [&](auto tag) {
+                dispatch_act_t<HF_>(out_act, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
+                    constexpr bool HF = decltype(tag)::half;
 #pragma unroll
                     for (int ch = 0; ch < CPT / 8; ++ch) {
                         uint32_t o[4];
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             // the prediction as the network stores it (bf16), then the loss on that value
-                            const uint32_t y16 = act_pack_t<ACT>(__uint_as_float(v[ch * 8 + 2 * q]),
+                            const uint32_t y16 = act_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 2 * q]),
                                                                   __uint_as_float(v[ch * 8 + 2 * q + 1]));
-                            float d0 = ptx::bf16lo_to_f32(y16) - tg[ch * 8 + 2 * q];
-                            float d1 = ptx::bf16hi_to_f32(y16) - tg[ch * 8 + 2 * q + 1];
+                            float d0 = ptx::lo_f32<HF>(y16) - tg[ch * 8 + 2 * q];
+                            float d1 = ptx::hi_f32<HF>(y16) - tg[ch * 8 + 2 * q + 1];
                             if (!row_valid) d0 = d1 = 0.0f;
                             loss_local += d0 * d0 * inv_n + d1 * d1 * inv_n;
                             const uint32_t g16 =
-                                ptx::pack_bf16x2(loss_scale * 2.0f * d0 * inv_n, loss_scale * 2.0f * d1 * inv_n);
+                                ptx::pack2<HF>(loss_scale * 2.0f * d0 * inv_n, loss_scale * 2.0f * d1 * inv_n);
                             o[q] = (ACT == ACT_NONE)
                                        ? g16
-                                       : act_bwd_pack_t<ACT>(ptx::bf16lo_to_f32(g16), ptx::bf16hi_to_f32(g16), y16);
+                                       : act_bwd_pack_t<ACT, HF>(ptx::lo_f32<HF>(g16), ptx::hi_f32<HF>(g16), y16);
                         }
                         *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) = make_uint4(o[0], o[1], o[2], o[3]);
                     }
@@ -432,18 +445,19 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
                 }
                 const uint8_t *abuf = smem + S::A(l);
                 uint8_t *dst = smem + S::D(n_mat, p);
-                dispatch_act(act, [&](auto tag) {
+                dispatch_act_t<HF_>(act, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
+                    constexpr bool HF = decltype(tag)::half;
 #pragma unroll
                     for (int ch = 0; ch < CPT / 8; ++ch) {
                         const int off = chunk_at(ch);
                         uint4 f = make_uint4(0, 0, 0, 0);
                         if constexpr (ACT != ACT_NONE) f = *reinterpret_cast<const uint4 *>(abuf + off);
                         uint4 o;
-                        o.x = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 0]), __uint_as_float(v[ch * 8 + 1]), f.x);
-                        o.y = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 2]), __uint_as_float(v[ch * 8 + 3]), f.y);
-                        o.z = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 4]), __uint_as_float(v[ch * 8 + 5]), f.z);
-                        o.w = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 6]), __uint_as_float(v[ch * 8 + 7]), f.w);
+                        o.x = act_bwd_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 0]), __uint_as_float(v[ch * 8 + 1]), f.x);
+                        o.y = act_bwd_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 2]), __uint_as_float(v[ch * 8 + 3]), f.y);
+                        o.z = act_bwd_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 4]), __uint_as_float(v[ch * 8 + 5]), f.z);
+                        o.w = act_bwd_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 6]), __uint_as_float(v[ch * 8 + 7]), f.w);
                         *reinterpret_cast<uint4 *>(dst + off) = o;
                     }
                 });
@@ -527,7 +541,7 @@ template <int W> static cudaError_t launch_train_w(TrainLaunch &p) {
                                                    p.loss_scale, inv_n, tmem_cols, p.enc, p.status);
         return cudaGetLastError();
     };
-    return go(mlp_train_kernel<W>);
+    return p.fp16 ? go(mlp_train_kernel<W, true>) : go(mlp_train_kernel<W, false>);
 }
 
 cudaError_t launch_mlp_train(TrainLaunch &p) {

@@ -27,9 +27,11 @@ namespace tnn {
 
 constexpr int kPipeMaxMat = 12; // upper bound of the barrier array; what fits is decided by shared memory and TMEM columns
 
-// TGT: the fp32 targets of a tile (128 x W, twice the bytes of a bf16 tile) are staged by TMA into the delta_L
+// TGT (0, 1, 2): how a tile's fp32 targets reach the loss step.  0: per-thread global loads.  1: full-width rows
+// (128 x W fp32, twice the bytes of a bf16 tile) staged by TMA boxes.  2: narrow rows (n_targets < W: 128 * n_targets
+// contiguous floats) staged by one plain bulk copy.  Staged targets go into the delta_L
 // buffer plus one more tile right behind it; the loss step pulls its slice into registers before delta_L is written.
-template <int W, bool TGT> struct PipeSmem {
+template <int W, int TGT> struct PipeSmem {
     using T = Tile<W>;
     // delta tiles first (see mlp_train.cu: the M = 64 weight-gradient GEMM over-reads past them for W < 64)
     static constexpr int DL = 0;                                  // delta_L: forward stage -> backward stage
@@ -69,15 +71,16 @@ struct PipeBarriers {
 // inference kernel does, was measured slower here: the activations must be in shared memory anyway for the
 // weight-gradient GEMMs and the activation backward, and the extra tcgen05.st in every epilogue step costs more
 // than the shorter GEMMs save.)
-template <int W, bool TGT>
+template <int W, int TGT, bool HF_>
 __global__ void __launch_bounds__(PipeSmem<W, TGT>::THREADS, 1)
 mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_tgt,
                       const __nv_bfloat16 *__restrict__ wimg,
                       const float *__restrict__ targets, int n_targets, float *__restrict__ dw_slabs,
                       float *__restrict__ loss_partials, size_t batch, int n_tiles, int n_mat, int act, int out_act,
-                      float loss_scale, float inv_n, const EncodedInput enc, int narrow_targets, int *status) {
+                      float loss_scale, float inv_n, const EncodedInput enc, int *status) {
     using T = Tile<W>;
     using S = PipeSmem<W, TGT>;
+    constexpr int fp16 = HF_ ? 1 : 0; // element type of operands and activations: bf16 or fp16
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ PipeBarriers bars;
@@ -118,7 +121,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
         bars.abort_flag = 0;
         ptx::fence_barrier_init();
         if (!enc.x) ptx::prefetch_tmap(&tm_x);
-        if constexpr (TGT) ptx::prefetch_tmap(&tm_tgt);
+        if constexpr (TGT == 1) ptx::prefetch_tmap(&tm_tgt);
     }
     if (warp == 1) {
         ptx::tmem_alloc(&bars.tmem_base, kTmemCols);
@@ -133,21 +136,59 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
-        // Input tiles arrive by TMA (lane 0), or - with a folded identity encoding - are written by the whole warp
-        // from the fp32 coordinates.  Targets are staged by lane 0: full-width rows as swizzled TMA boxes, narrower
-        // rows (n_targets < W: 128 * n_targets contiguous floats per tile) by one plain bulk copy.
-        if (my_tiles > 0) {
+        // Weights once; then per tile the input (TMA by lane 0, or - with a folded identity encoding - written by
+        // the whole warp from the fp32 coordinates) and the staged targets (lane 0).
+        if (lane == 0 && my_tiles > 0) {
+            ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
+            for (int l = 0; l < n_mat; ++l)
+                ptx::bulk_load(smem + S::WBUF(n_mat) + l * T::WGT_BYTES,
+                               reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
+                               &bars.w_full);
+        }
+        // targets of tile t (lane 0; the staging area overlaps delta_L: both GEMMs that read delta_L of the previous
+        // tile must be complete)
+        auto stage_targets = [&](int t, int tile) -> bool {
+            if constexpr (TGT != 0) {
+                if (t > 0 && !ptx::mbar_wait(&bars.dl_free, (t - 1) & 1, abort_flag)) {
+                    atomicExch(status, KS_TIMEOUT_PRODUCER | 2);
+                    return false;
+                }
+                if constexpr (TGT == 2) {
+                    const size_t row0 = (size_t)tile * T::TM;
+                    const uint32_t rows = (uint32_t)(batch - row0 < (size_t)T::TM ? batch - row0 : (size_t)T::TM);
+                    const uint32_t bytes = rows * (uint32_t)n_targets * 4u; // rows % 8 == 0: a multiple of 16
+                    ptx::mbar_arrive_expect_tx(&bars.tgt_full, bytes);
+                    ptx::bulk_load(smem + S::DL, targets + row0 * n_targets, bytes, &bars.tgt_full);
+                } else {
+                    ptx::mbar_arrive_expect_tx(&bars.tgt_full, (uint32_t)(S::TGT_BOXES * S::TGT_BOX_BYTES));
+                    for (int bx = 0; bx < S::TGT_BOXES; ++bx)
+                        ptx::tma_load_2d(smem + S::DL + bx * S::TGT_BOX_BYTES, &tm_tgt, bx * 32, tile * T::TM,
+                                         &bars.tgt_full);
+                }
+            }
+            return true;
+        };
+        if (!enc.x) {
             if (lane == 0) {
-                ptx::mbar_arrive_expect_tx(&bars.w_full, (uint32_t)(n_mat * T::WGT_BYTES));
-                for (int l = 0; l < n_mat; ++l)
-                    ptx::bulk_load(smem + S::WBUF(n_mat) + l * T::WGT_BYTES,
-                                   reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
-                                   &bars.w_full);
+                for (int t = 0; t < my_tiles; ++t) {
+                    const int tile = blockIdx.x + t * gridDim.x;
+                    const int b = t & 1;
+                    if (t >= 2 && !ptx::mbar_wait(&bars.x_empty[b], ((t >> 1) - 1) & 1, abort_flag)) {
+                        atomicExch(status, KS_TIMEOUT_PRODUCER | 1);
+                        break;
+                    }
+                    ptx::mbar_arrive_expect_tx(&bars.x_full[b], T::ACT_BYTES);
+                    for (int at = 0; at < T::KATOMS; ++at)
+                        ptx::tma_load_2d(smem + S::X(b) + at * T::ACT_ATOM_BYTES, &tm_x, at * T::ATOM_COLS, tile * T::TM,
+                                         &bars.x_full[b]);
+                    if (!stage_targets(t, tile)) break;
+                }
             }
-            if (enc.x) {
-                fill_tiles_with_ones<W>(smem + S::X(0), 2, lane);
-                __syncwarp();
-            }
+        } else if (my_tiles > 0) {
+            fill_tiles_with_ones<W>(smem + S::X(0), 2, lane, fp16);
+            __syncwarp();
+            IdentityTileEncoder<W> encoder(enc, batch, lane, fp16);
+            encoder.fetch((size_t)blockIdx.x * T::TM);
             for (int t = 0; t < my_tiles; ++t) {
                 const int tile = blockIdx.x + t * gridDim.x;
                 const int b = t & 1;
@@ -156,44 +197,19 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | 1);
                     break;
                 }
-                if (enc.x) {
-                    encode_identity_tile<W>(smem + S::X(b), enc, (size_t)tile * T::TM, batch, lane);
-                    ptx::fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&bars.x_full[b]);
-                } else if (lane == 0) {
-                    ptx::mbar_arrive_expect_tx(&bars.x_full[b], T::ACT_BYTES);
-                    for (int at = 0; at < T::KATOMS; ++at)
-                        ptx::tma_load_2d(smem + S::X(b) + at * T::ACT_ATOM_BYTES, &tm_x, at * T::ATOM_COLS, tile * T::TM,
-                                         &bars.x_full[b]);
-                }
-                if constexpr (TGT) {
-                    // the staging area overlaps delta_L: both GEMMs that read delta_L of the previous tile are complete
-                    if (t > 0 && !__all_sync(0xffffffffu, lane != 0 || ptx::mbar_wait(&bars.dl_free, (t - 1) & 1, abort_flag))) {
-                        if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | 2);
-                        break;
-                    }
-                    if (lane == 0) {
-                        if (narrow_targets) {
-                            const size_t row0 = (size_t)tile * T::TM;
-                            const uint32_t rows = (uint32_t)(batch - row0 < (size_t)T::TM ? batch - row0 : (size_t)T::TM);
-                            const uint32_t bytes = rows * (uint32_t)n_targets * 4u; // rows % 8 == 0: a multiple of 16
-                            ptx::mbar_arrive_expect_tx(&bars.tgt_full, bytes);
-                            ptx::bulk_load(smem + S::DL, targets + row0 * n_targets, bytes, &bars.tgt_full);
-                        } else {
-                            ptx::mbar_arrive_expect_tx(&bars.tgt_full, (uint32_t)(S::TGT_BOXES * S::TGT_BOX_BYTES));
-                            for (int bx = 0; bx < S::TGT_BOXES; ++bx)
-                                ptx::tma_load_2d(smem + S::DL + bx * S::TGT_BOX_BYTES, &tm_tgt, bx * 32, tile * T::TM,
-                                                 &bars.tgt_full);
-                        }
-                    }
-                }
+                encoder.store(smem + S::X(b));
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&bars.x_full[b]);
+                // coordinates of the next tile travel while this one is consumed
+                if (t + 1 < my_tiles) encoder.fetch((size_t)(tile + gridDim.x) * T::TM);
+                if (!__all_sync(0xffffffffu, lane != 0 || stage_targets(t, tile))) break;
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ forward chain issuer
         if (my_tiles > 0) { // all lanes run the loop, one elected lane issues (see ptx::elect_one)
-            constexpr uint32_t idesc = ptx::make_idesc_bf16(128, W, 0, 1); // B = W_l read MN-major
+            const uint32_t idesc = ptx::make_idesc_16(128, W, 0, 1, fp16); // B = W_l read MN-major
             const uint64_t x_desc0 = T::kdesc_base(smem_base + S::X(0));
             const uint64_t ab_desc0 = T::kdesc_base(smem_base + S::AB(0));
             const uint64_t w_desc0 = T::mndesc_base(smem_base + S::WBUF(n_mat), T::WGT_ATOM_BYTES);
@@ -238,7 +254,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
     } else if (warp == 2) {
         // ------------------------------------------------------------ backward chain issuer
         if (my_tiles > 0) {
-            constexpr uint32_t idesc = ptx::make_idesc_bf16(128, W, 0, 0); // B = W_l read K-major
+            const uint32_t idesc = ptx::make_idesc_16(128, W, 0, 0, fp16); // B = W_l read K-major
             const uint64_t dl_desc = T::kdesc_base(smem_base + S::DL);
             const uint64_t dp_desc0 = T::kdesc_base(smem_base + S::DP(0));
             const uint64_t w_desc0 = T::kdesc_base(smem_base + S::WBUF(n_mat));
@@ -280,7 +296,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
         // ------------------------------------------------------------ weight-gradient issuer
         if (my_tiles > 0) {
             constexpr int DW_M = (W == 128) ? 128 : 64;
-            constexpr uint32_t idesc = ptx::make_idesc_bf16(DW_M, W, 1, 1);
+            const uint32_t idesc = ptx::make_idesc_16(DW_M, W, 1, 1, fp16);
             const uint64_t x_desc0 = T::mndesc_base(smem_base + S::X(0), T::ACT_ATOM_BYTES);
             const uint64_t ab_desc0 = T::mndesc_base(smem_base + S::AB(0), T::ACT_ATOM_BYTES);
             const uint64_t dl_desc = T::mndesc_base(smem_base + S::DL, T::ACT_ATOM_BYTES);
@@ -381,12 +397,13 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 uint32_t v[CPT];
                 load_acc(v);
                 uint8_t *dst = smem + S::AB(bi);
-                dispatch_act(act, [&](auto tag) {
+                dispatch_act_t<HF_>(act, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
+                    constexpr bool HF = decltype(tag)::half;
                     uint32_t pk[CPT / 2];
 #pragma unroll
                     for (int q = 0; q < CPT / 2; ++q)
-                        pk[q] = act_pack_t<ACT>(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
+                        pk[q] = act_pack_t<ACT, HF>(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
 #pragma unroll
                     for (int ch = 0; ch < CPT / 8; ++ch)
                         *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) =
@@ -400,12 +417,12 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
             if (!ok) break;
             // ---- output layer + L2 loss.  The target slice is requested before the wait for the last GEMM.
             float tg[CPT];
-            if constexpr (TGT) {
+            if constexpr (TGT != 0) {
                 if (!wait_u(&bars.tgt_full, t & 1, 8)) {
                     ok = false;
                     break;
                 }
-                if (narrow_targets) {
+                if constexpr (TGT == 2) {
                     // row-major rows of n_targets floats; columns past them (and rows past the batch) compare with 0
                     const float *src = reinterpret_cast<const float *>(smem + S::DL) + row * n_targets;
 #pragma unroll
@@ -454,7 +471,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&bars.f_ready);
-            if constexpr (!TGT) { // delta_L of the previous tile must have been consumed by its two GEMMs
+            if constexpr (TGT == 0) { // delta_L of the previous tile must have been consumed by its two GEMMs
                 if (t > 0 && !wait_u(&bars.dl_free, (t - 1) & 1, 4)) {
                     ok = false;
                     break;
@@ -464,24 +481,25 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
             // rows past the end of the batch contribute neither loss nor gradient
             const float gscale = row_valid ? loss_scale * 2.0f * inv_n : 0.0f;
             float sq = 0.0f;
-            dispatch_act(out_act, [&](auto tag) {
+            dispatch_act_t<HF_>(out_act, [&](auto tag) {
                 constexpr int ACT = decltype(tag)::value;
+                    constexpr bool HF = decltype(tag)::half;
 #pragma unroll
                 for (int ch = 0; ch < CPT / 8; ++ch) {
                     uint32_t o[4];
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         // the prediction as the network stores it (bf16), then the loss on that value
-                        const uint32_t y16 = act_pack_t<ACT>(__uint_as_float(v[ch * 8 + 2 * q]),
+                        const uint32_t y16 = act_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 2 * q]),
                                                               __uint_as_float(v[ch * 8 + 2 * q + 1]));
-                        const float d0 = ptx::bf16lo_to_f32(y16) - tg[ch * 8 + 2 * q];
-                        const float d1 = ptx::bf16hi_to_f32(y16) - tg[ch * 8 + 2 * q + 1];
+                        const float d0 = ptx::lo_f32<HF>(y16) - tg[ch * 8 + 2 * q];
+                        const float d1 = ptx::hi_f32<HF>(y16) - tg[ch * 8 + 2 * q + 1];
                         sq = fmaf(d0, d0, sq);
                         sq = fmaf(d1, d1, sq);
-                        const uint32_t g16 = ptx::pack_bf16x2(d0 * gscale, d1 * gscale);
+                        const uint32_t g16 = ptx::pack2<HF>(d0 * gscale, d1 * gscale);
                         o[q] = (ACT == ACT_NONE)
                                    ? g16
-                                   : act_bwd_pack_t<ACT>(ptx::bf16lo_to_f32(g16), ptx::bf16hi_to_f32(g16), y16);
+                                   : act_bwd_pack_t<ACT, HF>(ptx::lo_f32<HF>(g16), ptx::hi_f32<HF>(g16), y16);
                     }
                     *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) = make_uint4(o[0], o[1], o[2], o[3]);
                 }
@@ -566,16 +584,17 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 else
                     ptx::tmem_ld8(acc_addr, v);
                 ptx::tmem_ld_wait();
-                dispatch_act(act, [&](auto tag) {
+                dispatch_act_t<HF_>(act, [&](auto tag) {
                     constexpr int ACT = decltype(tag)::value;
+                    constexpr bool HF = decltype(tag)::half;
                     uint32_t pk[CPT / 2];
 #pragma unroll
                     for (int ch = 0; ch < CPT / 8; ++ch) {
                         const uint4 f = fa[ch];
-                        pk[ch * 4 + 0] = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 0]), __uint_as_float(v[ch * 8 + 1]), f.x);
-                        pk[ch * 4 + 1] = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 2]), __uint_as_float(v[ch * 8 + 3]), f.y);
-                        pk[ch * 4 + 2] = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 4]), __uint_as_float(v[ch * 8 + 5]), f.z);
-                        pk[ch * 4 + 3] = act_bwd_pack_t<ACT>(__uint_as_float(v[ch * 8 + 6]), __uint_as_float(v[ch * 8 + 7]), f.w);
+                        pk[ch * 4 + 0] = act_bwd_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 0]), __uint_as_float(v[ch * 8 + 1]), f.x);
+                        pk[ch * 4 + 1] = act_bwd_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 2]), __uint_as_float(v[ch * 8 + 3]), f.y);
+                        pk[ch * 4 + 2] = act_bwd_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 4]), __uint_as_float(v[ch * 8 + 5]), f.z);
+                        pk[ch * 4 + 3] = act_bwd_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 6]), __uint_as_float(v[ch * 8 + 7]), f.w);
                     }
 #pragma unroll
                     for (int ch = 0; ch < CPT / 8; ++ch)
@@ -637,13 +656,13 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
 // 227 KB per CTA minus the statically allocated barriers
 constexpr size_t kPipeSmemLimit = 227 * 1024 - 2048;
 
-template <int W, bool TGT> static cudaError_t launch_pipe_w(TrainLaunch &p) {
+template <int W, int TGT, bool HF_> static cudaError_t launch_pipe_t(TrainLaunch &p) {
     using T = Tile<W>;
     using S = PipeSmem<W, TGT>;
     const size_t smem = (size_t)S::WBUF(p.n_mat) + (size_t)p.n_mat * T::WGT_BYTES + 1024;
     const int cols_needed = 2 * W + p.n_mat * W;
     if (smem > kPipeSmemLimit || cols_needed > 512 || p.n_mat > kPipeMaxMat) return cudaErrorInvalidConfiguration;
-    auto kern = mlp_train_pipe_kernel<W, TGT>;
+    auto kern = mlp_train_pipe_kernel<W, TGT, HF_>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
@@ -652,21 +671,26 @@ template <int W, bool TGT> static cudaError_t launch_pipe_w(TrainLaunch &p) {
     if (grid == 0) return cudaSuccess;
     const float inv_n = 1.0f / ((float)p.batch * (float)W);
     count_launch();
-    kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, TGT ? p.tm_tgt : p.tm_x, p.wimg, p.targets, p.n_targets, p.dw_partials, p.loss_partials,
+    kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, TGT == 1 ? p.tm_tgt : p.tm_x, p.wimg, p.targets, p.n_targets, p.dw_partials, p.loss_partials,
                                                p.batch, n_tiles, p.n_mat, p.act, p.out_act, p.loss_scale, inv_n,
-                                               p.enc, TGT && p.tgt_mode == 2 ? 1 : 0, p.status);
+                                               p.enc, p.status);
     return cudaGetLastError();
+}
+
+template <int W, int TGT> static cudaError_t launch_pipe_w(TrainLaunch &p) {
+    return p.fp16 ? launch_pipe_t<W, TGT, true>(p) : launch_pipe_t<W, TGT, false>(p);
 }
 
 cudaError_t launch_mlp_train_pipe(TrainLaunch &p) {
     // staged targets (tgt_mode 1: TMA boxes, 2: one bulk copy of narrow rows) need one more tile of shared memory:
     // without room for it the per-thread loads remain
     cudaError_t e = cudaErrorInvalidConfiguration;
-    if (p.width == 16) return launch_pipe_w<16, false>(p); // 64-byte target rows: read directly
+    if (p.width == 16) return launch_pipe_w<16, 0>(p); // 64-byte target rows: read directly
     if (p.width != 64 && p.width != 32) return e;
     const bool w64 = p.width == 64;
-    if (p.tgt_mode) e = w64 ? launch_pipe_w<64, true>(p) : launch_pipe_w<32, true>(p);
-    if (e == cudaErrorInvalidConfiguration) e = w64 ? launch_pipe_w<64, false>(p) : launch_pipe_w<32, false>(p);
+    if (p.tgt_mode == 1) e = w64 ? launch_pipe_w<64, 1>(p) : launch_pipe_w<32, 1>(p);
+    if (p.tgt_mode == 2) e = w64 ? launch_pipe_w<64, 2>(p) : launch_pipe_w<32, 2>(p);
+    if (e == cudaErrorInvalidConfiguration) e = w64 ? launch_pipe_w<64, 0>(p) : launch_pipe_w<32, 0>(p);
     return e;
 }
 

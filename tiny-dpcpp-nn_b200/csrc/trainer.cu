@@ -24,6 +24,7 @@
 #include "mlp_common.cuh"
 
 #include <cmath>
+#include <cuda_fp16.h>
 #include <cstring>
 #include <dlfcn.h>
 #include <mutex>
@@ -113,7 +114,7 @@ __global__ void __launch_bounds__(128)
 adam_refresh_kernel(float *__restrict__ master, float *__restrict__ m, float *__restrict__ v, float *__restrict__ grads,
                     const float *__restrict__ slabs, int n_slabs, const float *__restrict__ loss_partials, int n_loss,
                     float *__restrict__ loss_out, int n_mat, int one_padded_in, int unpadded_out, float grad_scale,
-                    float lr, float b1, float b2, float eps, float bc1, float bc2_sqrt,
+                    float lr, float b1, float b2, float eps, float bc1, float bc2_sqrt, int net_fp16,
                     __nv_bfloat16 *__restrict__ packed_out, __nv_bfloat16 *__restrict__ wimg,
                     __nv_bfloat16 *__restrict__ wimg_t) {
     using T = Tile<W>;
@@ -154,7 +155,8 @@ adam_refresh_kernel(float *__restrict__ master, float *__restrict__ m, float *__
     master[pk] = p;
     if (l == 0 && i >= one_padded_in) p = 0.0f;
     if (l == n_mat - 1 && o >= unpadded_out) p = 0.0f;
-    const __nv_bfloat16 b = __float2bfloat16_rn(p);
+    // the 16 bits the kernels read: bf16, or the bits of the fp16 value
+    const __nv_bfloat16 b = net_fp16 ? __ushort_as_bfloat16(__half_as_ushort(__float2half_rn(p))) : __float2bfloat16_rn(p);
     packed_out[pk] = b;
     uint8_t *wi = reinterpret_cast<uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES;
     uint8_t *wt = reinterpret_cast<uint8_t *>(wimg_t) + (size_t)l * T::WGT_BYTES;
@@ -166,7 +168,7 @@ template <bool FROM_SLABS>
 static cudaError_t launch_adam_refresh(int width, float *master, float *m, float *v, float *grads, const float *slabs,
                                        int n_slabs, const float *loss_partials, int n_loss, float *loss_out, int n_mat,
                                        int one_padded_in, int unpadded_out, float grad_scale, int step, float lr, float b1,
-                                       float b2, float eps, __nv_bfloat16 *packed, __nv_bfloat16 *wimg,
+                                       float b2, float eps, int net_fp16, __nv_bfloat16 *packed, __nv_bfloat16 *wimg,
                                        __nv_bfloat16 *wimg_t, cudaStream_t s) {
     const int n = n_mat * width * width;
     const int blocks = (n + 127) / 128;
@@ -177,8 +179,8 @@ static cudaError_t launch_adam_refresh(int width, float *master, float *m, float
     case WW:                                                                                                            \
         adam_refresh_kernel<WW, FROM_SLABS><<<blocks, 128, 0, s>>>(master, m, v, grads, slabs, n_slabs, loss_partials,  \
                                                                    n_loss, loss_out, n_mat, one_padded_in, unpadded_out, \
-                                                                   grad_scale, lr, b1, b2, eps, bc1, bc2_sqrt, packed,  \
-                                                                   wimg, wimg_t);                                       \
+                                                                   grad_scale, lr, b1, b2, eps, bc1, bc2_sqrt, net_fp16, \
+                                                                   packed, wimg, wimg_t);                               \
         break;
     switch (width) {
         TNN_CASE(16) TNN_CASE(32) TNN_CASE(64) TNN_CASE(128)
@@ -331,7 +333,8 @@ int tnn_trainer_create(tnn_network *net, tnn_encoding *enc, float lr, float beta
     t->grads = t->v + n;
     t->loss = t->grads + n;
     // master copy = the network's current (bf16) weights; tnn_trainer_set_master_params replaces it with the fp32 draw
-    e = tnn::launch_bf16_to_f32(net->packed, t->master, n, nullptr);
+    e = net->fp16 ? tnn::launch_fp16_to_f32(net->packed, t->master, n, nullptr)
+                  : tnn::launch_bf16_to_f32(net->packed, t->master, n, nullptr);
     if (e == cudaSuccess) e = cudaStreamSynchronize(nullptr);
     if (e != cudaSuccess) {
         tnn_trainer_destroy(t);
@@ -400,7 +403,7 @@ int tnn_trainer_reduce(tnn_trainer *t, void *stream) {
     cudaStream_t s = (cudaStream_t)stream;
     tnn_network *n = t->net;
     TNN_CUDA(tnn::launch_sum_partials(n->loss_partials, t->n_loss, t->loss, s));
-    TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, t->n_slabs, n->n_mat, n->width, 1, 1.0f, t->grads, nullptr, s));
+    TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, t->n_slabs, n->n_mat, n->width, 1, 1.0f, t->grads, nullptr, 0, s));
     t->reduced = true;
     return 0;
 }
@@ -419,11 +422,11 @@ int tnn_trainer_optimizer_step(tnn_trainer *t, void *stream) {
     if (world > 1 || t->reduced) {
         TNN_CUDA(tnn::launch_adam_refresh<false>(n->width, t->master, t->m, t->v, t->grads, nullptr, 0, nullptr, 0, nullptr,
                                                  n->n_mat, n->one_padded_input(), n->output_width, grad_scale, t->step,
-                                                 t->lr, t->b1, t->b2, t->eps, n->packed, n->wimg, n->wimg_t, s));
+                                                 t->lr, t->b1, t->b2, t->eps, n->fp16, n->packed, n->wimg, n->wimg_t, s));
     } else {
         TNN_CUDA(tnn::launch_adam_refresh<true>(n->width, t->master, t->m, t->v, t->grads, n->dw_slabs, t->n_slabs,
                                                 n->loss_partials, t->n_loss, t->loss, n->n_mat, n->one_padded_input(),
-                                                n->output_width, grad_scale, t->step, t->lr, t->b1, t->b2, t->eps,
+                                                n->output_width, grad_scale, t->step, t->lr, t->b1, t->b2, t->eps, n->fp16,
                                                 n->packed, n->wimg, n->wimg_t, s));
         t->reduced = true;
     }

@@ -9,6 +9,7 @@
 #include <cstdint>
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 namespace tnn {
 namespace ptx {
@@ -197,13 +198,17 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
     d |= static_cast<uint64_t>(swz & 7u) << 61;
     return d;
 }
-// Instruction descriptor for kind::f16 with bf16 operands and fp32 accumulation.
-//   [4,6) D format (1 = f32)  [7,10) A format (1 = bf16)  [10,13) B format (1 = bf16)
+// Instruction descriptor for kind::f16 with 16-bit operands and fp32 accumulation.
+//   [4,6) D format (1 = f32)  [7,10) A format (0 = fp16, 1 = bf16)  [10,13) B format (same codes)
 //   [15] A major (0 = K, 1 = MN)  [16] B major  [17,23) N >> 3  [24,29) M >> 4
 __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, int a_mn_major, int b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
            (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
            (static_cast<uint32_t>(m >> 4) << 24);
+}
+// Same for either operand type: fp16 != 0 selects fp16 operands (the two format fields become 0).
+__host__ __device__ constexpr uint32_t make_idesc_16(int m, int n, int a_mn_major, int b_mn_major, int fp16) {
+    return make_idesc_bf16(m, n, a_mn_major, b_mn_major) & (fp16 ? ~((1u << 7) | (1u << 10)) : ~0u);
 }
 // D[tmem] (+)= A[smem] * B[smem]; accumulate = 0 overwrites D.
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -286,6 +291,44 @@ __device__ __forceinline__ uint32_t pack_bf16x2_relu(float lo, float hi) {
 }
 __device__ __forceinline__ float bf16lo_to_f32(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16hi_to_f32(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+// the same four for fp16 pairs
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+__device__ __forceinline__ uint32_t pack_f16x2_relu(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+__device__ __forceinline__ float f16lo_to_f32(uint32_t v) {
+    float f;
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %1;\n\tcvt.f32.f16 %0, l;\n\t}" : "=f"(f) : "r"(v));
+    return f;
+}
+__device__ __forceinline__ float f16hi_to_f32(uint32_t v) {
+    float f;
+    asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %1;\n\tcvt.f32.f16 %0, h;\n\t}" : "=f"(f) : "r"(v));
+    return f;
+}
+// Element type of the network as a template switch: H = false bf16, H = true fp16.
+template <bool H> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    if constexpr (H) return pack_f16x2(lo, hi);
+    return pack_bf16x2(lo, hi);
+}
+template <bool H> __device__ __forceinline__ uint32_t pack2_relu(float lo, float hi) {
+    if constexpr (H) return pack_f16x2_relu(lo, hi);
+    return pack_bf16x2_relu(lo, hi);
+}
+template <bool H> __device__ __forceinline__ float lo_f32(uint32_t v) {
+    if constexpr (H) return f16lo_to_f32(v);
+    return bf16lo_to_f32(v);
+}
+template <bool H> __device__ __forceinline__ float hi_f32(uint32_t v) {
+    if constexpr (H) return f16hi_to_f32(v);
+    return bf16hi_to_f32(v);
+}
 
 } // namespace ptx
 } // namespace tnn

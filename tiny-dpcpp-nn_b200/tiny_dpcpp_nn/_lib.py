@@ -64,7 +64,9 @@ _SIGNATURES = {
     "tnn_encoding_bind_params": (ctypes.c_int, [_vp, _vp]),
     "tnn_encoding_forward": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _c.c_size_t, _vp]),
     "tnn_encoding_backward": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _vp, _c.c_size_t, _c.c_int, _vp]),
+    "tnn_encoding_backward_input": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _vp, _c.c_size_t, _vp]),
     "tnn_l2_loss": (_c.c_int, [_vp, _vp, _c.c_int, _vp, _vp, _c.c_size_t, _c.c_int, _c.c_float, _vp, _vp]),
+    "tnn_l2_loss_dtype": (_c.c_int, [_vp, _c.c_int, _vp, _c.c_int, _vp, _vp, _c.c_size_t, _c.c_int, _c.c_float, _vp, _vp]),
     "tnn_l2_loss_static": (_c.c_int, [_vp, _vp, _c.c_int, _vp, _vp, _c.c_size_t, _c.c_int, _c.c_float, _vp, _vp]),
     "tnn_adam_step": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_size_t, _c.c_float, _c.c_int, _c.c_float, _c.c_float,
                                  _c.c_float, _c.c_float, _vp]),
@@ -184,6 +186,7 @@ class NetworkModule:
         self._h = h
         self._lib = lib
         self.width = int(width)
+        self.dtype = torch.bfloat16 if dtype == "torch.bfloat16" else torch.float16
         self.n_mat = int(n_hidden_layers) + 1
         self._interm_fwd = None
         self._batch = 0
@@ -217,8 +220,8 @@ class NetworkModule:
     def _check_input(self, x):
         if x.dim() != 2 or x.shape[1] != self.width:
             raise TnnError(f"Input has {tuple(x.shape)} but the network expects (batch, {self.width})")
-        if x.dtype != torch.bfloat16:
-            raise TnnError("network tensors must be torch.bfloat16")
+        if x.dtype != self.dtype:
+            raise TnnError(f"network tensors must be {self.dtype}")
 
     def inference(self, x):
         self._check_input(x)
@@ -230,7 +233,7 @@ class NetworkModule:
         self._check_input(x)
         batch = x.shape[0]
         if self._interm_fwd is None or self._interm_fwd.shape[1] != batch:
-            self._interm_fwd = torch.empty((self.n_mat + 1, batch, self.width), dtype=torch.bfloat16, device=x.device)
+            self._interm_fwd = torch.empty((self.n_mat + 1, batch, self.width), dtype=self.dtype, device=x.device)
         self._batch = batch
         check(self._lib.tnn_network_forward(self._h, dptr(x), None, dptr(self._interm_fwd), batch, stream_ptr()))
         return self._interm_fwd[self.n_mat].clone()
@@ -239,7 +242,8 @@ class NetworkModule:
         return self._interm_fwd
 
     def bwd_no_encoding_grad(self, grad_output, pack_gradient, get_dl_dinput, want_interm_bwd=False,
-                             grads_dtype=torch.bfloat16):
+                             grads_dtype=None):
+        grads_dtype = grads_dtype or self.dtype  # the reference returns gradients in the network's type
         if grad_output.dim() != 2 or grad_output.shape[1] != self.width:
             raise TnnError(f"grad_output.size(1): {grad_output.shape[-1]} is not equal to get_padded_output_width "
                            f"{self.width}")
@@ -248,8 +252,10 @@ class NetworkModule:
             raise TnnError("backward_pass needs the forward pass of the same batch first")
         dev = grad_output.device
         grads = torch.empty((self.n_params(), 1), dtype=grads_dtype, device=dev)
-        dx = torch.empty((batch, self.width), dtype=torch.bfloat16, device=dev) if get_dl_dinput else None
-        ibwd = torch.empty((self.n_mat, batch, self.width), dtype=torch.bfloat16, device=dev) if want_interm_bwd else None
+        if grad_output.dtype != self.dtype:
+            raise TnnError(f"grad_output must be {self.dtype}")
+        dx = torch.empty((batch, self.width), dtype=self.dtype, device=dev) if get_dl_dinput else None
+        ibwd = torch.empty((self.n_mat, batch, self.width), dtype=self.dtype, device=dev) if want_interm_bwd else None
         check(self._lib.tnn_network_backward(self._h, dptr(grad_output), dptr(self._interm_fwd), dptr(grads),
                                              _dtype_code(grads_dtype), int(bool(pack_gradient)), dptr(dx), dptr(ibwd),
                                              batch, stream_ptr()))
@@ -276,7 +282,7 @@ class NetworkModule:
         params.record_stream(torch.cuda.current_stream())
 
     def get_params(self):
-        out = torch.empty((self.n_params(), 1), dtype=torch.bfloat16, device="cuda")
+        out = torch.empty((self.n_params(), 1), dtype=self.dtype, device="cuda")
         check(self._lib.tnn_network_get_params(self._h, dptr(out), stream_ptr()))
         return out
 
@@ -364,6 +370,17 @@ class EncodingModule:
                                               int(bool(deterministic)), stream_ptr()))
         return None, grads
 
+    def bwd_input(self, grad_output, input_from_fwd):
+        """dL/dinput (batch x n_input_dims, float32) of the encoding: tnn_encoding_backward_input."""
+        batch = grad_output.shape[0]
+        if input_from_fwd.dim() != 2 or input_from_fwd.shape[0] != batch or input_from_fwd.shape[1] != self.n_input_dims() \
+                or grad_output.shape[1] != self.n_output_dims():
+            raise TnnError("Size mismatch for input_from_fwd")
+        dx = torch.empty((batch, self.n_input_dims()), dtype=torch.float32, device=grad_output.device)
+        check(self._lib.tnn_encoding_backward_input(self._h, dptr(input_from_fwd), dptr(grad_output),
+                                                    _dtype_code(grad_output.dtype), dptr(dx), batch, stream_ptr()))
+        return dx
+
     def initial_params(self, tensor=None):
         if tensor is not None:
             self.set_params(tensor, False)
@@ -419,8 +436,8 @@ def l2_loss(pred, target, loss_scale=1.0, want_values=False):
     grads = torch.empty_like(pred)
     values = torch.empty((batch, stride), dtype=torch.float32, device=pred.device) if want_values else None
     loss_sum = torch.zeros(1, dtype=torch.float32, device=pred.device)
-    check(lib.tnn_l2_loss(dptr(pred), dptr(target), target.shape[1], dptr(values), dptr(grads), batch, stride,
-                          float(loss_scale), dptr(loss_sum), stream_ptr()))
+    check(lib.tnn_l2_loss_dtype(dptr(pred), _dtype_code(pred.dtype), dptr(target), target.shape[1], dptr(values),
+                                dptr(grads), batch, stride, float(loss_scale), dptr(loss_sum), stream_ptr()))
     return loss_sum, grads, values
 
 
@@ -439,7 +456,7 @@ def nwe_inference(net, enc, x, out=None):
     lib = load()
     if x.dtype != torch.float32 or x.dim() != 2 or x.shape[1] != enc.n_input_dims():
         raise TnnError("encoding input must be (batch, n_input_dims) float32")
-    y = out if out is not None else torch.empty((x.shape[0], net.width), dtype=torch.bfloat16, device=x.device)
+    y = out if out is not None else torch.empty((x.shape[0], net.width), dtype=net.dtype, device=x.device)
     check(lib.tnn_network_with_encoding_inference(net._h, enc._h, dptr(x), dptr(y), x.shape[0], stream_ptr()))
     return y
 
@@ -450,7 +467,7 @@ def nwe_forward(net, enc, x):
     lib = load()
     batch = x.shape[0]
     if net._interm_fwd is None or net._interm_fwd.shape[1] != batch:
-        net._interm_fwd = torch.empty((net.n_mat + 1, batch, net.width), dtype=torch.bfloat16, device=x.device)
+        net._interm_fwd = torch.empty((net.n_mat + 1, batch, net.width), dtype=net.dtype, device=x.device)
     net._batch = batch
     check(lib.tnn_network_with_encoding_forward(net._h, enc._h, dptr(x), None, dptr(net._interm_fwd), batch,
                                                 stream_ptr()))

@@ -6,11 +6,12 @@ of use_bias), loss scaling, packed parameter vector and autograd contract - with
 the B200 kernels behind it.  Differences that are deliberate:
   * parameters are pushed to the backend with a device-to-device kernel, not through the host
     (reference: tnn_api.h:637-641 copies the tensor to a std::vector on every forward);
-  * only HashGrid and Identity encodings exist.
+  * NetworkWithInputEncoding with an Identity encoding runs as ONE kernel per pass: the encoding is folded into the
+    network kernels' first-layer load instead of chaining two modules through a batch x width matrix.
 """
 import torch
 
-from ._lib import Activation, TnnError, create_encoding, create_network
+from ._lib import Activation, TnnError, create_encoding, create_network, nwe_forward, nwe_inference
 
 MIN_BATCH_SIZE = 8  # smallest batch granularity of the network kernels (SwiftNetMLP.h:293-302)
 
@@ -86,19 +87,52 @@ class _module_function(torch.autograd.Function):
         with torch.no_grad():
             if "encoding_config" in ctx.info:
                 input_grad = None
+                dy = doutput if doutput.dtype in (torch.bfloat16, torch.float16) else doutput.float()
                 if batch_size == 0 or params.numel() <= 1:
                     grad = torch.zeros_like(params)
                 else:
-                    dy = doutput if doutput.dtype == torch.bfloat16 else doutput.float()
                     _, grad = ctx.native_tnn_module.bwd_with_encoding_grad(dy, input, False, False)
+                if ctx.needs_input_grad[1] and batch_size > 0:
+                    # gradient with respect to the encoded positions (the reference's Python layer cannot provide it:
+                    # include/tnn_api.h:380-382)
+                    input_grad = ctx.native_tnn_module.bwd_input(dy, input)
             else:
                 input_grad, grad = ctx.native_tnn_module.bwd_no_encoding_grad(
-                    doutput.to(torch.bfloat16), True, True, grads_dtype=torch.float32)
+                    doutput.to(ctx.native_tnn_module.dtype), True, True, grads_dtype=torch.float32)
                 if input_grad is not None:
                     input_grad = input_grad.reshape(batch_size, -1).to(input.dtype)
         grad = None if grad is None else (grad.reshape(params.shape).to(params.dtype) / loss_scale)
         input_grad = None if input_grad is None else (input_grad / loss_scale)
         return (None, input_grad, grad, None, None)
+
+
+class _folded_module_function(torch.autograd.Function):
+    """Encoding + network as one operator (the encoding has no parameters and is folded into the network kernels):
+    same contract as _module_function for the network's parameters; the input gets no gradient."""
+
+    @staticmethod
+    def forward(ctx, native_network, native_encoding, input, params, info, loss_scale):
+        if info["is_in_eval_mode"]:
+            output = nwe_inference(native_network, native_encoding, input)
+        else:
+            output = nwe_forward(native_network, native_encoding, input)
+        ctx.save_for_backward(params)
+        ctx.info = info
+        ctx.native_network = native_network
+        ctx.loss_scale = loss_scale
+        return output[..., : info["output_dim"]]
+
+    @staticmethod
+    def backward(ctx, doutput):
+        (params,) = ctx.saved_tensors
+        width = ctx.info["width"]
+        if doutput.shape[1] < width:
+            doutput = torch.nn.functional.pad(doutput, [0, width - doutput.shape[1]])
+        doutput = (doutput * ctx.loss_scale).to(ctx.native_network.dtype).contiguous()
+        with torch.no_grad():
+            _, grad = ctx.native_network.bwd_no_encoding_grad(doutput, True, False, grads_dtype=torch.float32)
+        grad = grad.reshape(params.shape).to(params.dtype) / ctx.loss_scale
+        return (None, None, None, grad, None, None)
 
 
 class Module(torch.nn.Module):
@@ -141,7 +175,7 @@ class Module(torch.nn.Module):
             return
         if self.name == "encoding":
             src = src.to(torch.float32)
-        elif src.dtype not in (torch.float32, torch.bfloat16):
+        elif src.dtype not in (torch.float32, torch.bfloat16, torch.float16):
             src = src.to(torch.float32)
         self.tnn_module.set_params(src, packed)
         if not packed and self.name != "encoding":
@@ -240,8 +274,7 @@ class NetworkWithInputEncoding(Module):
                                  store_params_as_full_precision=store_params_as_full_precision,
                                  n_output_dims=network_config["n_neurons"], seed=seed)
         assert self.encoding.n_output_dims == network_config["n_neurons"]
-        if dtype == torch.bfloat16:
-            self.encoding.output_dtype = dtype  # the reference casts in Python (modules.py:223); here the kernel does
+        self.encoding.output_dtype = dtype  # the reference casts in Python (modules.py:223); here the kernel does
         self.network = Network(self.encoding.n_output_dims, n_output_dims, network_config, device=device, dtype=dtype,
                                store_params_as_full_precision=store_params_as_full_precision, use_bias=use_bias,
                                seed=seed)
@@ -257,8 +290,23 @@ class NetworkWithInputEncoding(Module):
     def set_params(self, params=None):
         self.network.set_params(params)
 
+    def _foldable(self):
+        return self.encoding.encoding_name == "Identity" and self.encoding.n_input_dims <= 16
+
     def forward(self, x):
-        return self.network_with_encoding(x)
+        if not self._foldable() or x.requires_grad:
+            return self.network_with_encoding(x)
+        # one kernel per pass: the identity encoding is folded into the network's first-layer load
+        batch_size = x.shape[0]
+        padded = (batch_size + MIN_BATCH_SIZE - 1) // MIN_BATCH_SIZE * MIN_BATCH_SIZE
+        xin = x.to(torch.float32)
+        if padded != batch_size:
+            xin = torch.nn.functional.pad(xin, [0, 0, 0, padded - batch_size])
+        info = {"is_in_eval_mode": not self.training, "output_dim": self.n_output_dims, "width": self.width}
+        self.network.set_params()
+        out = _folded_module_function.apply(self.network.tnn_module, self.encoding.tnn_module, xin.contiguous(),
+                                            self.network.params, info, self.network.loss_scale)
+        return out[:batch_size, ...]
 
 
 __all__ = ["Network", "Encoding", "NetworkWithInputEncoding", "free_temporary_memory", "TnnError"]

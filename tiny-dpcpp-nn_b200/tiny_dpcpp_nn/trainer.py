@@ -82,7 +82,7 @@ class Trainer:
         src.record_stream(torch.cuda.current_stream())
 
     def _check(self, x, targets):
-        want = torch.float32 if self.encoding is not None else torch.bfloat16
+        want = torch.float32 if self.encoding is not None else self.net.dtype
         if x.dtype != want or targets.dtype != torch.float32 or x.dim() != 2 or targets.dim() != 2 \
                 or targets.shape[0] != x.shape[0]:
             raise _lib.TnnError(f"training inputs must be (batch, n) {want} and targets (batch, n_targets) float32")
