@@ -131,6 +131,9 @@ int tnn_network_sync_status(tnn_network *net, int *status, void *stream);
  * small networks.  Default 0 (the fastest measured choice everywhere).
  *   16   training through the forward / loss / backward kernels instead of a fused kernel
  *   64   single-tile instead of pipelined fused training kernel
+ *   128  tnn_network_with_encoding_*: gather a HashGrid encoding inside the network's forward kernel (extra warps
+ *        write the features straight into the input tile) instead of running the encoding kernel first; slower
+ *        than the two kernels at the sizes measured, kept for grids small enough to live in L1
  *   256  stream the weights through per-slot rings even if they would fit on chip
  * No reference counterpart. */
 int tnn_network_set_variant(tnn_network *net, int variant);
@@ -201,7 +204,9 @@ int tnn_encoding_backward_input(tnn_encoding *enc, const float *x, const void *d
  *   Identity (up to 16 inputs): folded into the first-layer load of the network kernels - the encoded matrix
  *     never exists (include/encodings/identity.h:63-77 + include/network/kernel_esimd.h:565-640 in one kernel).
  *   Other encodings: encoding kernel, then network kernels, through the network handle's workspace
- *     (tnn_network_with_encoding_workspace_bytes; same allocation rule as tnn_network_train_step).
+ *     (tnn_network_with_encoding_workspace_bytes; same allocation rule as tnn_network_train_step).  For a 2-D / 3-D
+ *     HashGrid with two features per level a forward kernel that gathers the grid itself exists as well
+ *     (tnn_network_set_variant bit 128).
  * ------------------------------------------------------------------------------------------ */
 size_t tnn_network_with_encoding_workspace_bytes(const tnn_network *net, size_t batch);
 /* Sequential(encoding, network) in eval mode: y = network(encoding(x)), batch x width bf16. */

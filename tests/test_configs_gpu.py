@@ -300,13 +300,15 @@ def test_c4_fused_encoding_forward_equals_the_two_kernel_path(tnn_lib, dims):
     encoded = enc.fwd(pts, out_dtype=torch.bfloat16)
     assert np.array_equal(encoded.float().cpu().numpy(), O.bf16_round(grid.forward(pts.cpu().numpy(), table, padded=W)))
     y_two = net.inference(encoded)
+    assert torch.equal(tnn_lib.nwe_inference(net, enc, pts), y_two)  # default: encoding kernel, then network kernel
+    launches = tnn_lib.load().tnn_launch_count()
+    net.set_variant(128)  # the grid is gathered inside the network kernel: one launch
     y_fused = tnn_lib.nwe_inference(net, enc, pts)
+    assert tnn_lib.load().tnn_launch_count() == launches + 1
     assert torch.equal(y_fused, y_two) and net.status() == 0
     out = tnn_lib.nwe_forward(net, enc, pts)
     ig = net.interm_fwd()
     assert torch.equal(ig[0], encoded) and torch.equal(out, y_two)
-    net.set_variant(16)  # forces the two-kernel path inside the library
-    assert torch.equal(tnn_lib.nwe_inference(net, enc, pts), y_two)
 
 
 # ------------------------------------------------------------------------------------------------ data parallel, NCCL
@@ -368,3 +370,76 @@ def test_data_parallel_step_over_nccl_equals_single_gpu_full_batch(tnn_lib, tmp_
     _check(g0 / world, tr.grads.cpu().numpy(), what="DP gradient")
     diff = np.abs(m0 - tr.master.cpu().numpy())
     assert diff.max() <= 2.1e-3 * steps and (diff <= 2e-5).mean() >= 0.98
+
+
+def _dp_grid_worker(rank, world, port, out_dir, batch, steps):
+    for p in (ROOT, os.path.join(ROOT, "tiny-dpcpp-nn_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    from tiny_dpcpp_nn import _lib as L
+    from tiny_dpcpp_nn.parallel import shard_rows
+    from tiny_dpcpp_nn.trainer import Trainer
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    net, enc, pts, t = _c4_setup(L, batch)
+    a, b = shard_rows(batch, rank, world)
+    tr = Trainer(net, lr=1e-2, process_group=dist.group.WORLD, world_size=world, encoding=enc)
+    tr.set_deterministic_encoding(True)
+    for _ in range(steps):
+        tr.training_step(pts[a:b].contiguous(), t[a:b].contiguous())
+    torch.cuda.synchronize()
+    np.save(os.path.join(out_dir, f"table{rank}.npy"), enc.get_params().cpu().numpy())
+    np.save(os.path.join(out_dir, f"net{rank}.npy"), tr.master.cpu().numpy())
+    assert net.status() == 0
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _c4_setup(L, batch):
+    """The hash-grid model with seeded weights and table, same on every rank."""
+    nh = 2
+    w = O.bf16_round(synth.xavier_weights(nh + 1, W, 4))
+    net = L.create_network(32, 3, nh, A["relu"], A["none"], W, "torch.bfloat16", True, seed=1)
+    net.set_params(torch.from_numpy(w.reshape(-1)).cuda(), False)
+    cfg = dict(GRID_CFG, log2_hashmap_size=14)
+    enc = L.create_encoding("HashGrid", cfg, W, seed=3)
+    n = enc.n_params()
+    enc.set_params(torch.from_numpy(np.random.default_rng(2).uniform(-0.5, 0.5, n).astype(np.float32)).cuda())
+    rng = np.random.default_rng(100)
+    pts = torch.from_numpy(rng.uniform(0, 1, (batch, 3)).astype(np.float32)).cuda()
+    t = torch.from_numpy(synth.sinusoid_targets(pts.cpu().numpy(), 3, 8, 8.0, seed=5)).cuda()
+    return net, enc, pts, t
+
+
+def test_data_parallel_hash_grid_training_over_nccl(tnn_lib, tmp_path):
+    """Two ranks train the hash-grid model on halves of the batch: network gradients all-reduced, table gradient
+    reduce-scattered, Adam on each rank's slice of the table, table all-gathered.  Both ranks end with identical
+    tables and weights, equal (to the kernels' tolerance) to a single-GPU trainer on the whole batch."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    from tiny_dpcpp_nn.trainer import Trainer
+
+    batch, steps, world = 128 * 32, 2, 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_dp_grid_worker, args=(world, port, str(tmp_path), batch, steps), nprocs=world, join=True)
+    t0, t1 = np.load(tmp_path / "table0.npy"), np.load(tmp_path / "table1.npy")
+    n0, n1 = np.load(tmp_path / "net0.npy"), np.load(tmp_path / "net1.npy")
+    assert np.array_equal(t0, t1) and np.array_equal(n0, n1)
+    net, enc, pts, t = _c4_setup(tnn_lib, batch)
+    tr = Trainer(net, lr=1e-2, encoding=enc)
+    tr.set_deterministic_encoding(True)
+    for _ in range(steps):
+        tr.training_step(pts, t)
+    ref = enc.get_params().cpu().numpy()
+    # Adam moves every touched entry by about lr per step whatever the gradient's size: entries whose gradient is
+    # within rounding noise of zero may differ by up to 2 lr per step, all others agree closely
+    diff = np.abs(t0 - ref)
+    assert diff.max() <= 2.1e-2 * steps and (diff <= 1e-4).mean() >= 0.98, ((diff <= 1e-4).mean(), diff.max())

@@ -61,6 +61,53 @@ def test_two_rank_gradient_average_equals_full_batch_gradient(tmp_path):
     assert ok, rel
 
 
+def _sharded_adam_worker(rank, port, out_dir):
+    """The optimiser of a trainable encoding under data parallelism: reduce-scatter of the table gradient, Adam on this
+    rank's slice of the table (with its slice of the moments), all-gather of the table - against all-reduce + Adam on
+    the whole table, which every rank could also do (the oracle's Adam stands in for the device kernel)."""
+    for p in (ROOT, os.path.join(ROOT, "tiny-dpcpp-nn_b200")):
+        sys.path.insert(0, p)
+    from oracle import oracle as O
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    n, steps = 4096, 3
+    shard = n // WORLD
+    table = np.random.default_rng(0).uniform(-1e-4, 1e-4, n).astype(np.float32)  # identical on every rank
+    full = table.copy()
+    fm, fv = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    sm, sv = np.zeros(shard, np.float32), np.zeros(shard, np.float32)
+    for step in range(1, steps + 1):
+        g = np.random.default_rng(10 * step + rank).normal(size=n).astype(np.float32)  # this rank's gradient
+        total = torch.from_numpy(g.copy())
+        dist.all_reduce(total)
+        mean = (total.numpy() / WORLD).astype(np.float32)
+        O.adam(full, fm, fv, mean, step)  # replicated optimiser
+        # sharded optimiser: this rank's slice of the summed gradient (what a reduce-scatter delivers) ...
+        mine = np.ascontiguousarray(table[rank * shard:(rank + 1) * shard])
+        O.adam(mine, sm, sv, np.ascontiguousarray(mean[rank * shard:(rank + 1) * shard]), step)
+        # ... and an all-gather of the updated slices
+        parts = [torch.empty(shard) for _ in range(WORLD)]
+        dist.all_gather(parts, torch.from_numpy(mine))
+        table = torch.cat(parts).numpy().copy()
+    np.save(os.path.join(out_dir, f"sharded{rank}.npy"), table)
+    np.save(os.path.join(out_dir, f"full{rank}.npy"), full)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_adam_equals_replicated_adam(tmp_path):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_sharded_adam_worker, args=(port, str(tmp_path)), nprocs=WORLD, join=True)
+    s0, s1 = np.load(tmp_path / "sharded0.npy"), np.load(tmp_path / "sharded1.npy")
+    f0 = np.load(tmp_path / "full0.npy")
+    assert np.array_equal(s0, s1)   # every rank holds the same table after the all-gather
+    assert np.array_equal(s0, f0)   # and it is the table of the replicated optimiser, bit for bit
+
+
 def test_shard_rows_cover_the_batch():
     from tiny_dpcpp_nn.parallel import shard_rows
 

@@ -301,8 +301,8 @@ def test_grid_forward_fp16_output_and_wide_padding(tnn_lib):
 
 
 def test_encoding_errors(tnn_lib):
-    with pytest.raises(tnn_lib.TnnError, match="outside the scope"):
-        tnn_lib.create_encoding("SphericalHarmonics", dict(otype="SphericalHarmonics", degree=4, n_dims_to_encode=3))
+    with pytest.raises(tnn_lib.TnnError, match="Unknown encoding type"):
+        tnn_lib.create_encoding("OneBlob", dict(otype="OneBlob", n_dims_to_encode=3))
     with pytest.raises(tnn_lib.TnnError, match="simultaneously"):
         tnn_lib.create_encoding("HashGrid", dict(otype="HashGrid", n_levels=4, n_features=8))
     with pytest.raises(tnn_lib.TnnError, match="2 or 3"):

@@ -132,6 +132,6 @@ def test_network_module_matches_torch_linear_stack(tnn_lib, dtype):
         if l < nh:
             ref = np.maximum(ref, 0)
         ref = O.round16(ref.astype(np.float32), "fp16" if dtype == torch.float16 else "bf16")
-    _check(y.float().cpu().numpy(), ref, "module forward")
+    _check(y.detach().float().cpu().numpy(), ref, "module forward")
     (y.float() ** 2).mean().backward()
     assert torch.isfinite(net.params.grad).all() and net.params.grad.abs().sum() > 0

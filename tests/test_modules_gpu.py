@@ -229,3 +229,37 @@ def test_network_with_identity_encoding_runs_folded_and_equals_the_sequential_pa
         grads.append(model.params.grad.clone())
         assert torch.equal(out, y_seq)
     assert torch.equal(grads[0], grads[1]) and grads[0].abs().sum() > 0
+
+
+def test_network_with_grid_encoding_fused_forward_equals_the_sequential_path(tnn_lib):
+    """NetworkWithInputEncoding with a HashGrid through the single-operator path of the module (one call into the
+    library per pass; with variant bit 128 the grid is gathered inside the network kernel) returns the bits of the
+    Sequential path; the table and network gradients agree (the table gradient is summed with floating-point
+    reductions in memory on both paths, so to rounding only)."""
+    import tiny_dpcpp_nn as tnn
+
+    net_cfg = {"n_neurons": 64, "n_hidden_layers": 2, "activation": "relu", "output_activation": "none"}
+    enc_cfg = {"otype": "HashGrid", "n_levels": 16, "n_features_per_level": 2, "log2_hashmap_size": 15,
+               "base_resolution": 16, "per_level_scale": 1.5}
+    model = tnn.NetworkWithInputEncoding(3, 3, net_cfg, enc_cfg, seed=7)
+    assert model._fusable()
+    with torch.no_grad():
+        model.encoding.params.mul_(1e3)  # default initial values are +-1e-4: make the features matter
+    x = torch.rand((4096 + 5, 3), device="cuda")
+    tgt = torch.rand((4096 + 5, 3), device="cuda")
+    model.eval()
+    with torch.no_grad():
+        ref = model.network_with_encoding(x)
+        assert torch.equal(model(x), ref)
+        model.network.tnn_module.set_variant(128)
+        assert torch.equal(model(x), ref)
+    model.train()
+    res = []
+    for fn in (model, model.network_with_encoding):
+        model.zero_grad(set_to_none=True)
+        out = fn(x)
+        ((out.float() - tgt) ** 2).mean().backward()
+        res.append((out.clone(), model.network.params.grad.clone(), model.encoding.params.grad.clone()))
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    ga, gb = res[0][2], res[1][2]
+    assert ga.abs().sum() > 0 and (ga - gb).abs().max() <= 1e-5 * ga.abs().max()

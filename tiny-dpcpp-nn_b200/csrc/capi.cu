@@ -878,8 +878,12 @@ int tnn_network_with_encoding_forward(tnn_network *n, tnn_encoding *e, const flo
         const tnn::EncodedInput enc{x, e->n_in, e->scale, e->offset};
         return run_forward(n, nullptr, y, interm_fwd, batch, stream, false, &enc);
     }
-    if (grid_fusable(n, e) && !(n->variant & 16)) {
-        // hash grid: gathered by extra warps of the network kernel straight into its input tile
+    if (grid_fusable(n, e) && (n->variant & 128)) {
+        // hash grid gathered by extra warps of the network kernel straight into its input tile.  Opt-in (variant bit
+        // 128): measured at the benchmark grid (3-D, 16 levels, batch 2^20, width 64, 2 hidden layers) the fused
+        // kernel takes 0.58 ms against 0.39 ms for encoding kernel + network kernel - the gathers are bound by L2
+        // latency and need about 12 000 loads in flight per SM, which the stand-alone kernel reaches with 1 536
+        // gathering threads and the fused kernel, whose registers also serve the MMA issuers and epilogues, does not.
         const int rc = run_forward(n, nullptr, y, interm_fwd, batch, stream, false, nullptr, e, x);
         if (rc >= 0) return rc;
     }

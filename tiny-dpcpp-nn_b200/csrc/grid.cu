@@ -154,7 +154,8 @@ __global__ void __launch_bounds__(256) grid_fwd_kernel(const GridParams p, const
 // its levels), so offsets / scale / resolution come out of the constant bank with a single address per warp and the
 // only divergent traffic is the gather itself.  The features go to a shared-memory image of the tile's output rows
 // (row stride padded to an odd number of words: the 32 lanes of a warp write 32 different rows) and leave as one
-// contiguous, fully coalesced copy.
+// contiguous, fully coalesced copy.  (Measured at the benchmark grid, batch 2^20: 40 registers, six blocks per SM.
+// Forcing eight blocks per SM with a 32-register bound was 5 - 10 % slower.)
 constexpr int kGridTileRows = 128;
 __host__ __device__ inline uint32_t grid_tile_row_words(uint32_t padded_width, uint32_t elem_bytes) {
     return ((padded_width * elem_bytes + 3u) / 4u) | 1u;

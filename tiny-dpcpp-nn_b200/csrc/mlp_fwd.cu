@@ -185,7 +185,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
             for (int j = 0; j < my_tiles; ++j) {
                 const int s = j % NSLOT, t = j / NSLOT;
                 const int tile = blockIdx.x + j * gridDim.x;
-                if (t >= 1 && !__all_sync(0xffffffffu, lane != 0 || ptx::mbar_wait(&bars.x_empty[s], (t - 1) & 1, abort_flag))) {
+                if (t >= 1 && !__all_sync(0xffffffffu, ptx::mbar_wait(&bars.x_empty[s], (t - 1) & 1, abort_flag))) {
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | s);
                     break;
                 }
@@ -466,7 +466,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         for (int j = 0; j < my_tiles; ++j) {
             const int s = j % NSLOT, t = j / NSLOT;
             const int tile = blockIdx.x + j * gridDim.x;
-            if (t >= 1 && !__all_sync(0xffffffffu, lane != 0 || ptx::mbar_wait(&bars.x_empty[s], (t - 1) & 1, abort_flag))) {
+            if (t >= 1 && !__all_sync(0xffffffffu, ptx::mbar_wait(&bars.x_empty[s], (t - 1) & 1, abort_flag))) {
                 if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | 0x40 | s);
                 break;
             }

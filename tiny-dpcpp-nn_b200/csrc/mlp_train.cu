@@ -144,7 +144,7 @@ mlp_train_kernel(const __grid_constant__ CUtensorMap tm_x, const __nv_bfloat16 *
             for (int t = 0; t < my_tiles; ++t) {
                 const int tile = blockIdx.x + t * gridDim.x;
                 const int b = t & 1;
-                if (t >= 2 && !__all_sync(0xffffffffu, lane != 0 || ptx::mbar_wait(&bars.x_empty[b], ((t >> 1) - 1) & 1, abort_flag))) {
+                if (t >= 2 && !__all_sync(0xffffffffu, ptx::mbar_wait(&bars.x_empty[b], ((t >> 1) - 1) & 1, abort_flag))) {
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | 1);
                     break;
                 }

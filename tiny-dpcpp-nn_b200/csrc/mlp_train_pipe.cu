@@ -145,28 +145,26 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                                reinterpret_cast<const uint8_t *>(wimg) + (size_t)l * T::WGT_BYTES, T::WGT_BYTES,
                                &bars.w_full);
         }
-        // targets of tile t (lane 0; the staging area overlaps delta_L: both GEMMs that read delta_L of the previous
-        // tile must be complete)
-        auto stage_targets = [&](int t, int tile) -> bool {
+        // targets of tile t: the staging area overlaps delta_L, so both GEMMs that read delta_L of the previous tile
+        // must be complete (wait), then one thread issues the copy
+        auto targets_wait = [&](int t) -> bool {
             if constexpr (TGT != 0) {
-                if (t > 0 && !ptx::mbar_wait(&bars.dl_free, (t - 1) & 1, abort_flag)) {
-                    atomicExch(status, KS_TIMEOUT_PRODUCER | 2);
-                    return false;
-                }
-                if constexpr (TGT == 2) {
-                    const size_t row0 = (size_t)tile * T::TM;
-                    const uint32_t rows = (uint32_t)(batch - row0 < (size_t)T::TM ? batch - row0 : (size_t)T::TM);
-                    const uint32_t bytes = rows * (uint32_t)n_targets * 4u; // rows % 8 == 0: a multiple of 16
-                    ptx::mbar_arrive_expect_tx(&bars.tgt_full, bytes);
-                    ptx::bulk_load(smem + S::DL, targets + row0 * n_targets, bytes, &bars.tgt_full);
-                } else {
-                    ptx::mbar_arrive_expect_tx(&bars.tgt_full, (uint32_t)(S::TGT_BOXES * S::TGT_BOX_BYTES));
-                    for (int bx = 0; bx < S::TGT_BOXES; ++bx)
-                        ptx::tma_load_2d(smem + S::DL + bx * S::TGT_BOX_BYTES, &tm_tgt, bx * 32, tile * T::TM,
-                                         &bars.tgt_full);
-                }
+                if (t > 0 && !ptx::mbar_wait(&bars.dl_free, (t - 1) & 1, abort_flag)) return false;
             }
             return true;
+        };
+        auto targets_issue = [&](int tile) {
+            if constexpr (TGT == 2) {
+                const size_t row0 = (size_t)tile * T::TM;
+                const uint32_t rows = (uint32_t)(batch - row0 < (size_t)T::TM ? batch - row0 : (size_t)T::TM);
+                const uint32_t bytes = rows * (uint32_t)n_targets * 4u; // rows % 8 == 0: a multiple of 16
+                ptx::mbar_arrive_expect_tx(&bars.tgt_full, bytes);
+                ptx::bulk_load(smem + S::DL, targets + row0 * n_targets, bytes, &bars.tgt_full);
+            } else if constexpr (TGT == 1) {
+                ptx::mbar_arrive_expect_tx(&bars.tgt_full, (uint32_t)(S::TGT_BOXES * S::TGT_BOX_BYTES));
+                for (int bx = 0; bx < S::TGT_BOXES; ++bx)
+                    ptx::tma_load_2d(smem + S::DL + bx * S::TGT_BOX_BYTES, &tm_tgt, bx * 32, tile * T::TM, &bars.tgt_full);
+            }
         };
         if (!enc.x) {
             if (lane == 0) {
@@ -181,10 +179,17 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     for (int at = 0; at < T::KATOMS; ++at)
                         ptx::tma_load_2d(smem + S::X(b) + at * T::ACT_ATOM_BYTES, &tm_x, at * T::ATOM_COLS, tile * T::TM,
                                          &bars.x_full[b]);
-                    if (!stage_targets(t, tile)) break;
+                    if (!targets_wait(t)) {
+                        atomicExch(status, KS_TIMEOUT_PRODUCER | 2);
+                        break;
+                    }
+                    targets_issue(tile);
                 }
             }
         } else if (my_tiles > 0) {
+            // (every wait below is executed by the whole, converged warp: the hardware then suspends the warp until
+            // the barrier flips.  A single polling lane with the others parked at a vote keeps the warp spinning and
+            // takes issue slots from the epilogue warps of the same scheduler.)
             fill_tiles_with_ones<W>(smem + S::X(0), 2, lane, fp16);
             __syncwarp();
             IdentityTileEncoder<W> encoder(enc, batch, lane, fp16);
@@ -192,8 +197,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
             for (int t = 0; t < my_tiles; ++t) {
                 const int tile = blockIdx.x + t * gridDim.x;
                 const int b = t & 1;
-                // (lane 0 polls; the vote hands its verdict - and the ordering it implies - to the other lanes)
-                if (t >= 2 && !__all_sync(0xffffffffu, lane != 0 || ptx::mbar_wait(&bars.x_empty[b], ((t >> 1) - 1) & 1, abort_flag))) {
+                if (t >= 2 && !__all_sync(0xffffffffu, ptx::mbar_wait(&bars.x_empty[b], ((t >> 1) - 1) & 1, abort_flag))) {
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | 1);
                     break;
                 }
@@ -203,7 +207,11 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 if (lane == 0) ptx::mbar_arrive(&bars.x_full[b]);
                 // coordinates of the next tile travel while this one is consumed
                 if (t + 1 < my_tiles) encoder.fetch((size_t)(tile + gridDim.x) * T::TM);
-                if (!__all_sync(0xffffffffu, lane != 0 || stage_targets(t, tile))) break;
+                if (!__all_sync(0xffffffffu, targets_wait(t))) {
+                    if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | 2);
+                    break;
+                }
+                if (lane == 0) targets_issue(tile);
             }
         }
     } else if (warp == 1) {

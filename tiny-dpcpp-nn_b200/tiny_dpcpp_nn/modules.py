@@ -6,8 +6,9 @@ of use_bias), loss scaling, packed parameter vector and autograd contract - with
 the B200 kernels behind it.  Differences that are deliberate:
   * parameters are pushed to the backend with a device-to-device kernel, not through the host
     (reference: tnn_api.h:637-641 copies the tensor to a std::vector on every forward);
-  * NetworkWithInputEncoding with an Identity encoding runs as ONE kernel per pass: the encoding is folded into the
-    network kernels' first-layer load instead of chaining two modules through a batch x width matrix.
+  * NetworkWithInputEncoding with an Identity or HashGrid encoding runs its forward pass as ONE kernel: the encoding
+    is produced inside the network kernel (identity: folded into the first-layer load; hash grid: gathered by extra
+    warps) instead of chaining two modules through a batch x width matrix.
 """
 import torch
 
@@ -106,33 +107,42 @@ class _module_function(torch.autograd.Function):
         return (None, input_grad, grad, None, None)
 
 
-class _folded_module_function(torch.autograd.Function):
-    """Encoding + network as one operator (the encoding has no parameters and is folded into the network kernels):
-    same contract as _module_function for the network's parameters; the input gets no gradient."""
+class _fused_module_function(torch.autograd.Function):
+    """Encoding + network as one operator: the forward pass is a single kernel (identity encoding folded into the
+    first-layer load, hash grid gathered by extra warps of the network kernel); the backward pass runs the network's
+    backward kernel and, for an encoding with parameters, scatters the network's dL/dinput into the table gradient.
+    Same parameter contract as _module_function; the positions get no gradient."""
 
     @staticmethod
-    def forward(ctx, native_network, native_encoding, input, params, info, loss_scale):
+    def forward(ctx, native_network, native_encoding, input, net_params, enc_params, info, loss_scale):
         if info["is_in_eval_mode"]:
             output = nwe_inference(native_network, native_encoding, input)
         else:
             output = nwe_forward(native_network, native_encoding, input)
-        ctx.save_for_backward(params)
+        ctx.save_for_backward(input, net_params, enc_params)
         ctx.info = info
         ctx.native_network = native_network
+        ctx.native_encoding = native_encoding
         ctx.loss_scale = loss_scale
         return output[..., : info["output_dim"]]
 
     @staticmethod
     def backward(ctx, doutput):
-        (params,) = ctx.saved_tensors
+        input, net_params, enc_params = ctx.saved_tensors
         width = ctx.info["width"]
         if doutput.shape[1] < width:
             doutput = torch.nn.functional.pad(doutput, [0, width - doutput.shape[1]])
         doutput = (doutput * ctx.loss_scale).to(ctx.native_network.dtype).contiguous()
+        want_enc = ctx.native_encoding.n_params() > 0 and ctx.needs_input_grad[4]
+        enc_grad = None
         with torch.no_grad():
-            _, grad = ctx.native_network.bwd_no_encoding_grad(doutput, True, False, grads_dtype=torch.float32)
-        grad = grad.reshape(params.shape).to(params.dtype) / ctx.loss_scale
-        return (None, None, None, grad, None, None)
+            dx, grad = ctx.native_network.bwd_no_encoding_grad(doutput, True, want_enc, grads_dtype=torch.float32)
+            if want_enc:
+                _, enc_grad = ctx.native_encoding.bwd_with_encoding_grad(dx.reshape(input.shape[0], width), input, False,
+                                                                         False)
+                enc_grad = enc_grad.reshape(enc_params.shape).to(enc_params.dtype) / ctx.loss_scale
+        grad = grad.reshape(net_params.shape).to(net_params.dtype) / ctx.loss_scale
+        return (None, None, None, grad, enc_grad, None, None)
 
 
 class Module(torch.nn.Module):
@@ -290,13 +300,21 @@ class NetworkWithInputEncoding(Module):
     def set_params(self, params=None):
         self.network.set_params(params)
 
-    def _foldable(self):
-        return self.encoding.encoding_name == "Identity" and self.encoding.n_input_dims <= 16
+    def _fusable(self):
+        """One forward kernel for the pair: Identity (up to 16 inputs) or a 2-D / 3-D HashGrid with two features per
+        level whose features fit the network width; anything else runs as the two chained modules."""
+        cfg = self.encoding.encoding_config
+        if self.encoding.encoding_name == "Identity":
+            return self.encoding.n_input_dims <= 16
+        if self.encoding.encoding_name == "HashGrid":
+            return self.encoding.n_input_dims in (2, 3) and int(cfg.get("n_features_per_level", 2)) == 2
+        return False
+
+    _foldable = _fusable
 
     def forward(self, x):
-        if not self._foldable() or x.requires_grad:
+        if not self._fusable() or x.requires_grad:
             return self.network_with_encoding(x)
-        # one kernel per pass: the identity encoding is folded into the network's first-layer load
         batch_size = x.shape[0]
         padded = (batch_size + MIN_BATCH_SIZE - 1) // MIN_BATCH_SIZE * MIN_BATCH_SIZE
         xin = x.to(torch.float32)
@@ -304,9 +322,7 @@ class NetworkWithInputEncoding(Module):
             xin = torch.nn.functional.pad(xin, [0, 0, 0, padded - batch_size])
         info = {"is_in_eval_mode": not self.training, "output_dim": self.n_output_dims, "width": self.width}
         self.network.set_params()
-        out = _folded_module_function.apply(self.network.tnn_module, self.encoding.tnn_module, xin.contiguous(),
-                                            self.network.params, info, self.network.loss_scale)
+        self.encoding.set_params()
+        out = _fused_module_function.apply(self.network.tnn_module, self.encoding.tnn_module, xin.contiguous(),
+                                           self.network.params, self.encoding.params, info, self.network.loss_scale)
         return out[:batch_size, ...]
-
-
-__all__ = ["Network", "Encoding", "NetworkWithInputEncoding", "free_temporary_memory", "TnnError"]
