@@ -50,7 +50,7 @@ BYTES_INFER_64 = 2 * WIDTH * 2                   # x in + y out, bf16
 BYTES_TRAIN_64 = WIDTH * 2 + WIDTH * 4           # x bf16 + targets fp32
 # DRAM bytes (read + write) per sample of the fused training kernel from profiler captures at batch 2^19
 # (the traffic is proportional to the batch: inputs and targets are read once, nothing else is streamed)
-TRAIN_DRAM_BYTES_PER_SAMPLE = {"c5": None, "64x64": 391.0}
+TRAIN_DRAM_BYTES_PER_SAMPLE = {"c5": 20.26, "64x64": 391.0}
 TRAIN_DRAM_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum at batch 2^19, scaled by the batch"
 N_ROTATE = 4  # distinct input batches used in turn: 4 x 84 MB > 126 MB of L2, so no step finds its inputs cached
 
@@ -461,6 +461,11 @@ def run_gpu_arm(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
     torch.cuda.set_device(local_rank)
+    # The one JSON line must be the only thing on stdout: libraries (NCCL prints its version when a communicator is
+    # created) write there at C level, so stdout points at stderr until the line is printed.
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
     pg = None
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -696,8 +701,8 @@ def run_gpu_arm(args):
                     "note": "copy of step i + 1 overlaps the compute of step i (two streams, two device buffers)"},
             "gpu_launches": launches,
             "kernels_per_step": (["mlp_train_pipe_kernel", "adam_refresh_kernel"] if world == 1 else
-                                 ["mlp_train_pipe_kernel", "sum_partials_kernel", "reduce_dw_kernel",
-                                  "ncclAllReduce (80 KiB)", "adam_refresh_kernel"]),
+                                 ["mlp_train_pipe_kernel", "reduce_dw_kernel", "ncclAllReduce (80 KiB)",
+                                  "adam_refresh_kernel"]),
             "roofline": roofline, "rooflines": rooflines, "swiftnet_64x64": swiftnet, "grid_rooflines": grid_roofs,
             "clocks": clocks, "kernel_status": status, "final_loss_sum": loss_value,
         }
@@ -712,7 +717,10 @@ def run_gpu_arm(args):
                         "hbm_gbs": round(BYTES_INFER_C5 * infer_value * 1e-9 / world, 1),
                         "frac_of_hbm_peak": round(BYTES_INFER_C5 * infer_value * 1e-9 / world / peaks["hbm_gbs"], 4),
                         "scaling": "batch sharded over the GPUs, no communication"}
-        print(json.dumps(out))
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        print(json.dumps(out), flush=True)
+        os.dup2(2, 1)
     if world > 1:
         dist.destroy_process_group()
 

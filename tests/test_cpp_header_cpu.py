@@ -12,7 +12,7 @@ SRC = r"""
 int main() {
     std::printf("%s\n", tnn_version());
     try {
-        tnn::NetworkModule bad(64, 64, 4, tnn::Activation::ReLU, tnn::Activation::None, /*width*/ 48, true);
+        tnn::Network<tnn::half> bad(64, 64, 4, tnn::Activation::ReLU, tnn::Activation::None, /*width*/ 48, true);
         return 1;
     } catch (const std::runtime_error &e) {
         if (!std::strstr(e.what(), "power of 2")) return 2;
@@ -23,7 +23,13 @@ int main() {
     } catch (const std::runtime_error &e) {
         if (!std::strstr(e.what(), "Unknown encoding type")) return 4;
     }
-    return 0;
+    // the whole surface instantiates: Network<T>, SwiftNetMLP<T>, Encoding, Loss<T>, Optimizer, Trainer<T>, DataParallel
+    using Net = tnn::SwiftNetMLP<tnn::bf16>;
+    void (Net::*inf)(const void *, void *, size_t, void *) = &Net::inference;
+    void (tnn::Trainer<tnn::bf16>::*step)(const void *, const float *, int, size_t, void *) = &tnn::Trainer<tnn::bf16>::training_step;
+    void (*loss)(void *, float, const void *, const float *, int, float *, void *, size_t, int, float *) = &tnn::Loss<tnn::half>::evaluate;
+    tnn::Optimizer opt;
+    return (inf && step && loss && opt.lr > 0 && sizeof(tnn::DataParallel) && sizeof(tnn::EncodingModule)) ? 0 : 5;
 }
 """
 

@@ -470,9 +470,8 @@ static int train_step_impl(tnn_network *n, const void *x, const tnn::EncodedInpu
             return 0;
         }
         if (e == cudaSuccess) {
-            if (loss_sum) TNN_CUDA(tnn::launch_sum_partials(n->loss_partials, p.grid_out, loss_sum, s));
             TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, p.grid_out, n->n_mat, n->width, pack_transpose, 1.0f, gf, gb,
-                                           grads_dtype == TNN_DTYPE_FP16, s));
+                                           grads_dtype == TNN_DTYPE_FP16, s, n->loss_partials, p.grid_out, loss_sum));
             return 0;
         }
         if (e != cudaErrorInvalidConfiguration) TNN_CUDA(e);

@@ -75,9 +75,22 @@ cudaError_t launch_set_params(int width, const void *src, int src_dtype, int src
 // (DeviceMatrix.h:469-488 PackAndTranspose).
 __global__ void reduce_dw_kernel(const float *__restrict__ slabs, int n_slabs, int n_mat, int W, int pack_transpose,
                                  float scale, float *__restrict__ out_f32, __nv_bfloat16 *__restrict__ out_16,
-                                 int out_fp16) {
+                                 int out_fp16, const float *__restrict__ loss_partials, int n_loss,
+                                 float *__restrict__ loss_out) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     const int per = n_mat * W * W;
+    if (loss_out && blockIdx.x == 0) { // the loss partials of the same pass, summed in a fixed order by block 0
+        __shared__ float red[128];
+        float local = 0.0f;
+        for (int i = threadIdx.x; i < n_loss; i += 128) local += loss_partials[i];
+        red[threadIdx.x] = local;
+        __syncthreads();
+        for (int s = 64; s > 0; s >>= 1) {
+            if ((int)threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) *loss_out = red[0];
+    }
     if (idx >= per) return;
     float acc = 0.0f;
     for (int s = 0; s < n_slabs; ++s) acc += slabs[(size_t)s * per + idx];
@@ -91,11 +104,12 @@ __global__ void reduce_dw_kernel(const float *__restrict__ slabs, int n_slabs, i
 }
 
 cudaError_t launch_reduce_dw(const float *slabs, int n_slabs, int n_mat, int width, int pack_transpose, float scale,
-                             float *out_f32, __nv_bfloat16 *out_16, int out_fp16, cudaStream_t stream) {
+                             float *out_f32, __nv_bfloat16 *out_16, int out_fp16, cudaStream_t stream,
+                             const float *loss_partials, int n_loss, float *loss_out) {
     const int n = n_mat * width * width;
     count_launch();
     reduce_dw_kernel<<<(n + 127) / 128, 128, 0, stream>>>(slabs, n_slabs, n_mat, width, pack_transpose, scale, out_f32,
-                                                         out_16, out_fp16);
+                                                         out_16, out_fp16, loss_partials, n_loss, loss_out);
     return cudaGetLastError();
 }
 

@@ -17,8 +17,10 @@ enum DType : int { DT_BF16 = 0, DT_FP16 = 1, DT_FP32 = 2 };
 cudaError_t launch_set_params(int width, const void *src, int src_dtype, int src_packed, int n_mat, int one_padded_in,
                               int unpadded_out, int net_fp16, __nv_bfloat16 *packed_out, float *master_out,
                               __nv_bfloat16 *wimg, __nv_bfloat16 *wimg_t, cudaStream_t stream);
+// loss_out (optional): also receives the sum of the n_loss loss partials of the same pass
 cudaError_t launch_reduce_dw(const float *slabs, int n_slabs, int n_mat, int width, int pack_transpose, float scale,
-                             float *out_f32, __nv_bfloat16 *out_16, int out_fp16, cudaStream_t stream);
+                             float *out_f32, __nv_bfloat16 *out_16, int out_fp16, cudaStream_t stream,
+                             const float *loss_partials = nullptr, int n_loss = 0, float *loss_out = nullptr);
 cudaError_t launch_identity_fwd(const float *x, void *out, int out_dtype, size_t batch, int n_in, int padded,
                                 float scale, float offset, cudaStream_t stream);
 cudaError_t launch_frequency_fwd(const float *x, void *out, int out_dtype, size_t batch, int n_in, int n_freq, int padded,

@@ -402,8 +402,8 @@ int tnn_trainer_reduce(tnn_trainer *t, void *stream) {
     if (t->reduced) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     tnn_network *n = t->net;
-    TNN_CUDA(tnn::launch_sum_partials(n->loss_partials, t->n_loss, t->loss, s));
-    TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, t->n_slabs, n->n_mat, n->width, 1, 1.0f, t->grads, nullptr, 0, s));
+    TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, t->n_slabs, n->n_mat, n->width, 1, 1.0f, t->grads, nullptr, 0, s,
+                                   n->loss_partials, t->n_loss, t->loss));
     t->reduced = true;
     return 0;
 }
