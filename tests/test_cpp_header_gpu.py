@@ -59,7 +59,7 @@ def test_training_through_the_cpp_layer_matches_the_python_front_end(tnn_lib, tm
     r = subprocess.run([str(exe)], capture_output=True, text=True)
     assert r.returncode == 0, (r.returncode, r.stdout[-500:], r.stderr[-500:])
     cpp_losses = np.array([float(x) for x in r.stdout.split()])
-    assert len(cpp_losses) == 20 and cpp_losses[-1] < 0.5 * cpp_losses[0]
+    assert len(cpp_losses) == 20 and cpp_losses[-1] < 0.8 * cpp_losses[0]
 
     batch = 128 * 20 + 8
     i = np.arange(batch)

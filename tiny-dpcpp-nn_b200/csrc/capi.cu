@@ -168,7 +168,9 @@ int tnn_network_create(int input_width, int output_width, int n_hidden_layers, i
     cudaError_t e = cudaMalloc(&n->packed, bytes);
     if (e == cudaSuccess) e = cudaMalloc(&n->wimg, bytes);
     if (e == cudaSuccess) e = cudaMalloc(&n->wimg_t, bytes);
-    if (e == cudaSuccess) e = cudaMalloc(&n->dw_slabs, (size_t)n->n_sm * n->n_params * sizeof(float));
+    // one weight-gradient slab per CTA of the training kernels: up to two CTAs per SM at widths 16 and 32
+    n->max_slabs = n->n_sm * (width <= 32 ? 2 : 1);
+    if (e == cudaSuccess) e = cudaMalloc(&n->dw_slabs, (size_t)n->max_slabs * n->n_params * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&n->loss_partials, 1024 * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&n->status, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(n->packed, 0, bytes);
@@ -447,6 +449,7 @@ static int train_step_impl(tnn_network *n, const void *x, const tnn::EncodedInpu
         p.tgt_mode = (!aligned || n->width < 32) ? 0 : (n_targets == n->width ? 1 : 2);
         if (p.tgt_mode == 1) make_tgt_tmap(&p.tm_tgt, targets, batch, n->width);
         p.dw_partials = n->dw_slabs;
+        p.max_slabs = n->max_slabs;
         p.loss_partials = n->loss_partials;
         p.batch = batch;
         p.width = n->width;

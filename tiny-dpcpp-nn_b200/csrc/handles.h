@@ -20,6 +20,7 @@ struct tnn_network {
     int fp16 = 0; // element type of operands and activations: bf16 (0) or fp16 (1)
     int variant = 0;
     int n_sm = 0;
+    int max_slabs = 0; // capacity of dw_slabs in slabs (CTAs of a training kernel)
     size_t n_params = 0;
     // (16-bit buffers are typed __nv_bfloat16 whatever the element type; see fp16)
     __nv_bfloat16 *packed = nullptr; // packed-layout 16-bit weights (what get_params returns)

@@ -78,6 +78,7 @@ struct TrainLaunch {
     int tgt_mode;
     EncodedInput enc;       // enc.x != nullptr: the input tile is produced in the kernel from fp32 coordinates
     float *dw_partials;     // [grid][L+1][W][W] fp32, layout (out, in)
+    int max_slabs;          // slabs dw_partials has room for: the launcher never starts more CTAs than that
     float *loss_partials;   // [grid] fp32
     size_t batch;
     int width;

@@ -46,6 +46,9 @@ template <int W, int TGT> struct PipeSmem {
     static constexpr int GROUP_WARPS = GROUP_THREADS / 32;
     static constexpr int THREADS = 128 + 2 * GROUP_THREADS;
     static constexpr int CPT = W / 2; // columns per epilogue thread
+    // Narrow layers are pure latency chains - an MMA or two per step - and their tiles are small: two CTAs share an SM
+    // where shared memory and tensor memory allow (the launcher decides), which doubles the chains in flight.
+    static constexpr int CTAS_PER_SM = W <= 32 ? 2 : 1;
 };
 
 struct PipeBarriers {
@@ -71,13 +74,13 @@ struct PipeBarriers {
 // inference kernel does, was measured slower here: the activations must be in shared memory anyway for the
 // weight-gradient GEMMs and the activation backward, and the extra tcgen05.st in every epilogue step costs more
 // than the shorter GEMMs save.)
-template <int W, int TGT, bool HF_>
-__global__ void __launch_bounds__(PipeSmem<W, TGT>::THREADS, 1)
+template <int W, int TGT, bool HF_, int MINB>
+__global__ void __launch_bounds__(PipeSmem<W, TGT>::THREADS, MINB)
 mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_tgt,
                       const __nv_bfloat16 *__restrict__ wimg,
                       const float *__restrict__ targets, int n_targets, float *__restrict__ dw_slabs,
                       float *__restrict__ loss_partials, size_t batch, int n_tiles, int n_mat, int act, int out_act,
-                      float loss_scale, float inv_n, const EncodedInput enc, int *status) {
+                      float loss_scale, float inv_n, const EncodedInput enc, int tmem_cols, int *status) {
     using T = Tile<W>;
     using S = PipeSmem<W, TGT>;
     constexpr int fp16 = HF_ ? 1 : 0; // element type of operands and activations: bf16 or fp16
@@ -91,7 +94,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
     const uint32_t smem_base = ptx::smem_u32(smem);
     volatile uint32_t *abort_flag = &bars.abort_flag;
     const int my_tiles = (n_tiles > (int)blockIdx.x) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-    constexpr uint32_t kTmemCols = 512;
+    const uint32_t kTmemCols = (uint32_t)tmem_cols; // power of two covering the accumulators of this network
 
     // activation buffer of a_j (j = 1..L) of this CTA's t-th tile
     auto ab_index = [L](int t, int j) { return (t & 1) ? L + 1 - j : j - 1; };
@@ -664,24 +667,42 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
 // 227 KB per CTA minus the statically allocated barriers
 constexpr size_t kPipeSmemLimit = 227 * 1024 - 2048;
 
+template <int W, int TGT, bool HF_, int MINB> static cudaError_t launch_pipe_b(TrainLaunch &p);
+
 template <int W, int TGT, bool HF_> static cudaError_t launch_pipe_t(TrainLaunch &p) {
+    using TileT = Tile<W>;
+    const size_t smem_probe = (size_t)PipeSmem<W, TGT>::WBUF(p.n_mat) + (size_t)p.n_mat * TileT::WGT_BYTES + 1024;
+    int cols = 32;
+    while (cols < 2 * W + p.n_mat * W) cols *= 2;
+    // two CTAs per SM (registers capped at half the file) only where shared and tensor memory hold two of them
+    if constexpr (PipeSmem<W, TGT>::CTAS_PER_SM == 2) {
+        if (2 * (smem_probe + 2048) <= 227 * 1024 && 2 * cols <= 512) return launch_pipe_b<W, TGT, HF_, 2>(p);
+    }
+    return launch_pipe_b<W, TGT, HF_, 1>(p);
+}
+
+template <int W, int TGT, bool HF_, int MINB> static cudaError_t launch_pipe_b(TrainLaunch &p) {
     using T = Tile<W>;
     using S = PipeSmem<W, TGT>;
     const size_t smem = (size_t)S::WBUF(p.n_mat) + (size_t)p.n_mat * T::WGT_BYTES + 1024;
     const int cols_needed = 2 * W + p.n_mat * W;
     if (smem > kPipeSmemLimit || cols_needed > 512 || p.n_mat > kPipeMaxMat) return cudaErrorInvalidConfiguration;
-    auto kern = mlp_train_pipe_kernel<W, TGT, HF_>;
+    int tmem_cols = 32;
+    while (tmem_cols < cols_needed) tmem_cols *= 2;
+    const int per_sm = MINB;
+    auto kern = mlp_train_pipe_kernel<W, TGT, HF_, MINB>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
-    const int grid = n_tiles < p.n_sm ? n_tiles : p.n_sm;
+    const int max_ctas = p.n_sm * per_sm <= p.max_slabs ? p.n_sm * per_sm : p.max_slabs;
+    const int grid = n_tiles < max_ctas ? n_tiles : max_ctas;
     p.grid_out = grid;
     if (grid == 0) return cudaSuccess;
     const float inv_n = 1.0f / ((float)p.batch * (float)W);
     count_launch();
     kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, TGT == 1 ? p.tm_tgt : p.tm_x, p.wimg, p.targets, p.n_targets, p.dw_partials, p.loss_partials,
                                                p.batch, n_tiles, p.n_mat, p.act, p.out_act, p.loss_scale, inv_n,
-                                               p.enc, p.status);
+                                               p.enc, tmem_cols, p.status);
     return cudaGetLastError();
 }
 
