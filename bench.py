@@ -269,12 +269,15 @@ def make_c5(L, torch, batch, rank, n_batches):
     return net, enc, batches
 
 
-def grid_leg(L, torch, batch, steps, timed):
-    """Forward and parameter-gradient backward of the 16-level hash grid (3-D inputs, 2 features per level)."""
-    enc = L.create_encoding("HashGrid", GRID_CFG, 32, seed=3)
+def grid_leg(L, torch, batch, steps, timed, n_levels=16, base_resolution=16):
+    """Forward and parameter-gradient backward of the hash grid (3-D inputs, 2 features per level; 16 levels from
+    resolution 16 unless told otherwise: `--grid-levels 13 --grid-base-resolution 128` are the hashed levels of the
+    same grid alone, `--grid-levels 1` its coarsest level alone)."""
+    cfg = dict(GRID_CFG, n_levels=n_levels, base_resolution=base_resolution)
+    enc = L.create_encoding("HashGrid", cfg, 2 * n_levels, seed=3)
     gen = torch.Generator(device="cuda").manual_seed(7)
     pos = torch.rand((batch, 3), device="cuda", generator=gen)
-    dy = torch.rand((batch, 32), device="cuda", generator=gen) - 0.5
+    dy = torch.rand((batch, 2 * n_levels), device="cuda", generator=gen) - 0.5
     res = {}
     fwd = lambda: enc.fwd(pos)  # noqa: E731
     for name, fn in (("grid_fwd", fwd),
@@ -372,7 +375,7 @@ def run_only(args):
 
     out = {"only": args.only, "log2_batch": args.log2_batch, "steps": args.steps}
     if args.only == "grid":
-        out.update(grid_leg(L, torch, batch, args.steps, timed))
+        out.update(grid_leg(L, torch, batch, args.steps, timed, args.grid_levels, args.grid_base_resolution))
     elif args.only == "c4":
         # hash grid (3-D, 16 levels x 2 features, 2^19 entries per level) feeding a width-64 network with 2 hidden
         # layers and 3 outputs: through the C ABI trainer, and through the torch.nn.Module front end
@@ -747,6 +750,8 @@ def main():
     ap.add_argument("--log2-batch", type=int, default=LOG2_BATCH)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--brief", action="store_true", help="skip the hash-grid and sweep legs")
+    ap.add_argument("--grid-levels", type=int, default=16, help="levels of the grid of `--only grid`")
+    ap.add_argument("--grid-base-resolution", type=int, default=16, help="coarsest resolution of that grid")
     ap.add_argument("--only", choices=["train", "infer", "c5", "grid", "sweep", "c4"],
                     help="run one part only: a single kernel (profiler captures), the width / depth sweep, or the "
                          "grid -> MLP model")
