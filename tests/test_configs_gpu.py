@@ -283,6 +283,38 @@ def test_c4_table_gradient_through_the_network(tnn_lib):
         _check(got[a:b], exp_table[a:b], what=f"C4 table gradient, level {l}")
 
 
+@pytest.mark.parametrize("width,nh,nt", [(64, 1, 3), (64, 2, 64), (64, 4, 3), (32, 3, 5), (32, 1, 32), (16, 2, 2)])
+def test_dl_dinput_of_the_fused_training_kernel(tnn_lib, width, nh, nt):
+    """The pipelined training kernel's extra backward step (dL/dinput = delta_0 W_0^T, stored by TMA) feeds a trainable
+    encoding: the table gradient it produces must equal the one of the forward / loss / backward kernel path
+    (variant 16), and the network gradients must be unchanged."""
+    from tiny_dpcpp_nn.trainer import Trainer
+
+    batch = 128 * 150 + 72
+    cfg = dict(otype="HashGrid", n_dims_to_encode=3, n_levels=width // 4, n_features_per_level=2, log2_hashmap_size=12,
+               base_resolution=4, per_level_scale=1.5)
+    w = O.bf16_round(synth.xavier_weights(nh + 1, width, 9))
+    rng = np.random.default_rng(5)
+    pts = torch.from_numpy(rng.uniform(0, 1, (batch, 3)).astype(np.float32)).cuda()
+    t = torch.from_numpy(rng.uniform(-1, 1, (batch, nt)).astype(np.float32)).cuda()
+    out = []
+    for variant in (0, 16):
+        net = tnn_lib.create_network(width // 2, min(nt, width), nh, A["relu"], A["none"], width, "torch.bfloat16", True, seed=1)
+        net.set_params(torch.from_numpy(w.reshape(-1)).cuda(), False)
+        net.set_variant(variant)
+        enc = tnn_lib.create_encoding("HashGrid", cfg, width, seed=3)
+        enc.set_params(torch.from_numpy(np.random.default_rng(2).uniform(-0.5, 0.5, enc.n_params()).astype(np.float32)).cuda())
+        tr = Trainer(net, encoding=enc)
+        tr.set_deterministic_encoding(True)
+        loss = tr.forward_backward(pts, t).item()
+        assert net.status() == 0
+        out.append((loss, tr.grads.clone(), tr.encoding_grads.clone()))
+    assert abs(out[0][0] - out[1][0]) <= 1e-5 * abs(out[1][0])
+    _check(out[0][1].cpu().numpy(), out[1][1].cpu().numpy(), what="network gradients")
+    assert out[1][2].abs().max() > 0
+    _check(out[0][2].cpu().numpy(), out[1][2].cpu().numpy(), what="table gradient through the fused kernel's dL/dinput")
+
+
 @pytest.mark.parametrize("dims", [3, 2])
 def test_c4_fused_encoding_forward_equals_the_two_kernel_path(tnn_lib, dims):
     """Hash grid gathered by extra warps of the network kernel straight into its input tile: inference and the stored

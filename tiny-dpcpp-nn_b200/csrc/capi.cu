@@ -436,7 +436,7 @@ static int train_step_impl(tnn_network *n, const void *x, const tnn::EncodedInpu
     float *gf = grads_dtype == TNN_DTYPE_FP32 ? (float *)grads : nullptr;
     __nv_bfloat16 *gb = grads_dtype != TNN_DTYPE_FP32 ? (__nv_bfloat16 *)grads : nullptr;
 
-    if (!(n->variant & 16) && !dx) { // fused single-kernel path
+    if (!(n->variant & 16)) { // fused single-kernel path
         tnn::TrainLaunch p{};
         if (enc)
             p.enc = *enc;
@@ -448,6 +448,10 @@ static int train_step_impl(tnn_network *n, const void *x, const tnn::EncodedInpu
         const bool aligned = reinterpret_cast<uintptr_t>(targets) % 16 == 0;
         p.tgt_mode = (!aligned || n->width < 32) ? 0 : (n_targets == n->width ? 1 : 2);
         if (p.tgt_mode == 1) make_tgt_tmap(&p.tm_tgt, targets, batch, n->width);
+        if (dx) {
+            p.want_dx = 1;
+            make_act_tmap(&p.tm_dx, dx, batch, n->width, 1);
+        }
         p.dw_partials = n->dw_slabs;
         p.max_slabs = n->max_slabs;
         p.loss_partials = n->loss_partials;

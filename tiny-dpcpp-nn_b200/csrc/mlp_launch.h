@@ -77,6 +77,8 @@ struct TrainLaunch {
     // 16-byte aligned targets
     int tgt_mode;
     EncodedInput enc;       // enc.x != nullptr: the input tile is produced in the kernel from fp32 coordinates
+    int want_dx;            // also compute dL/dinput (batch x width, the network's type) and store it through tm_dx
+    CUtensorMap tm_dx;      // (pipelined kernel only; the single-tile kernel reports cudaErrorInvalidConfiguration)
     float *dw_partials;     // [grid][L+1][W][W] fp32, layout (out, in)
     int max_slabs;          // slabs dw_partials has room for: the launcher never starts more CTAs than that
     float *loss_partials;   // [grid] fp32

@@ -545,6 +545,7 @@ template <int W> static cudaError_t launch_train_w(TrainLaunch &p) {
 }
 
 cudaError_t launch_mlp_train(TrainLaunch &p) {
+    if (p.want_dx) return cudaErrorInvalidConfiguration; // dL/dinput: pipelined kernel or the three-kernel path
     switch (p.width) {
     case 32: return launch_train_w<32>(p);
     case 64: return launch_train_w<64>(p);

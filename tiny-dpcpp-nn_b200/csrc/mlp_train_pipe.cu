@@ -74,9 +74,12 @@ struct PipeBarriers {
 // inference kernel does, was measured slower here: the activations must be in shared memory anyway for the
 // weight-gradient GEMMs and the activation backward, and the extra tcgen05.st in every epilogue step costs more
 // than the shorter GEMMs save.)
-template <int W, int TGT, bool HF_, int MINB>
+// DX: the backward stage takes one more step per tile, dL/dinput = delta_0 W_0^T (kernel_esimd.h:213-228), and stores
+// it through tm_dx: what a trainable encoding in front of the network needs.
+template <int W, int TGT, bool HF_, int MINB, bool DX>
 __global__ void __launch_bounds__(PipeSmem<W, TGT>::THREADS, MINB)
 mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_tgt,
+                      const __grid_constant__ CUtensorMap tm_dx,
                       const __nv_bfloat16 *__restrict__ wimg,
                       const float *__restrict__ targets, int n_targets, float *__restrict__ dw_slabs,
                       float *__restrict__ loss_partials, size_t batch, int n_tiles, int n_mat, int act, int out_act,
@@ -125,6 +128,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
         ptx::fence_barrier_init();
         if (!enc.x) ptx::prefetch_tmap(&tm_x);
         if constexpr (TGT == 1) ptx::prefetch_tmap(&tm_tgt);
+        if constexpr (DX) ptx::prefetch_tmap(&tm_dx);
     }
     if (warp == 1) {
         ptx::tmem_alloc(&bars.tmem_base, kTmemCols);
@@ -300,6 +304,21 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     }
                     __syncwarp();
                     ++ci_count;
+                }
+                if constexpr (DX) { // dL/dinput = delta_0 W_0^T, once delta_0 is written
+                    if (ok && !ptx::mbar_wait(&bars.b_ready, br_parity, abort_flag)) {
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 6);
+                        ok = false;
+                    }
+                    br_parity ^= 1u;
+                    if (!ok) break;
+                    ptx::tc_fence_after_sync();
+                    const uint64_t d_desc = dp_desc0 + (uint64_t)(((L - 1) & 1) * T::ACT_UNITS); // delta_0
+                    if (ptx::elect_one()) {
+                        T::template issue_chain<false>(accb_tmem, d_desc, w_desc0, idesc);
+                        ptx::mma_commit(&bars.accb_full);
+                    }
+                    __syncwarp();
                 }
             }
         }
@@ -545,6 +564,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
         uint32_t ab_parity = 0;
         uint32_t dp_parity = 0, dp_written = 0; // bit p: phase to wait for / buffer p was written before
         uint32_t go_count = 0;
+        [[maybe_unused]] bool dx_store_pending = false;
         bool ok = true;
         auto chunk_at = [&](int ch) {
             const int c = col0 + ch * 8;
@@ -566,6 +586,13 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 // this step completes: wait for the former and fetch the latter first, so that both
                 // shared-memory round trips hide under the GEMM (see the forward stage).
                 const int p = (L - l) & 1; // delta_{l-1} goes to ping-pong buffer (L - l) & 1
+                if constexpr (DX) { // the buffer may still be read by the store of the previous tile's dL/dinput
+                    if (dx_store_pending && p == (L & 1)) {
+                        if (threadIdx.x == S::THREADS - S::GROUP_THREADS) ptx::tma_wait_group_read<0>();
+                        ptx::named_bar_sync(2, S::GROUP_THREADS);
+                        dx_store_pending = false;
+                    }
+                }
                 if ((dp_written >> p) & 1u) { // all but the first write wait for the GEMM that read the buffer
                     if (!wait_u(&bars.dp_free[p], (dp_parity >> p) & 1u, 6 | (l << 4))) {
                         ok = false;
@@ -622,6 +649,62 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 }
                 ++go_count;
             }
+            if constexpr (DX) {
+                // ---- dL/dinput of this tile: delta_0 W_0^T, rounded to the network type, stored by TMA
+                if (!ok) break;
+                const int p = L & 1; // the buffer that held delta_1
+                if (dx_store_pending) { // (a one-hidden-layer network writes this buffer here only)
+                    if (threadIdx.x == S::THREADS - S::GROUP_THREADS) ptx::tma_wait_group_read<0>();
+                    ptx::named_bar_sync(2, S::GROUP_THREADS);
+                    dx_store_pending = false;
+                }
+                if ((dp_written >> p) & 1u) {
+                    if (!wait_u(&bars.dp_free[p], (dp_parity >> p) & 1u, 11)) {
+                        ok = false;
+                        break;
+                    }
+                    dp_parity ^= 1u << p;
+                }
+                dp_written &= ~(1u << p); // no weight-gradient GEMM reads this tile: its reuse waits for the store instead
+                if (!wait_u(&bars.accb_full, ab_parity, 12)) {
+                    ok = false;
+                    break;
+                }
+                ab_parity ^= 1u;
+                ptx::tc_fence_after_sync();
+                uint32_t v[CPT];
+                if constexpr (CPT == 32)
+                    ptx::tmem_ld32(acc_addr, v);
+                else if constexpr (CPT == 16)
+                    ptx::tmem_ld16(acc_addr, v);
+                else
+                    ptx::tmem_ld8(acc_addr, v);
+                ptx::tmem_ld_wait();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&bars.b_ready); // accumulator B is drained
+                uint8_t *dst = smem + S::DP(p);
+#pragma unroll
+                for (int ch = 0; ch < CPT / 8; ++ch) {
+                    uint32_t o[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        o[q] = ptx::pack2<HF_>(__uint_as_float(v[ch * 8 + 2 * q]), __uint_as_float(v[ch * 8 + 2 * q + 1]));
+                    *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+                ptx::fence_proxy_async_smem();
+                ptx::named_bar_sync(2, S::GROUP_THREADS);
+                if (threadIdx.x == S::THREADS - S::GROUP_THREADS) {
+                    const int tile = blockIdx.x + t * gridDim.x;
+                    for (int at = 0; at < T::KATOMS; ++at)
+                        ptx::tma_store_2d(&tm_dx, dst + at * T::ACT_ATOM_BYTES, at * T::ATOM_COLS, tile * T::TM);
+                    ptx::tma_commit_group();
+                }
+                dx_store_pending = true;
+            }
+        }
+        if constexpr (DX) {
+            if (threadIdx.x == S::THREADS - S::GROUP_THREADS) ptx::tma_wait_group<0>();
         }
         // ---- drain the weight-gradient accumulators into this CTA's slab
         if (ok && my_tiles > 0 && !wait_u(&bars.all_done, 0, 7)) ok = false;
@@ -667,7 +750,10 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
 // 227 KB per CTA minus the statically allocated barriers
 constexpr size_t kPipeSmemLimit = 227 * 1024 - 2048;
 
-template <int W, int TGT, bool HF_, int MINB> static cudaError_t launch_pipe_b(TrainLaunch &p);
+template <int W, int TGT, bool HF_, int MINB, bool DX> static cudaError_t launch_pipe_d(TrainLaunch &p);
+template <int W, int TGT, bool HF_, int MINB> static cudaError_t launch_pipe_b(TrainLaunch &p) {
+    return p.want_dx ? launch_pipe_d<W, TGT, HF_, MINB, true>(p) : launch_pipe_d<W, TGT, HF_, MINB, false>(p);
+}
 
 template <int W, int TGT, bool HF_> static cudaError_t launch_pipe_t(TrainLaunch &p) {
     using TileT = Tile<W>;
@@ -681,7 +767,7 @@ template <int W, int TGT, bool HF_> static cudaError_t launch_pipe_t(TrainLaunch
     return launch_pipe_b<W, TGT, HF_, 1>(p);
 }
 
-template <int W, int TGT, bool HF_, int MINB> static cudaError_t launch_pipe_b(TrainLaunch &p) {
+template <int W, int TGT, bool HF_, int MINB, bool DX> static cudaError_t launch_pipe_d(TrainLaunch &p) {
     using T = Tile<W>;
     using S = PipeSmem<W, TGT>;
     const size_t smem = (size_t)S::WBUF(p.n_mat) + (size_t)p.n_mat * T::WGT_BYTES + 1024;
@@ -690,7 +776,7 @@ template <int W, int TGT, bool HF_, int MINB> static cudaError_t launch_pipe_b(T
     int tmem_cols = 32;
     while (tmem_cols < cols_needed) tmem_cols *= 2;
     const int per_sm = MINB;
-    auto kern = mlp_train_pipe_kernel<W, TGT, HF_, MINB>;
+    auto kern = mlp_train_pipe_kernel<W, TGT, HF_, MINB, DX>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
@@ -700,7 +786,7 @@ template <int W, int TGT, bool HF_, int MINB> static cudaError_t launch_pipe_b(T
     if (grid == 0) return cudaSuccess;
     const float inv_n = 1.0f / ((float)p.batch * (float)W);
     count_launch();
-    kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, TGT == 1 ? p.tm_tgt : p.tm_x, p.wimg, p.targets, p.n_targets, p.dw_partials, p.loss_partials,
+    kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, TGT == 1 ? p.tm_tgt : p.tm_x, DX ? p.tm_dx : p.tm_x, p.wimg, p.targets, p.n_targets, p.dw_partials, p.loss_partials,
                                                p.batch, n_tiles, p.n_mat, p.act, p.out_act, p.loss_scale, inv_n,
                                                p.enc, tmem_cols, p.status);
     return cudaGetLastError();
