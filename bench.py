@@ -257,7 +257,7 @@ def make_c5(L, torch, batch, rank, n_batches):
     for i0 in range(0, IMAGE_RES, 256):  # in slabs: the phase tensor of the whole image would be 1 GiB
         u = axis[i0:i0 + 256, None, None] * ft[None, None, :, 0]
         v = axis[None, :, None] * ft[None, None, :, 1]
-        image[i0:i0 + 256] = torch.sin(2 * np.pi * (u + v) + phit) @ at
+        image[i0:i0 + 256] = (torch.sin(2 * np.pi * (u + v) + phit)[..., None] * at).sum(-2)
     batches = []
     gen = torch.Generator(device="cuda").manual_seed(100 + rank)
     for _ in range(n_batches):

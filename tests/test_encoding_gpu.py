@@ -300,6 +300,36 @@ def test_grid_forward_fp16_output_and_wide_padding(tnn_lib):
         assert np.array_equal(enc.fwd(_t(p), out_dtype=torch.bfloat16).float().cpu().numpy(), O.bf16_round(ref))
 
 
+def test_unaligned_pointers_are_refused_not_faulted(tnn_lib):
+    """The L2 and grid-backward kernels move 16 bytes at a time: an offset view handed through the ABI must come back
+    as an error code with a message, never as a misaligned-address fault on the device."""
+    lib = tnn_lib.load()
+    s = tnn_lib.stream_ptr()
+    pred = torch.zeros(64 * 64 + 8, dtype=torch.bfloat16, device="cuda")
+    target = torch.zeros(64 * 64 + 4, dtype=torch.float32, device="cuda")
+    grads = torch.zeros(64 * 64 + 8, dtype=torch.bfloat16, device="cuda")
+    loss = torch.zeros(1, device="cuda")
+    ok = lib.tnn_l2_loss(tnn_lib.dptr(pred), tnn_lib.dptr(target), 64, None, tnn_lib.dptr(grads), 64, 64, 1.0,
+                         tnn_lib.dptr(loss), s)
+    assert ok == 0
+    for fn in (lib.tnn_l2_loss, lib.tnn_l2_loss_static):
+        assert fn(tnn_lib.dptr(pred[1:]), tnn_lib.dptr(target), 64, None, tnn_lib.dptr(grads), 64, 64, 1.0,
+                  tnn_lib.dptr(loss), s) != 0
+        assert b"16-byte aligned" in lib.tnn_last_error()
+        assert fn(tnn_lib.dptr(pred), tnn_lib.dptr(target[1:]), 64, None, tnn_lib.dptr(grads), 64, 64, 1.0,
+                  tnn_lib.dptr(loss), s) != 0
+        # narrow targets only need 4-byte alignment
+        assert fn(tnn_lib.dptr(pred), tnn_lib.dptr(target[1:]), 3, None, tnn_lib.dptr(grads), 64, 64, 1.0,
+                  tnn_lib.dptr(loss), s) == 0
+    enc = tnn_lib.create_encoding("HashGrid", dict(otype="HashGrid", n_dims_to_encode=2, n_levels=2), None, seed=1)
+    g = torch.zeros(enc.n_params() + 4, device="cuda")
+    x = torch.rand((8, 2), device="cuda")
+    dy = torch.rand((8, 4), device="cuda")
+    rc = lib.tnn_encoding_backward(enc._h, tnn_lib.dptr(x), tnn_lib.dptr(dy), 2, tnn_lib.dptr(g[1:]), 8, 0, s)
+    assert rc != 0 and b"16-byte aligned" in lib.tnn_last_error()
+    torch.cuda.synchronize()  # the context is intact
+
+
 def test_encoding_errors(tnn_lib):
     with pytest.raises(tnn_lib.TnnError, match="Unknown encoding type"):
         tnn_lib.create_encoding("OneBlob", dict(otype="OneBlob", n_dims_to_encode=3))
