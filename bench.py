@@ -534,6 +534,42 @@ def run_gpu_arm(args):
     loss_value = float(trainer._loss.item())
     ms_step = ms_total / args.steps
     value = world * batch / (ms_step * 1e-3)
+    # the same step with the gradient exchange as reduction kernel + ncclAllReduce + Adam kernel, for comparison
+    windowed = bool(trainer.peer_window)
+    dp_exchange = None
+    if world > 1:
+        dp_exchange = {"used": "peer_window" if windowed else "nccl_allreduce", "ms_per_step": round(ms_step, 5)}
+        if windowed:
+            trainer.set_peer_window(False)
+            for _ in range(3):
+                step()
+            dp_exchange["ms_per_step_nccl_allreduce"] = round(timed(step, args.steps) / args.steps, 5)
+            trainer.set_peer_window(True)
+        # and with no exchange at all, per rank: what each GPU alone needs for the step (a second trainer without
+        # a communicator on the same network; the data-parallel trainer's next step rewrites the weights from its
+        # own master copy, so the ranks stay replicas)
+        alone_tr = Trainer(net, lr=1e-3, betas=(0.9, 0.99), eps=1e-15, encoding=enc)
+
+        def step_alone():
+            q, t = batches[turn[0] % N_ROTATE]
+            turn[0] += 1
+            alone_tr.training_step(q, t)
+
+        for _ in range(3):
+            step_alone()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step_alone()
+        e1.record()
+        torch.cuda.synchronize()
+        alone = torch.tensor([e0.elapsed_time(e1) / args.steps], device="cuda")
+        every = [torch.zeros_like(alone) for _ in range(world)]
+        dist.all_gather(every, alone)
+        dp_exchange["ms_per_step_without_exchange_by_rank"] = [round(v.item(), 5) for v in every]
+        del alone_tr
+        step()
 
     # -------- inference at the same batch: coordinates in, padded bf16 output rows out (512 MiB written per call)
     q0, t0_ = batches[0]
@@ -704,11 +740,15 @@ def run_gpu_arm(args):
                     "note": "copy of step i + 1 overlaps the compute of step i (two streams, two device buffers)"},
             "gpu_launches": launches,
             "kernels_per_step": (["mlp_train_pipe_kernel", "adam_refresh_kernel"] if world == 1 else
+                                 ["mlp_train_pipe_kernel", "dp_adam_refresh_kernel (gradient exchange over peer windows inside)"]
+                                 if windowed else
                                  ["mlp_train_pipe_kernel", "reduce_dw_kernel", "ncclAllReduce (80 KiB)",
                                   "adam_refresh_kernel"]),
             "roofline": roofline, "rooflines": rooflines, "swiftnet_64x64": swiftnet, "grid_rooflines": grid_roofs,
             "clocks": clocks, "kernel_status": status, "final_loss_sum": loss_value,
         }
+        if dp_exchange is not None:
+            out["dp_exchange"] = dp_exchange
         if sweep is not None:
             out["sweep"] = sweep
         if cpu is not None:

@@ -272,20 +272,34 @@ int tnn_network_adam_step(tnn_network *net, float *master, float *m, float *v, c
 /* ------------------------------------------------------------------------------------------
  * Data parallelism.  No reference counterpart: the reference's multi-GPU benchmarks are independent MPI replicas
  * without any exchange (benchmarks/common_benchmarks.h:53-54).  One process per GPU; the only exchange of a
- * training step is one ncclAllReduce(sum) of the (n_hidden_layers + 1) * width^2 fp32 weight-gradient buffer
+ * training step is the sum of the (n_hidden_layers + 1) * width^2 fp32 weight-gradient buffer over the ranks
  * (plus reduce-scatter / all-gather of a trainable encoding's table).  NCCL is loaded with dlopen("libnccl.so.2")
  * at the first of these calls - the copy the process already uses, if it has one.
+ *
+ * Peer windows: when all ranks (at most 8) run on one host and can map each other's memory (CUDA IPC over NVLink),
+ * making a communicator also gives every rank a window in every other rank's address space, and the optimiser
+ * kernel of a trainer exchanges the weight gradient itself: it sums the per-CTA slabs, stores the result into
+ * every peer's window with a flag per block, waits for the peers' blocks (bounded: TNN_DP_WAIT_MS, default 30 000,
+ * after which tnn_network_sync_status reports 2 and the step is invalid), adds the ranks' contributions in rank
+ * order - every rank computes bit-identical parameters - and applies Adam.  Otherwise (several hosts, no peer
+ * access, more than 262 144 parameters, or TNN_DP_PEER_WINDOW=0 in the environment of every rank) the exchange is
+ * one ncclAllReduce(sum) between a reduction kernel and the Adam kernel.  Windows cost 2 MiB per rank pair.
  * ------------------------------------------------------------------------------------------ */
 /* ncclGetUniqueId into 128 caller bytes (rank 0 calls this and sends the bytes to the other ranks). */
 int tnn_dp_get_unique_id(void *id128);
-/* ncclCommInitRank on the current device: collective over all `world` ranks. */
+/* ncclCommInitRank on the current device, then the peer windows: collective over all `world` ranks;
+ * allocates and synchronises the device. */
 int tnn_dp_comm_create(const void *id128, int rank, int world, tnn_dp_comm **out);
 /* Wraps a communicator the application already has (an ncclComm_t passed as void*); not destroyed by
- * tnn_dp_comm_destroy. */
+ * tnn_dp_comm_destroy.  Collective like tnn_dp_comm_create (the peer windows are set up over it). */
 int tnn_dp_init(void *nccl_comm, tnn_dp_comm **out);
 int tnn_dp_comm_destroy(tnn_dp_comm *comm);
 int tnn_dp_rank(const tnn_dp_comm *comm);
 int tnn_dp_world_size(const tnn_dp_comm *comm);
+/* 1 when trainers on this communicator exchange gradients through peer windows, 0 when through ncclAllReduce. */
+int tnn_dp_peer_window(const tnn_dp_comm *comm);
+/* Turns the windowed exchange off (0) or back on (1); to be called alike on every rank, between steps. */
+int tnn_dp_set_peer_window(tnn_dp_comm *comm, int enable);
 /* In-place sum of n fp32 values over the ranks, enqueued on `stream` (comm == NULL: single process, no-op). */
 int tnn_dp_allreduce_sum(tnn_dp_comm *comm, float *buf, size_t n, void *stream);
 
@@ -320,8 +334,9 @@ int tnn_trainer_forward_backward(tnn_trainer *trainer, const void *x, const floa
 /* Finishes the sums of the last forward_backward into tnn_trainer_grads / tnn_trainer_loss without an optimiser
  * step (tnn_trainer_optimizer_step does this itself). */
 int tnn_trainer_reduce(tnn_trainer *trainer, void *stream);
-/* optimizer.step() + Module.set_params(): gradient all-reduce when a communicator is set, Adam on the master
- * copy, refresh of the bf16 weights the kernels read. */
+/* optimizer.step() + Module.set_params(): gradient sum over the ranks when a communicator is set (inside the
+ * optimiser kernel with peer windows, else ncclAllReduce), Adam on the master copy, refresh of the 16-bit weights
+ * the kernels read. */
 int tnn_trainer_optimizer_step(tnn_trainer *trainer, void *stream);
 /* forward_backward + optimizer_step: one call enqueues the whole loop body. */
 int tnn_trainer_training_step(tnn_trainer *trainer, const void *x, const float *targets, int n_targets,

@@ -344,7 +344,7 @@ def test_c4_fused_encoding_forward_equals_the_two_kernel_path(tnn_lib, dims):
 
 
 # ------------------------------------------------------------------------------------------------ data parallel, NCCL
-def _dp_worker(rank, world, port, out_dir, batch, steps):
+def _dp_worker(rank, world, port, out_dir, batch, steps, window):
     for p in (ROOT, os.path.join(ROOT, "tiny-dpcpp-nn_b200")):
         if p not in sys.path:
             sys.path.insert(0, p)
@@ -362,10 +362,18 @@ def _dp_worker(rank, world, port, out_dir, batch, steps):
     net, enc = _c5_modules(L, w)
     tr = Trainer(net, lr=1e-3, process_group=dist.group.WORLD, world_size=world, encoding=enc)
     tr.set_master_params(torch.from_numpy(O.pack_weights(w, N_MAT, W)).cuda())
+    if not window:
+        tr.set_peer_window(False)
     qt, tt = torch.from_numpy(q[a:b]).cuda(), torch.from_numpy(t[a:b]).cuda()
-    for _ in range(steps):
-        tr.training_step(qt, tt)
+    for i in range(steps):
+        if i % 2 == 0:
+            tr.training_step(qt, tt)
+        else:  # the two halves of a step as separate calls: the exchange starts from the reduced gradient
+            tr.forward_backward(qt, tt)
+            tr.optimizer_step()
     torch.cuda.synchronize()
+    with open(os.path.join(out_dir, f"window{rank}.txt"), "w") as f:
+        f.write(str(int(tr.peer_window)))
     np.save(os.path.join(out_dir, f"master{rank}.npy"), tr.master.cpu().numpy())
     np.save(os.path.join(out_dir, f"grads{rank}.npy"), tr.grads.cpu().numpy())
     assert net.status() == 0
@@ -373,21 +381,26 @@ def _dp_worker(rank, world, port, out_dir, batch, steps):
     dist.destroy_process_group()
 
 
-def test_data_parallel_step_over_nccl_equals_single_gpu_full_batch(tnn_lib, tmp_path):
-    """Two ranks, each on its half of the batch, one NCCL all-reduce of the weight-gradient buffer per step: after the
-    steps both ranks hold identical bits, and they equal (within the kernel tolerance) a single-GPU trainer that saw
-    the whole batch."""
+@pytest.mark.parametrize("exchange", ["window", "nccl"])
+def test_data_parallel_step_equals_single_gpu_full_batch(tnn_lib, tmp_path, exchange):
+    """Two ranks, each on its half of the batch, the weight-gradient buffer summed over the ranks once per step -
+    inside the optimiser kernel through the peer windows, or by one NCCL all-reduce: after the steps both ranks hold
+    identical bits, and they equal (within the kernel tolerance) a single-GPU trainer that saw the whole batch."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
 
     from tiny_dpcpp_nn.trainer import Trainer
 
-    batch, steps, world = 128 * 64, 2, 2
+    batch, steps, world = 128 * 64, 4, 2
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    mp.spawn(_dp_worker, args=(world, port, str(tmp_path), batch, steps), nprocs=world, join=True)
+    mp.spawn(_dp_worker, args=(world, port, str(tmp_path), batch, steps, exchange == "window"), nprocs=world, join=True)
+    active = [int((tmp_path / f"window{r}.txt").read_text()) for r in range(world)]
+    if exchange == "window" and active != [1] * world:
+        pytest.skip("the ranks of this host cannot map each other's memory: no peer windows")
+    assert exchange == "window" or active == [0] * world
     m0, m1 = np.load(tmp_path / "master0.npy"), np.load(tmp_path / "master1.npy")
     g0, g1 = np.load(tmp_path / "grads0.npy"), np.load(tmp_path / "grads1.npy")
     assert np.array_equal(m0, m1) and np.array_equal(g0, g1)  # replicas stay bit-identical

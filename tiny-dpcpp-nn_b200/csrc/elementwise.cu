@@ -2,6 +2,7 @@
 // encoding, L2 loss, Adam, and the deterministic reduction of per-CTA weight-gradient slabs.
 #include "elementwise.h"
 #include "mlp_common.cuh"
+#include "slab_sum.cuh"
 
 #include <cmath>
 #include <cuda_fp16.h>
@@ -69,31 +70,34 @@ cudaError_t launch_set_params(int width, const void *src, int src_dtype, int src
     return cudaGetLastError();
 }
 
-// Sum the per-CTA fp32 slabs [n_slabs][n_mat][W(out)][W(in)] in slab order (deterministic) and emit
+// Sum the per-CTA fp32 slabs [n_slabs][n_mat][W(out)][W(in)] in a fixed order (slab_sum: deterministic) and emit
 // the gradient in the requested layout: (out x in) row-major as the reference's gemm_batch leaves it
 // (kernel_esimd.h:234-239), or transposed to (in x out) and packed like the weights
 // (DeviceMatrix.h:469-488 PackAndTranspose).
-__global__ void reduce_dw_kernel(const float *__restrict__ slabs, int n_slabs, int n_mat, int W, int pack_transpose,
-                                 float scale, float *__restrict__ out_f32, __nv_bfloat16 *__restrict__ out_16,
-                                 int out_fp16, const float *__restrict__ loss_partials, int n_loss,
-                                 float *__restrict__ loss_out) {
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(kSlabBlock *kSlabWays)
+reduce_dw_kernel(const float *__restrict__ slabs, int n_slabs, int n_mat, int W, int pack_transpose, float scale,
+                 float *__restrict__ out_f32, __nv_bfloat16 *__restrict__ out_16, int out_fp16,
+                 const float *__restrict__ loss_partials, int n_loss, float *__restrict__ loss_out) {
+    __shared__ float part[kSlabWays][kSlabBlock];
+    const int idx = blockIdx.x * kSlabBlock + threadIdx.x;
     const int per = n_mat * W * W;
     if (loss_out && blockIdx.x == 0) { // the loss partials of the same pass, summed in a fixed order by block 0
-        __shared__ float red[128];
-        float local = 0.0f;
-        for (int i = threadIdx.x; i < n_loss; i += 128) local += loss_partials[i];
-        red[threadIdx.x] = local;
+        float *red = part[0];
+        if (threadIdx.y == 0) {
+            float local = 0.0f;
+            for (int i = threadIdx.x; i < n_loss; i += kSlabBlock) local += loss_partials[i];
+            red[threadIdx.x] = local;
+        }
         __syncthreads();
-        for (int s = 64; s > 0; s >>= 1) {
-            if ((int)threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+        for (int s = kSlabBlock / 2; s > 0; s >>= 1) {
+            if (threadIdx.y == 0 && (int)threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
             __syncthreads();
         }
-        if (threadIdx.x == 0) *loss_out = red[0];
+        if (threadIdx.y == 0 && threadIdx.x == 0) *loss_out = red[0];
+        __syncthreads();
     }
-    if (idx >= per) return;
-    float acc = 0.0f;
-    for (int s = 0; s < n_slabs; ++s) acc += slabs[(size_t)s * per + idx];
+    float acc = slab_sum(slabs, n_slabs, per, idx, part);
+    if (threadIdx.y != 0 || idx >= per) return;
     acc *= scale;
     const int l = idx / (W * W);
     const int o = (idx / W) % W; // output feature
@@ -108,8 +112,8 @@ cudaError_t launch_reduce_dw(const float *slabs, int n_slabs, int n_mat, int wid
                              const float *loss_partials, int n_loss, float *loss_out) {
     const int n = n_mat * width * width;
     count_launch();
-    reduce_dw_kernel<<<(n + 127) / 128, 128, 0, stream>>>(slabs, n_slabs, n_mat, width, pack_transpose, scale, out_f32,
-                                                         out_16, out_fp16, loss_partials, n_loss, loss_out);
+    reduce_dw_kernel<<<(n + kSlabBlock - 1) / kSlabBlock, dim3(kSlabBlock, kSlabWays), 0, stream>>>(
+        slabs, n_slabs, n_mat, width, pack_transpose, scale, out_f32, out_16, out_fp16, loss_partials, n_loss, loss_out);
     return cudaGetLastError();
 }
 

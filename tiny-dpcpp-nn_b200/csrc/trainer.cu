@@ -7,8 +7,12 @@
 //   single GPU     fused forward + L2 + backward kernel -> ONE kernel that sums the per-CTA weight-gradient slabs
 //                  and loss partials, applies Adam to the fp32 master parameters and rewrites the bf16 operand
 //                  images the kernels read
-//   data parallel  fused kernel -> slab / loss reduction -> ncclAllReduce(sum) of the (L+1) W^2 fp32 gradient
-//                  buffer -> Adam + operand refresh
+//   data parallel  fused kernel -> ONE kernel that sums the slabs, pushes this rank's gradient into every peer's
+//                  window over NVLink (plain peer stores + a flag per block), waits for the peers' blocks, adds the
+//                  ranks' gradients in rank order (every rank gets the same bits) and applies Adam + operand refresh.
+//                  Without peer windows (ranks on several hosts, no peer access, or a network larger than a window
+//                  slot): slab / loss reduction -> ncclAllReduce(sum) of the (L+1) W^2 fp32 gradient buffer ->
+//                  Adam + operand refresh.
 //
 // The reference has no data-parallel training (its MPI benchmarks run independent replicas,
 // benchmarks/common_benchmarks.h:53-54); the exchange is what a data-parallel use of its modules needs: one
@@ -22,13 +26,17 @@
 #include "elementwise.h"
 #include "handles.h"
 #include "mlp_common.cuh"
+#include "slab_sum.cuh"
 
 #include <cmath>
 #include <cuda_fp16.h>
+#include <cstdlib>
 #include <cstring>
 #include <dlfcn.h>
 #include <mutex>
 #include <string>
+#include <unistd.h>
+#include <vector>
 
 // ------------------------------------------------------------------------------------ NCCL by dlopen
 namespace {
@@ -91,11 +99,148 @@ int nccl_fail(const char *what, int rc) {
 
 } // namespace
 
+// Peer window of a communicator: one device buffer per rank, mapped into every rank of the same host (CUDA IPC).
+// Rank s pushes its contribution of exchange number q into slot [q & 1][s] of every rank's window and then stores q
+// into flag [q & 1][s][block]; the receiver polls its own memory.  Two slots per source are enough: a rank can start
+// exchange q + 2 only after it finished q + 1, which needed every peer's contribution to q + 1, which a peer sends
+// only after its kernel of exchange q has finished reading.
+constexpr int kMaxPeers = 8;
+constexpr size_t kWinSlotFloats = 256 * 1024; // largest gradient buffer exchanged through the window
+constexpr int kWinBlock = tnn::kSlabBlock;     // weights per block of the exchange kernel
+constexpr size_t kWinFlagsPerSlot = kWinSlotFloats / kWinBlock;
+struct PeerWindow {
+    float *slots[kMaxPeers];    // slots[r]: rank r's window as mapped in this process (own window at [rank])
+    unsigned *flags[kMaxPeers]; // flags[r]: the flag area of rank r's window
+    int rank, world;
+};
+constexpr size_t win_slot_floats_total(int world) { return 2 * (size_t)world * kWinSlotFloats; }
+constexpr size_t win_bytes(int world) {
+    return win_slot_floats_total(world) * sizeof(float) + 2 * (size_t)world * kWinFlagsPerSlot * sizeof(unsigned);
+}
+
 struct tnn_dp_comm {
     void *comm = nullptr; // ncclComm_t
     int rank = 0, world = 1;
     bool owned = false;
+    // peer window (all null / false when the ranks cannot map each other's memory)
+    void *win = nullptr;               // this rank's window (cudaMalloc)
+    void *peer_base[kMaxPeers] = {};   // peers' windows as opened here
+    PeerWindow pw{};
+    bool peer_ok = false, peer_enabled = true;
+    unsigned seq = 0; // exchanges enqueued so far
 };
+
+namespace {
+
+struct WinExchange { // what the ranks tell each other when a communicator is made
+    cudaIpcMemHandle_t handle;
+    char host[64];
+    char boot[48];
+    int ok;
+    int pad[3];
+};
+static_assert(sizeof(WinExchange) == 192, "exchange record");
+constexpr int kNcclInt8 = 0;
+
+void release_peer_window(tnn_dp_comm *c) {
+    for (int r = 0; r < kMaxPeers; ++r) {
+        if (c->peer_base[r]) cudaIpcCloseMemHandle(c->peer_base[r]);
+        c->peer_base[r] = nullptr;
+    }
+    if (c->win) cudaFree(c->win);
+    c->win = nullptr;
+    c->peer_ok = false;
+    cudaGetLastError();
+}
+
+// Collective over the communicator: every rank allocates its window, the IPC handles travel by ncclAllGather,
+// every rank maps the others' windows, and a vote (ncclAllReduce) keeps the windows only if every rank mapped
+// every peer.  Returns non-zero only when the collective itself failed; "no windows" is not an error.
+int setup_peer_window(tnn_dp_comm *c) {
+    c->peer_ok = false;
+    const char *env = getenv("TNN_DP_PEER_WINDOW");
+    if (env && env[0] == '0') return 0; // (the same on every rank)
+    if (c->world < 2 || c->world > kMaxPeers) return 0;
+    const int world = c->world;
+    bool ok = true;
+    WinExchange mine{};
+    const size_t bytes = win_bytes(world);
+    if (cudaMalloc(&c->win, bytes) != cudaSuccess) {
+        c->win = nullptr;
+        ok = false;
+    }
+    if (ok && cudaMemset(c->win, 0, bytes) != cudaSuccess) ok = false;
+    if (ok && cudaIpcGetMemHandle(&mine.handle, c->win) != cudaSuccess) ok = false;
+    cudaGetLastError();
+    gethostname(mine.host, sizeof(mine.host) - 1);
+    if (FILE *f = fopen("/proc/sys/kernel/random/boot_id", "r")) {
+        if (!fgets(mine.boot, sizeof(mine.boot), f)) mine.boot[0] = 0;
+        fclose(f);
+    }
+    mine.ok = ok ? 1 : 0;
+
+    WinExchange *dev = nullptr; // [world] gathered records, then this rank's own
+    TNN_CUDA(cudaMalloc(&dev, (world + 1) * sizeof(WinExchange)));
+    std::vector<WinExchange> all(world);
+    int rc = 0;
+    cudaError_t e = cudaMemcpy(dev + world, &mine, sizeof(mine), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) rc = nccl().AllGather(dev + world, dev, sizeof(WinExchange), kNcclInt8, c->comm, nullptr);
+    if (e == cudaSuccess && rc == 0) e = cudaStreamSynchronize(nullptr);
+    if (e == cudaSuccess && rc == 0) e = cudaMemcpy(all.data(), dev, world * sizeof(WinExchange), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess || rc != 0) {
+        cudaFree(dev);
+        release_peer_window(c);
+        return rc ? nccl_fail("ncclAllGather (peer windows)", rc)
+                  : tnn::api_fail(std::string("peer windows: ") + cudaGetErrorString(e), 2);
+    }
+    for (int r = 0; r < world && ok; ++r) {
+        if (!all[r].ok || strncmp(all[r].host, mine.host, sizeof(mine.host)) != 0 ||
+            strncmp(all[r].boot, mine.boot, sizeof(mine.boot)) != 0)
+            ok = false;
+    }
+    for (int r = 0; r < world && ok; ++r) {
+        if (r == c->rank) continue;
+        if (cudaIpcOpenMemHandle(&c->peer_base[r], all[r].handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+            c->peer_base[r] = nullptr;
+            ok = false;
+        }
+    }
+    cudaGetLastError();
+    // the vote; it also orders every rank's memset before any peer's first store
+    float vote = ok ? 1.0f : 0.0f;
+    float *dv = reinterpret_cast<float *>(dev);
+    e = cudaMemcpy(dv, &vote, sizeof(float), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) rc = nccl().AllReduce(dv, dv, 1, kNcclFloat32, kNcclSum, c->comm, nullptr);
+    if (e == cudaSuccess && rc == 0) e = cudaStreamSynchronize(nullptr);
+    if (e == cudaSuccess && rc == 0) e = cudaMemcpy(&vote, dv, sizeof(float), cudaMemcpyDeviceToHost);
+    cudaFree(dev);
+    if (e != cudaSuccess || rc != 0) {
+        release_peer_window(c);
+        return rc ? nccl_fail("ncclAllReduce (peer windows)", rc)
+                  : tnn::api_fail(std::string("peer windows: ") + cudaGetErrorString(e), 2);
+    }
+    if (vote < (float)world - 0.5f) {
+        release_peer_window(c);
+        return 0;
+    }
+    c->pw.rank = c->rank;
+    c->pw.world = world;
+    for (int r = 0; r < world; ++r) {
+        char *base = static_cast<char *>(r == c->rank ? c->win : c->peer_base[r]);
+        c->pw.slots[r] = reinterpret_cast<float *>(base);
+        c->pw.flags[r] = reinterpret_cast<unsigned *>(base + win_slot_floats_total(world) * sizeof(float));
+    }
+    c->peer_ok = true;
+    return 0;
+}
+
+unsigned long long peer_wait_ns() {
+    const char *env = getenv("TNN_DP_WAIT_MS");
+    const long ms = env ? atol(env) : 0;
+    return (unsigned long long)(ms > 0 ? ms : 30000) * 1000000ull;
+}
+
+} // namespace
 
 // ------------------------------------------------------------------------------------ kernels
 namespace tnn {
@@ -109,43 +254,16 @@ __host__ __device__ inline int packed_coord_(int i, int j, int cols) {
 // rows / columns forced to zero (Network.h:171-233).  One thread per weight.
 // FROM_SLABS: the gradient is summed here from the per-CTA slabs of the training kernel (fixed order), and block 0
 // also sums the loss partials; otherwise it is read from `grads` (already reduced, e.g. across ranks).
-template <int W, bool FROM_SLABS>
-__global__ void __launch_bounds__(128)
-adam_refresh_kernel(float *__restrict__ master, float *__restrict__ m, float *__restrict__ v, float *__restrict__ grads,
-                    const float *__restrict__ slabs, int n_slabs, const float *__restrict__ loss_partials, int n_loss,
-                    float *__restrict__ loss_out, int n_mat, int one_padded_in, int unpadded_out, float grad_scale,
-                    float lr, float b1, float b2, float eps, float bc1, float bc2_sqrt, int net_fp16,
-                    __nv_bfloat16 *__restrict__ packed_out, __nv_bfloat16 *__restrict__ wimg,
-                    __nv_bfloat16 *__restrict__ wimg_t) {
+// The arithmetic shared by the two optimiser kernels: Adam on weight `pk` with gradient g (already scaled), then the
+// refresh of the three 16-bit copies.
+template <int W>
+__device__ __forceinline__ void adam_and_refresh(int l, int o, int i, int pk, float g, float *__restrict__ master,
+                                                 float *__restrict__ m, float *__restrict__ v, int n_mat,
+                                                 int one_padded_in, int unpadded_out, float lr, float b1, float b2,
+                                                 float eps, float bc1, float bc2_sqrt, int net_fp16,
+                                                 __nv_bfloat16 *__restrict__ packed_out, __nv_bfloat16 *__restrict__ wimg,
+                                                 __nv_bfloat16 *__restrict__ wimg_t) {
     using T = Tile<W>;
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x; // slab order: (matrix, output feature, input feature)
-    const int per = n_mat * W * W;
-    if (FROM_SLABS && blockIdx.x == 0 && loss_out) {
-        __shared__ float red[128];
-        float local = 0.0f;
-        for (int i = threadIdx.x; i < n_loss; i += 128) local += loss_partials[i];
-        red[threadIdx.x] = local;
-        __syncthreads();
-        for (int s = 64; s > 0; s >>= 1) {
-            if ((int)threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
-            __syncthreads();
-        }
-        if (threadIdx.x == 0) *loss_out = red[0];
-    }
-    if (idx >= per) return;
-    const int l = idx / (W * W);
-    const int o = (idx / W) % W; // output feature
-    const int i = idx % W;       // input feature
-    const int pk = l * W * W + packed_coord_(i, o, W);
-    float g;
-    if constexpr (FROM_SLABS) {
-        g = 0.0f;
-        for (int s = 0; s < n_slabs; ++s) g += slabs[(size_t)s * per + idx];
-        grads[pk] = g;
-    } else {
-        g = grads[pk];
-    }
-    g *= grad_scale;
     const float mi = b1 * m[pk] + (1.0f - b1) * g;
     const float vi = b2 * v[pk] + (1.0f - b2) * g * g;
     m[pk] = mi;
@@ -164,6 +282,52 @@ adam_refresh_kernel(float *__restrict__ master, float *__restrict__ m, float *__
     *reinterpret_cast<__nv_bfloat16 *>(wt + T::elem_off(o, i, T::WGT_ATOM_BYTES)) = b;
 }
 
+// Sum of this rank's loss partials by the threads with threadIdx.y == 0 of one block (fixed order).
+__device__ __forceinline__ void loss_sum_block(const float *__restrict__ loss_partials, int n_loss,
+                                               float *__restrict__ loss_out, float *red) {
+    if (threadIdx.y == 0) {
+        float local = 0.0f;
+        for (int i = threadIdx.x; i < n_loss; i += kSlabBlock) local += loss_partials[i];
+        red[threadIdx.x] = local;
+    }
+    __syncthreads();
+    for (int s = kSlabBlock / 2; s > 0; s >>= 1) {
+        if (threadIdx.y == 0 && (int)threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.y == 0 && threadIdx.x == 0) *loss_out = red[0];
+    __syncthreads();
+}
+
+// Blocks of (128, 8) threads when FROM_SLABS (see slab_sum), of (128, 1) otherwise.
+template <int W, bool FROM_SLABS>
+__global__ void __launch_bounds__(kSlabBlock *kSlabWays)
+adam_refresh_kernel(float *__restrict__ master, float *__restrict__ m, float *__restrict__ v, float *__restrict__ grads,
+                    const float *__restrict__ slabs, int n_slabs, const float *__restrict__ loss_partials, int n_loss,
+                    float *__restrict__ loss_out, int n_mat, int one_padded_in, int unpadded_out, float grad_scale,
+                    float lr, float b1, float b2, float eps, float bc1, float bc2_sqrt, int net_fp16,
+                    __nv_bfloat16 *__restrict__ packed_out, __nv_bfloat16 *__restrict__ wimg,
+                    __nv_bfloat16 *__restrict__ wimg_t) {
+    __shared__ float part[FROM_SLABS ? kSlabWays : 1][kSlabBlock];
+    const int idx = blockIdx.x * kSlabBlock + threadIdx.x; // slab order: (matrix, output feature, input feature)
+    const int per = n_mat * W * W;                          // a multiple of the block's 128 weights
+    if (FROM_SLABS && blockIdx.x == 0 && loss_out) loss_sum_block(loss_partials, n_loss, loss_out, part[0]);
+    const int l = idx / (W * W);
+    const int o = (idx / W) % W; // output feature
+    const int i = idx % W;       // input feature
+    const int pk = l * W * W + packed_coord_(i, o, W);
+    float g;
+    if constexpr (FROM_SLABS) {
+        g = slab_sum(slabs, n_slabs, per, idx, part);
+        if (threadIdx.y != 0) return;
+        grads[pk] = g;
+    } else {
+        g = grads[pk];
+    }
+    adam_and_refresh<W>(l, o, i, pk, g * grad_scale, master, m, v, n_mat, one_padded_in, unpadded_out, lr, b1, b2, eps,
+                        bc1, bc2_sqrt, net_fp16, packed_out, wimg, wimg_t);
+}
+
 template <bool FROM_SLABS>
 static cudaError_t launch_adam_refresh(int width, float *master, float *m, float *v, float *grads, const float *slabs,
                                        int n_slabs, const float *loss_partials, int n_loss, float *loss_out, int n_mat,
@@ -171,16 +335,16 @@ static cudaError_t launch_adam_refresh(int width, float *master, float *m, float
                                        float b2, float eps, int net_fp16, __nv_bfloat16 *packed, __nv_bfloat16 *wimg,
                                        __nv_bfloat16 *wimg_t, cudaStream_t s) {
     const int n = n_mat * width * width;
-    const int blocks = (n + 127) / 128;
+    const int blocks = n / kSlabBlock;
+    const dim3 threads(kSlabBlock, FROM_SLABS ? kSlabWays : 1);
     const float bc1 = 1.0f - powf(b1, (float)step);
     const float bc2_sqrt = sqrtf(1.0f - powf(b2, (float)step));
     count_launch();
 #define TNN_CASE(WW)                                                                                                    \
     case WW:                                                                                                            \
-        adam_refresh_kernel<WW, FROM_SLABS><<<blocks, 128, 0, s>>>(master, m, v, grads, slabs, n_slabs, loss_partials,  \
-                                                                   n_loss, loss_out, n_mat, one_padded_in, unpadded_out, \
-                                                                   grad_scale, lr, b1, b2, eps, bc1, bc2_sqrt, net_fp16, \
-                                                                   packed, wimg, wimg_t);                               \
+        adam_refresh_kernel<WW, FROM_SLABS><<<blocks, threads, 0, s>>>(                                                 \
+            master, m, v, grads, slabs, n_slabs, loss_partials, n_loss, loss_out, n_mat, one_padded_in, unpadded_out,   \
+            grad_scale, lr, b1, b2, eps, bc1, bc2_sqrt, net_fp16, packed, wimg, wimg_t);                                \
         break;
     switch (width) {
         TNN_CASE(16) TNN_CASE(32) TNN_CASE(64) TNN_CASE(128)
@@ -190,6 +354,126 @@ static cudaError_t launch_adam_refresh(int width, float *master, float *m, float
     return cudaGetLastError();
 }
 
+
+// ---- data-parallel variant: gradient exchange through the peer windows inside the optimiser kernel
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// One block = 128 consecutive weights (slab order), (128, 8) threads when FROM_SLABS, (128, 1) otherwise.  Sum the
+// slabs (or take the already reduced gradient), store the 128 values into slot [seq & 1][rank] of every rank's
+// window, publish flag [seq & 1][rank][block] = seq on every rank, wait (bounded: `wait_ns`) for the same flag of
+// every source rank in this rank's own window, add the world contributions in rank order and run Adam + refresh on
+// the sum.  A wait that runs out sets *status and the block leaves its weights untouched.
+template <int W, bool FROM_SLABS>
+__global__ void __launch_bounds__(kSlabBlock *kSlabWays)
+dp_adam_refresh_kernel(PeerWindow pw, unsigned seq, unsigned long long wait_ns, int *__restrict__ status,
+                       float *__restrict__ master, float *__restrict__ m, float *__restrict__ v,
+                       float *__restrict__ grads, const float *__restrict__ slabs, int n_slabs,
+                       const float *__restrict__ loss_partials, int n_loss, float *__restrict__ loss_out, int n_mat,
+                       int one_padded_in, int unpadded_out, float grad_scale, float lr, float b1, float b2, float eps,
+                       float bc1, float bc2_sqrt, int net_fp16, __nv_bfloat16 *__restrict__ packed_out,
+                       __nv_bfloat16 *__restrict__ wimg, __nv_bfloat16 *__restrict__ wimg_t) {
+    __shared__ float part[FROM_SLABS ? kSlabWays : 1][kSlabBlock];
+    __shared__ int gave_up;
+    const int tid = threadIdx.x;
+    const int idx = blockIdx.x * kSlabBlock + tid;
+    const int per = n_mat * W * W; // a multiple of the block's 128 weights
+    const size_t parity = seq & 1u;
+    if (tid == 0 && threadIdx.y == 0) gave_up = 0;
+    if (FROM_SLABS && blockIdx.x == 0 && loss_out) loss_sum_block(loss_partials, n_loss, loss_out, part[0]);
+    const int l = idx / (W * W);
+    const int o = (idx / W) % W; // output feature
+    const int i = idx % W;       // input feature
+    const int pk = l * W * W + packed_coord_(i, o, W);
+    float g;
+    if constexpr (FROM_SLABS) {
+        g = slab_sum(slabs, n_slabs, per, idx, part);
+    } else {
+        g = grads[pk];
+    }
+    // push: thread (x, y) stores weight x into the windows of the ranks y, y + 8, ...: slot [parity][rank] of every
+    // window (this rank's own included, so that the sum below reads all ranks alike)
+    const size_t slot = (parity * pw.world + pw.rank) * kWinSlotFloats + idx;
+    if constexpr (FROM_SLABS) {
+        if (threadIdx.y == 0) part[0][tid] = g;
+        __syncthreads();
+        g = part[0][tid];
+    }
+    for (int r = threadIdx.y; r < pw.world; r += blockDim.y) pw.slots[r][slot] = g;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.y != 0) return;
+    if (tid < pw.world) {
+        const size_t f = (parity * pw.world + pw.rank) * kWinFlagsPerSlot + blockIdx.x;
+        st_release_sys(pw.flags[tid] + f, seq);
+        // wait for the same block of source rank `tid`
+        const unsigned *flag = pw.flags[pw.rank] + (parity * pw.world + tid) * kWinFlagsPerSlot + blockIdx.x;
+        const unsigned long long t0 = global_timer_ns();
+        bool ok = false;
+        for (unsigned it = 0; it < (1u << 30); ++it) {
+            if (ld_acquire_sys(flag) == seq) {
+                ok = true;
+                break;
+            }
+            if ((it & 15u) == 15u) {
+                if (global_timer_ns() - t0 > wait_ns) break;
+                __nanosleep(32);
+            }
+        }
+        if (!ok) {
+            gave_up = 1;
+            atomicOr(status, 2);
+        }
+    }
+    // (the threads with threadIdx.y == 0 are the first four warps of the block)
+    asm volatile("bar.sync 1, %0;" ::"n"(kSlabBlock) : "memory");
+    if (gave_up) return;
+    const float *own = pw.slots[pw.rank] + parity * pw.world * kWinSlotFloats + idx;
+    g = 0.0f;
+    for (int r = 0; r < pw.world; ++r) g += __ldcg(own + (size_t)r * kWinSlotFloats);
+    grads[pk] = g; // the sum over ranks (what the all-reduce path leaves here)
+    adam_and_refresh<W>(l, o, i, pk, g * grad_scale, master, m, v, n_mat, one_padded_in, unpadded_out, lr, b1, b2, eps,
+                        bc1, bc2_sqrt, net_fp16, packed_out, wimg, wimg_t);
+}
+
+template <bool FROM_SLABS>
+static cudaError_t launch_dp_adam_refresh(const PeerWindow &pw, unsigned seq, unsigned long long wait_ns, int *status,
+                                          int width, float *master, float *m, float *v, float *grads,
+                                          const float *slabs, int n_slabs, const float *loss_partials, int n_loss,
+                                          float *loss_out, int n_mat, int one_padded_in, int unpadded_out,
+                                          float grad_scale, int step, float lr, float b1, float b2, float eps,
+                                          int net_fp16, __nv_bfloat16 *packed, __nv_bfloat16 *wimg,
+                                          __nv_bfloat16 *wimg_t, cudaStream_t s) {
+    const int n = n_mat * width * width;
+    const int blocks = n / kWinBlock;
+    const dim3 threads(kSlabBlock, FROM_SLABS ? kSlabWays : 1);
+    const float bc1 = 1.0f - powf(b1, (float)step);
+    const float bc2_sqrt = sqrtf(1.0f - powf(b2, (float)step));
+    count_launch();
+#define TNN_CASE(WW)                                                                                                    \
+    case WW:                                                                                                            \
+        dp_adam_refresh_kernel<WW, FROM_SLABS><<<blocks, threads, 0, s>>>(                                            \
+            pw, seq, wait_ns, status, master, m, v, grads, slabs, n_slabs, loss_partials, n_loss, loss_out, n_mat,      \
+            one_padded_in, unpadded_out, grad_scale, lr, b1, b2, eps, bc1, bc2_sqrt, net_fp16, packed, wimg, wimg_t);   \
+        break;
+    switch (width) {
+        TNN_CASE(16) TNN_CASE(32) TNN_CASE(64) TNN_CASE(128)
+    default: return cudaErrorInvalidValue;
+    }
+#undef TNN_CASE
+    return cudaGetLastError();
+}
 } // namespace tnn
 
 // entry points of capi.cu that hand the raw per-CTA results to the trainer instead of reducing them
@@ -271,6 +555,10 @@ int tnn_dp_comm_create(const void *id128, int rank, int world, tnn_dp_comm **out
     c->rank = rank;
     c->world = world;
     c->owned = true;
+    if (int rc = setup_peer_window(c)) {
+        tnn_dp_comm_destroy(c);
+        return rc;
+    }
     *out = c;
     return 0;
 }
@@ -287,12 +575,17 @@ int tnn_dp_init(void *nccl_comm, tnn_dp_comm **out) {
     c->rank = rank;
     c->world = world;
     c->owned = false;
+    if (int rc = setup_peer_window(c)) {
+        tnn_dp_comm_destroy(c);
+        return rc;
+    }
     *out = c;
     return 0;
 }
 
 int tnn_dp_comm_destroy(tnn_dp_comm *c) {
     if (!c) return 0;
+    release_peer_window(c);
     if (c->owned && c->comm && nccl().ok) nccl().CommDestroy(c->comm);
     delete c;
     return 0;
@@ -300,6 +593,13 @@ int tnn_dp_comm_destroy(tnn_dp_comm *c) {
 
 int tnn_dp_rank(const tnn_dp_comm *c) { return c ? c->rank : 0; }
 int tnn_dp_world_size(const tnn_dp_comm *c) { return c ? c->world : 1; }
+
+int tnn_dp_peer_window(const tnn_dp_comm *c) { return (c && c->peer_ok && c->peer_enabled) ? 1 : 0; }
+int tnn_dp_set_peer_window(tnn_dp_comm *c, int enable) {
+    if (!c) return tnn::api_fail("communicator is null");
+    c->peer_enabled = enable != 0;
+    return 0;
+}
 
 int tnn_dp_allreduce_sum(tnn_dp_comm *c, float *buf, size_t n, void *stream) {
     if (!buf) return tnn::api_fail("null argument");
@@ -415,11 +715,28 @@ int tnn_trainer_optimizer_step(tnn_trainer *t, void *stream) {
     const int world = world_of(t);
     const float grad_scale = 1.0f / (t->loss_scale * (float)world);
     t->step += 1;
-    if (world > 1) {
+    const bool windowed = world > 1 && tnn_dp_peer_window(t->dp) && n->n_params <= kWinSlotFloats;
+    if (world > 1 && !windowed) {
         if (int rc = tnn_trainer_reduce(t, stream)) return rc;
         if (int rc = tnn_dp_allreduce_sum(t->dp, t->grads, n->n_params, stream)) return rc;
     }
-    if (world > 1 || t->reduced) {
+    if (windowed) {
+        // slab sum + exchange over the peer windows + Adam + refresh in one kernel
+        const unsigned seq = ++t->dp->seq;
+        if (t->reduced)
+            TNN_CUDA(tnn::launch_dp_adam_refresh<false>(t->dp->pw, seq, peer_wait_ns(), n->status, n->width, t->master,
+                                                        t->m, t->v, t->grads, nullptr, 0, nullptr, 0, nullptr, n->n_mat,
+                                                        n->one_padded_input(), n->output_width, grad_scale, t->step,
+                                                        t->lr, t->b1, t->b2, t->eps, n->fp16, n->packed, n->wimg,
+                                                        n->wimg_t, s));
+        else
+            TNN_CUDA(tnn::launch_dp_adam_refresh<true>(t->dp->pw, seq, peer_wait_ns(), n->status, n->width, t->master,
+                                                       t->m, t->v, t->grads, n->dw_slabs, t->n_slabs, n->loss_partials,
+                                                       t->n_loss, t->loss, n->n_mat, n->one_padded_input(),
+                                                       n->output_width, grad_scale, t->step, t->lr, t->b1, t->b2, t->eps,
+                                                       n->fp16, n->packed, n->wimg, n->wimg_t, s));
+        t->reduced = true;
+    } else if (world > 1 || t->reduced) {
         TNN_CUDA(tnn::launch_adam_refresh<false>(n->width, t->master, t->m, t->v, t->grads, nullptr, 0, nullptr, 0, nullptr,
                                                  n->n_mat, n->one_padded_input(), n->output_width, grad_scale, t->step,
                                                  t->lr, t->b1, t->b2, t->eps, n->fp16, n->packed, n->wimg, n->wimg_t, s));

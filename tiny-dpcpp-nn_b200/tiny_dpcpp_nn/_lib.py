@@ -78,6 +78,8 @@ _SIGNATURES = {
     "tnn_dp_comm_destroy": (_c.c_int, [_vp]),
     "tnn_dp_rank": (_c.c_int, [_vp]),
     "tnn_dp_world_size": (_c.c_int, [_vp]),
+    "tnn_dp_peer_window": (_c.c_int, [_vp]),
+    "tnn_dp_set_peer_window": (_c.c_int, [_vp, _c.c_int]),
     "tnn_dp_allreduce_sum": (_c.c_int, [_vp, _vp, _c.c_size_t, _vp]),
     "tnn_trainer_create": (_c.c_int, [_vp, _vp, _c.c_float, _c.c_float, _c.c_float, _c.c_float, _c.c_float,
                                       _c.POINTER(_vp)]),

@@ -6,8 +6,9 @@ backward_pass only ("no optimisation as we run benchmarking", trainer.h:39); its
 loops add torch's loss and torch.optim.Adam around the module.  This class is a thin front end of the
 library's tnn_trainer, the device-resident equivalent of that whole loop body: nothing leaves the GPU
 between the kernels, the parameter vector keeps the packed layout the reference exposes to optimisers
-(modules.py:169-175), and in data-parallel runs the only communication is one all-reduce of the fp32
-weight-gradient buffer (plus reduce-scatter / all-gather of a trainable encoding's table).
+(modules.py:169-175), and in data-parallel runs the only communication is the sum of the fp32
+weight-gradient buffer over the ranks - inside the optimiser kernel through peer windows when the ranks share a
+host, else one NCCL all-reduce - plus reduce-scatter / all-gather of a trainable encoding's table.
 """
 import ctypes
 
@@ -70,6 +71,16 @@ class Trainer:
             pass
 
     @property
+    def peer_window(self):
+        """True when the gradient exchange runs inside the optimiser kernel over peer windows (not NCCL)."""
+        return bool(self._comm) and bool(self._lib.tnn_dp_peer_window(self._comm))
+
+    def set_peer_window(self, on=True):
+        """To be called alike on every rank, between steps."""
+        if self._comm:
+            _lib.check(self._lib.tnn_dp_set_peer_window(self._comm, int(bool(on))))
+
+    @property
     def step(self):
         return int(self._lib.tnn_trainer_step_count(self._h))
 
@@ -102,7 +113,8 @@ class Trainer:
 
     def training_step(self, x, targets):
         """One call: fused forward / loss / backward kernel, then one kernel that finishes the gradient sums,
-        applies Adam and refreshes the weights (data parallel: with the all-reduce between two kernels)."""
+        applies Adam and refreshes the weights (data parallel: that kernel also exchanges the gradient through the
+        peer windows; without them the all-reduce runs between two kernels)."""
         self._check(x, targets)
         _lib.check(self._lib.tnn_trainer_training_step(self._h, _lib.dptr(x), _lib.dptr(targets), targets.shape[1],
                                                        x.shape[0], _lib.stream_ptr()))
