@@ -185,6 +185,27 @@ def test_c5_inference_and_stored_forward(tnn_lib):
     assert net.status() == 0
 
 
+@pytest.mark.parametrize("n_in, batch, shift", [(2, 128 * 9 + 40, 0), (3, 128 * 5 + 48, 0), (1, 136, 0), (4, 128 * 700, 0),
+                                                (2, 128 * 3 + 8, 1), (3, 24, 0), (7, 128 * 150 + 16, 0)])
+def test_folded_identity_forward_equals_the_two_module_path(tnn_lib, n_in, batch, shift):
+    """Inference (input tiles written by the issuer warps) and stored forward (by the producer warp) from fp32
+    coordinates give the bits of identity kernel -> network: ragged last tiles, fewer tiles than slots, a coordinate
+    pointer that is only 4-byte aligned, more coordinates than the encoder keeps in registers."""
+    rng = np.random.default_rng(40 + n_in)
+    w = O.bf16_round(synth.xavier_weights(N_MAT, W, 9))
+    net = tnn_lib.create_network(n_in, 3, NH, A["relu"], A["none"], W, "torch.bfloat16", True, seed=1)
+    net.set_params(torch.from_numpy(w.reshape(-1)).cuda(), False)
+    enc = tnn_lib.create_encoding("Identity", {"n_dims_to_encode": n_in, "scale": 1.5, "offset": -0.25}, W)
+    store = torch.from_numpy(rng.uniform(0, 1, batch * n_in + 4).astype(np.float32)).cuda()
+    q = store[shift:shift + batch * n_in].view(batch, n_in)
+    y_two = net.inference(enc.fwd(q, out_dtype=torch.bfloat16)).clone()
+    y = tnn_lib.nwe_inference(net, enc, q)
+    assert torch.equal(y, y_two)
+    out = tnn_lib.nwe_forward(net, enc, q)
+    assert torch.equal(out, y_two) and torch.equal(net.interm_fwd()[0], enc.fwd(q, out_dtype=torch.bfloat16))
+    assert net.status() == 0
+
+
 def test_narrow_targets_other_widths_and_alignments(tnn_lib):
     """Bulk-staged narrow targets at W = 32, an unaligned target pointer (falls back to per-thread loads), 63 of 64."""
     from tiny_dpcpp_nn.trainer import Trainer

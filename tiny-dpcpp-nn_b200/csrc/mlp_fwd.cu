@@ -116,6 +116,10 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
     const int L = n_mat - 1; // index of the output layer
     const uint32_t smem_base = ptx::smem_u32(smem);
     volatile uint32_t *abort_flag = &bars.abort_flag;
+    // Inference with a folded identity encoding: the input tile of a slot is written by that slot's issuer warp, in
+    // the shadow of its first epilogue step.  (One producer warp encoding for all slots needs about 1 800 cycles per
+    // tile - waits, conversions, stores and fences in sequence - which is the whole tile period of this kernel.)
+    const bool ISSUER_ENCODES = !STORE_ALL && NENC == 0 && enc.x != nullptr;
 
     // tiles handled by this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; local tile j runs in slot j % NSLOT
     const int my_tiles = (n_tiles > (int)blockIdx.x) ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
@@ -177,6 +181,8 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                                          a * T::ATOM_COLS, tile * T::TM, &bars.x_full[s]);
                 }
             }
+        } else if (ISSUER_ENCODES) {
+            // each slot's issuer warp writes its own input tiles (below)
         } else if (my_tiles > 0) {
             fill_tiles_with_ones<W>(smem + S::XBUF, NSLOT, lane, fp16);
             __syncwarp();
@@ -244,10 +250,24 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
             uint32_t ar_parity = 0; // parity of the next a_ready completion to wait for
             uint32_t xf_parity = 0;
             const int my_slot_tiles = (my_tiles - s + NSLOT - 1) / NSLOT;
+            // ISSUER_ENCODES: coordinates of this slot's next tile wait in registers
+            IdentityTileEncoder<W> encoder(enc, batch, lane, fp16);
+            uint8_t *const xt = smem + S::XBUF + s * T::ACT_BYTES;
+            if (ISSUER_ENCODES) {
+                encoder.fetch((size_t)(blockIdx.x + s * gridDim.x) * T::TM);
+                fill_tiles_with_ones<W>(xt, 1, lane, fp16);
+                __syncwarp();
+                encoder.store(xt);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (my_slot_tiles > 1) encoder.fetch((size_t)(blockIdx.x + (s + NSLOT) * gridDim.x) * T::TM);
+            }
             for (int t = 0; ok && t < my_slot_tiles; ++t) {
                 // layer 0: needs the input tile and (from the second tile on) the drained accumulator
-                ok = ptx::mbar_wait(&bars.x_full[s], xf_parity, abort_flag);
-                xf_parity ^= 1u;
+                if (!ISSUER_ENCODES) {
+                    ok = ptx::mbar_wait(&bars.x_full[s], xf_parity, abort_flag);
+                    xf_parity ^= 1u;
+                }
                 if (ok && t > 0) {
                     ok = ptx::mbar_wait(a_ready, ar_parity, abort_flag);
                     ar_parity ^= 1u;
@@ -277,6 +297,19 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                 }
                 __syncwarp();
                 ++wg;
+                if (ISSUER_ENCODES && t + 1 < my_slot_tiles) {
+                    // once layer 0 has read the input tile, write the slot's next one while the epilogue works
+                    if (!ptx::mbar_wait(&bars.x_empty[s], t & 1, abort_flag)) {
+                        if (lane == 0) atomicExch(status, KS_TIMEOUT_PRODUCER | s);
+                        ok = false;
+                        break;
+                    }
+                    encoder.store(xt);
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (t + 2 < my_slot_tiles)
+                        encoder.fetch((size_t)(blockIdx.x + (s + (t + 2) * NSLOT) * gridDim.x) * T::TM);
+                }
                 uint64_t w_desc = w_desc0;
                 for (int l = 1; l <= L; ++l) {
                     w_desc += T::WGT_UNITS;
