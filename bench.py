@@ -670,7 +670,7 @@ def run_gpu_arm(args):
             sweep = sweep_rows(L, torch, Trainer, batch, max(3, min(args.steps, 5)), timed_local, peaks)
     dom_r = rooflines[0]
     tps = TRAIN_DRAM_BYTES_PER_SAMPLE["c5"]
-    roofline = {"bound": "tensor", "kernel": "mlp_train_pipe_kernel<64, true> (identity fold, 3 narrow targets)",
+    roofline = {"bound": "tensor", "kernel": "mlp_train_pipe_kernel<64, narrow targets, bf16> (identity encoding folded in, 3 targets per sample)",
                 "achieved": dom_r["tflops"], "peak": peaks["tflops"],
                 "unit": "TFLOP/s", "frac": dom_r["frac_tensor"],
                 "traffic": tps * batch if tps else None, "traffic_source": TRAIN_DRAM_SOURCE if tps else None,
