@@ -138,6 +138,36 @@ def test_grid_backward_zero_upstream(tnn_lib):
     assert torch.equal(enc.get_params().reshape(-1), torch.ones(enc.n_params(), device="cuda"))
 
 
+@pytest.mark.parametrize("cfg", [
+    dict(n_dims_to_encode=3, n_levels=6, base_resolution=2, log2_hashmap_size=12),          # levels 0, 1 of 6
+    dict(n_dims_to_encode=3, n_levels=5, base_resolution=2, log2_hashmap_size=6),           # every level (hashed too)
+    dict(n_dims_to_encode=2, n_levels=6, n_features_per_level=4, base_resolution=2, log2_hashmap_size=10),
+    dict(n_dims_to_encode=3, n_levels=3, n_features_per_level=1, base_resolution=2, interpolation="Nearest"),
+])
+def test_grid_backward_with_coarse_levels_in_shared_memory(tnn_lib, cfg):
+    """At 2^16 samples the first levels of these small grids get thousands of contributions per entry: the backward
+    kernels accumulate them per CTA in shared memory and add each copy to the table gradient once.  Same sums as the
+    oracle's (1e-5 against its double accumulation), the fixed-point path still repeats bit for bit, with fp32 and
+    bf16 upstream gradients."""
+    g = O.Grid(**cfg)
+    F, NL = g.F, g.n_levels
+    padded = ((NL * F + 15) // 16) * 16
+    enc = tnn_lib.create_encoding("HashGrid", dict(otype="HashGrid", **cfg), padded, seed=3)
+    batch = 1 << 16
+    rng = np.random.default_rng(7)
+    x = rng.uniform(0, 1, (batch, g.D)).astype(np.float32)
+    dy = O.bf16_round(rng.uniform(-1, 1, (batch, padded)).astype(np.float32))
+    gref = g.backward(x, dy)
+    for dt in (torch.float32, torch.bfloat16):
+        for det in (False, True):
+            _, grads = enc.bwd_with_encoding_grad(_t(dy).to(dt), _t(x), False, False, deterministic=det)
+            ok, rel = O.within_tolerance(grads.cpu().numpy().reshape(-1), gref, 1e-5)
+            assert ok, (dt, det, rel)
+    _, g1 = enc.bwd_with_encoding_grad(_t(dy), _t(x), False, False, deterministic=True)
+    _, g2 = enc.bwd_with_encoding_grad(_t(dy), _t(x), False, False, deterministic=True)
+    assert torch.equal(g1, g2)
+
+
 def test_grid_benchmark_config_against_oracle(tnn_lib):
     """Benchmark grid (16 x 2, T = 2^19, base 16) at 2^16 samples, bf16 dy as the network hands it over."""
     g = O.Grid(n_dims_to_encode=3)

@@ -134,7 +134,9 @@ struct Optimizer {
     }
 };
 
-// One process per GPU: the communicator over which a Trainer averages its gradients.
+// One process per GPU: the communicator over which a Trainer averages its gradients.  On one host whose GPUs can map
+// each other's memory it also carries peer windows, through which the optimiser kernel exchanges the weight gradient
+// itself; otherwise the exchange is one ncclAllReduce per step.
 class DataParallel {
   public:
     static void unique_id(void *id128) { check(tnn_dp_get_unique_id(id128)); }
@@ -147,6 +149,8 @@ class DataParallel {
     DataParallel &operator=(const DataParallel &) = delete;
     int rank() const { return tnn_dp_rank(c_); }
     int world_size() const { return tnn_dp_world_size(c_); }
+    bool peer_window() const { return tnn_dp_peer_window(c_) != 0; }
+    void set_peer_window(bool on) { check(tnn_dp_set_peer_window(c_, on ? 1 : 0)); } // alike on every rank
     void allreduce_sum(float *buf, size_t n, void *stream) { check(tnn_dp_allreduce_sum(c_, buf, n, stream)); }
     tnn_dp_comm *handle() { return c_; }
 

@@ -365,4 +365,28 @@ cudaError_t launch_grid_bwd_input(const GridParams &p, const float *x, const flo
     TNN_GRID_DISPATCH(launch_bwd_input_df, p, x, table, dy, dy_dtype, dx, batch, stream);
 }
 
+uint32_t grid_coarse_levels(const GridParams &p, size_t batch, size_t acc_bytes, int *grid_out) {
+    static int sm_count[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (sm_count[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 0;
+        sm_count[dev] = n;
+    }
+    const int grid = sm_count[dev];
+    *grid_out = grid;
+    const size_t smem_budget = 160 * 1024;
+    const size_t contributions = batch << p.n_dims; // per level
+    uint32_t n = 0;
+    while (n < p.n_levels) {
+        const size_t entries_upto = p.offsets[n + 1];
+        const size_t entries_here = p.offsets[n + 1] - p.offsets[n];
+        if (entries_upto * p.features_per_level * acc_bytes > smem_budget) break;
+        if (contributions < 8 * (size_t)grid * entries_here) break;
+        ++n;
+    }
+    return n;
+}
+
 } // namespace tnn

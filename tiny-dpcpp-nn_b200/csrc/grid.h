@@ -42,6 +42,15 @@ cudaError_t launch_grid_fwd(const GridParams &p, const float *x, const float *ta
 cudaError_t launch_grid_bwd_input(const GridParams &p, const float *x, const float *table, const void *dy, int dy_dtype,
                                   float *dx, size_t batch, cudaStream_t stream);
 
+// Coarse levels of a backward pass: the first levels of a grid have few entries, each hit by thousands of samples, and
+// reductions into so few addresses queue up in L2.  The backward kernels therefore add the contributions of levels
+// [0, n) in shared-memory accumulators (one copy per CTA, one CTA per SM) and add each copy to the table gradient
+// once.  (Run beside the kernel of the other levels on a second stream the pair was slower than one after the other:
+// 0.55 against 0.50 ms at the benchmark grid, batch 2^20.)  Returns n: the leading levels whose accumulators (acc_bytes per table float) fit into shared memory together
+// and receive at least 8 contributions per accumulator copy and entry; *grid_out = CTAs to launch.
+constexpr int kGridCoarseThreads = 1024; // CTA of the coarse-level kernels (one per SM)
+uint32_t grid_coarse_levels(const GridParams &p, size_t batch, size_t acc_bytes, int *grid_out);
+
 // Scratch (bytes) the deterministic backward needs for `batch` samples.
 size_t grid_bwd_scratch_bytes(const GridParams &p, size_t batch);
 cudaError_t launch_grid_bwd(const GridParams &p, const float *x, const void *dy, int dy_dtype, float *grads,

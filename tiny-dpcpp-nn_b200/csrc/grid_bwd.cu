@@ -36,11 +36,11 @@ template <int F> __device__ __forceinline__ void red_add_entry(float *dst, const
 template <int D, int F, typename DyT>
 __global__ void __launch_bounds__(256) grid_bwd_atomic_kernel(const GridParams p, const float *__restrict__ x,
                                                                const DyT *__restrict__ dy, float *__restrict__ grads,
-                                                               size_t batch) {
+                                                               size_t batch, uint32_t first_level) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const uint32_t NL = p.n_levels;
+    const uint32_t NL = p.n_levels - first_level; // levels [first_level, n_levels): the coarser ones are privatised
     const size_t i = idx / NL;
-    const uint32_t level = (uint32_t)(idx % NL);
+    const uint32_t level = first_level + (uint32_t)(idx % NL);
     if (i >= batch) return;
     const float max_level = (p.max_level * (float)p.n_features) / (float)F;
     if ((float)level >= max_level + 1e-3f) return;
@@ -110,22 +110,81 @@ __global__ void __launch_bounds__(256) grid_bwd_atomic_kernel(const GridParams p
     }
 }
 
+// Levels [0, n_coarse): per-CTA accumulators in shared memory (see grid_coarse_levels), added to the table gradient
+// once per CTA.  One CTA per SM walks over (sample, level) pairs.
+template <int D, int F, typename DyT>
+__global__ void __launch_bounds__(kGridCoarseThreads) grid_bwd_coarse_kernel(const GridParams p, const float *__restrict__ x,
+                                                                const DyT *__restrict__ dy, float *__restrict__ grads,
+                                                                size_t batch, uint32_t n_coarse) {
+    extern __shared__ float coarse_acc[]; // [offsets[n_coarse] * F]
+    const uint32_t n_acc = p.offsets[n_coarse] * F;
+    for (uint32_t k = threadIdx.x; k < n_acc; k += blockDim.x) coarse_acc[k] = 0.0f;
+    __syncthreads();
+    const float max_level = (p.max_level * (float)p.n_features) / (float)F;
+    const size_t total = batch * n_coarse;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t i = idx / n_coarse;
+        const uint32_t level = (uint32_t)(idx % n_coarse);
+        if ((float)level >= max_level + 1e-3f) continue;
+        uint32_t ent[1 << D];
+        float wt[1 << D];
+        const int n = grid_corner_entries<D>(p, level, x + i * D, ent, wt);
+        float gr[F];
+#pragma unroll
+        for (int f = 0; f < F; ++f) gr[f] = (float)dy[i * p.padded_width + level * F + f];
+        float *al = coarse_acc + (size_t)p.offsets[level] * F;
+#pragma unroll
+        for (int c = 0; c < (1 << D); ++c) {
+            if (c < n) {
+#pragma unroll
+                for (int f = 0; f < F; ++f) atomicAdd(al + ent[c] * F + f, __fmul_rn(wt[c], gr[f]));
+            }
+        }
+    }
+    __syncthreads();
+    // (offsets[0] = 0: the coarse levels are the first n_acc floats of the gradient)
+    if constexpr (F % 2 == 0) {
+        for (uint32_t k = threadIdx.x; k < n_acc / 2; k += blockDim.x) {
+            const float v[2] = {coarse_acc[2 * k], coarse_acc[2 * k + 1]};
+            if (v[0] != 0.0f || v[1] != 0.0f) red_add_entry<2>(grads + 2 * (size_t)k, v);
+        }
+    } else {
+        for (uint32_t k = threadIdx.x; k < n_acc; k += blockDim.x)
+            if (coarse_acc[k] != 0.0f) atomicAdd(grads + k, coarse_acc[k]);
+    }
+}
+
+template <int D, int F, typename DyT>
+static cudaError_t launch_bwd_atomic_t(const GridParams &p, const float *x, const DyT *dy, float *grads, size_t batch,
+                                       cudaStream_t stream) {
+    int grid = 0;
+    const uint32_t n_coarse = grid_coarse_levels(p, batch, sizeof(float), &grid);
+    cudaError_t e;
+    if (n_coarse > 0) {
+        const size_t smem = (size_t)p.offsets[n_coarse] * F * sizeof(float);
+        auto kern = grid_bwd_coarse_kernel<D, F, DyT>;
+        if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+        count_launch();
+        kern<<<grid, kGridCoarseThreads, smem, stream>>>(p, x, dy, grads, batch, n_coarse);
+    }
+    if (n_coarse < p.n_levels) {
+        const size_t n = batch * (p.n_levels - n_coarse);
+        count_launch();
+        grid_bwd_atomic_kernel<D, F, DyT><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p, x, dy, grads, batch, n_coarse);
+    }
+    return cudaGetLastError();
+}
+
 template <int D, int F>
 static cudaError_t launch_bwd_atomic_df(const GridParams &p, const float *x, const void *dy, int dy_dtype, float *grads,
                                         size_t batch, cudaStream_t stream) {
     const size_t n_params = (size_t)p.offsets[p.n_levels] * F;
     cudaError_t e = cudaMemsetAsync(grads, 0, n_params * sizeof(float), stream); // grid.h:758-762
     if (e != cudaSuccess) return e;
-    const size_t n = batch * p.n_levels;
-    const unsigned blocks = (unsigned)((n + 255) / 256);
-    count_launch();
-    if (dy_dtype == 0)
-        grid_bwd_atomic_kernel<D, F, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p, x, (const __nv_bfloat16 *)dy, grads, batch);
-    else if (dy_dtype == 1)
-        grid_bwd_atomic_kernel<D, F, __half><<<blocks, 256, 0, stream>>>(p, x, (const __half *)dy, grads, batch);
-    else
-        grid_bwd_atomic_kernel<D, F, float><<<blocks, 256, 0, stream>>>(p, x, (const float *)dy, grads, batch);
-    return cudaGetLastError();
+    if (batch == 0) return cudaSuccess;
+    if (dy_dtype == 0) return launch_bwd_atomic_t<D, F>(p, x, (const __nv_bfloat16 *)dy, grads, batch, stream);
+    if (dy_dtype == 1) return launch_bwd_atomic_t<D, F>(p, x, (const __half *)dy, grads, batch, stream);
+    return launch_bwd_atomic_t<D, F>(p, x, (const float *)dy, grads, batch, stream);
 }
 
 cudaError_t launch_grid_bwd_det(const GridParams &p, const float *x, const void *dy, int dy_dtype, float *grads,

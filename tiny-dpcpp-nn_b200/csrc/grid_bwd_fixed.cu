@@ -64,11 +64,12 @@ __device__ __forceinline__ int fixed_exponent(uint32_t absmax_bits, size_t contr
 template <int D, int F, typename DyT>
 __global__ void __launch_bounds__(256) grid_bwd_fixed_kernel(const GridParams p, const float *__restrict__ x,
                                                               const DyT *__restrict__ dy, const FixedHeader *hdr,
-                                                              unsigned long long *__restrict__ acc, size_t batch) {
+                                                              unsigned long long *__restrict__ acc, size_t batch,
+                                                              uint32_t first_level) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const uint32_t NL = p.n_levels;
+    const uint32_t NL = p.n_levels - first_level; // levels [first_level, n_levels): the coarser ones are privatised
     const size_t i = idx / NL;
-    const uint32_t level = (uint32_t)(idx % NL);
+    const uint32_t level = first_level + (uint32_t)(idx % NL);
     if (i >= batch) return;
     const float max_level = (p.max_level * (float)p.n_features) / (float)F;
     if ((float)level >= max_level + 1e-3f) return;
@@ -123,6 +124,71 @@ __global__ void __launch_bounds__(256) grid_bwd_fixed_kernel(const GridParams p,
     for (int c = 0; c < (1 << D); ++c) add(ent[c], wt[c]);
 }
 
+// Levels [0, n_coarse): the same fixed-point sums in per-CTA shared-memory accumulators (see grid_coarse_levels),
+// added to the global accumulators once per CTA.  Integer sums: still independent of every order.
+template <int D, int F, typename DyT>
+__global__ void __launch_bounds__(kGridCoarseThreads) grid_bwd_fixed_coarse_kernel(const GridParams p, const float *__restrict__ x,
+                                                                      const DyT *__restrict__ dy, const FixedHeader *hdr,
+                                                                      unsigned long long *__restrict__ acc, size_t batch,
+                                                                      uint32_t n_coarse) {
+    extern __shared__ unsigned long long coarse_fixed[]; // [offsets[n_coarse] * F]
+    const uint32_t n_acc = p.offsets[n_coarse] * F;
+    for (uint32_t k = threadIdx.x; k < n_acc; k += blockDim.x) coarse_fixed[k] = 0ull;
+    __syncthreads();
+    const float max_level = (p.max_level * (float)p.n_features) / (float)F;
+    const float scale = ldexpf(1.0f, fixed_exponent(hdr->absmax_bits, batch << D));
+    const size_t total = batch * n_coarse;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t i = idx / n_coarse;
+        const uint32_t level = (uint32_t)(idx % n_coarse);
+        if ((float)level >= max_level + 1e-3f) continue;
+        uint32_t ent[1 << D];
+        float wt[1 << D];
+        const int n = grid_corner_entries<D>(p, level, x + i * D, ent, wt);
+        float gr[F];
+#pragma unroll
+        for (int f = 0; f < F; ++f) gr[f] = (float)dy[i * p.padded_width + level * F + f];
+        unsigned long long *al = coarse_fixed + (size_t)p.offsets[level] * F;
+#pragma unroll
+        for (int c = 0; c < (1 << D); ++c) {
+            if (c < n) {
+#pragma unroll
+                for (int f = 0; f < F; ++f) {
+                    const float prod = __fmul_rn(__fmul_rn(wt[c], gr[f]), scale);
+                    const long long q = fabsf(prod) <= 3.0e38f ? __float2ll_rn(prod) : 0ll;
+                    if (q != 0) atomicAdd(al + ent[c] * F + f, (unsigned long long)q);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (uint32_t k = threadIdx.x; k < n_acc; k += blockDim.x)
+        if (coarse_fixed[k] != 0ull) atomicAdd(acc + k, coarse_fixed[k]);
+}
+
+template <int D, int F, typename DyT>
+cudaError_t run_fixed_t(const GridParams &p, const float *x, const DyT *dy, FixedHeader *hdr, unsigned long long *acc,
+                        size_t batch, unsigned red_blocks, cudaStream_t stream) {
+    grid_absmax_kernel<DyT><<<red_blocks ? red_blocks : 1, 256, 0, stream>>>(dy, batch, p.n_features, p.padded_width, hdr);
+    count_launch();
+    int grid = 0;
+    const uint32_t n_coarse = grid_coarse_levels(p, batch, sizeof(unsigned long long), &grid);
+    cudaError_t e;
+    if (n_coarse > 0) {
+        const size_t smem = (size_t)p.offsets[n_coarse] * F * sizeof(unsigned long long);
+        auto kern = grid_bwd_fixed_coarse_kernel<D, F, DyT>;
+        if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return e;
+        count_launch();
+        kern<<<grid, kGridCoarseThreads, smem, stream>>>(p, x, dy, hdr, acc, batch, n_coarse);
+    }
+    if (n_coarse < p.n_levels) {
+        const size_t n = batch * (p.n_levels - n_coarse);
+        count_launch();
+        grid_bwd_fixed_kernel<D, F, DyT><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(p, x, dy, hdr, acc, batch, n_coarse);
+    }
+    return cudaGetLastError();
+}
+
 __global__ void __launch_bounds__(256) grid_fixed_finalize_kernel(const unsigned long long *__restrict__ acc,
                                                                    const FixedHeader *hdr, float *__restrict__ grads,
                                                                    size_t n, size_t contributions) {
@@ -143,22 +209,14 @@ cudaError_t run_fixed(const GridParams &p, const float *x, const void *dy, int d
     if (e != cudaSuccess) return e;
     const size_t n_dy = batch * (size_t)p.n_features;
     const unsigned red_blocks = (unsigned)((n_dy + 256 * 8 - 1) / (256 * 8) < 148 * 8 ? (n_dy + 256 * 8 - 1) / (256 * 8) : 148 * 8);
-    const size_t n = batch * p.n_levels;
-    const unsigned blocks = (unsigned)((n + 255) / 256);
-    count_launch(3);
-    if (dy_dtype == 0) {
-        grid_absmax_kernel<__nv_bfloat16><<<red_blocks ? red_blocks : 1, 256, 0, stream>>>(
-            (const __nv_bfloat16 *)dy, batch, p.n_features, p.padded_width, hdr);
-        grid_bwd_fixed_kernel<D, F, __nv_bfloat16><<<blocks, 256, 0, stream>>>(p, x, (const __nv_bfloat16 *)dy, hdr, acc, batch);
-    } else if (dy_dtype == 1) {
-        grid_absmax_kernel<__half><<<red_blocks ? red_blocks : 1, 256, 0, stream>>>((const __half *)dy, batch, p.n_features,
-                                                                                    p.padded_width, hdr);
-        grid_bwd_fixed_kernel<D, F, __half><<<blocks, 256, 0, stream>>>(p, x, (const __half *)dy, hdr, acc, batch);
-    } else {
-        grid_absmax_kernel<float><<<red_blocks ? red_blocks : 1, 256, 0, stream>>>((const float *)dy, batch, p.n_features,
-                                                                                   p.padded_width, hdr);
-        grid_bwd_fixed_kernel<D, F, float><<<blocks, 256, 0, stream>>>(p, x, (const float *)dy, hdr, acc, batch);
-    }
+    if (dy_dtype == 0)
+        e = run_fixed_t<D, F>(p, x, (const __nv_bfloat16 *)dy, hdr, acc, batch, red_blocks, stream);
+    else if (dy_dtype == 1)
+        e = run_fixed_t<D, F>(p, x, (const __half *)dy, hdr, acc, batch, red_blocks, stream);
+    else
+        e = run_fixed_t<D, F>(p, x, (const float *)dy, hdr, acc, batch, red_blocks, stream);
+    if (e != cudaSuccess) return e;
+    count_launch();
     grid_fixed_finalize_kernel<<<(unsigned)((n_params + 255) / 256), 256, 0, stream>>>(acc, hdr, grads, n_params,
                                                                                       batch << D);
     return cudaGetLastError();

@@ -170,4 +170,42 @@ __device__ __forceinline__ void grid_level_features(const GridCommon &gc, const 
         for (int f = 0; f < F; ++f) res_v[f] = fmaf(wt[c], vals[c][f], res_v[f]);
 }
 
+// The table entries one sample touches at one level and their interpolation weights, in the corner order of the
+// reference's kernels (include/encodings/grid.h:137-245): n = 2^D, or 1 with nearest-neighbour interpolation.
+template <int D>
+__device__ __forceinline__ int grid_corner_entries(const GridParams &p, uint32_t level, const float *__restrict__ xrow,
+                                                   uint32_t (&ent)[1 << D], float (&wt)[1 << D]) {
+    const uint32_t hsize = p.offsets[level + 1] - p.offsets[level];
+    const uint32_t res = p.resolution[level];
+    float w[D], xin[D];
+    uint32_t g[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) xin[d] = __ldg(xrow + d);
+    grid_pos<D>(xin, p.scale[level], p.interpolation, w, g);
+    if (p.interpolation == INTERP_NEAREST) {
+        ent[0] = grid_index<D>(p.grid_type, p.hash_type, hsize, res, g);
+        wt[0] = 1.0f;
+        return 1;
+    }
+#pragma unroll
+    for (int c = 0; c < (1 << D); ++c) {
+        float weight = 1.0f;
+        uint32_t gc[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            if ((c & (1 << d)) == 0) {
+                weight = __fmul_rn(weight, __fsub_rn(1.0f, w[d]));
+                gc[d] = g[d];
+            } else {
+                weight = __fmul_rn(weight, w[d]);
+                gc[d] = g[d] + 1u;
+            }
+        }
+        wt[c] = weight;
+        ent[c] = grid_index_raw<D>(p.grid_type, p.hash_type, hsize, res, gc);
+    }
+    grid_wrap<(1 << D)>(ent, hsize);
+    return 1 << D;
+}
+
 } // namespace tnn
