@@ -282,6 +282,7 @@ def grid_leg(L, torch, batch, steps, timed, n_levels=16, base_resolution=16):
     fwd = lambda: enc.fwd(pos)  # noqa: E731
     for name, fn in (("grid_fwd", fwd),
                      ("grid_bwd_deterministic", lambda: enc.bwd_with_encoding_grad(dy, pos, False, False, deterministic=True)),
+                     ("grid_bwd_segmented_atomic_free", lambda: enc.bwd_with_encoding_grad(dy, pos, False, False, deterministic=2)),
                      ("grid_bwd_atomic", lambda: enc.bwd_with_encoding_grad(dy, pos, False, False, deterministic=False))):
         for _ in range(2):
             fn()

@@ -179,10 +179,13 @@ int tnn_encoding_forward(tnn_encoding *enc, const float *x, void *out, int out_d
                          void *stream);
 /* EncodingModule::backward_pass(grad_output, input_from_fwd, false, false) - include/tnn_api.h:368-416
  * (kernel_grid_backward, grid.h:137-245).  grads: n_params fp32, overwritten.  deterministic == 0: fp32
- * reductions in memory like the reference (summation order not fixed); otherwise 64-bit fixed-point integer
+ * reductions in memory like the reference (summation order not fixed); 1: 64-bit fixed-point integer
  * reductions, whose result does not depend on the order and repeats bit for bit (an inf or NaN in dy then makes
- * every gradient of the call NaN).  grads must be 16-byte aligned.  The deterministic path keeps 8 bytes of
- * scratch per parameter in the handle, allocated (with a synchronisation of `stream`) at its first use. */
+ * every gradient of the call NaN); 2: no atomics at all - the contributions are written out sorted by table
+ * bucket and summed as a segmented reduction in a fixed order (bit-reproducible too, plain fp32 sums, about three
+ * times slower than 1 at the benchmark grid).  grads must be 16-byte aligned.  Modes 1 and 2 keep scratch in the
+ * handle (8 bytes per parameter; for 2 up to 1 GiB of records), allocated - with a synchronisation of `stream` -
+ * at first use and when a larger batch needs more. */
 int tnn_encoding_backward(tnn_encoding *enc, const float *x, const void *dy, int dy_dtype, float *grads,
                           size_t batch, int deterministic, void *stream);
 

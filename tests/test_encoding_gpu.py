@@ -73,16 +73,17 @@ def test_grid_forward_bit_exact_and_backward(tnn_lib, cfg):
         assert np.array_equal(out16, O.bf16_round(ref))
         dy = rng.uniform(-1, 1, (batch, padded)).astype(np.float32)
         gref = g.backward(x, dy)
-        for det in (False, True):
+        for det in (False, True, 2):  # fp32 atomics, fixed-point atomics, atomic-free segmented reduction
             _, grads = enc.bwd_with_encoding_grad(_t(dy), _t(x), False, False, deterministic=det)
             ok, rel = O.within_tolerance(grads.cpu().numpy().reshape(-1), gref, 1e-5)
             assert ok, (det, rel)
-        _, g1 = enc.bwd_with_encoding_grad(_t(dy), _t(x), False, False, deterministic=True)
-        _, g2 = enc.bwd_with_encoding_grad(_t(dy), _t(x), False, False, deterministic=True)
-        assert torch.equal(g1, g2)
+        for det in (True, 2):
+            _, g1 = enc.bwd_with_encoding_grad(_t(dy), _t(x), False, False, deterministic=det)
+            _, g2 = enc.bwd_with_encoding_grad(_t(dy), _t(x), False, False, deterministic=det)
+            assert torch.equal(g1, g2)
 
 
-@pytest.mark.parametrize("deterministic", [False, True])
+@pytest.mark.parametrize("deterministic", [False, True, 2])
 @pytest.mark.parametrize("dy_dtype", [torch.float32, torch.bfloat16])
 def test_grid_backward_hand_checked_fixture(tnn_lib, deterministic, dy_dtype):
     """The hand-derived gradient of tests/golden/grid_backward_handcheck.json (see make_grid_backward_fixture.py) on

@@ -11,7 +11,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libtnn_b200.so")
-SOURCES = ["capi.cu", "mlp_fwd.cu", "mlp_bwd.cu", "mlp_train.cu", "mlp_train_pipe.cu", "elementwise.cu", "l2_static.cu", "trainer.cu", "grid.cu", "grid_bwd.cu", "grid_bwd_fixed.cu"]
+SOURCES = ["capi.cu", "mlp_fwd.cu", "mlp_bwd.cu", "mlp_train.cu", "mlp_train_pipe.cu", "elementwise.cu", "l2_static.cu", "trainer.cu", "grid.cu", "grid_bwd.cu", "grid_bwd_fixed.cu", "grid_bwd_segmented.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

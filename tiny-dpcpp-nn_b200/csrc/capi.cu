@@ -798,7 +798,8 @@ int tnn_encoding_backward(tnn_encoding *e, const float *x, const void *dy, int d
         return fail("dy must be fp32, bf16 or fp16");
     if (batch > 0xFFFFFFFFull / 8) return fail("batch too large");
     if (reinterpret_cast<uintptr_t>(grads) % 16 != 0) return fail("grads must be 16-byte aligned (vector reductions)");
-    size_t need = deterministic ? tnn::grid_bwd_scratch_bytes(e->gp, batch) : 0;
+    if (deterministic < 0 || deterministic > 2) return fail("deterministic must be 0, 1 or 2");
+    size_t need = tnn::grid_bwd_scratch_bytes(e->gp, batch, deterministic);
     if (need > e->scratch_bytes) {
         TNN_CUDA(cudaStreamSynchronize(s));
         cudaFree(e->scratch);
@@ -808,7 +809,7 @@ int tnn_encoding_backward(tnn_encoding *e, const float *x, const void *dy, int d
         e->scratch_bytes = need;
     }
     TNN_CUDA(tnn::launch_grid_bwd(e->gp, x, dy, dy_dtype, grads, batch,
-                                  deterministic ? e->scratch : nullptr, e->scratch_bytes, s));
+                                  deterministic ? e->scratch : nullptr, e->scratch_bytes, s, deterministic));
     return 0;
     TNN_GUARD_END
 }

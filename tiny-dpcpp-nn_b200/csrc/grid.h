@@ -51,9 +51,14 @@ cudaError_t launch_grid_bwd_input(const GridParams &p, const float *x, const flo
 constexpr int kGridCoarseThreads = 1024; // CTA of the coarse-level kernels (one per SM)
 uint32_t grid_coarse_levels(const GridParams &p, size_t batch, size_t acc_bytes, int *grid_out);
 
-// Scratch (bytes) the deterministic backward needs for `batch` samples.
-size_t grid_bwd_scratch_bytes(const GridParams &p, size_t batch);
+// Backward modes: reductions in memory with fp32 atomics (the reference's structure, order not fixed), with 64-bit
+// fixed-point integer atomics (order-independent: deterministic), or an atomic-free segmented reduction
+// (deterministic; see grid_bwd_segmented.cu).
+enum GridBackwardMode : int { GRID_BWD_ATOMIC = 0, GRID_BWD_FIXED = 1, GRID_BWD_SEGMENTED = 2 };
+// Scratch (bytes) a backward pass of `mode` needs for `batch` samples (0 for GRID_BWD_ATOMIC).
+size_t grid_bwd_scratch_bytes(const GridParams &p, size_t batch, int mode = GRID_BWD_FIXED);
 cudaError_t launch_grid_bwd(const GridParams &p, const float *x, const void *dy, int dy_dtype, float *grads,
-                            size_t batch, void *scratch, size_t scratch_bytes, cudaStream_t stream);
+                            size_t batch, void *scratch, size_t scratch_bytes, cudaStream_t stream,
+                            int mode = GRID_BWD_FIXED /* ignored (atomic) when scratch is null */);
 
 } // namespace tnn

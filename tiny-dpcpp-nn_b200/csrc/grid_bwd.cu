@@ -190,8 +190,13 @@ static cudaError_t launch_bwd_atomic_df(const GridParams &p, const float *x, con
 cudaError_t launch_grid_bwd_det(const GridParams &p, const float *x, const void *dy, int dy_dtype, float *grads,
                                 size_t batch, void *scratch, size_t scratch_bytes, cudaStream_t stream);
 
+cudaError_t launch_grid_bwd_segmented(const GridParams &p, const float *x, const void *dy, int dy_dtype, float *grads,
+                                      size_t batch, void *scratch, size_t scratch_bytes, cudaStream_t stream);
+
 cudaError_t launch_grid_bwd(const GridParams &p, const float *x, const void *dy, int dy_dtype, float *grads,
-                            size_t batch, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
+                            size_t batch, void *scratch, size_t scratch_bytes, cudaStream_t stream, int mode) {
+    if (scratch && mode == GRID_BWD_SEGMENTED)
+        return launch_grid_bwd_segmented(p, x, dy, dy_dtype, grads, batch, scratch, scratch_bytes, stream);
     if (scratch) return launch_grid_bwd_det(p, x, dy, dy_dtype, grads, batch, scratch, scratch_bytes, stream);
     const int key = (int)p.n_dims * 16 + (int)p.features_per_level;
     switch (key) {

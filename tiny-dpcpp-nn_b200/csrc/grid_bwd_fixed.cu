@@ -224,7 +224,11 @@ cudaError_t run_fixed(const GridParams &p, const float *x, const void *dy, int d
 
 } // namespace
 
-size_t grid_bwd_scratch_bytes(const GridParams &p, size_t) {
+size_t grid_bwd_segmented_scratch_bytes(const GridParams &p, size_t batch);
+
+size_t grid_bwd_scratch_bytes(const GridParams &p, size_t batch, int mode) {
+    if (mode == GRID_BWD_ATOMIC) return 0;
+    if (mode == GRID_BWD_SEGMENTED) return grid_bwd_segmented_scratch_bytes(p, batch);
     return sizeof(FixedHeader) + (size_t)p.offsets[p.n_levels] * p.features_per_level * sizeof(unsigned long long);
 }
 

@@ -350,7 +350,8 @@ class EncodingModule:
 
     #: default summation of the table gradient: False = floating-point reductions in memory like the reference's
     #: kernel_grid_backward (grid.h:177-183, order not fixed, fastest); True = 64-bit fixed-point accumulation whose
-    #: result repeats bit for bit (about 3x slower at the benchmark grid)
+    #: result repeats bit for bit (about 3x slower at the benchmark grid); 2 = atomic-free segmented reduction in a
+    #: fixed order (bit-reproducible as well, slower again)
     deterministic_backward = False
 
     def bwd_with_encoding_grad(self, grad_output, input_from_fwd, pack_gradient, get_dl_dinput, deterministic=None):
@@ -369,7 +370,7 @@ class EncodingModule:
         grads = torch.empty((self.n_params(), 1), dtype=torch.float32, device=grad_output.device)
         check(self._lib.tnn_encoding_backward(self._h, dptr(input_from_fwd), dptr(grad_output),
                                               _dtype_code(grad_output.dtype), dptr(grads), batch,
-                                              int(bool(deterministic)), stream_ptr()))
+                                              int(deterministic), stream_ptr()))
         return None, grads
 
     def bwd_input(self, grad_output, input_from_fwd):
