@@ -339,7 +339,8 @@ int tnn_trainer_forward_backward(tnn_trainer *trainer, const void *x, const floa
 int tnn_trainer_reduce(tnn_trainer *trainer, void *stream);
 /* optimizer.step() + Module.set_params(): gradient sum over the ranks when a communicator is set (inside the
  * optimiser kernel with peer windows, else ncclAllReduce), Adam on the master copy, refresh of the 16-bit weights
- * the kernels read. */
+ * the kernels read.  Refused (error code) on a stream that is being captured into a CUDA graph: the step count
+ * and the exchange number are host state passed as kernel arguments, which a replay would not advance. */
 int tnn_trainer_optimizer_step(tnn_trainer *trainer, void *stream);
 /* forward_backward + optimizer_step: one call enqueues the whole loop body. */
 int tnn_trainer_training_step(tnn_trainer *trainer, const void *x, const float *targets, int n_targets,

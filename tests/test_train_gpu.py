@@ -114,3 +114,32 @@ def test_trainer_reduces_the_loss(tnn_lib):
         last = tr.training_step(xt, tt).item()
     assert net.status() == 0
     assert last < 0.7 * first, (first, last)
+
+
+def test_optimizer_step_refuses_graph_capture_but_forward_backward_is_capturable(tnn_lib):
+    """The fused forward / loss / backward call holds no host state and replays from a CUDA graph; the optimiser step
+    passes the step count to its kernel and says no on a capturing stream instead of baking a stale count in."""
+    from tiny_dpcpp_nn.trainer import Trainer
+
+    W, nh, batch = 64, 2, 128 * 9
+    x = synth.uniform_inputs(batch, W, seed=3)
+    t = synth.uniform_inputs(batch, W, seed=4)
+    net = tnn_lib.create_network(W, W, nh, A["relu"], A["none"], W, "torch.bfloat16", True, seed=0)
+    tr = Trainer(net)
+    xt, tt = _bf16(x), torch.from_numpy(t).cuda()
+    tr.forward_backward(xt, tt)
+    want = tr.grads.clone()
+    tr.grads.zero_()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        tr.forward_backward(xt, tt)  # warm-up on the capturing stream
+        with torch.cuda.graph(graph, stream=side):
+            tr.forward_backward(xt, tt)
+            with pytest.raises(tnn_lib.TnnError, match="CUDA graph"):
+                tr.optimizer_step()
+    tr.grads.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(tr.grads, want) and net.status() == 0

@@ -180,7 +180,10 @@ int setup_peer_window(tnn_dp_comm *c) {
     mine.ok = ok ? 1 : 0;
 
     WinExchange *dev = nullptr; // [world] gathered records, then this rank's own
-    TNN_CUDA(cudaMalloc(&dev, (world + 1) * sizeof(WinExchange)));
+    if (cudaError_t ea = cudaMalloc(&dev, (world + 1) * sizeof(WinExchange)); ea != cudaSuccess) {
+        release_peer_window(c);
+        return tnn::api_fail(std::string("peer windows: ") + cudaGetErrorString(ea), 2);
+    }
     std::vector<WinExchange> all(world);
     int rc = 0;
     cudaError_t e = cudaMemcpy(dev + world, &mine, sizeof(mine), cudaMemcpyHostToDevice);
@@ -711,6 +714,12 @@ int tnn_trainer_reduce(tnn_trainer *t, void *stream) {
 int tnn_trainer_optimizer_step(tnn_trainer *t, void *stream) {
     if (!t) return tnn::api_fail("trainer is null");
     cudaStream_t s = (cudaStream_t)stream;
+    // the step count (Adam's bias correction) and the exchange number of the peer windows are host state that goes
+    // into the kernels' arguments: a captured graph would replay stale values
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &capturing) == cudaSuccess && capturing != cudaStreamCaptureStatusNone)
+        return tnn::api_fail("tnn_trainer_optimizer_step cannot be captured into a CUDA graph: step count and "
+                             "exchange number are arguments of its kernels");
     tnn_network *n = t->net;
     const int world = world_of(t);
     const float grad_scale = 1.0f / (t->loss_scale * (float)world);
