@@ -13,7 +13,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liboracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "libref_mlp.so")
-REFERENCE_ROOT = os.environ.get("TNN_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: TNN_REFERENCE_ROOT, else a directory "reference" beside this repository
+REFERENCE_ROOT = os.environ.get("TNN_REFERENCE_ROOT",
+                                os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 
 def _run(cmd):
