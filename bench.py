@@ -320,14 +320,14 @@ def grid_rooflines(grid_ms, grid_batch, peaks):
     return out
 
 
-def sweep_rows(L, torch, Trainer, batch, steps, timed, peaks):
+def sweep_rows(L, torch, Trainer, batch, steps, timed, peaks, widths=(16, 32, 64, 128), layers=(2, 4, 8)):
     """The reference's sweep (benchmarks/benchmark_all.cpp:53-104): widths 16..128, 2 / 4 / 8 hidden layers."""
     rows = []
-    for width in (16, 32, 64, 128):
+    for width in widths:
         gen = torch.Generator(device="cuda").manual_seed(100)
         x = (torch.rand((batch, width), device="cuda", generator=gen) * 2 - 1).to(torch.bfloat16)
         targets = torch.rand((batch, width), device="cuda", generator=gen) * 2 - 1
-        for n_hidden in (2, 4, 8):
+        for n_hidden in layers:
             net = L.create_network(width, width, n_hidden, 0, 8, width, "torch.bfloat16", True, seed=0)
             net.set_params(torch.from_numpy(xavier_weights(n_hidden + 1, width, 2).reshape(-1)).cuda(), False)
             tr = Trainer(net)
@@ -417,7 +417,9 @@ def run_only(args):
         out["c4_training_samples_per_s"] = batch / out["c4_trainer_step_ms"] * 1e3
         out["kernel_status"] = net.status()
     elif args.only == "sweep":
-        out["sweep"] = sweep_rows(L, torch, Trainer, batch, args.steps, timed, peaks)
+        out["sweep"] = sweep_rows(L, torch, Trainer, batch, args.steps, timed, peaks,
+                                  widths=(args.sweep_width,) if args.sweep_width else (16, 32, 64, 128),
+                                  layers=(args.sweep_layers,) if args.sweep_layers else (2, 4, 8))
     elif args.only == "c5":
         net, enc, batches = make_c5(L, torch, batch, 0, 1)
         net.set_params(torch.from_numpy(c5_weights().reshape(-1)).cuda(), False)
@@ -792,6 +794,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--brief", action="store_true", help="skip the hash-grid and sweep legs")
     ap.add_argument("--grid-levels", type=int, default=16, help="levels of the grid of `--only grid`")
+    ap.add_argument("--sweep-width", type=int, default=0, help="`--only sweep`: this width alone (16, 32, 64, 128)")
+    ap.add_argument("--sweep-layers", type=int, default=0, help="`--only sweep`: this number of hidden layers alone")
     ap.add_argument("--grid-base-resolution", type=int, default=16, help="coarsest resolution of that grid")
     ap.add_argument("--only", choices=["train", "infer", "c5", "grid", "sweep", "c4"],
                     help="run one part only: a single kernel (profiler captures), the width / depth sweep, or the "

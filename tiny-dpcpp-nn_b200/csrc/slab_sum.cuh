@@ -17,8 +17,17 @@ __device__ __forceinline__ float slab_sum(const float *__restrict__ slabs, int n
                                           float (*part)[kSlabBlock]) {
     float g = 0.0f;
     if (idx < per) {
-#pragma unroll 4
-        for (int s = threadIdx.y; s < n_slabs; s += kSlabWays) g += slabs[(size_t)s * per + idx];
+        // eight loads in flight per thread; the additions keep the slab order (absent slabs add an exact zero)
+        for (int s0 = threadIdx.y; s0 < n_slabs; s0 += 8 * kSlabWays) {
+            float t[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int s = s0 + k * kSlabWays;
+                t[k] = s < n_slabs ? __ldcg(slabs + (size_t)s * per + idx) : 0.0f;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) g += t[k];
+        }
     }
     part[threadIdx.y][threadIdx.x] = g;
     __syncthreads();
