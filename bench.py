@@ -612,6 +612,10 @@ def run_gpu_arm(args):
         L.check(lib.tnn_network_backward(net64._h, L.dptr(dy), L.dptr(interm), L.dptr(grads), L.DTYPE_FP32, 1, None,
                                          None, batch, s))
 
+    def k_bwd_from_input():
+        L.check(lib.tnn_network_backward_from_input(net64._h, L.dptr(x64), L.dptr(dy), L.dptr(grads), L.DTYPE_FP32, 1,
+                                                    None, batch, s))
+
     def k_loss():
         L.check(lib.tnn_l2_loss(L.dptr(interm[N_MAT]), L.dptr(t64), WIDTH, None, L.dptr(dy), batch, WIDTH, 1.0,
                                 L.dptr(loss1), s))
@@ -621,7 +625,7 @@ def run_gpu_arm(args):
     kernel_ms = {}
     for name, fn in (("mlp_train_fused_c5", k_train_c5), ("mlp_inference_c5", infer), ("mlp_train_fused_64x64", k_train_64),
                      ("train_step_64x64", step64), ("mlp_inference_64x64", infer64), ("mlp_fwd_store", k_fwd),
-                     ("l2_loss", k_loss), ("mlp_bwd", k_bwd)):
+                     ("l2_loss", k_loss), ("mlp_bwd", k_bwd), ("mlp_bwd_from_input", k_bwd_from_input)):
         for _ in range(2):
             fn()
         kernel_ms[name] = timed(fn, args.steps) / args.steps
@@ -642,6 +646,9 @@ def run_gpu_arm(args):
         roof("mlp_inference_64x64", FLOPS_FWD, BYTES_INFER_64, "x in, y out"),
         roof("mlp_fwd_store", FLOPS_FWD, act_bytes * (N_MAT + 2), "unfused path: x in, input copy + every activation out"),
         roof("mlp_bwd", FLOPS_BWD, act_bytes * (N_MAT + 1), "unfused path: dy + a_L..a_0 in"),
+        roof("mlp_bwd_from_input", FLOPS_TRAIN - 2 * WIDTH * WIDTH, act_bytes * 2,
+             "backward pass of the autograd module: x and dy in, hidden activations recomputed on chip "
+             "(forward without the output layer + backward flop)"),
         roof("l2_loss", 0, act_bytes * 2 + WIDTH * 4, "unfused path: y in, dy out, targets in"),
     ]
     swiftnet = {"workload": f"swiftnet_w{WIDTH}_l{N_HIDDEN}_in64_out64_batch2^{args.log2_batch}: 64 bf16 inputs, 64 fp32 targets",

@@ -101,6 +101,17 @@ int tnn_network_forward(tnn_network *net, const void *x, void *y, void *interm_f
 int tnn_network_backward(tnn_network *net, const void *dy, const void *interm_fwd, void *grads,
                          int grads_dtype, int pack_transpose, void *dx, void *interm_bwd,
                          size_t batch, void *stream);
+/* The same backward pass without stored activations: Module::backward_pass (include/tnn_api.h:561-620) given the
+ * input x of the forward pass instead of interm_fwd.  One fused kernel recomputes the activations tile by tile on
+ * chip (they never reach HBM), applies dy and runs the delta chain and the weight-gradient reduction: a training
+ * loop then needs tnn_network_inference for its forward pass, not tnn_network_forward with its
+ * (n_hidden_layers + 2) x batch x width store.  x, dy: batch x width of the network's type; grads, pack_transpose,
+ * dl_dinput (optional, batch x width of the network's type) as in tnn_network_backward; 16-byte aligned pointers.
+ * Supported where the network fits the fused training kernel (widths 16 / 32 / 64, e.g. up to 5 hidden layers at
+ * width 64): ask tnn_network_backward_from_input_supported first (1 / 0). */
+int tnn_network_backward_from_input_supported(const tnn_network *net);
+int tnn_network_backward_from_input(tnn_network *net, const void *x, const void *dy, void *grads, int grads_dtype,
+                                    int pack_transpose, void *dl_dinput, size_t batch, void *stream);
 /* Trainer<T>::training_step - include/trainer.h:23-46 (forward_pass then backward_pass), with the L2
  * loss of include/losses/l2.h:19-41 evaluated in between as the reference's training loops do:
  * forward, loss, backward and the weight-gradient reduction in one pass.  x: batch x width bf16;

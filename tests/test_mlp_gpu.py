@@ -68,6 +68,28 @@ def test_forward_backward_matrix(tnn_lib, W, nh, act, oact):
             _check(ibg[l], ib[l])
             _check(g[l], gr[l])
         _check(dxg.float().cpu().numpy().reshape(batch, W), dx)
+        # the same backward pass from the input alone: one fused kernel recomputes the activations on chip
+        assert net.recompute_supported()
+        dxr, gr2 = net.bwd_from_input(xt, _bf16(dy), False, True, grads_dtype=torch.float32)
+        assert net.status() == 0
+        gr2 = gr2.cpu().numpy().reshape(n_mat, W, W)
+        for l in range(n_mat):
+            _check(gr2[l], gr[l])
+        _check(dxr.float().cpu().numpy().reshape(batch, W), dx)
+        _, gp = net.bwd_from_input(xt, _bf16(dy), True, False, grads_dtype=torch.float32)
+        assert np.allclose(O.unpack_weights(gp.cpu().numpy().reshape(-1), n_mat, W).reshape(n_mat, W, W),
+                           np.transpose(gr2, (0, 2, 1)), rtol=0, atol=0)
+
+
+def test_backward_from_input_limits(tnn_lib):
+    """Networks that do not fit the fused training kernel say so (and the stored-activation path serves them)."""
+    w, _ = synth.mlp_case(128, 2, 8, w_seed=2, x_seed=1)
+    assert not _net(tnn_lib, 128, 2, "relu", "none", w).recompute_supported()
+    w, x = synth.mlp_case(64, 8, 64, w_seed=2, x_seed=1)
+    net = _net(tnn_lib, 64, 8, "relu", "none", w)
+    assert not net.recompute_supported()
+    with pytest.raises(tnn_lib.TnnError, match="does not fit the fused kernel"):
+        net.bwd_from_input(_bf16(x), _bf16(x), False, False)
 
 
 @pytest.mark.parametrize("W,nh,variant,act,oact", [

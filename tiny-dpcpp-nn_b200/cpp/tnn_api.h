@@ -66,6 +66,14 @@ template <typename T = bf16> class Network {
         check(tnn_network_backward(h_, grad_output, interm_fwd, grads, grads_dtype, pack_transpose_gradient ? 1 : 0,
                                    dl_dinput, interm_bwd, batch, stream));
     }
+    // backward_pass from the input of the forward pass instead of stored activations (recomputed on chip by one fused
+    // kernel); supported where the network fits the fused training kernel
+    bool backward_from_input_supported() const { return tnn_network_backward_from_input_supported(h_) != 0; }
+    void backward_pass_from_input(const void *x, const void *grad_output, void *grads, int grads_dtype,
+                                  bool pack_transpose_gradient, void *dl_dinput, size_t batch, void *stream) {
+        check(tnn_network_backward_from_input(h_, x, grad_output, grads, grads_dtype, pack_transpose_gradient ? 1 : 0,
+                                              dl_dinput, batch, stream));
+    }
     int sync_status(void *stream) { // non-zero: a bounded device-side wait gave up, results are invalid
         int st = 0;
         check(tnn_network_sync_status(h_, &st, stream));

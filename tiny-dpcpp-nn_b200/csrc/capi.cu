@@ -506,6 +506,56 @@ int tnn_network_train_step(tnn_network *n, const void *x, const float *targets, 
                            nullptr, loss_sum, stream);
 }
 
+int tnn_network_backward_from_input_supported(const tnn_network *n) {
+    return (n && !(n->variant & (16 | 64)) && tnn::mlp_train_pipe_fits(n->width, n->n_mat, 3)) ? 1 : 0;
+}
+
+int tnn_network_backward_from_input(tnn_network *n, const void *x, const void *dy, void *grads, int grads_dtype,
+                                    int pack_transpose, void *dl_dinput, size_t batch, void *stream) {
+    TNN_GUARD_BEGIN
+    if (!n) return fail("network is null");
+    if (!x || !dy || !grads) return fail("x, dy and grads are required");
+    if (grads_dtype != TNN_DTYPE_BF16 && grads_dtype != TNN_DTYPE_FP16 && grads_dtype != TNN_DTYPE_FP32)
+        return fail("grads must be bf16, fp16 or fp32");
+    if (batch == 0) return fail("batch_size == 0");
+    if (batch % 8 != 0) return fail("Batch size is not divisible by 8.");
+    if (!tnn_network_backward_from_input_supported(n))
+        return fail("this network does not fit the fused kernel: use tnn_network_forward + tnn_network_backward");
+    for (const void *ptr : {x, dy, (const void *)dl_dinput})
+        if (reinterpret_cast<uintptr_t>(ptr) % 16 != 0) return fail("x, dy and dl_dinput must be 16-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    tnn::TrainLaunch p{};
+    make_act_tmap(&p.tm_x, x, batch, n->width, 1);
+    make_act_tmap(&p.tm_tgt, dy, batch, n->width, 1);
+    p.tgt_mode = 3;
+    p.wimg = n->wimg;
+    p.n_targets = n->width;
+    if (dl_dinput) {
+        p.want_dx = 1;
+        make_act_tmap(&p.tm_dx, dl_dinput, batch, n->width, 1);
+    }
+    p.dw_partials = n->dw_slabs;
+    p.max_slabs = n->max_slabs;
+    p.loss_partials = nullptr;
+    p.batch = batch;
+    p.width = n->width;
+    p.n_mat = n->n_mat;
+    p.act = n->act;
+    p.out_act = n->out_act;
+    p.fp16 = n->fp16;
+    p.loss_scale = 1.0f;
+    p.n_sm = n->n_sm;
+    p.status = n->status;
+    p.stream = s;
+    TNN_CUDA(tnn::launch_mlp_train_pipe(p));
+    float *gf = grads_dtype == TNN_DTYPE_FP32 ? (float *)grads : nullptr;
+    __nv_bfloat16 *gb = grads_dtype != TNN_DTYPE_FP32 ? (__nv_bfloat16 *)grads : nullptr;
+    TNN_CUDA(tnn::launch_reduce_dw(n->dw_slabs, p.grid_out, n->n_mat, n->width, pack_transpose, 1.0f, gf, gb,
+                                   grads_dtype == TNN_DTYPE_FP16, s, nullptr, 0, nullptr));
+    return 0;
+    TNN_GUARD_END
+}
+
 size_t tnn_network_workspace_bytes(const tnn_network *n, size_t batch) { return n ? unfused_workspace_bytes(n, batch) : 0; }
 
 int tnn_network_set_workspace(tnn_network *n, void *workspace, size_t bytes) {

@@ -74,7 +74,8 @@ struct TrainLaunch {
     CUtensorMap tm_tgt;     // the same targets as a tiled map, box 128 x 32 fp32 (valid when tgt_mode == 1)
     // how the pipelined kernel fetches targets: 0 = per-thread loads, 1 = TMA boxes (n_targets == width),
     // 2 = one bulk copy of the tile's 128 * n_targets contiguous floats (n_targets < width); 1 and 2 need
-    // 16-byte aligned targets
+    // 16-byte aligned targets.  3 = no targets and no loss: tm_tgt maps the upstream gradient dL/dy ([batch][W] of the
+    // network's type, like tm_x) and the pass is the backward pass of the network with its forward recomputed on chip
     int tgt_mode;
     EncodedInput enc;       // enc.x != nullptr: the input tile is produced in the kernel from fp32 coordinates
     int want_dx;            // also compute dL/dinput (batch x width, the network's type) and store it through tm_dx
@@ -97,5 +98,7 @@ struct TrainLaunch {
 cudaError_t launch_mlp_train(TrainLaunch &p);
 // Same pass with the forward stage of one tile overlapped with the backward stage of the previous one.
 cudaError_t launch_mlp_train_pipe(TrainLaunch &p);
+// Whether that kernel takes a network of this shape (tgt_mode as in TrainLaunch).
+bool mlp_train_pipe_fits(int width, int n_mat, int tgt_mode);
 
 } // namespace tnn

@@ -35,7 +35,7 @@ template <int W, int TGT> struct PipeSmem {
     using T = Tile<W>;
     // delta tiles first (see mlp_train.cu: the M = 64 weight-gradient GEMM over-reads past them for W < 64)
     static constexpr int DL = 0;                                  // delta_L: forward stage -> backward stage
-    static constexpr int NB = TGT ? 2 : 1;                        // tiles in front of the ping-pong buffers
+    static constexpr int NB = (TGT == 1 || TGT == 2) ? 2 : 1;     // tiles in front of the ping-pong buffers
     static constexpr int TGT_BOX_BYTES = 128 * 128;               // one box: 128 rows x 32 fp32
     static constexpr int TGT_BOXES = W / 32;
     __host__ __device__ static constexpr int DP(int p) { return (NB + p) * T::ACT_BYTES; } // delta ping-pong
@@ -127,7 +127,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
         bars.abort_flag = 0;
         ptx::fence_barrier_init();
         if (!enc.x) ptx::prefetch_tmap(&tm_x);
-        if constexpr (TGT == 1) ptx::prefetch_tmap(&tm_tgt);
+        if constexpr (TGT == 1 || TGT == 3) ptx::prefetch_tmap(&tm_tgt);
         if constexpr (DX) ptx::prefetch_tmap(&tm_dx);
     }
     if (warp == 1) {
@@ -171,6 +171,12 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 ptx::mbar_arrive_expect_tx(&bars.tgt_full, (uint32_t)(S::TGT_BOXES * S::TGT_BOX_BYTES));
                 for (int bx = 0; bx < S::TGT_BOXES; ++bx)
                     ptx::tma_load_2d(smem + S::DL + bx * S::TGT_BOX_BYTES, &tm_tgt, bx * 32, tile * T::TM, &bars.tgt_full);
+            } else if constexpr (TGT == 3) {
+                // the upstream gradient dL/dy of the tile lands where delta_L lives, already in operand layout
+                ptx::mbar_arrive_expect_tx(&bars.tgt_full, T::ACT_BYTES);
+                for (int at = 0; at < T::KATOMS; ++at)
+                    ptx::tma_load_2d(smem + S::DL + at * T::ACT_ATOM_BYTES, &tm_tgt, at * T::ATOM_COLS, tile * T::TM,
+                                     &bars.tgt_full);
             }
         };
         if (!enc.x) {
@@ -249,7 +255,9 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     ptx::mma_commit(&bars.x_empty[b]);
                 }
                 __syncwarp();
-                for (int l = 1; l <= L; ++l) {
+                // (with dL/dy given and no output activation the output layer is not evaluated: delta_L is dL/dy)
+                const int l_last = (TGT == 3 && out_act == ACT_NONE) ? L - 1 : L;
+                for (int l = 1; l <= l_last; ++l) {
                     if (!ptx::mbar_wait(&bars.f_ready, fr_parity, abort_flag)) {
                         if (lane == 0) atomicExch(status, KS_TIMEOUT_MMA | 2 | (l << 4));
                         ok = false;
@@ -447,7 +455,14 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
             if (!ok) break;
             // ---- output layer + L2 loss.  The target slice is requested before the wait for the last GEMM.
             float tg[CPT];
-            if constexpr (TGT != 0) {
+            if constexpr (TGT == 3) {
+                // dL/dy is given: the staged tile IS delta_L (times act_out'(y), applied in place below); every thread
+                // touches its own chunks only, so there is no hand-shake before the first write
+                if (!wait_u(&bars.tgt_full, t & 1, 8)) {
+                    ok = false;
+                    break;
+                }
+            } else if constexpr (TGT != 0) {
                 if (!wait_u(&bars.tgt_full, t & 1, 8)) {
                     ok = false;
                     break;
@@ -489,18 +504,20 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 for (int q = 0; q < CPT; ++q)
                     tg[q] = (row_valid && col0 + q < n_targets) ? __ldg(targets + grow * n_targets + col0 + q) : 0.0f;
             }
-            if (!wait_u(&bars.accf_full, af_parity, 3)) {
-                ok = false;
-                break;
-            }
-            af_parity ^= 1u;
-            ptx::tc_fence_after_sync();
             uint32_t v[CPT];
-            load_acc(v);
-            // the accumulator is in registers: layer 0 of the next tile may run under the loss arithmetic
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&bars.f_ready);
+            if (!(TGT == 3 && out_act == ACT_NONE)) { // (else: no output-layer GEMM was issued, see the issuer)
+                if (!wait_u(&bars.accf_full, af_parity, 3)) {
+                    ok = false;
+                    break;
+                }
+                af_parity ^= 1u;
+                ptx::tc_fence_after_sync();
+                load_acc(v);
+                // the accumulator is in registers: layer 0 of the next tile may run under the loss arithmetic
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&bars.f_ready);
+            }
             if constexpr (TGT == 0) { // delta_L of the previous tile must have been consumed by its two GEMMs
                 if (t > 0 && !wait_u(&bars.dl_free, (t - 1) & 1, 4)) {
                     ok = false;
@@ -508,9 +525,33 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 }
             }
             uint8_t *dst = smem + S::DL;
+            if constexpr (TGT == 3) {
+                // delta_L = dL/dy (.) act_out'(y), in place (rows past the batch were zero-filled by the copy)
+                if (out_act != ACT_NONE) {
+                    dispatch_act_t<HF_>(out_act, [&](auto tag) {
+                        constexpr int ACT = decltype(tag)::value;
+                        constexpr bool HF = decltype(tag)::half;
+#pragma unroll
+                        for (int ch = 0; ch < CPT / 8; ++ch) {
+                            uint4 *cell = reinterpret_cast<uint4 *>(dst + chunk_at(ch));
+                            const uint4 d = *cell;
+                            const uint32_t din[4] = {d.x, d.y, d.z, d.w};
+                            uint32_t o[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const uint32_t y16 = act_pack_t<ACT, HF>(__uint_as_float(v[ch * 8 + 2 * q]),
+                                                                         __uint_as_float(v[ch * 8 + 2 * q + 1]));
+                                o[q] = act_bwd_pack_t<ACT, HF>(ptx::lo_f32<HF>(din[q]), ptx::hi_f32<HF>(din[q]), y16);
+                            }
+                            *cell = make_uint4(o[0], o[1], o[2], o[3]);
+                        }
+                    });
+                }
+            }
             // rows past the end of the batch contribute neither loss nor gradient
             const float gscale = row_valid ? loss_scale * 2.0f * inv_n : 0.0f;
             float sq = 0.0f;
+            if constexpr (TGT != 3)
             dispatch_act_t<HF_>(out_act, [&](auto tag) {
                 constexpr int ACT = decltype(tag)::value;
                     constexpr bool HF = decltype(tag)::half;
@@ -786,7 +827,7 @@ template <int W, int TGT, bool HF_, int MINB, bool DX> static cudaError_t launch
     if (grid == 0) return cudaSuccess;
     const float inv_n = 1.0f / ((float)p.batch * (float)W);
     count_launch();
-    kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, TGT == 1 ? p.tm_tgt : p.tm_x, DX ? p.tm_dx : p.tm_x, p.wimg, p.targets, p.n_targets, p.dw_partials, p.loss_partials,
+    kern<<<grid, S::THREADS, smem, p.stream>>>(p.tm_x, (TGT == 1 || TGT == 3) ? p.tm_tgt : p.tm_x, DX ? p.tm_dx : p.tm_x, p.wimg, p.targets, p.n_targets, p.dw_partials, p.loss_partials,
                                                p.batch, n_tiles, p.n_mat, p.act, p.out_act, p.loss_scale, inv_n,
                                                p.enc, tmem_cols, p.status);
     return cudaGetLastError();
@@ -796,10 +837,32 @@ template <int W, int TGT> static cudaError_t launch_pipe_w(TrainLaunch &p) {
     return p.fp16 ? launch_pipe_t<W, TGT, true>(p) : launch_pipe_t<W, TGT, false>(p);
 }
 
+// Whether the pipelined kernel takes a network of this shape with targets / upstream gradients fetched by `tgt_mode`.
+template <int W> static bool pipe_fits_w(int n_mat, int tgt_mode) {
+    using T = Tile<W>;
+    const int nb = (tgt_mode == 1 || tgt_mode == 2) ? 2 : 1;
+    const size_t smem = (size_t)(nb + 4 + n_mat) * T::ACT_BYTES + (size_t)n_mat * T::WGT_BYTES + 1024;
+    return smem <= kPipeSmemLimit && 2 * W + n_mat * W <= 512 && n_mat <= kPipeMaxMat;
+}
+bool mlp_train_pipe_fits(int width, int n_mat, int tgt_mode) {
+    switch (width) {
+    case 16: return pipe_fits_w<16>(n_mat, tgt_mode);
+    case 32: return pipe_fits_w<32>(n_mat, tgt_mode);
+    case 64: return pipe_fits_w<64>(n_mat, tgt_mode);
+    default: return false;
+    }
+}
+
 cudaError_t launch_mlp_train_pipe(TrainLaunch &p) {
     // staged targets (tgt_mode 1: TMA boxes, 2: one bulk copy of narrow rows) need one more tile of shared memory:
     // without room for it the per-thread loads remain
     cudaError_t e = cudaErrorInvalidConfiguration;
+    if (p.tgt_mode == 3) { // dL/dy given instead of targets (backward pass that recomputes the forward)
+        if (p.width == 16) return launch_pipe_w<16, 3>(p);
+        if (p.width == 32) return launch_pipe_w<32, 3>(p);
+        if (p.width == 64) return launch_pipe_w<64, 3>(p);
+        return e;
+    }
     if (p.width == 16) return launch_pipe_w<16, 0>(p); // 64-byte target rows: read directly
     if (p.width != 64 && p.width != 32) return e;
     const bool w64 = p.width == 64;

@@ -41,6 +41,8 @@ _SIGNATURES = {
     "tnn_network_backward": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _vp, _vp, _c.c_size_t, _vp]),
     "tnn_network_train_step": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _c.c_size_t, _c.c_float, _vp, _c.c_int, _c.c_int,
                                           _vp, _vp]),
+    "tnn_network_backward_from_input_supported": (_c.c_int, [_vp]),
+    "tnn_network_backward_from_input": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _vp, _c.c_size_t, _vp]),
     "tnn_network_workspace_bytes": (_c.c_size_t, [_vp, _c.c_size_t]),
     "tnn_network_set_workspace": (_c.c_int, [_vp, _vp, _c.c_size_t]),
     "tnn_network_with_encoding_workspace_bytes": (_c.c_size_t, [_vp, _c.c_size_t]),
@@ -262,6 +264,25 @@ class NetworkModule:
                                              _dtype_code(grads_dtype), int(bool(pack_gradient)), dptr(dx), dptr(ibwd),
                                              batch, stream_ptr()))
         self._interm_bwd = ibwd
+        return (dx.reshape(-1, 1) if dx is not None else None), grads
+
+    def recompute_supported(self):
+        """True when bwd_from_input can serve this network (it fits the fused training kernel)."""
+        return bool(self._lib.tnn_network_backward_from_input_supported(self._h))
+
+    def bwd_from_input(self, x, grad_output, pack_gradient, get_dl_dinput, grads_dtype=None):
+        """backward_pass given the input of the forward pass instead of stored activations: one fused kernel
+        recomputes them on chip.  Returns (dL/dinput or None, grads) like bwd_no_encoding_grad."""
+        grads_dtype = grads_dtype or self.dtype
+        self._check_input(x)
+        if grad_output.shape != x.shape or grad_output.dtype != self.dtype:
+            raise TnnError(f"grad_output must be {tuple(x.shape)} {self.dtype}")
+        batch = x.shape[0]
+        grads = torch.empty((self.n_params(), 1), dtype=grads_dtype, device=x.device)
+        dx = torch.empty((batch, self.width), dtype=self.dtype, device=x.device) if get_dl_dinput else None
+        check(self._lib.tnn_network_backward_from_input(self._h, dptr(x), dptr(grad_output), dptr(grads),
+                                                        _dtype_code(grads_dtype), int(bool(pack_gradient)), dptr(dx),
+                                                        batch, stream_ptr()))
         return (dx.reshape(-1, 1) if dx is not None else None), grads
 
     def bwd_with_encoding_grad(self, grad_output, input_from_fwd, pack_gradient, get_dl_dinput):

@@ -63,6 +63,11 @@ class _module_function(torch.autograd.Function):
             output = native_tnn_module.fwd(input, out_dtype=info["encoding_out_dtype"])
         elif info["is_in_eval_mode"]:
             output = native_tnn_module.inference(input)
+        elif getattr(native_tnn_module, "recompute_supported", lambda: False)():
+            # the backward pass recomputes the activations on chip from `input` (one fused kernel), so the forward
+            # pass stores none of them: the (n_hidden_layers + 2) x batch x width block is neither written nor read
+            output = native_tnn_module.inference(input)
+            ctx.recompute = True
         else:
             output = native_tnn_module.fwd(input)
         if batch_size > 0:
@@ -98,8 +103,12 @@ class _module_function(torch.autograd.Function):
                     # include/tnn_api.h:380-382)
                     input_grad = ctx.native_tnn_module.bwd_input(dy, input)
             else:
-                input_grad, grad = ctx.native_tnn_module.bwd_no_encoding_grad(
-                    doutput.to(ctx.native_tnn_module.dtype), True, True, grads_dtype=torch.float32)
+                if getattr(ctx, "recompute", False):
+                    input_grad, grad = ctx.native_tnn_module.bwd_from_input(
+                        input, doutput.to(ctx.native_tnn_module.dtype), True, True, grads_dtype=torch.float32)
+                else:
+                    input_grad, grad = ctx.native_tnn_module.bwd_no_encoding_grad(
+                        doutput.to(ctx.native_tnn_module.dtype), True, True, grads_dtype=torch.float32)
                 if input_grad is not None:
                     input_grad = input_grad.reshape(batch_size, -1).to(input.dtype)
         grad = None if grad is None else (grad.reshape(params.shape).to(params.dtype) / loss_scale)
