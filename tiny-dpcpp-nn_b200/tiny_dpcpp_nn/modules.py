@@ -117,15 +117,23 @@ class _module_function(torch.autograd.Function):
 
 
 class _fused_module_function(torch.autograd.Function):
-    """Encoding + network as one operator: the forward pass is a single kernel (identity encoding folded into the
-    first-layer load, hash grid gathered by extra warps of the network kernel); the backward pass runs the network's
-    backward kernel and, for an encoding with parameters, scatters the network's dL/dinput into the table gradient.
-    Same parameter contract as _module_function; the positions get no gradient."""
+    """Encoding + network as one operator.  Inference is a single library call (identity encoding folded into the
+    first-layer load).  Training keeps only the encoded rows between the passes: forward = encoding kernel + inference
+    kernel, backward = one fused kernel that recomputes the network's activations on chip and yields the weight
+    gradients and dL/d(encoded rows), which an encoding with parameters scatters into its table gradient (networks
+    outside the fused kernel's limits store their activations instead).  Same parameter contract as _module_function;
+    the positions get no gradient."""
 
     @staticmethod
     def forward(ctx, native_network, native_encoding, input, net_params, enc_params, info, loss_scale):
+        ctx.encoded = None
         if info["is_in_eval_mode"]:
             output = nwe_inference(native_network, native_encoding, input)
+        elif native_network.recompute_supported():
+            # training forward without stored activations: the encoded rows (128 bytes per sample at width 64) are all
+            # the backward pass needs, it recomputes the network's activations on chip
+            ctx.encoded = native_encoding.fwd(input, out_dtype=native_network.dtype)
+            output = native_network.inference(ctx.encoded)
         else:
             output = nwe_forward(native_network, native_encoding, input)
         ctx.save_for_backward(input, net_params, enc_params)
@@ -145,7 +153,12 @@ class _fused_module_function(torch.autograd.Function):
         want_enc = ctx.native_encoding.n_params() > 0 and ctx.needs_input_grad[4]
         enc_grad = None
         with torch.no_grad():
-            dx, grad = ctx.native_network.bwd_no_encoding_grad(doutput, True, want_enc, grads_dtype=torch.float32)
+            if ctx.encoded is not None:
+                dx, grad = ctx.native_network.bwd_from_input(ctx.encoded, doutput, True, want_enc,
+                                                             grads_dtype=torch.float32)
+                ctx.encoded = None
+            else:
+                dx, grad = ctx.native_network.bwd_no_encoding_grad(doutput, True, want_enc, grads_dtype=torch.float32)
             if want_enc:
                 _, enc_grad = ctx.native_encoding.bwd_with_encoding_grad(dx.reshape(input.shape[0], width), input, False,
                                                                          False)
