@@ -232,6 +232,33 @@ def test_narrow_targets_other_widths_and_alignments(tnn_lib):
         _check(tr.grads.cpu().numpy(), packed, what=f"W{width} nt{nt}")
 
 
+@pytest.mark.parametrize("out_w, nt, oact, width", [(8, 8, "none", 64), (8, 5, "relu", 64), (9, 9, "none", 64),
+                                                     (3, 3, "relu", 64), (1, 1, "none", 32), (8, 3, "none", 32)])
+def test_few_live_output_columns(tnn_lib, out_w, nt, oact, width):
+    """Networks with at most 8 real outputs and a linear or ReLU output layer: the padded output columns are exactly
+    zero and the fused kernel evaluates the loss on the first 8-column chunk of a row only (9 outputs: all columns).
+    Loss and gradients as the oracle computes them over all columns."""
+    from tiny_dpcpp_nn.trainer import Trainer
+
+    nh, batch = 2, 128 * 5 + 24
+    w, x = synth.mlp_case(width, nh, batch, w_seed=11)
+    w[-1][:, out_w:] = 0.0  # what Network::set_weights_matrices makes of the padded output columns
+    t = synth.uniform_inputs(batch, nt, seed=3)
+    net = tnn_lib.create_network(width, out_w, nh, A["relu"], A[oact], width, "torch.bfloat16", True, seed=1)
+    net.set_params(torch.from_numpy(w.reshape(-1)).cuda(), False)
+    tr = Trainer(net)
+    loss = tr.forward_backward(_bf16(x), torch.from_numpy(t).cuda()).item()
+    assert net.status() == 0
+    interm = O.mlp_forward(x, w, nh + 1, width, "relu", oact, bf16=True)
+    tpad = np.zeros((batch, width), np.float32)
+    tpad[:, :nt] = t
+    vals, dy = O.l2_loss(interm[-1], tpad, 1.0, bf16_grads=True)
+    _, gr, _ = O.mlp_backward(dy, interm, w, nh + 1, width, "relu", oact, bf16=True, want_dx=False)
+    packed = O.pack_weights(np.ascontiguousarray(np.transpose(gr, (0, 2, 1))).astype(np.float32), nh + 1, width)
+    assert abs(loss - float(vals.astype(np.float64).sum())) <= 1e-4 * abs(loss)
+    _check(tr.grads.cpu().numpy(), packed, what=f"out {out_w} targets {nt} {oact}")
+
+
 def test_workspace_lent_by_the_caller(tnn_lib):
     """The three-kernel path on a caller-owned workspace: no allocation inside the step; too small a workspace is an
     error with a message, not a reallocation."""

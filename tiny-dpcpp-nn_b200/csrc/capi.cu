@@ -447,6 +447,11 @@ static int train_step_impl(tnn_network *n, const void *x, const tnn::EncodedInpu
         p.n_targets = n_targets;
         const bool aligned = reinterpret_cast<uintptr_t>(targets) % 16 == 0;
         p.tgt_mode = (!aligned || n->width < 32) ? 0 : (n_targets == n->width ? 1 : 2);
+        // output columns past the targets and past the network's real outputs hold act_out(0) under zero weights:
+        // exactly zero for a linear or ReLU output, so they carry neither loss nor gradient
+        const int live_out = n_targets > n->output_width ? n_targets : n->output_width;
+        if (p.tgt_mode == 2 && live_out <= 8 && (n->out_act == tnn::ACT_NONE || n->out_act == tnn::ACT_RELU))
+            p.tgt_mode = 4;
         if (p.tgt_mode == 1) make_tgt_tmap(&p.tm_tgt, targets, batch, n->width);
         if (dx) {
             p.want_dx = 1;

@@ -74,7 +74,8 @@ struct TrainLaunch {
     CUtensorMap tm_tgt;     // the same targets as a tiled map, box 128 x 32 fp32 (valid when tgt_mode == 1)
     // how the pipelined kernel fetches targets: 0 = per-thread loads, 1 = TMA boxes (n_targets == width),
     // 2 = one bulk copy of the tile's 128 * n_targets contiguous floats (n_targets < width); 1 and 2 need
-    // 16-byte aligned targets.  3 = no targets and no loss: tm_tgt maps the upstream gradient dL/dy ([batch][W] of the
+    // 16-byte aligned targets.  4 = 2 for a network whose output columns from the 9th on are exactly zero (they are
+    // weight padding, have no target, and act_out(0) = 0): only the first 8 columns take part in the loss.  3 = no targets and no loss: tm_tgt maps the upstream gradient dL/dy ([batch][W] of the
     // network's type, like tm_x) and the pass is the backward pass of the network with its forward recomputed on chip
     int tgt_mode;
     EncodedInput enc;       // enc.x != nullptr: the input tile is produced in the kernel from fp32 coordinates

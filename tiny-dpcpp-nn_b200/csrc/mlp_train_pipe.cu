@@ -27,15 +27,17 @@ namespace tnn {
 
 constexpr int kPipeMaxMat = 12; // upper bound of the barrier array; what fits is decided by shared memory and TMEM columns
 
-// TGT (0, 1, 2): how a tile's fp32 targets reach the loss step.  0: per-thread global loads.  1: full-width rows
-// (128 x W fp32, twice the bytes of a bf16 tile) staged by TMA boxes.  2: narrow rows (n_targets < W: 128 * n_targets
-// contiguous floats) staged by one plain bulk copy.  Staged targets go into the delta_L
-// buffer plus one more tile right behind it; the loss step pulls its slice into registers before delta_L is written.
+// TGT: how a tile's fp32 targets reach the loss step.  0: per-thread global loads.  1: full-width rows (128 x W fp32,
+// twice the bytes of a bf16 tile) staged by TMA boxes.  2: narrow rows (n_targets < W: 128 * n_targets contiguous
+// floats) staged by one plain bulk copy.  4: like 2 for a network with at most 8 live output columns (only the first
+// 8-column chunk of a row is evaluated in the loss step).  3: no targets - the upstream gradient dL/dy is given.
+// Staged targets go into the delta_L buffer plus one more tile right behind it; the loss step pulls its slice into
+// registers before delta_L is written.
 template <int W, int TGT> struct PipeSmem {
     using T = Tile<W>;
     // delta tiles first (see mlp_train.cu: the M = 64 weight-gradient GEMM over-reads past them for W < 64)
     static constexpr int DL = 0;                                  // delta_L: forward stage -> backward stage
-    static constexpr int NB = (TGT == 1 || TGT == 2) ? 2 : 1;     // tiles in front of the ping-pong buffers
+    static constexpr int NB = (TGT == 1 || TGT == 2 || TGT == 4) ? 2 : 1; // tiles in front of the ping-pong buffers
     static constexpr int TGT_BOX_BYTES = 128 * 128;               // one box: 128 rows x 32 fp32
     static constexpr int TGT_BOXES = W / 32;
     __host__ __device__ static constexpr int DP(int p) { return (NB + p) * T::ACT_BYTES; } // delta ping-pong
@@ -161,7 +163,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
             return true;
         };
         auto targets_issue = [&](int tile) {
-            if constexpr (TGT == 2) {
+            if constexpr (TGT == 2 || TGT == 4) {
                 const size_t row0 = (size_t)tile * T::TM;
                 const uint32_t rows = (uint32_t)(batch - row0 < (size_t)T::TM ? batch - row0 : (size_t)T::TM);
                 const uint32_t bytes = rows * (uint32_t)n_targets * 4u; // rows % 8 == 0: a multiple of 16
@@ -467,7 +469,7 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     ok = false;
                     break;
                 }
-                if constexpr (TGT == 2) {
+                if constexpr (TGT == 2 || TGT == 4) {
                     // row-major rows of n_targets floats; columns past them (and rows past the batch) compare with 0
                     const float *src = reinterpret_cast<const float *>(smem + S::DL) + row * n_targets;
 #pragma unroll
@@ -557,6 +559,17 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     constexpr bool HF = decltype(tag)::half;
 #pragma unroll
                 for (int ch = 0; ch < CPT / 8; ++ch) {
+                    if constexpr (TGT == 4) {
+                        // At most 8 live output columns (the 3 of an RGB regression): the others hold act_out(0) = 0
+                        // under zero weight columns and have no target, so their loss and gradient are exactly zero
+                        // and only the first chunk of a row is evaluated.  (Decided at compile time: the same test
+                        // as a run-time branch cost more than the arithmetic it saves, this kernel sits at its
+                        // register limit.)
+                        if (ch > 0 || col0 != 0) {
+                            *reinterpret_cast<uint4 *>(dst + chunk_at(ch)) = make_uint4(0u, 0u, 0u, 0u);
+                            continue;
+                        }
+                    }
                     uint32_t o[4];
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
@@ -840,7 +853,7 @@ template <int W, int TGT> static cudaError_t launch_pipe_w(TrainLaunch &p) {
 // Whether the pipelined kernel takes a network of this shape with targets / upstream gradients fetched by `tgt_mode`.
 template <int W> static bool pipe_fits_w(int n_mat, int tgt_mode) {
     using T = Tile<W>;
-    const int nb = (tgt_mode == 1 || tgt_mode == 2) ? 2 : 1;
+    const int nb = (tgt_mode == 1 || tgt_mode == 2 || tgt_mode == 4) ? 2 : 1;
     const size_t smem = (size_t)(nb + 4 + n_mat) * T::ACT_BYTES + (size_t)n_mat * T::WGT_BYTES + 1024;
     return smem <= kPipeSmemLimit && 2 * W + n_mat * W <= 512 && n_mat <= kPipeMaxMat;
 }
@@ -868,6 +881,7 @@ cudaError_t launch_mlp_train_pipe(TrainLaunch &p) {
     const bool w64 = p.width == 64;
     if (p.tgt_mode == 1) e = w64 ? launch_pipe_w<64, 1>(p) : launch_pipe_w<32, 1>(p);
     if (p.tgt_mode == 2) e = w64 ? launch_pipe_w<64, 2>(p) : launch_pipe_w<32, 2>(p);
+    if (p.tgt_mode == 4) e = w64 ? launch_pipe_w<64, 4>(p) : launch_pipe_w<32, 4>(p);
     if (e == cudaErrorInvalidConfiguration) e = w64 ? launch_pipe_w<64, 0>(p) : launch_pipe_w<32, 0>(p);
     return e;
 }
