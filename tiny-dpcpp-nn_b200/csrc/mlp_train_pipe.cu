@@ -474,9 +474,10 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                     const float *src = reinterpret_cast<const float *>(smem + S::DL) + row * n_targets;
 #pragma unroll
                     for (int q = 0; q < CPT; ++q) tg[q] = 0.0f;
+                    constexpr int kTgtCols = (TGT == 4) ? 8 : CPT; // TGT == 4: targets in the first 8 columns only
                     if (col0 < n_targets && row_valid) {
 #pragma unroll
-                        for (int q = 0; q < CPT; ++q)
+                        for (int q = 0; q < kTgtCols; ++q)
                             if (col0 + q < n_targets) tg[q] = src[col0 + q];
                     }
                 } else {
@@ -514,7 +515,17 @@ mlp_train_pipe_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_con
                 }
                 af_parity ^= 1u;
                 ptx::tc_fence_after_sync();
-                load_acc(v);
+                if constexpr (TGT == 4) { // only the first 8 columns of a row are looked at (see below)
+                    if (col0 == 0) {
+                        uint32_t v8[8];
+                        ptx::tmem_ld8(acc_addr, v8);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) v[k] = v8[k];
+                    }
+                } else {
+                    load_acc(v);
+                }
                 // the accumulator is in registers: layer 0 of the next tile may run under the loss arithmetic
                 ptx::tc_fence_before_sync();
                 __syncwarp();
