@@ -297,6 +297,7 @@ static int run_forward(tnn_network *n, const void *x, void *y, void *interm, siz
     p.fp16 = n->fp16;
     p.store_all = interm ? 1 : 0;
     p.write_y = y ? 1 : 0;
+    p.live8 = (!interm && n->output_width <= 8 && (n->out_act == tnn::ACT_NONE || n->out_act == tnn::ACT_RELU)) ? 1 : 0;
     p.variant = n->variant;
     p.n_sm = n->n_sm;
     p.status = n->status;

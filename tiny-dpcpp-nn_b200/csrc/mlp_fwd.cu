@@ -95,7 +95,11 @@ __device__ __forceinline__ void encode_grid_rows(uint8_t *xt, int row, int level
     }
 }
 
-template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN_MAJOR, bool STREAM_W, int NENC, bool HF_>
+// LIVE8 (inference with the hidden activations in tensor memory): the network has at most 8 real outputs and
+// act_out(0) = 0, so the output columns from the 9th on are exactly zero (zero weight columns).  The output tile of
+// a slot is zeroed once and the output layer's epilogue step - a code region of its own, selected at compile time -
+// converts and writes the first 8-column chunk of a row only.
+template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN_MAJOR, bool STREAM_W, int NENC, bool HF_, bool LIVE8>
 __global__ void __launch_bounds__(FwdSmem<W, NSLOT, TMEM_A, STORE_ALL>::THREADS + 32 * NENC, 1)
 mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                const __grid_constant__ CUtensorMap tm_interm, const __nv_bfloat16 *__restrict__ wimg,
@@ -360,9 +364,18 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
         uint64_t *const acc_full = &bars.acc_full[s];
         uint32_t af_parity = 0;
         bool ok = true;
+        if constexpr (LIVE8) {
+            // this thread's row of the slot's output tile: zeros now, only its first chunk is written per tile
+            uint8_t *out_tile = smem + S::ABUF + s * S::NABUF * T::ACT_BYTES;
+            for (int at = 0; at < T::KATOMS; ++at)
+                for (int ch = 0; ch < T::CHUNKS; ++ch)
+                    *reinterpret_cast<uint4 *>(out_tile + at * T::ACT_ATOM_BYTES + T::chunk_off(row, ch)) =
+                        make_uint4(0u, 0u, 0u, 0u);
+        }
+        const int l_loop_end = LIVE8 ? L - 1 : L; // LIVE8: the output layer's step is the block behind the loop
         for (int j = s; ok && j < my_tiles; j += NSLOT) {
             const int tile = blockIdx.x + j * gridDim.x;
-            for (int l = 0; l <= L; ++l) {
+            for (int l = 0; l <= l_loop_end; ++l) {
                 // the verdict must be warp-uniform: the TMEM accesses below are .aligned
                 if (!__all_sync(0xffffffffu, ptx::mbar_wait(acc_full, af_parity, abort_flag))) {
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | (l << 4) | s);
@@ -473,6 +486,44 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                     }
                 }
             }
+            if constexpr (LIVE8) {
+                if (!ok) break;
+                // ---- output layer, first 8 columns only
+                if (!__all_sync(0xffffffffu, ptx::mbar_wait(acc_full, af_parity, abort_flag))) {
+                    if (lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | (L << 4) | s);
+                    ok = false;
+                    break;
+                }
+                af_parity ^= 1u;
+                ptx::tc_fence_after_sync();
+                uint32_t v8[8];
+                ptx::tmem_ld8(acc_addr, v8);
+                uint8_t *out_tile = smem + S::ABUF + s * S::NABUF * T::ACT_BYTES;
+                // the previous tile's output store must have read the tile before its first chunk is overwritten
+                if (leader) ptx::tma_wait_group_read<0>();
+                ptx::named_bar_sync(1 + s, 128);
+                ptx::tmem_ld_wait();
+                dispatch_act_t<HF_>(out_act, [&](auto tag) {
+                    constexpr int ACT = decltype(tag)::value;
+                    constexpr bool HF = decltype(tag)::half;
+                    uint32_t p[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        p[q] = act_pack_t<ACT, HF>(__uint_as_float(v8[2 * q]), __uint_as_float(v8[2 * q + 1]));
+                    *reinterpret_cast<uint4 *>(out_tile + T::chunk_off(row, 0)) = make_uint4(p[0], p[1], p[2], p[3]);
+                });
+                ptx::fence_proxy_async_smem();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(a_ready);
+                ptx::named_bar_sync(1 + s, 128);
+                if (leader) {
+                    if (write_y)
+                        for (int at = 0; at < T::KATOMS; ++at)
+                            ptx::tma_store_2d(&tm_y, out_tile + at * T::ACT_ATOM_BYTES, at * T::ATOM_COLS, tile * T::TM);
+                    ptx::tma_commit_group();
+                }
+            }
         }
         if (leader) ptx::tma_wait_group<0>();
     } else if constexpr (NENC > 0) {
@@ -548,13 +599,13 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
 }
 
 // ---------------------------------------------------------------------- host side
-template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN, bool STREAM_W, int NENC, bool HF_>
+template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN, bool STREAM_W, int NENC, bool HF_, bool LIVE8>
 static cudaError_t launch_variant_t(const FwdLaunch &p) {
     using T = Tile<W>;
     using S = FwdSmem<W, NSLOT, TMEM_A, STORE_ALL, STREAM_W>;
     const size_t smem = (size_t)S::WBUF + (size_t)S::weight_tiles(p.n_mat) * T::WGT_BYTES + 1024;
     if (smem > 227 * 1024 - 1024 || !S::fits_tmem) return cudaErrorInvalidConfiguration;
-    auto kern = mlp_fwd_kernel<W, NSLOT, STORE_ALL, TMEM_A, B_MN, STREAM_W, NENC, HF_>;
+    auto kern = mlp_fwd_kernel<W, NSLOT, STORE_ALL, TMEM_A, B_MN, STREAM_W, NENC, HF_, LIVE8>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const int n_tiles = (int)((p.batch + T::TM - 1) / T::TM);
@@ -567,10 +618,10 @@ static cudaError_t launch_variant_t(const FwdLaunch &p) {
     return cudaGetLastError();
 }
 
-template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN, bool STREAM_W = false, int NENC = 0>
+template <int W, int NSLOT, bool STORE_ALL, bool TMEM_A, bool B_MN, bool STREAM_W = false, int NENC = 0, bool LIVE8 = false>
 static cudaError_t launch_variant(const FwdLaunch &p) {
-    return p.fp16 ? launch_variant_t<W, NSLOT, STORE_ALL, TMEM_A, B_MN, STREAM_W, NENC, true>(p)
-                  : launch_variant_t<W, NSLOT, STORE_ALL, TMEM_A, B_MN, STREAM_W, NENC, false>(p);
+    return p.fp16 ? launch_variant_t<W, NSLOT, STORE_ALL, TMEM_A, B_MN, STREAM_W, NENC, true, LIVE8>(p)
+                  : launch_variant_t<W, NSLOT, STORE_ALL, TMEM_A, B_MN, STREAM_W, NENC, false, LIVE8>(p);
 }
 
 // fused hash-grid encoding: two tiles in flight (the gathers, not the GEMMs, set the pace), weights resident
@@ -604,6 +655,9 @@ template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
         // measured at W = 64, batch 2^22: four tiles in flight win up to 4 hidden layers (0.170 / 0.213 ms at 2 / 4),
         // three from 6 on (0.261 vs 0.272 ms at 6, 0.337 vs 0.465 ms at 8 layers)
         if (e == cudaErrorInvalidConfiguration && p.n_mat >= 7) e = launch_variant<W, 3, false, TA, false>(p);
+        if constexpr (W == 64) {
+            if (e == cudaErrorInvalidConfiguration && p.live8) e = launch_variant<W, 4, false, TA, false, false, 0, true>(p);
+        }
         if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 4, false, TA, false>(p);
         if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, false, TA, false>(p);
     }

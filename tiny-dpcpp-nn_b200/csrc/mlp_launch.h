@@ -29,6 +29,7 @@ struct FwdLaunch {
     int fp16; // operands and activations are fp16 instead of bf16
     int store_all;
     int write_y;
+    int live8; // inference: output columns from the 9th on are exactly zero (<= 8 real outputs, act_out(0) = 0)
     EncodedInput enc; // enc.x != nullptr: the input tile is produced in the kernel from fp32 coordinates
     // grid_params != nullptr: the input tile is the hash-grid encoding (2-D or 3-D, 2 features per level, at most
     // `width` features) of the fp32 positions grid_x, gathered from grid_table by extra warps of the kernel
