@@ -648,16 +648,21 @@ template <int W> static cudaError_t launch_w(const FwdLaunch &p) {
     // inference: hidden activations in tensor memory where the A operand can live there (W >= 32)
     constexpr bool TA = W >= 32;
     if (!force_stream) {
+        if constexpr (W == 32) {
+            if (p.live8) e = launch_variant<W, 6, false, TA, false, false, 0, true>(p);
+        }
         if constexpr (W <= 32) {
             // narrow layers are pure latency chains (one or two MMAs per layer): six tiles in flight
-            e = launch_variant<W, 6, false, TA, false>(p);
+            if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 6, false, TA, false>(p);
         }
         // measured at W = 64, batch 2^22: four tiles in flight win up to 4 hidden layers (0.170 / 0.213 ms at 2 / 4),
         // three from 6 on (0.261 vs 0.272 ms at 6, 0.337 vs 0.465 ms at 8 layers)
-        if (e == cudaErrorInvalidConfiguration && p.n_mat >= 7) e = launch_variant<W, 3, false, TA, false>(p);
         if constexpr (W == 64) {
-            if (e == cudaErrorInvalidConfiguration && p.live8) e = launch_variant<W, 4, false, TA, false, false, 0, true>(p);
+            if (e == cudaErrorInvalidConfiguration && p.live8)
+                e = p.n_mat >= 7 ? launch_variant<W, 3, false, TA, false, false, 0, true>(p)
+                                 : launch_variant<W, 4, false, TA, false, false, 0, true>(p);
         }
+        if (e == cudaErrorInvalidConfiguration && p.n_mat >= 7) e = launch_variant<W, 3, false, TA, false>(p);
         if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 4, false, TA, false>(p);
         if (e == cudaErrorInvalidConfiguration) e = launch_variant<W, 2, false, TA, false>(p);
     }
