@@ -28,6 +28,8 @@
 #include "mlp_common.cuh"
 #include "elementwise.h"
 #include "grid_device.cuh"
+
+#include <type_traits>
 #include "mlp_launch.h"
 
 namespace tnn {
@@ -372,20 +374,22 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                     *reinterpret_cast<uint4 *>(out_tile + at * T::ACT_ATOM_BYTES + T::chunk_off(row, ch)) =
                         make_uint4(0u, 0u, 0u, 0u);
         }
-        const int l_loop_end = LIVE8 ? L - 1 : L; // LIVE8: the output layer's step is the block behind the loop
         for (int j = s; ok && j < my_tiles; j += NSLOT) {
             const int tile = blockIdx.x + j * gridDim.x;
-            for (int l = 0; l <= l_loop_end; ++l) {
+            // One epilogue step; `last` (a compile-time tag) tells the output layer from the hidden ones, so that each
+            // call site is a straight-line body of its own: where the result goes (tensor memory for the next GEMM or
+            // shared memory for the store) is then no run-time question inside the per-element code.
+            auto epi_step = [&](int l, auto last) -> bool {
+                constexpr bool IS_LAST = decltype(last)::value;
                 // the verdict must be warp-uniform: the TMEM accesses below are .aligned
                 if (!__all_sync(0xffffffffu, ptx::mbar_wait(acc_full, af_parity, abort_flag))) {
                     if (lane == 0) atomicExch(status, KS_TIMEOUT_EPILOGUE | (l << 4) | s);
-                    ok = false;
-                    break;
+                    return false;
                 }
                 af_parity ^= 1u;
                 ptx::tc_fence_after_sync();
-                const int a = (l == L) ? out_act : act;
-                const bool to_tmem = TMEM_A && l < L;
+                const int a = IS_LAST ? out_act : act;
+                constexpr bool to_tmem = TMEM_A && !IS_LAST;
                 uint8_t *abuf = smem + S::ABUF +
                                 (S::SHARED_OUT ? 0 : (s * S::NABUF + (l & (S::NABUF - 1))) * T::ACT_BYTES);
                 constexpr int CW = (W >= 32) ? 32 : 16; // columns per TMEM load
@@ -399,7 +403,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                         ptx::tmem_ld16(acc_addr + i * CW, v[i]);
                 }
                 if constexpr (S::SHARED_OUT) {
-                    if (l == L) {
+                    if (IS_LAST) {
                         // take the shared output tile: the previous owner releases it once its store has read it
                         if (leader) {
                             bool got = false;
@@ -418,8 +422,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                         }
                         // (one verdict for the whole group: nobody is left alone at a later barrier)
                         if (ptx::named_bar_red_or(1 + s, 128, *abort_flag != 0)) {
-                            ok = false;
-                            break;
+                            return false;
                         }
                     }
                 } else if (!to_tmem && (STORE_ALL || TMEM_A || l == 0)) {
@@ -435,7 +438,7 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                     ptx::named_bar_sync(1 + s, 128);
                 }
                 ptx::tmem_ld_wait();
-                if (TMEM_A && l == L) {
+                if constexpr (TMEM_A && IS_LAST) {
                     // output layer: the accumulator is in registers and nothing else is handed to the issuer, so the
                     // first GEMM of the slot's next tile may run under the conversion and the store of this one
                     // (measured neutral to 6 % slower at width 16, whose kernels keep the arrival behind the stores)
@@ -473,15 +476,15 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                     ptx::fence_proxy_async_smem();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0 && !(TMEM_A && l == L)) ptx::mbar_arrive(a_ready);
-                if (!to_tmem && (STORE_ALL || l == L)) {
+                if (lane == 0 && !(TMEM_A && IS_LAST)) ptx::mbar_arrive(a_ready);
+                if (!to_tmem && (STORE_ALL || IS_LAST)) {
                     ptx::named_bar_sync(1 + s, 128);
                     if (leader) {
                         for (int at = 0; at < T::KATOMS; ++at) {
                             if (STORE_ALL)
                                 ptx::tma_store_3d(&tm_interm, abuf + at * T::ACT_ATOM_BYTES, at * T::ATOM_COLS,
                                                   tile * T::TM, l + 1);
-                            if (l == L && write_y)
+                            if (IS_LAST && write_y)
                                 ptx::tma_store_2d(&tm_y, abuf + at * T::ACT_ATOM_BYTES, at * T::ATOM_COLS,
                                                   tile * T::TM);
                         }
@@ -493,6 +496,11 @@ mlp_fwd_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__
                         }
                     }
                 }
+                return true;
+            };
+            for (int l = 0; ok && l < L; ++l) ok = epi_step(l, std::false_type{});
+            if constexpr (!LIVE8) {
+                if (ok) ok = epi_step(L, std::true_type{});
             }
             if constexpr (LIVE8) {
                 if (!ok) break;
