@@ -414,10 +414,13 @@ dp_adam_refresh_kernel(PeerWindow pw, unsigned seq, unsigned long long wait_ns, 
         g = part[0][tid];
     }
     for (int r = threadIdx.y; r < pw.world; r += blockDim.y) pw.slots[r][slot] = g;
-    __threadfence_system();
     __syncthreads();
     if (threadIdx.y != 0) return;
     if (tid < pw.world) {
+        // One fence per flag, not one per thread: the block barrier orders every thread's stores before this thread,
+        // and its system-scope fence is cumulative over them (the pattern of a grid-wide barrier).  A thousand
+        // system fences per block cost the exchange several microseconds.
+        __threadfence_system();
         const size_t f = (parity * pw.world + pw.rank) * kWinFlagsPerSlot + blockIdx.x;
         st_release_sys(pw.flags[tid] + f, seq);
         // wait for the same block of source rank `tid`
