@@ -292,12 +292,13 @@ int tnn_network_adam_step(tnn_network *net, float *master, float *m, float *v, c
  *
  * Peer windows: when all ranks (at most 8) run on one host and can map each other's memory (CUDA IPC over NVLink),
  * making a communicator also gives every rank a window in every other rank's address space, and the optimiser
- * kernel of a trainer exchanges the weight gradient itself: it sums the per-CTA slabs, stores the result into
- * every peer's window with a flag per block, waits for the peers' blocks (bounded: TNN_DP_WAIT_MS, default 30 000,
- * after which tnn_network_sync_status reports 2 and the step is invalid), adds the ranks' contributions in rank
- * order - every rank computes bit-identical parameters - and applies Adam.  Otherwise (several hosts, no peer
+ * kernel of a trainer exchanges the weight gradient itself: it sums the per-CTA slabs, stores every value together
+ * with the number of the exchange - one 8-byte store per element, no fence, no separate flag - into every peer's
+ * window, polls its own window until the elements of all ranks carry that number (bounded: TNN_DP_WAIT_MS, default
+ * 30 000, after which tnn_network_sync_status reports 2 and the step is invalid), adds the ranks' contributions in
+ * rank order - every rank computes bit-identical parameters - and applies Adam.  Otherwise (several hosts, no peer
  * access, more than 262 144 parameters, or TNN_DP_PEER_WINDOW=0 in the environment of every rank) the exchange is
- * one ncclAllReduce(sum) between a reduction kernel and the Adam kernel.  Windows cost 2 MiB per rank pair.
+ * one ncclAllReduce(sum) between a reduction kernel and the Adam kernel.  Windows cost 4 MiB per rank pair.
  * ------------------------------------------------------------------------------------------ */
 /* ncclGetUniqueId into 128 caller bytes (rank 0 calls this and sends the bytes to the other ranks). */
 int tnn_dp_get_unique_id(void *id128);

@@ -100,23 +100,21 @@ int nccl_fail(const char *what, int rc) {
 } // namespace
 
 // Peer window of a communicator: one device buffer per rank, mapped into every rank of the same host (CUDA IPC).
-// Rank s pushes its contribution of exchange number q into slot [q & 1][s] of every rank's window and then stores q
-// into flag [q & 1][s][block]; the receiver polls its own memory.  Two slots per source are enough: a rank can start
-// exchange q + 2 only after it finished q + 1, which needed every peer's contribution to q + 1, which a peer sends
-// only after its kernel of exchange q has finished reading.
+// An element is 8 bytes: {fp32 value, exchange number}, written with ONE 8-byte store, so value and "it has arrived"
+// travel together and no fence or separate flag is needed (the low-latency scheme of collective libraries; a
+// release fence over outstanding peer stores alone costs several microseconds).  Rank s pushes its contribution of
+// exchange number q into slot [q & 1][s] of every rank's window; the receiver polls its own memory until an element
+// carries q.  Two slots per source are enough: a rank can start exchange q + 2 only after it finished q + 1, which
+// needed every peer's contribution to q + 1, which a peer sends only after its kernel of exchange q has finished
+// reading.
 constexpr int kMaxPeers = 8;
 constexpr size_t kWinSlotFloats = 256 * 1024; // largest gradient buffer exchanged through the window
 constexpr int kWinBlock = tnn::kSlabBlock;     // weights per block of the exchange kernel
-constexpr size_t kWinFlagsPerSlot = kWinSlotFloats / kWinBlock;
 struct PeerWindow {
-    float *slots[kMaxPeers];    // slots[r]: rank r's window as mapped in this process (own window at [rank])
-    unsigned *flags[kMaxPeers]; // flags[r]: the flag area of rank r's window
+    uint2 *slots[kMaxPeers]; // slots[r]: rank r's window as mapped in this process (own window at [rank])
     int rank, world;
 };
-constexpr size_t win_slot_floats_total(int world) { return 2 * (size_t)world * kWinSlotFloats; }
-constexpr size_t win_bytes(int world) {
-    return win_slot_floats_total(world) * sizeof(float) + 2 * (size_t)world * kWinFlagsPerSlot * sizeof(unsigned);
-}
+constexpr size_t win_bytes(int world) { return 2 * (size_t)world * kWinSlotFloats * sizeof(uint2); }
 
 struct tnn_dp_comm {
     void *comm = nullptr; // ncclComm_t
@@ -230,8 +228,7 @@ int setup_peer_window(tnn_dp_comm *c) {
     c->pw.world = world;
     for (int r = 0; r < world; ++r) {
         char *base = static_cast<char *>(r == c->rank ? c->win : c->peer_base[r]);
-        c->pw.slots[r] = reinterpret_cast<float *>(base);
-        c->pw.flags[r] = reinterpret_cast<unsigned *>(base + win_slot_floats_total(world) * sizeof(float));
+        c->pw.slots[r] = reinterpret_cast<uint2 *>(base);
     }
     c->peer_ok = true;
     return 0;
@@ -359,13 +356,14 @@ static cudaError_t launch_adam_refresh(int width, float *master, float *m, float
 
 
 // ---- data-parallel variant: gradient exchange through the peer windows inside the optimiser kernel
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+// 8-byte element {value bits, exchange number}: single stores and loads, never torn
+__device__ __forceinline__ void st_elem(uint2 *p, float value, unsigned seq) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(value)), "r"(seq) : "memory");
 }
-__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ uint2 ld_elem(const uint2 *p) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
 }
 __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
@@ -374,10 +372,10 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 }
 
 // One block = 128 consecutive weights (slab order), (128, 8) threads when FROM_SLABS, (128, 1) otherwise.  Sum the
-// slabs (or take the already reduced gradient), store the 128 values into slot [seq & 1][rank] of every rank's
-// window, publish flag [seq & 1][rank][block] = seq on every rank, wait (bounded: `wait_ns`) for the same flag of
-// every source rank in this rank's own window, add the world contributions in rank order and run Adam + refresh on
-// the sum.  A wait that runs out sets *status and the block leaves its weights untouched.
+// slabs (or take the already reduced gradient), store every value together with the exchange number into slot
+// [seq & 1][rank] of every rank's window, then - one thread per weight - poll this rank's own window until the element
+// of every source rank carries the exchange number (bounded: `wait_ns`), add the world contributions in rank order
+// and run Adam + refresh on the sum.  A wait that runs out sets *status and the thread leaves its weight untouched.
 template <int W, bool FROM_SLABS>
 __global__ void __launch_bounds__(kSlabBlock *kSlabWays)
 dp_adam_refresh_kernel(PeerWindow pw, unsigned seq, unsigned long long wait_ns, int *__restrict__ status,
@@ -388,12 +386,10 @@ dp_adam_refresh_kernel(PeerWindow pw, unsigned seq, unsigned long long wait_ns, 
                        float bc1, float bc2_sqrt, int net_fp16, __nv_bfloat16 *__restrict__ packed_out,
                        __nv_bfloat16 *__restrict__ wimg, __nv_bfloat16 *__restrict__ wimg_t) {
     __shared__ float part[FROM_SLABS ? kSlabWays : 1][kSlabBlock];
-    __shared__ int gave_up;
     const int tid = threadIdx.x;
     const int idx = blockIdx.x * kSlabBlock + tid;
     const int per = n_mat * W * W; // a multiple of the block's 128 weights
     const size_t parity = seq & 1u;
-    if (tid == 0 && threadIdx.y == 0) gave_up = 0;
     if (FROM_SLABS && blockIdx.x == 0 && loss_out) loss_sum_block(loss_partials, n_loss, loss_out, part[0]);
     const int l = idx / (W * W);
     const int o = (idx / W) % W; // output feature
@@ -413,41 +409,27 @@ dp_adam_refresh_kernel(PeerWindow pw, unsigned seq, unsigned long long wait_ns, 
         __syncthreads();
         g = part[0][tid];
     }
-    for (int r = threadIdx.y; r < pw.world; r += blockDim.y) pw.slots[r][slot] = g;
-    __syncthreads();
+    for (int r = threadIdx.y; r < pw.world; r += blockDim.y) st_elem(pw.slots[r] + slot, g, seq);
     if (threadIdx.y != 0) return;
-    if (tid < pw.world) {
-        // One fence per flag, not one per thread: the block barrier orders every thread's stores before this thread,
-        // and its system-scope fence is cumulative over them (the pattern of a grid-wide barrier).  A thousand
-        // system fences per block cost the exchange several microseconds.
-        __threadfence_system();
-        const size_t f = (parity * pw.world + pw.rank) * kWinFlagsPerSlot + blockIdx.x;
-        st_release_sys(pw.flags[tid] + f, seq);
-        // wait for the same block of source rank `tid`
-        const unsigned *flag = pw.flags[pw.rank] + (parity * pw.world + tid) * kWinFlagsPerSlot + blockIdx.x;
-        const unsigned long long t0 = global_timer_ns();
-        bool ok = false;
-        for (unsigned it = 0; it < (1u << 30); ++it) {
-            if (ld_acquire_sys(flag) == seq) {
-                ok = true;
-                break;
-            }
-            if ((it & 15u) == 15u) {
-                if (global_timer_ns() - t0 > wait_ns) break;
-                __nanosleep(32);
-            }
-        }
-        if (!ok) {
-            gave_up = 1;
-            atomicOr(status, 2);
-        }
-    }
-    // (the threads with threadIdx.y == 0 are the first four warps of the block)
-    asm volatile("bar.sync 1, %0;" ::"n"(kSlabBlock) : "memory");
-    if (gave_up) return;
-    const float *own = pw.slots[pw.rank] + parity * pw.world * kWinSlotFloats + idx;
+    // gather: the elements of all source ranks, in rank order
+    const uint2 *own = pw.slots[pw.rank] + parity * pw.world * kWinSlotFloats + idx;
+    const unsigned long long t0 = global_timer_ns();
     g = 0.0f;
-    for (int r = 0; r < pw.world; ++r) g += __ldcg(own + (size_t)r * kWinSlotFloats);
+    for (int r = 0; r < pw.world; ++r) {
+        const uint2 *src = own + (size_t)r * kWinSlotFloats;
+        uint2 e = ld_elem(src);
+        for (unsigned it = 0; e.y != seq; ++it) {
+            if ((it & 63u) == 63u) {
+                if (global_timer_ns() - t0 > wait_ns) {
+                    atomicOr(status, 2);
+                    return;
+                }
+                __nanosleep(20);
+            }
+            e = ld_elem(src);
+        }
+        g += __uint_as_float(e.x);
+    }
     grads[pk] = g; // the sum over ranks (what the all-reduce path leaves here)
     adam_and_refresh<W>(l, o, i, pk, g * grad_scale, master, m, v, n_mat, one_padded_in, unpadded_out, lr, b1, b2, eps,
                         bc1, bc2_sqrt, net_fp16, packed_out, wimg, wimg_t);
