@@ -486,6 +486,60 @@ def test_data_parallel_step_equals_single_gpu_full_batch(tnn_lib, tmp_path, exch
     assert diff.max() <= 2.1e-3 * steps and (diff <= 2e-5).mean() >= 0.98
 
 
+def _dp_timeout_worker(rank, world, port, out_dir):
+    for p in (ROOT, os.path.join(ROOT, "tiny-dpcpp-nn_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", TNN_DP_WAIT_MS="300")
+    import time
+
+    import torch.distributed as dist
+
+    from tiny_dpcpp_nn import _lib as L
+    from tiny_dpcpp_nn.trainer import Trainer
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    batch = 128 * 8
+    q, t, w = _c5_case(batch)
+    net, enc = _c5_modules(L, w)
+    tr = Trainer(net, lr=1e-3, process_group=dist.group.WORLD, world_size=world, encoding=enc)
+    qt, tt = torch.from_numpy(q).cuda(), torch.from_numpy(t).cuda()
+    seen = [int(tr.peer_window)]
+    tr.training_step(qt, tt)
+    seen.append(net.status())  # 0: both ranks arrived together
+    dist.barrier()
+    if rank == 1:
+        time.sleep(2.0)  # rank 0 waits 300 ms for this rank's gradient, then gives up
+    tr.training_step(qt, tt)
+    seen.append(net.status())  # rank 0: 2 (wait ran out, its weights of this step untouched), rank 1: 0
+    dist.barrier()
+    tr.training_step(qt, tt)
+    seen.append(net.status())  # the context and the windows are usable afterwards
+    with open(os.path.join(out_dir, f"timeout{rank}.txt"), "w") as f:
+        f.write(" ".join(str(v) for v in seen))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_peer_window_wait_gives_up_and_reports(tnn_lib, tmp_path):
+    """A rank whose peer is late by more than TNN_DP_WAIT_MS: the exchange kernel stops polling, leaves its weights
+    alone and sets bit 2 of the status word; nothing hangs or faults and the next step runs normally."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_dp_timeout_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0 = [int(v) for v in (tmp_path / "timeout0.txt").read_text().split()]
+    r1 = [int(v) for v in (tmp_path / "timeout1.txt").read_text().split()]
+    if r0[0] != 1 or r1[0] != 1:
+        pytest.skip("the ranks of this host cannot map each other's memory: no peer windows")
+    assert r0[1:] == [0, 2, 0] and r1[1:] == [0, 0, 0]
+
+
 def _dp_grid_worker(rank, world, port, out_dir, batch, steps):
     for p in (ROOT, os.path.join(ROOT, "tiny-dpcpp-nn_b200")):
         if p not in sys.path:
