@@ -351,8 +351,11 @@ int tnn_trainer_forward_backward(tnn_trainer *trainer, const void *x, const floa
 int tnn_trainer_reduce(tnn_trainer *trainer, void *stream);
 /* optimizer.step() + Module.set_params(): gradient sum over the ranks when a communicator is set (inside the
  * optimiser kernel with peer windows, else ncclAllReduce), Adam on the master copy, refresh of the 16-bit weights
- * the kernels read.  Refused (error code) on a stream that is being captured into a CUDA graph: the step count
- * and the exchange number are host state passed as kernel arguments, which a replay would not advance. */
+ * the kernels read.  A single-GPU trainer without a trainable encoding counts its steps on the device: its
+ * training step (both calls, or tnn_trainer_training_step) can be captured into a CUDA graph and replayed, every
+ * replay being one more optimiser step (tnn_trainer_step_count counts calls, not replays).  With a communicator or
+ * a trainable encoding the call is refused (error code) on a capturing stream: the exchange number and the step
+ * count of the encoding's Adam kernel are host state passed as kernel arguments. */
 int tnn_trainer_optimizer_step(tnn_trainer *trainer, void *stream);
 /* forward_backward + optimizer_step: one call enqueues the whole loop body. */
 int tnn_trainer_training_step(tnn_trainer *trainer, const void *x, const float *targets, int n_targets,

@@ -116,30 +116,36 @@ def test_trainer_reduces_the_loss(tnn_lib):
     assert last < 0.7 * first, (first, last)
 
 
-def test_optimizer_step_refuses_graph_capture_but_forward_backward_is_capturable(tnn_lib):
-    """The fused forward / loss / backward call holds no host state and replays from a CUDA graph; the optimiser step
-    passes the step count to its kernel and says no on a capturing stream instead of baking a stale count in."""
+def test_training_step_replays_from_a_cuda_graph(tnn_lib):
+    """A single-GPU trainer counts its optimiser steps on the device, so the whole training step (fused kernel +
+    optimiser kernel) is capturable: three replays of the captured step leave the bits of three eager steps of a twin
+    trainer (Adam's bias correction advances with every replay)."""
     from tiny_dpcpp_nn.trainer import Trainer
 
     W, nh, batch = 64, 2, 128 * 9
     x = synth.uniform_inputs(batch, W, seed=3)
     t = synth.uniform_inputs(batch, W, seed=4)
-    net = tnn_lib.create_network(W, W, nh, A["relu"], A["none"], W, "torch.bfloat16", True, seed=0)
-    tr = Trainer(net)
+    w = synth.xavier_weights(nh + 1, W, 5)
     xt, tt = _bf16(x), torch.from_numpy(t).cuda()
-    tr.forward_backward(xt, tt)
-    want = tr.grads.clone()
-    tr.grads.zero_()
+    trainers = []
+    for _ in range(2):
+        net = tnn_lib.create_network(W, W, nh, A["relu"], A["none"], W, "torch.bfloat16", True, seed=0)
+        tr = Trainer(net, lr=1e-2)
+        tr.set_master_params(torch.from_numpy(O.pack_weights(w, nh + 1, W)).cuda())
+        trainers.append((net, tr))
+    (net_e, eager), (net_g, graphed) = trainers
+    for _ in range(4):
+        eager.training_step(xt, tt)
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(side):
-        tr.forward_backward(xt, tt)  # warm-up on the capturing stream
+        graphed.training_step(xt, tt)  # step 1, eager, on the capturing stream (warm-up)
         with torch.cuda.graph(graph, stream=side):
-            tr.forward_backward(xt, tt)
-            with pytest.raises(tnn_lib.TnnError, match="CUDA graph"):
-                tr.optimizer_step()
-    tr.grads.zero_()
-    graph.replay()
+            graphed.training_step(xt, tt)  # captured, not executed
+    for _ in range(3):
+        graph.replay()  # steps 2, 3, 4
     torch.cuda.synchronize()
-    assert torch.equal(tr.grads, want) and net.status() == 0
+    assert torch.equal(graphed.master, eager.master) and torch.equal(graphed.grads, eager.grads)
+    assert torch.equal(net_g.get_params(), net_e.get_params())
+    assert net_e.status() == 0 and net_g.status() == 0

@@ -307,10 +307,18 @@ adam_refresh_kernel(float *__restrict__ master, float *__restrict__ m, float *__
                     float *__restrict__ loss_out, int n_mat, int one_padded_in, int unpadded_out, float grad_scale,
                     float lr, float b1, float b2, float eps, float bc1, float bc2_sqrt, int net_fp16,
                     __nv_bfloat16 *__restrict__ packed_out, __nv_bfloat16 *__restrict__ wimg,
-                    __nv_bfloat16 *__restrict__ wimg_t) {
+                    __nv_bfloat16 *__restrict__ wimg_t, int *__restrict__ counters) {
     __shared__ float part[FROM_SLABS ? kSlabWays : 1][kSlabBlock];
     const int idx = blockIdx.x * kSlabBlock + threadIdx.x; // slab order: (matrix, output feature, input feature)
     const int per = n_mat * W * W;                          // a multiple of the block's 128 weights
+    // counters (optional): {optimiser steps done, blocks of this launch that have read it}.  With it the step number
+    // - Adam's bias correction - is device state: a CUDA graph that holds this launch advances it at every replay.
+    int step_now = 0;
+    if (counters) {
+        step_now = *reinterpret_cast<volatile int *>(counters) + 1;
+        bc1 = 1.0f - powf(b1, (float)step_now);
+        bc2_sqrt = sqrtf(1.0f - powf(b2, (float)step_now));
+    }
     if (FROM_SLABS && blockIdx.x == 0 && loss_out) loss_sum_block(loss_partials, n_loss, loss_out, part[0]);
     const int l = idx / (W * W);
     const int o = (idx / W) % W; // output feature
@@ -318,11 +326,22 @@ adam_refresh_kernel(float *__restrict__ master, float *__restrict__ m, float *__
     const int pk = l * W * W + packed_coord_(i, o, W);
     float g;
     if constexpr (FROM_SLABS) {
-        g = slab_sum(slabs, n_slabs, per, idx, part);
-        if (threadIdx.y != 0) return;
-        grads[pk] = g;
+        g = slab_sum(slabs, n_slabs, per, idx, part); // (holds a block barrier: every thread has read the counter)
     } else {
         g = grads[pk];
+        if (counters) __syncthreads();
+    }
+    if (counters && threadIdx.x == 0 && threadIdx.y == 0) {
+        // the last block to get here knows that every block has read the old count: it publishes the new one
+        int *ticket = counters + 1;
+        if (atomicAdd(ticket, 1) == (int)gridDim.x - 1) {
+            *ticket = 0;
+            *reinterpret_cast<volatile int *>(counters) = step_now;
+        }
+    }
+    if constexpr (FROM_SLABS) {
+        if (threadIdx.y != 0) return;
+        grads[pk] = g;
     }
     adam_and_refresh<W>(l, o, i, pk, g * grad_scale, master, m, v, n_mat, one_padded_in, unpadded_out, lr, b1, b2, eps,
                         bc1, bc2_sqrt, net_fp16, packed_out, wimg, wimg_t);
@@ -333,7 +352,7 @@ static cudaError_t launch_adam_refresh(int width, float *master, float *m, float
                                        int n_slabs, const float *loss_partials, int n_loss, float *loss_out, int n_mat,
                                        int one_padded_in, int unpadded_out, float grad_scale, int step, float lr, float b1,
                                        float b2, float eps, int net_fp16, __nv_bfloat16 *packed, __nv_bfloat16 *wimg,
-                                       __nv_bfloat16 *wimg_t, cudaStream_t s) {
+                                       __nv_bfloat16 *wimg_t, cudaStream_t s, int *counters = nullptr) {
     const int n = n_mat * width * width;
     const int blocks = n / kSlabBlock;
     const dim3 threads(kSlabBlock, FROM_SLABS ? kSlabWays : 1);
@@ -344,7 +363,7 @@ static cudaError_t launch_adam_refresh(int width, float *master, float *m, float
     case WW:                                                                                                            \
         adam_refresh_kernel<WW, FROM_SLABS><<<blocks, threads, 0, s>>>(                                                 \
             master, m, v, grads, slabs, n_slabs, loss_partials, n_loss, loss_out, n_mat, one_padded_in, unpadded_out,   \
-            grad_scale, lr, b1, b2, eps, bc1, bc2_sqrt, net_fp16, packed, wimg, wimg_t);                                \
+            grad_scale, lr, b1, b2, eps, bc1, bc2_sqrt, net_fp16, packed, wimg, wimg_t, counters);                                \
         break;
     switch (width) {
         TNN_CASE(16) TNN_CASE(32) TNN_CASE(64) TNN_CASE(128)
@@ -479,6 +498,7 @@ struct tnn_trainer {
     int step = 0;
     float *master = nullptr, *m = nullptr, *v = nullptr, *grads = nullptr; // network: n_params fp32 each (one block)
     float *loss = nullptr;                                                  // one fp32: loss sum of the last step
+    int *counters = nullptr; // {optimiser steps done, ticket}: the device-side step count of the optimiser kernel
     // trainable encoding: gradient of the whole table; moments for this rank's slice of it
     float *enc_grads = nullptr, *enc_m = nullptr, *enc_v = nullptr;
     size_t enc_shard = 0;      // table elements whose moments this rank keeps
@@ -610,8 +630,8 @@ int tnn_trainer_create(tnn_network *net, tnn_encoding *enc, float lr, float beta
     t->enc = enc;
     t->lr = lr, t->b1 = beta1, t->b2 = beta2, t->eps = eps, t->loss_scale = loss_scale;
     const size_t n = net->n_params;
-    cudaError_t e = cudaMalloc(&t->master, (4 * n + 4) * sizeof(float));
-    if (e == cudaSuccess) e = cudaMemset(t->master, 0, (4 * n + 4) * sizeof(float));
+    cudaError_t e = cudaMalloc(&t->master, (4 * n + 8) * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemset(t->master, 0, (4 * n + 8) * sizeof(float));
     if (e != cudaSuccess) {
         delete t;
         return tnn::api_fail(std::string("device allocation failed: ") + cudaGetErrorString(e), 2);
@@ -620,6 +640,7 @@ int tnn_trainer_create(tnn_network *net, tnn_encoding *enc, float lr, float beta
     t->v = t->m + n;
     t->grads = t->v + n;
     t->loss = t->grads + n;
+    t->counters = reinterpret_cast<int *>(t->loss + 4);
     // master copy = the network's current (bf16) weights; tnn_trainer_set_master_params replaces it with the fp32 draw
     e = net->fp16 ? tnn::launch_fp16_to_f32(net->packed, t->master, n, nullptr)
                   : tnn::launch_bf16_to_f32(net->packed, t->master, n, nullptr);
@@ -699,12 +720,15 @@ int tnn_trainer_reduce(tnn_trainer *t, void *stream) {
 int tnn_trainer_optimizer_step(tnn_trainer *t, void *stream) {
     if (!t) return tnn::api_fail("trainer is null");
     cudaStream_t s = (cudaStream_t)stream;
-    // the step count (Adam's bias correction) and the exchange number of the peer windows are host state that goes
-    // into the kernels' arguments: a captured graph would replay stale values
+    // A single-GPU trainer without a trainable encoding keeps its step count (Adam's bias correction) on the device,
+    // so its step can be captured into a CUDA graph and replayed.  With a communicator the exchange number of the
+    // peer windows, and with a trainable encoding the step count of its Adam kernel, are host state that goes into
+    // kernel arguments: a captured graph would replay stale values.
     cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(s, &capturing) == cudaSuccess && capturing != cudaStreamCaptureStatusNone)
-        return tnn::api_fail("tnn_trainer_optimizer_step cannot be captured into a CUDA graph: step count and "
-                             "exchange number are arguments of its kernels");
+    if ((world_of(t) > 1 || (t->enc && t->enc->n_params)) && cudaStreamIsCapturing(s, &capturing) == cudaSuccess &&
+        capturing != cudaStreamCaptureStatusNone)
+        return tnn::api_fail("tnn_trainer_optimizer_step cannot be captured into a CUDA graph with a communicator or a "
+                             "trainable encoding: step count and exchange number are arguments of its kernels");
     tnn_network *n = t->net;
     const int world = world_of(t);
     const float grad_scale = 1.0f / (t->loss_scale * (float)world);
@@ -733,12 +757,13 @@ int tnn_trainer_optimizer_step(tnn_trainer *t, void *stream) {
     } else if (world > 1 || t->reduced) {
         TNN_CUDA(tnn::launch_adam_refresh<false>(n->width, t->master, t->m, t->v, t->grads, nullptr, 0, nullptr, 0, nullptr,
                                                  n->n_mat, n->one_padded_input(), n->output_width, grad_scale, t->step,
-                                                 t->lr, t->b1, t->b2, t->eps, n->fp16, n->packed, n->wimg, n->wimg_t, s));
+                                                 t->lr, t->b1, t->b2, t->eps, n->fp16, n->packed, n->wimg, n->wimg_t, s,
+                                                 world == 1 ? t->counters : nullptr));
     } else {
         TNN_CUDA(tnn::launch_adam_refresh<true>(n->width, t->master, t->m, t->v, t->grads, n->dw_slabs, t->n_slabs,
                                                 n->loss_partials, t->n_loss, t->loss, n->n_mat, n->one_padded_input(),
                                                 n->output_width, grad_scale, t->step, t->lr, t->b1, t->b2, t->eps, n->fp16,
-                                                n->packed, n->wimg, n->wimg_t, s));
+                                                n->packed, n->wimg, n->wimg_t, s, t->counters));
         t->reduced = true;
     }
     if (t->enc && t->enc->n_params) {
