@@ -313,12 +313,7 @@ adam_refresh_kernel(float *__restrict__ master, float *__restrict__ m, float *__
     const int per = n_mat * W * W;                          // a multiple of the block's 128 weights
     // counters (optional): {optimiser steps done, blocks of this launch that have read it}.  With it the step number
     // - Adam's bias correction - is device state: a CUDA graph that holds this launch advances it at every replay.
-    int step_now = 0;
-    if (counters) {
-        step_now = *reinterpret_cast<volatile int *>(counters) + 1;
-        bc1 = 1.0f - powf(b1, (float)step_now);
-        bc2_sqrt = sqrtf(1.0f - powf(b2, (float)step_now));
-    }
+    const int step_now = counters ? *reinterpret_cast<volatile int *>(counters) + 1 : 0;
     if (FROM_SLABS && blockIdx.x == 0 && loss_out) loss_sum_block(loss_partials, n_loss, loss_out, part[0]);
     const int l = idx / (W * W);
     const int o = (idx / W) % W; // output feature
@@ -331,20 +326,25 @@ adam_refresh_kernel(float *__restrict__ master, float *__restrict__ m, float *__
         g = grads[pk];
         if (counters) __syncthreads();
     }
-    if (counters && threadIdx.x == 0 && threadIdx.y == 0) {
-        // the last block to get here knows that every block has read the old count: it publishes the new one
+    if constexpr (FROM_SLABS) {
+        if (threadIdx.y != 0) return;
+        grads[pk] = g;
+    }
+    if (counters) { // (only the 128 threads that apply the update pay for the two powf)
+        bc1 = 1.0f - powf(b1, (float)step_now);
+        bc2_sqrt = sqrtf(1.0f - powf(b2, (float)step_now));
+    }
+    adam_and_refresh<W>(l, o, i, pk, g * grad_scale, master, m, v, n_mat, one_padded_in, unpadded_out, lr, b1, b2, eps,
+                        bc1, bc2_sqrt, net_fp16, packed_out, wimg, wimg_t);
+    if (counters && threadIdx.x == 0) {
+        // Every thread of this block read the old count before the block barrier above.  The last block to get here
+        // therefore knows that every block has read it, and publishes the new one.
         int *ticket = counters + 1;
         if (atomicAdd(ticket, 1) == (int)gridDim.x - 1) {
             *ticket = 0;
             *reinterpret_cast<volatile int *>(counters) = step_now;
         }
     }
-    if constexpr (FROM_SLABS) {
-        if (threadIdx.y != 0) return;
-        grads[pk] = g;
-    }
-    adam_and_refresh<W>(l, o, i, pk, g * grad_scale, master, m, v, n_mat, one_padded_in, unpadded_out, lr, b1, b2, eps,
-                        bc1, bc2_sqrt, net_fp16, packed_out, wimg, wimg_t);
 }
 
 template <bool FROM_SLABS>
