@@ -266,18 +266,19 @@ def test_inference_of_networks_with_few_outputs(tnn_lib, width, nh, out_w, oact)
     """Inference of networks with at most 8 real outputs (linear / ReLU output: the output layer's epilogue writes the
     first chunk of a row only) gives the bits of the stored forward pass, whose kernel has no such path, zeros in the
     padded columns, and the oracle's values; 9 outputs, a sigmoid output and width 16 take the generic path."""
-    batch = 128 * 21 + 8
-    w, x = synth.mlp_case(width, nh, batch, w_seed=12)
-    w[-1][:, out_w:] = 0.0
-    net = tnn_lib.create_network(width, out_w, nh, A["relu"], A[oact], width, "torch.bfloat16", True, seed=1)
-    net.set_params(torch.from_numpy(w.reshape(-1)).cuda(), False)
-    xt = _bf16(x)
-    y = net.inference(xt)
-    assert torch.equal(y, net.fwd(xt)) and net.status() == 0
-    if oact != "sigmoid":
-        assert torch.all(y[:, out_w:] == 0)
-    interm = O.mlp_forward(x, w, nh + 1, width, "relu", oact, bf16=True)
-    _check(y.float().cpu().numpy(), interm[-1], what=f"W{width} L{nh} out {out_w} {oact}")
+    for batch in (8, 128 + 16, 128 * 21 + 8, 128 * 148 * 5):  # fewer tiles than slots, ragged, several tiles per slot
+        w, x = synth.mlp_case(width, nh, batch, w_seed=12)
+        w[-1][:, out_w:] = 0.0
+        net = tnn_lib.create_network(width, out_w, nh, A["relu"], A[oact], width, "torch.bfloat16", True, seed=1)
+        net.set_params(torch.from_numpy(w.reshape(-1)).cuda(), False)
+        xt = _bf16(x)
+        y = net.inference(xt)
+        assert torch.equal(y, net.fwd(xt)) and net.status() == 0
+        if oact != "sigmoid":
+            assert torch.all(y[:, out_w:] == 0)
+        if batch <= 128 * 21 + 8:
+            interm = O.mlp_forward(x, w, nh + 1, width, "relu", oact, bf16=True)
+            _check(y.float().cpu().numpy(), interm[-1], what=f"W{width} L{nh} out {out_w} {oact} batch {batch}")
 
 
 def test_workspace_lent_by_the_caller(tnn_lib):
